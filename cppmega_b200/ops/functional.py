@@ -1,0 +1,203 @@
+"""Operator front door.
+
+Every model calls the functions here.  On a CUDA tensor they run the sm_100a
+kernels from :mod:`cppmega_b200.ops.cuda` (wrapped in autograd Functions); on a CPU
+tensor they run the PyTorch definitions in :mod:`cppmega_b200.ops.reference`.  A CUDA call
+for which no kernel is registered is counted in :func:`fallback_counts` and runs
+the PyTorch definition on the GPU, so a training log can prove "zero fallbacks"
+(the reference keeps equivalent counters for its MXFP8 routing,
+scripts/cppmega_fp8_shim.py:445-500).  If the extension failed to load on a machine
+that has a GPU, the first CUDA call raises instead of silently falling back.
+"""
+from __future__ import annotations
+
+import collections
+from typing import Callable, Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import reference as ref
+from . import mimo_scan_ref
+
+_CUDA_IMPL: Dict[str, Callable] = {}
+_FALLBACKS: "collections.Counter[str]" = collections.Counter()
+_LAUNCHES: "collections.Counter[str]" = collections.Counter()
+_DISABLED: set = set()
+_ext_checked = False
+
+
+def register_cuda(name: str, fn: Callable) -> None:
+    _CUDA_IMPL[name] = fn
+
+
+def disable_cuda(*names: str) -> None:
+    """Route the named ops through the PyTorch definitions (used by A/B benchmarks)."""
+    _DISABLED.update(names)
+
+
+def enable_cuda(*names: str) -> None:
+    for n in names:
+        _DISABLED.discard(n)
+
+
+def fallback_counts() -> Dict[str, int]:
+    return dict(_FALLBACKS)
+
+
+def launch_counts() -> Dict[str, int]:
+    """Number of calls that reached one of this package's own CUDA kernels, per op."""
+    return dict(_LAUNCHES)
+
+
+def reset_counters() -> None:
+    _FALLBACKS.clear()
+    _LAUNCHES.clear()
+
+
+def count_launch(name: str, n: int = 1) -> None:
+    _LAUNCHES[name] += n
+
+
+def _ensure_ext() -> None:
+    global _ext_checked
+    if _ext_checked:
+        return
+    _ext_checked = True
+    from . import cuda  # noqa: F401  (registers kernels; raises if the .so is missing on a GPU box)
+
+
+def _cuda(name: str, *tensors) -> Optional[Callable]:
+    t = tensors[0]
+    if not t.is_cuda:
+        return None
+    _ensure_ext()
+    fn = _CUDA_IMPL.get(name)
+    if fn is None or name in _DISABLED:
+        _FALLBACKS[name] += 1
+        return None
+    return fn
+
+
+# ---- dense ---------------------------------------------------------------
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w^T``; w is [out, in]."""
+    fn = _cuda("linear", x)
+    if fn is not None:
+        y = fn(x, w)
+        if y is not None:
+            return y
+    return F.linear(x, w.to(x.dtype) if w.dtype != x.dtype else w)
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, counts_host=None) -> torch.Tensor:
+    """Rows of x sorted by expert; w [E, out, in]; counts [E] rows per expert."""
+    fn = _cuda("grouped_linear", x)
+    if fn is not None:
+        y = fn(x, w, counts, counts_host)
+        if y is not None:
+            return y
+    ch = counts_host if counts_host is not None else counts.tolist()
+    return ref.grouped_gemm(x, w.transpose(1, 2).to(x.dtype), ch)
+
+
+# ---- norms / activations ---------------------------------------------------
+
+def rmsnorm(x, weight, eps: float = 1e-5):
+    fn = _cuda("rmsnorm", x)
+    if fn is not None:
+        return fn(x, weight, eps)
+    return ref.rmsnorm(x, weight, eps)
+
+
+def rmsnorm_gated(x, weight, z=None, eps: float = 1e-5, group_size=None, norm_before_gate=True):
+    return ref.rmsnorm_gated(x, weight, z, eps, group_size, norm_before_gate)
+
+
+def swiglu(gate_up):
+    fn = _cuda("swiglu", gate_up)
+    if fn is not None:
+        return fn(gate_up)
+    return ref.swiglu(gate_up)
+
+
+def apply_rope(x, cos, sin):
+    return ref.apply_rope(x, cos, sin)
+
+
+# ---- embeddings --------------------------------------------------------------
+
+def ngram_hash_embed(token_ids, table, mults, bias, table_sizes, table_offsets, order_of_table):
+    fn = _cuda("ngram_hash_embed", table)
+    if fn is not None:
+        return fn(token_ids, table, mults, bias, table_sizes, table_offsets, order_of_table)
+    return ref.ngram_hash_embed(token_ids, table, mults, bias, table_sizes, table_offsets, order_of_table)
+
+
+# ---- sequence mixers ----------------------------------------------------------
+
+def mimo_scan(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Psi, Zeta, Phi, angles, D, Z,
+              rotary_dim_divisor: int = 4, chunk_size: int = 16):
+    fn = _cuda("mimo_scan", V)
+    if fn is not None:
+        return fn(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Psi, Zeta, Phi, angles, D, Z,
+                  rotary_dim_divisor, chunk_size)
+    return mimo_scan_ref.mimo_scan_chunked(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Psi, Zeta, Phi,
+                                           angles, D, Z, rotary_dim_divisor, chunk_size)
+
+
+def angle_cumsum(angles_raw, dt):
+    return mimo_scan_ref.angle_cumsum(angles_raw, dt)
+
+
+def m2rnn_scan(q, k, v, W, f):
+    fn = _cuda("m2rnn_scan", v)
+    if fn is not None:
+        return fn(q, k, v, W, f)
+    return ref.m2rnn_scan(q, k, v, W, f)[0]
+
+
+# ---- DSA ---------------------------------------------------------------------
+
+def indexer_topk(q_idx, k_idx, w, topk: int):
+    fn = _cuda("indexer_topk", q_idx)
+    if fn is not None:
+        return fn(q_idx, k_idx, w, topk)
+    with torch.no_grad():
+        return ref.indexer_topk(q_idx, k_idx, w, topk)
+
+
+def sparse_mla(q, kv, indices, scale: float, d_v: int):
+    fn = _cuda("sparse_mla", q)
+    if fn is not None:
+        return fn(q, kv, indices, scale, d_v)
+    return ref.sparse_mla(q, kv, indices, scale, d_v)[0]
+
+
+def causal_attention(q, k, v, scale: float):
+    """Dense causal attention, q/k [B,S,H,Dqk], v [B,S,H,Dv]."""
+    fn = _cuda("causal_attention", q)
+    if fn is not None:
+        return fn(q, k, v, scale)
+    o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                       is_causal=True, scale=scale)
+    return o.transpose(1, 2)
+
+
+# ---- loss --------------------------------------------------------------------
+
+def linear_cross_entropy(hidden, weight, labels, ignore_index: int = -100, reduction: str = "none"):
+    fn = _cuda("linear_cross_entropy", hidden)
+    if fn is not None:
+        return fn(hidden, weight, labels, ignore_index, reduction)
+    return ref.linear_cross_entropy(hidden, weight, labels, ignore_index, reduction)
+
+
+# ---- MoE ---------------------------------------------------------------------
+
+def router_topk(logits, topk, score_function="sigmoid", expert_bias=None, norm_topk_prob=True):
+    fn = _cuda("router_topk", logits)
+    if fn is not None:
+        return fn(logits, topk, score_function, expert_bias, norm_topk_prob)
+    return ref.router_topk(logits, topk, score_function, expert_bias, norm_topk_prob)

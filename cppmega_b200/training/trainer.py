@@ -1,0 +1,222 @@
+"""Training loop: micro-batch accumulation, pipeline schedule, optimizer step, logging.
+
+The reference delegates all of this to Megatron's ``pretrain`` (scripts/remote_smoke_h200_dsa_9_4_m.sh:691-740);
+here it is a small explicit loop.  The batch / loss contract matches the schedules of the
+reference: a batch carries ``tokens, labels, loss_mask`` and the loss function returns
+``(sum(loss*mask), num_tokens)`` (cppmega/megatron/hybrid_schedule_plan.py:403-452).
+
+Public entry points: :class:`Trainer` (``train_step(batch)``, ``fit(iterator, steps)``) and
+:func:`synthetic_batches`.
+"""
+from __future__ import annotations
+
+import math
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Iterator, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config.model import ModelConfig
+from ..models.nam56r import NAM56RModel, build_model
+from ..parallel import state as pstate
+from ..parallel.dist_optimizer import DistributedOptimizer, OptimizerConfig
+from ..parallel.state import ParallelConfig, ParallelContext
+from ..parallel.tensor_parallel import allreduce_sequence_parallel_grads
+from .lr import LRSchedule
+
+
+@dataclass
+class TrainConfig:
+    micro_batch_size: int = 4
+    global_batch_size: Optional[int] = None      # default: micro_batch_size * dp
+    seq_length: int = 4096
+    dtype: str = "bf16"                          # bf16 | fp32
+    recompute: str = "none"                      # none | selective | full
+    seed: int = 1234
+    log_interval: int = 1
+    check_finite: bool = True
+    precision_recipe: str = "bf16"               # bf16 | mxfp8 (block-scaled linears)
+    optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
+    lr_schedule: Optional[LRSchedule] = None
+    update_router_bias: bool = True
+    pipeline_schedule: str = "1f1b"              # 1f1b | interleaved | dualpipev
+
+    def torch_dtype(self) -> torch.dtype:
+        return {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[self.dtype]
+
+
+class NonFiniteLossError(RuntimeError):
+    pass
+
+
+class Trainer:
+    def __init__(self, model_cfg: ModelConfig, train_cfg: TrainConfig,
+                 pc: Optional[ParallelContext] = None, device: Optional[torch.device] = None,
+                 model: Optional[NAM56RModel] = None):
+        self.model_cfg, self.cfg = model_cfg, train_cfg
+        self.pc = pc or pstate.get_context()
+        if device is None:
+            device = (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
+                      else torch.device("cpu"))
+        self.device = device
+        self.model = model or build_model(model_cfg, self.pc, dtype=train_cfg.torch_dtype(), seed=train_cfg.seed,
+                                          recompute=train_cfg.recompute, device=device)
+        self.optimizer = DistributedOptimizer(self.model, train_cfg.optimizer, self.pc)
+        if self.pc.world_size > 1 and device.type == "cuda" and self.pc.config.fused_collectives:
+            self._attach_fused_paths()
+        self.lr_schedule = train_cfg.lr_schedule or LRSchedule(lr=train_cfg.optimizer.lr, style="constant")
+        self.step = 0
+        dp = self.pc.dp
+        gbs = train_cfg.global_batch_size or train_cfg.micro_batch_size * dp
+        if gbs % (train_cfg.micro_batch_size * dp):
+            raise ValueError(f"global batch {gbs} not divisible by micro_batch*dp={train_cfg.micro_batch_size * dp}")
+        self.global_batch_size = gbs
+        self.num_microbatches = gbs // (train_cfg.micro_batch_size * dp)
+        self._sp_params = [p for p in self.model.parameters() if getattr(p, "sequence_parallel_grad", False)]
+        self.history: List[Dict[str, float]] = []
+        self.tokens_seen = 0
+        self.watchdog = None
+
+    def _attach_fused_paths(self):
+        try:
+            from ..parallel import fused_attach
+        except ImportError:
+            return
+        fused_attach.attach(self)
+
+    # ---- one optimizer step ------------------------------------------------
+    def _to_device(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        return {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}
+
+    def forward_backward(self, microbatches: List[Dict[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
+        pc = self.pc
+        if pc.pp > 1:
+            from ..parallel.pipeline import run_pipeline_schedule
+            return run_pipeline_schedule(self, microbatches)
+        n = len(microbatches)
+        tot_loss = None
+        tot_lm = None
+        mtp: Optional[List[torch.Tensor]] = None
+        for i, mb in enumerate(microbatches):
+            mb = self._to_device(mb)
+            self.optimizer.set_microbatch(is_last=(i == n - 1), grad_scale=1.0)
+            out = self.model(mb["input_ids"], mb["labels"], mb.get("loss_mask"),
+                             structure_inputs=mb.get("structure_inputs"))
+            (out["loss"] / n).backward()
+            l = out["loss"].detach()
+            tot_loss = l if tot_loss is None else tot_loss + l
+            tot_lm = out["lm_loss"] if tot_lm is None else tot_lm + out["lm_loss"]
+            if out["mtp_losses"]:
+                mtp = out["mtp_losses"] if mtp is None else [a + b for a, b in zip(mtp, out["mtp_losses"])]
+        res = {"loss": tot_loss / n, "lm_loss": tot_lm / n}
+        if mtp is not None:
+            res["mtp_losses"] = [m / n for m in mtp]
+        return res
+
+    def train_step(self, batch) -> Dict[str, torch.Tensor]:
+        """``batch``: one dict (split into micro-batches along dim 0) or a list of micro-batch
+        dicts.  Tensors may live in pinned host memory; they are copied to the device here.
+        Returns device scalars (no host sync) - call ``.item()`` on what you need."""
+        cfg = self.cfg
+        mbs = batch if isinstance(batch, list) else self._split(batch)
+        self.optimizer.zero_grad()
+        res = self.forward_backward(mbs)
+        if self._sp_params and self.pc.sequence_parallel:
+            self.optimizer.finish_grad_sync()      # sums commute: TP all-reduce after the DP reduction
+            allreduce_sequence_parallel_grads_main(self._sp_params, self.pc)
+        lr = self.lr_schedule(self.step)
+        stats = self.optimizer.step(lr)
+        if cfg.update_router_bias:
+            self.model.update_router_biases()
+        self.step += 1
+        self.tokens_seen += self.global_batch_size * cfg.seq_length
+        res.update(stats)
+        res["lr"] = lr
+        if self.watchdog is not None:
+            self.watchdog.beat(self.step)
+        return res
+
+    def _split(self, batch: Dict[str, torch.Tensor]) -> List[Dict[str, torch.Tensor]]:
+        n = self.num_microbatches
+        if n == 1:
+            return [batch]
+        out = []
+        for i in range(n):
+            out.append({k: (v.chunk(n, dim=0)[i] if torch.is_tensor(v) else v) for k, v in batch.items()})
+        return out
+
+    def reduce_loss_for_logging(self, res: Dict[str, torch.Tensor]) -> Dict[str, float]:
+        """Average the reported losses over data-parallel ranks (one small all-reduce) and
+        move them to the host; raises on NaN/Inf when ``check_finite``."""
+        pc = self.pc
+        keys = ["loss", "lm_loss"]
+        vals = [res["loss"].float(), res["lm_loss"].float()]
+        for i, m in enumerate(res.get("mtp_losses", [])):
+            keys.append(f"mtp_{i + 1}_loss")
+            vals.append(m.float())
+        keys.append("grad_norm")
+        vals.append(res["grad_norm"].float())
+        t = torch.stack([v.reshape(()) for v in vals])
+        if pc.dp > 1:
+            gn = t[-1].clone()
+            dist.all_reduce(t, group=pc.dp_group)
+            t /= pc.dp
+            t[-1] = gn
+        host = t.tolist()
+        out = dict(zip(keys, host))
+        if self.cfg.check_finite and not all(math.isfinite(v) for v in host):
+            raise NonFiniteLossError(f"non-finite training statistics at step {self.step}: {out}")
+        return out
+
+    # ---- loop ---------------------------------------------------------------
+    def fit(self, batches: Iterator, steps: int, log=None) -> List[Dict[str, float]]:
+        cfg = self.cfg
+        flops_tok = self.model_cfg.flops_per_token(cfg.seq_length)
+        t_last = time.perf_counter()
+        for _ in range(steps):
+            res = self.train_step(next(batches))
+            if cfg.log_interval and self.step % cfg.log_interval == 0:
+                rec = self.reduce_loss_for_logging(res)
+                now = time.perf_counter()
+                dt = (now - t_last) / cfg.log_interval
+                t_last = now
+                toks = self.global_batch_size * cfg.seq_length
+                rec.update(step=self.step, lr=res["lr"], step_ms=dt * 1e3, tokens_per_s=toks / dt,
+                           tflops_per_gpu=flops_tok * toks / dt / 1e12 / max(self.pc.world_size, 1))
+                self.history.append(rec)
+                if log is not None and self.pc.rank == 0:
+                    log(rec)
+        return self.history
+
+
+def allreduce_sequence_parallel_grads_main(params, pc: ParallelContext) -> None:
+    """Same as :func:`allreduce_sequence_parallel_grads` but on ``main_grad`` buffers."""
+    if pc.tp == 1 or not pc.sequence_parallel:
+        return
+    for p in params:
+        g = getattr(p, "main_grad", None)
+        if g is not None:
+            dist.all_reduce(g, group=pc.tp_group)
+
+
+def synthetic_batches(vocab: int, micro_batch: int, seq: int, num_microbatches: int = 1, seed: int = 0,
+                      pin: bool = True, rank: int = 0) -> Iterator[List[Dict[str, torch.Tensor]]]:
+    """Endless stream of uniform-random token batches in (pinned) host memory; labels are
+    the next token."""
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(seed + 7919 * rank)
+    pin = pin and torch.cuda.is_available()
+    while True:
+        mbs = []
+        for _ in range(num_microbatches):
+            tok = torch.randint(0, vocab, (micro_batch, seq + 1), generator=gen, dtype=torch.long)
+            ids, lab = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+            if pin:
+                ids, lab = ids.pin_memory(), lab.pin_memory()
+            mbs.append({"input_ids": ids, "labels": lab})
+        yield mbs
+
+
+_ = (ParallelConfig, allreduce_sequence_parallel_grads)
