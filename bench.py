@@ -1,0 +1,245 @@
+#!/usr/bin/env python
+"""Headline benchmark: NAM56R training tokens/sec at seq 4096 on N B200 GPUs of one node.
+
+    python bench.py --gpus 1 --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Weak scaling: micro-batch 4 x seq 4096 per GPU, expert-parallel over all N ranks
+(EP = DP = N), ZeRO-1 distributed optimizer, bf16 compute, synthetic uniform tokens,
+random-init weights.  Rank 0 prints one JSON line.
+
+Two timed regions, both bracketed by barrier + synchronize, timed with CUDA events, max
+over ranks:
+  * ``value``: K optimizer steps on batches already resident on the device;
+  * ``e2e``: K steps through ``Trainer.train_step`` fed from pinned host memory, with the
+    loss read back to the host every step.
+``--impl reference`` reports why the reference stack cannot run on this machine.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "NAM56R train tokens/sec/box @seq4096"
+PUBLISHED_TOK_S_BOX = 74000.0      # reference bf16 record, 8xH200 (docs/production_status.md:48-53)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        super().__init__(daemon=True)
+        self.gpu_index = gpu_index
+        self.samples = []
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        while not self._stop_evt.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.gpu_index)], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 8:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.2)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=6)
+
+    def summary(self) -> dict:
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "", 1).isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "", 1).isdigit()]
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            for name, val in zip(names, s[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(self.samples)}
+
+
+def reference_arm(args) -> int:
+    """The reference needs its Megatron-LM fork, TransformerEngine fork, mamba_ssm and TileLang
+    (STACK.lock); none of them is installed or installable offline here."""
+    why = None
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    sys.path.insert(0, ref_dir)
+    missing = []
+    for mod in ("megatron.core", "transformer_engine", "mamba_ssm", "tilelang"):
+        try:
+            __import__(mod)
+        except Exception:
+            missing.append(mod)
+    if missing:
+        why = ("reference training entry point needs " + ", ".join(missing) +
+               " (pinned forks in STACK.lock), which are not in the image or the offline wheelhouse")
+    else:
+        why = "reference dependencies import, but its launcher needs a tokenised corpus and the pinned forks"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="nam56r")
+    ap.add_argument("--micro-batch", type=int, default=4)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--depth", type=int, default=0, help="debug: truncate the stack (result is then not the headline config)")
+    ap.add_argument("--recompute", default="auto", choices=["auto", "none", "selective", "full"])
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from cppmega_b200.config.model import get_preset
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.parallel import state as pstate
+    from cppmega_b200.parallel.dist_optimizer import OptimizerConfig
+    from cppmega_b200.parallel.state import ParallelConfig
+    from cppmega_b200.training.trainer import TrainConfig, Trainer, synthetic_batches
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(f"bench.py: --gpus {args.gpus} needs torch.distributed.run with {args.gpus} ranks", file=sys.stderr)
+            return 2
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+
+    overrides = {}
+    if args.depth:
+        overrides["depth"] = args.depth
+    if args.seq != 4096:
+        overrides["seq_length"] = args.seq
+    mcfg = get_preset(args.model, **overrides)
+    ep = world if mcfg.moe.num_experts % world == 0 else 1
+    pcfg = ParallelConfig(tp=1, pp=1, ep=ep, distributed_optimizer=True)
+    pc = pstate.initialize(pcfg)
+    recompute = args.recompute
+    if recompute == "auto":
+        # one GPU holds all 16 experts and the whole optimizer state (~16 bytes/param): only
+        # per-layer recomputation leaves room for activations.  With experts and optimizer
+        # state sharded over >= 4 ranks the activations fit without recomputation.
+        recompute = "full" if world < 4 else "selective"
+    tcfg = TrainConfig(micro_batch_size=args.micro_batch, seq_length=args.seq, dtype="bf16", recompute=recompute,
+                       optimizer=OptimizerConfig(lr=1e-5, weight_decay=0.1, grad_dtype="bf16" if world < 4 else "fp32"),
+                       log_interval=0)
+    trainer = Trainer(mcfg, tcfg, pc, device=device)
+    n_params = sum(p.numel() for p in trainer.model.parameters())
+
+    host_batches = synthetic_batches(mcfg.vocab_size, args.micro_batch, args.seq, seed=1234, rank=rank)
+    dev_pool = []
+    for _ in range(2):
+        mb = next(host_batches)
+        dev_pool.append([{k: v.to(device) for k, v in m.items()} for m in mb])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def step_device(i):
+        trainer.train_step(dev_pool[i % len(dev_pool)])
+
+    last_loss = []
+
+    def step_e2e(i):
+        res = trainer.train_step(next(host_batches))
+        last_loss.append(float(res["loss"].item()))       # device -> host read of the step's result
+
+    for i in range(args.warmup):
+        step_device(i)
+    torch.cuda.synchronize()
+    from cppmega_b200.ops import cuda as cu
+    cu.check_errors()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    F_.reset_counters()
+    ms_dev = timed(step_device, args.steps)
+    launches = sum(F_.launch_counts().values())
+    fallbacks = F_.fallback_counts()
+    e2e = None
+    if not args.no_e2e:
+        ms_e2e = timed(step_e2e, args.steps)
+    if rank == 0:
+        sampler.stop()
+    cu.check_errors()
+
+    tokens_per_step = args.micro_batch * args.seq * world
+    value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    if not args.no_e2e:
+        h2d = 2 * args.micro_batch * args.seq * 8             # input_ids + labels, int64, per rank
+        e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
+               "ms_per_step": ms_e2e / args.steps, "last_loss": last_loss[-1] if last_loss else None}
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": value / PUBLISHED_TOK_S_BOX, "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights",
+            "impl": "ours",
+            "config": {"model": f"{mcfg.name} {n_params / 1e9:.2f}B params on rank 0 ({mcfg.param_count()['total'] / 1e9:.2f}B total), "
+                                f"{mcfg.depth} layers {mcfg.pattern}, hidden {mcfg.hidden_size}, vocab {mcfg.vocab_size}, MTP {mcfg.mtp.num_layers}",
+                       "global_batch": args.micro_batch * world, "micro_batch": args.micro_batch, "seq_len": args.seq,
+                       "parallelism": f"ep{ep}dp{world}" if world > 1 else "single GPU (16 local experts)",
+                       "distributed_optimizer": True, "recompute": recompute,
+                       "l2": "weights + activations per step are far larger than the 126 MB L2",
+                       "headline_config": not args.depth and args.seq == 4096 and args.micro_batch == 4},
+            "clocks": sampler.summary() if rank == 0 else None,
+            "e2e": e2e, "gpu_launches": launches, "fallback_ops": fallbacks,
+            "model_tflops_per_gpu": mcfg.flops_per_token(args.seq) * value / world / 1e12,
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        pstate.destroy()
+    return 0
+
+
+if __name__ == "__main__":
+    t0 = time.time()
+    sys.exit(main())

@@ -86,9 +86,7 @@ class GroupedExperts(nn.Module):
         self.last_counts: Optional[torch.Tensor] = None
 
     def forward(self, x: torch.Tensor, counts: torch.Tensor, counts_host=None) -> torch.Tensor:
-        h = F_.grouped_linear(x, self.weight1, counts, counts_host)
-        h = F_.swiglu(h)
-        return F_.grouped_linear(h, self.weight2, counts, counts_host)
+        return F_.moe_experts(x, self.weight1, self.weight2, counts, counts_host)
 
 
 class MoELayer(nn.Module):

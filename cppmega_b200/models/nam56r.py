@@ -245,23 +245,29 @@ class NAM56RModel(nn.Module):
         w = self.output_weight()
         if pc.sequence_parallel:
             hiddens = [gather_seq(h, pc) for h in hiddens]
-        if cfg.mtp.fused_with_main_ce or len(hiddens) == 1:
-            hcat = torch.cat([h.reshape(B * S, -1) for h in hiddens], dim=0)
-            lcat = torch.cat([l.reshape(-1) for l in label_list], dim=0)
-            per_tok = self._ce(hcat, w, lcat).view(len(hiddens), B * S)
-        else:
-            per_tok = torch.stack([self._ce(h.reshape(B * S, -1), w, l.reshape(-1))
-                                   for h, l in zip(hiddens, label_list)])
-        n_main = mask_list[0].sum().clamp_min(1.0)
-        lm_loss = per_tok[0].sum() / n_main
-        total = lm_loss
-        mtp_losses: List[torch.Tensor] = []
+        # one weighted cross-entropy over [main | depth 1 | ... | depth D]: the row weights carry the
+        # loss mask, the per-head token count and the MTP depth scaling
         D = len(hiddens) - 1
+        counts = [m.sum().clamp_min(1.0) for m in mask_list]
+        scales = [1.0] + [cfg.mtp.loss_scaling_factor / D] * D
+        row_w = torch.cat([(m * (sc / n)).reshape(-1) for m, sc, n in zip(mask_list, scales, counts)])
+        if cfg.mtp.fused_with_main_ce or D == 0:
+            hcat = torch.cat([h.reshape(B * S, -1) for h in hiddens], dim=0) if D else hiddens[0].reshape(B * S, -1)
+            lcat = torch.cat([l.reshape(-1) for l in label_list], dim=0)
+            total, per_tok = self._ce(hcat, w, lcat, row_w)
+        else:
+            total, parts = None, []
+            for i, (h, l) in enumerate(zip(hiddens, label_list)):
+                t_i, p_i = self._ce(h.reshape(B * S, -1), w, l.reshape(-1), row_w[i * B * S:(i + 1) * B * S])
+                total = t_i if total is None else total + t_i
+                parts.append(p_i)
+            per_tok = torch.cat(parts)
+        per_tok = per_tok.view(D + 1, B * S)
+        n_main = counts[0]
+        lm_loss = (per_tok[0] * mask_list[0].reshape(-1)).sum() / n_main
+        mtp_losses: List[torch.Tensor] = []
         for d in range(1, D + 1):
-            n_d = mask_list[d].sum().clamp_min(1.0)
-            l_d = per_tok[d].sum() / n_d
-            mtp_losses.append(l_d.detach())
-            total = total + (cfg.mtp.loss_scaling_factor / D) * l_d
+            mtp_losses.append(((per_tok[d] * mask_list[d].reshape(-1)).sum() / counts[d]).detach())
         if hasattr(self, "fastmtp"):
             fl = self.fastmtp(x.detach(), input_ids, labels, loss_mask, self.embedding, w.detach())
             total = total + cfg.mtp.fastmtp_lambda * fl
@@ -274,11 +280,12 @@ class NAM56RModel(nn.Module):
         self.last_metrics = out
         return out
 
-    def _ce(self, hidden, weight, labels):
+    def _ce(self, hidden, weight, labels, row_weights):
         if self.pc.tp > 1:
             from ..parallel.vocab_parallel import vocab_parallel_linear_cross_entropy
-            return vocab_parallel_linear_cross_entropy(hidden, weight, labels, self.pc, IGNORE_INDEX)
-        return F_.linear_cross_entropy(hidden, weight, labels, IGNORE_INDEX, "none")
+            per_tok = vocab_parallel_linear_cross_entropy(hidden, weight, labels, self.pc, IGNORE_INDEX)
+            return (per_tok * row_weights).sum(), per_tok.detach()
+        return F_.linear_cross_entropy_weighted(hidden, weight, labels, row_weights, IGNORE_INDEX)
 
     # ---- housekeeping -----------------------------------------------------
     def moe_layers(self):

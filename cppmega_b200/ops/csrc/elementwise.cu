@@ -1,0 +1,448 @@
+// Bandwidth-bound kernels: RMSNorm fwd/bwd, SwiGLU fwd/bwd, fused AdamW shard update,
+// gradient-buffer sum of squares.  All use 16-byte accesses and keep a row in registers between
+// the reduction and the write so each element crosses HBM once per direction.
+// (Role of the TE norm / activation kernels the reference links, cppmega/megatron/nam56r_full_spec.py:224-240.)
+#include "common.cuh"
+
+namespace cm {
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm.  One CTA of TPB threads per row for wide rows; one warp per row for narrow rows.
+// ---------------------------------------------------------------------------------------------
+template <int TPB, int VPT>   // VPT 16-byte vectors per thread; row width <= TPB*VPT*8
+__global__ void __launch_bounds__(TPB) rmsnorm_fwd_wide(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                        __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
+                                                        int rows, int H, float eps) {
+  __shared__ float red[TPB / 32];
+  const int nvec = H / 8;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    uint4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * TPB;
+      if (idx < nvec) {
+        v[i] = xr[idx];
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __bfloat1622float2(b[j]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < TPB / 32; ++i) tot += red[i];
+    __syncthreads();
+    const float rstd = rsqrtf(tot / H + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * TPB;
+      if (idx < nvec) {
+        const uint4 wv = wr[idx];
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+        const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+        uint4 o;
+        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __bfloat1622float2(b[j]);
+          float2 g = __bfloat1622float2(wb[j]);
+          op[j] = pack_bf16(f.x * rstd * g.x, f.y * rstd * g.y);
+        }
+        yr[idx] = o;
+      }
+    }
+  }
+}
+
+// narrow rows: one warp per row, H multiple of 8, H <= 1024
+__global__ void __launch_bounds__(256) rmsnorm_fwd_narrow(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
+                                                          int rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int nvec = H / 8;
+  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    uint4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = lane + i * 32;
+      if (idx < nvec) {
+        v[i] = xr[idx];
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __bfloat1622float2(b[j]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / H + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = lane + i * 32;
+      if (idx < nvec) {
+        const uint4 wv = wr[idx];
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+        const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+        uint4 o;
+        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __bfloat1622float2(b[j]);
+          float2 g = __bfloat1622float2(wb[j]);
+          op[j] = pack_bf16(f.x * rstd * g.x, f.y * rstd * g.y);
+        }
+        yr[idx] = o;
+      }
+    }
+  }
+}
+
+// backward: dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); dw += sum_rows dy * xhat  (fp32 atomics)
+// generic layout: each warp owns a row; lanes stride over 16-byte vectors; dw partials are kept
+// per-thread for the columns that thread touches (same columns for every row it visits).
+template <int MAXV>   // max vectors per lane (H <= 32*MAXV*8)
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                          const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in,
+                                                          __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
+                                                          int rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int nvec = H / 8;
+  float dwacc[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  for (int row = blockIdx.x * wpb + (threadIdx.x >> 5); row < rows; row += gridDim.x * wpb) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * H);
+    const float rstd = rstd_in[row];
+    float xh[MAXV][8], gw[MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int idx = lane + i * 32;
+      if (idx < nvec) {
+        const uint4 xv = xr[idx], gv = gr[idx], wv = wr[idx];
+        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
+        const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 xf = __bfloat1622float2(xb[j]), gf = __bfloat1622float2(gb[j]), wf = __bfloat1622float2(wb[j]);
+          xh[i][2 * j] = xf.x * rstd;       xh[i][2 * j + 1] = xf.y * rstd;
+          gw[i][2 * j] = gf.x * wf.x;       gw[i][2 * j + 1] = gf.y * wf.y;
+          dwacc[i][2 * j] += gf.x * xh[i][2 * j];
+          dwacc[i][2 * j + 1] += gf.y * xh[i][2 * j + 1];
+          dot += gw[i][2 * j] * xh[i][2 * j] + gw[i][2 * j + 1] * xh[i][2 * j + 1];
+        }
+      }
+    }
+    dot = warp_sum(dot) / H;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * H);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int idx = lane + i * 32;
+      if (idx < nvec) {
+        uint4 o;
+        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          op[j] = pack_bf16(rstd * (gw[i][2 * j] - xh[i][2 * j] * dot), rstd * (gw[i][2 * j + 1] - xh[i][2 * j + 1] * dot));
+        dxr[idx] = o;
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int idx = lane + i * 32;
+      if (idx < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(dw + idx * 8 + j, dwacc[i][j]);
+      }
+    }
+  }
+}
+
+// wide rows: one CTA per row (grid-stride), dw partials for this thread's columns stay in registers
+template <int TPB, int VPT>
+__global__ void __launch_bounds__(TPB) rmsnorm_bwd_wide(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                        const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in,
+                                                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
+                                                        int rows, int H) {
+  __shared__ float red[TPB / 32];
+  const int nvec = H / 8;
+  float dwacc[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * H);
+    const float rstd = rstd_in[row];
+    float xh[VPT][8], gw[VPT][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * TPB;
+      if (idx < nvec) {
+        const uint4 xv = xr[idx], gv = gr[idx], wv = wr[idx];
+        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
+        const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 xf = __bfloat1622float2(xb[j]), gf = __bfloat1622float2(gb[j]), wf = __bfloat1622float2(wb[j]);
+          xh[i][2 * j] = xf.x * rstd;       xh[i][2 * j + 1] = xf.y * rstd;
+          gw[i][2 * j] = gf.x * wf.x;       gw[i][2 * j + 1] = gf.y * wf.y;
+          dwacc[i][2 * j] += gf.x * xh[i][2 * j];
+          dwacc[i][2 * j + 1] += gf.y * xh[i][2 * j + 1];
+          dot += gw[i][2 * j] * xh[i][2 * j] + gw[i][2 * j + 1] * xh[i][2 * j + 1];
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < TPB / 32; ++i) tot += red[i];
+    __syncthreads();
+    dot = tot / H;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * H);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * TPB;
+      if (idx < nvec) {
+        uint4 o;
+        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          op[j] = pack_bf16(rstd * (gw[i][2 * j] - xh[i][2 * j] * dot), rstd * (gw[i][2 * j + 1] - xh[i][2 * j + 1] * dot));
+        dxr[idx] = o;
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * TPB;
+      if (idx < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(dw + idx * 8 + j, dwacc[i][j]);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU: in = [a | b] (width 2F), out = silu(a) * b
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                                         long long rows, int F) {
+  const int fv = F / 8;
+  const long long total = rows * fv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / fv;
+    const int c = int(i - r * fv);
+    const uint4 a = reinterpret_cast<const uint4*>(in + r * 2 * F)[c];
+    const uint4 b = reinterpret_cast<const uint4*>(in + r * 2 * F + F)[c];
+    const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* bb = reinterpret_cast<const __nv_bfloat162*>(&b);
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 af = __bfloat1622float2(ab[j]), bf = __bfloat1622float2(bb[j]);
+      op[j] = pack_bf16(af.x / (1.f + __expf(-af.x)) * bf.x, af.y / (1.f + __expf(-af.y)) * bf.y);
+    }
+    reinterpret_cast<uint4*>(out + r * F)[c] = o;
+  }
+}
+
+__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
+                                                         __nv_bfloat16* __restrict__ din, long long rows, int F) {
+  const int fv = F / 8;
+  const long long total = rows * fv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / fv;
+    const int c = int(i - r * fv);
+    const uint4 a = reinterpret_cast<const uint4*>(in + r * 2 * F)[c];
+    const uint4 b = reinterpret_cast<const uint4*>(in + r * 2 * F + F)[c];
+    const uint4 g = reinterpret_cast<const uint4*>(dout + r * F)[c];
+    const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* bb = reinterpret_cast<const __nv_bfloat162*>(&b);
+    const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&g);
+    uint4 da, db;
+    uint32_t* dap = reinterpret_cast<uint32_t*>(&da);
+    uint32_t* dbp = reinterpret_cast<uint32_t*>(&db);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 af = __bfloat1622float2(ab[j]), bf = __bfloat1622float2(bb[j]), gf = __bfloat1622float2(gb[j]);
+      const float s0 = 1.f / (1.f + __expf(-af.x)), s1 = 1.f / (1.f + __expf(-af.y));
+      const float d0 = s0 * (1.f + af.x * (1.f - s0)), d1 = s1 * (1.f + af.y * (1.f - s1));
+      dap[j] = pack_bf16(gf.x * bf.x * d0, gf.y * bf.y * d1);
+      dbp[j] = pack_bf16(gf.x * af.x * s0, gf.y * af.y * s1);
+    }
+    reinterpret_cast<uint4*>(din + r * 2 * F)[c] = da;
+    reinterpret_cast<uint4*>(din + r * 2 * F + F)[c] = db;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused AdamW on a flat fp32 master shard; gradient in fp32 or bf16; writes the bf16/fp32 copy.
+// `clip` is a device scalar multiplied into the gradient (gradient clipping without a host sync).
+// ---------------------------------------------------------------------------------------------
+template <typename GradT, typename OutT>
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                                                    const GradT* __restrict__ g, OutT* __restrict__ out,
+                                                    const uint8_t* __restrict__ wd_mask, const float* __restrict__ clip,
+                                                    long long n, float lr, float b1, float b2, float eps, float wd,
+                                                    float inv_bc1, float inv_bc2) {
+  const float cs = clip ? *clip : 1.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gi = float(g[i]) * cs;
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    float p = master[i];
+    float upd = (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+    if (wd_mask[i]) upd += wd * p;
+    p -= lr * upd;
+    m[i] = mi;
+    v[i] = vi;
+    master[i] = p;
+    out[i] = OutT(p);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) sumsq_kernel(const T* __restrict__ g, long long n, float* __restrict__ out) {
+  float s = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float f = float(g[i]);
+    s += f * f;
+  }
+  s = warp_sum(s);
+  __shared__ float red[8];
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    atomicAdd(out, t);
+  }
+}
+
+}  // namespace cm
+
+using namespace cm;
+
+extern "C" int cm_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int H, float eps,
+                              cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (H % 8) return -10;
+  const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+  const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
+  __nv_bfloat16* yp = (__nv_bfloat16*)y;
+  if (H <= 1024) {
+    const int wpb = 8;
+    int grid = (rows + wpb - 1) / wpb;
+    grid = grid < sm_count() * 8 ? grid : sm_count() * 8;
+    rmsnorm_fwd_narrow<<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, H, eps);
+  } else if (H <= 128 * 4 * 8) {
+    int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
+    rmsnorm_fwd_wide<128, 4><<<grid, 128, 0, s>>>(xp, wp, yp, rstd, rows, H, eps);
+  } else if (H <= 256 * 8 * 8) {
+    int grid = rows < sm_count() * 4 ? rows : sm_count() * 4;
+    rmsnorm_fwd_wide<256, 8><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, H, eps);
+  } else {
+    return -12;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int cm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, float* dw,
+                              int rows, int H, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (H % 8) return -10;
+  const int wpb = 8;
+  int grid = (rows + wpb - 1) / wpb;
+  const int cap = sm_count() * 4;
+  grid = grid < cap ? grid : cap;
+  auto xp = (const __nv_bfloat16*)x; auto wp = (const __nv_bfloat16*)w; auto gp = (const __nv_bfloat16*)dy;
+  auto dxp = (__nv_bfloat16*)dx;
+  if (H <= 32 * 1 * 8) rmsnorm_bwd_kernel<1><<<grid, 256, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
+  else if (H <= 128 * 1 * 8) rmsnorm_bwd_wide<128, 1><<<(rows < cap ? rows : cap), 128, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
+  else if (H <= 128 * 4 * 8) rmsnorm_bwd_wide<128, 4><<<(rows < cap ? rows : cap), 128, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
+  else if (H <= 256 * 8 * 8) rmsnorm_bwd_wide<256, 8><<<(rows < cap ? rows : cap), 256, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
+  else return -12;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int cm_swiglu_fwd(const void* in, void* out, long long rows, int F, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (F % 8) return -10;
+  long long total = rows * (F / 8);
+  int grid = (int)((total + 255) / 256 < (long long)sm_count() * 16 ? (total + 255) / 256 : (long long)sm_count() * 16);
+  swiglu_fwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, F);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int cm_swiglu_bwd(const void* in, const void* dout, void* din, long long rows, int F, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (F % 8) return -10;
+  long long total = rows * (F / 8);
+  int grid = (int)((total + 255) / 256 < (long long)sm_count() * 16 ? (total + 255) / 256 : (long long)sm_count() * 16);
+  swiglu_bwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)dout, (__nv_bfloat16*)din, rows, F);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// grad_kind: 0 fp32, 1 bf16; out_kind: 0 fp32, 1 bf16
+extern "C" int cm_adamw(float* master, float* m, float* v, const void* g, void* out, const uint8_t* wd_mask,
+                        const float* clip, long long n, float lr, float b1, float b2, float eps, float wd, float bc1,
+                        float bc2, int grad_kind, int out_kind, cudaStream_t s) {
+  if (n <= 0) return 0;
+  long long blocks = (n + 255) / 256;
+  int grid = (int)(blocks < (long long)sm_count() * 16 ? blocks : (long long)sm_count() * 16);
+  const float i1 = 1.f / bc1, i2 = 1.f / bc2;
+  if (grad_kind == 0 && out_kind == 1)
+    adamw_kernel<float, __nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, (const float*)g, (__nv_bfloat16*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2);
+  else if (grad_kind == 1 && out_kind == 1)
+    adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, (const __nv_bfloat16*)g, (__nv_bfloat16*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2);
+  else if (grad_kind == 0 && out_kind == 0)
+    adamw_kernel<float, float><<<grid, 256, 0, s>>>(master, m, v, (const float*)g, (float*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2);
+  else
+    adamw_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(master, m, v, (const __nv_bfloat16*)g, (float*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// out (device float, caller zeroes it) += sum of squares of g.  kind: 0 fp32, 1 bf16
+extern "C" int cm_sumsq(const void* g, long long n, float* out, int kind, cudaStream_t s) {
+  if (n <= 0) return 0;
+  long long blocks = (n + 255) / 256;
+  int grid = (int)(blocks < (long long)sm_count() * 8 ? blocks : (long long)sm_count() * 8);
+  if (kind == 0) sumsq_kernel<float><<<grid, 256, 0, s>>>((const float*)g, n, out);
+  else sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, n, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

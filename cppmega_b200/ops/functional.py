@@ -102,6 +102,18 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, count
     return ref.grouped_gemm(x, w.transpose(1, 2).to(x.dtype), ch)
 
 
+def moe_experts(x_sorted: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, counts: torch.Tensor, counts_host=None):
+    """SwiGLU expert MLP over expert-sorted rows: ``fc2(swiglu(fc1(x)))`` with per-expert weights
+    ``w1`` [E, 2F, H] and ``w2`` [E, H, F]."""
+    fn = _cuda("moe_experts", x_sorted)
+    if fn is not None:
+        y = fn(x_sorted, w1, w2, counts)
+        if y is not None:
+            return y
+    h = grouped_linear(x_sorted, w1, counts, counts_host)
+    return grouped_linear(swiglu(h), w2, counts, counts_host)
+
+
 # ---- norms / activations ---------------------------------------------------
 
 def rmsnorm(x, weight, eps: float = 1e-5):
@@ -180,9 +192,12 @@ def causal_attention(q, k, v, scale: float):
     fn = _cuda("causal_attention", q)
     if fn is not None:
         return fn(q, k, v, scale)
+    dq, dv = q.shape[-1], v.shape[-1]
+    if q.is_cuda and dv < dq:          # library flash kernels want one head size: zero-pad V
+        v = F.pad(v, (0, dq - dv))
     o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                        is_causal=True, scale=scale)
-    return o.transpose(1, 2)
+    return o.transpose(1, 2)[..., :dv]
 
 
 # ---- loss --------------------------------------------------------------------
@@ -192,6 +207,19 @@ def linear_cross_entropy(hidden, weight, labels, ignore_index: int = -100, reduc
     if fn is not None:
         return fn(hidden, weight, labels, ignore_index, reduction)
     return ref.linear_cross_entropy(hidden, weight, labels, ignore_index, reduction)
+
+
+def linear_cross_entropy_weighted(hidden, weight, labels, row_weights, ignore_index: int = -100):
+    """Returns ``(sum_t row_weights[t] * CE_t, per-token CE)``; the second output carries no
+    gradient.  This is the form the model uses: main and MTP heads are one call whose row
+    weights hold mask / token-count / depth scaling."""
+    fn = _cuda("linear_cross_entropy_weighted", hidden)
+    if fn is not None:
+        out = fn(hidden, weight, labels, row_weights, ignore_index)
+        if out is not None:
+            return out
+    per_tok = ref.linear_cross_entropy(hidden, weight, labels, ignore_index, "none")
+    return (per_tok * row_weights.to(per_tok.dtype)).sum(), per_tok.detach()
 
 
 # ---- MoE ---------------------------------------------------------------------

@@ -144,8 +144,12 @@ def m2rnn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, W: torch.Tenso
 def indexer_scores(q_idx: torch.Tensor, k_idx: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``score[b,i,j] = sum_h w[b,i,h] relu(q_idx[b,i,h,:] . k_idx[b,j,:])`` in fp32
     (cppmega/megatron/dsa_indexer_fused_patch.py:71-133)."""
-    s = torch.einsum("bihd,bjd->bihj", q_idx.float(), k_idx.float())
-    return torch.einsum("bihj,bih->bij", F.relu(s), w.float())
+    qf, kf, wf = q_idx.float(), k_idx.float(), w.float()
+    out = None
+    for h in range(qf.shape[2]):        # one head at a time: never holds [B,S,H,S]
+        s = F.relu(torch.einsum("bid,bjd->bij", qf[:, :, h], kf)) * wf[:, :, h].unsqueeze(-1)
+        out = s if out is None else out + s
+    return out
 
 
 def indexer_topk(q_idx, k_idx, w, topk: int) -> torch.Tensor:

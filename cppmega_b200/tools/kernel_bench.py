@@ -1,0 +1,165 @@
+"""Per-kernel micro-benchmarks with roofline fractions.
+
+    python -m cppmega_b200.tools.kernel_bench [gemm] [grouped] [rmsnorm] [ce] [scan] ... [--out file.json]
+
+Each case is timed with CUDA events after warm-up, with an L2 flush (a write larger than
+the 126 MB L2) between timed iterations, and reported against the measured peaks in
+``MEASURED_PEAKS.json`` at the repository root (copy bandwidth and cuBLAS bf16 throughput)
+or, if that file is absent, against 6.65 TB/s and 1.59 PFLOP/s.
+(Counterpart of the reference's micro-benchmarks, e.g. scripts/bench_m2rnn.py and
+tools/probes/speed_harness.py.)
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from typing import Callable, Dict, List
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks() -> Dict[str, float]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "kind": "fallback"}
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def time_ms(fn: Callable, iters: int = 10, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm() -> List[dict]:
+    from cppmega_b200.ops import cuda as cu
+    pk = peaks()
+    out = []
+    shapes = [  # (M, N, K, a_mn, b_mn, label)
+        (16384, 24960, 4096, False, False, "mamba in_proj fwd"),
+        (16384, 4096, 8192, False, False, "mamba out_proj fwd"),
+        (16384, 4096, 24960, False, True, "mamba in_proj dgrad"),
+        (24960, 4096, 16384, True, True, "mamba in_proj wgrad"),
+        (8192, 8192, 8192, False, False, "square 8192"),
+        (4096, 131072, 4096, False, False, "lm head chunk fwd"),
+    ]
+    for M, N, K, a_mn, b_mn, label in shapes:
+        A = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+        B = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+        C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = time_ms(lambda: cu.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=C))
+        At = A.t() if a_mn else A
+        Bt = B if b_mn else B.t()
+        ms_lib = time_ms(lambda: torch.matmul(At, Bt, out=C))
+        tf = 2.0 * M * N * K / ms / 1e9
+        out.append({"kernel": "gemm_tcgen05", "case": label, "M": M, "N": N, "K": K, "ms": ms, "tflops": tf,
+                    "frac_of_" + pk["kind"]: tf / pk["bf16_tflops"], "cublas_ms": ms_lib,
+                    "cublas_tflops": 2.0 * M * N * K / ms_lib / 1e9})
+        cu.check_errors()
+    return out
+
+
+def bench_grouped() -> List[dict]:
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import extra
+    pk = peaks()
+    T, k, E, H, Fh = 16384, 4, 16, 4096, 896
+    ids = torch.randint(0, E, (T * k,), device="cuda")
+    counts = torch.bincount(ids, minlength=E)
+    x = torch.randn(T * k, H, device="cuda").bfloat16()
+    w1 = (torch.randn(E, 2 * Fh, H, device="cuda") * 0.02).bfloat16()
+    w2 = (torch.randn(E, H, Fh, device="cuda") * 0.02).bfloat16()
+    with torch.no_grad():
+        ms = time_ms(lambda: extra.moe_experts(x, w1, w2, counts))
+    cu.check_errors()
+    flops = 2.0 * T * k * H * Fh * 3
+    return [{"kernel": "moe_experts fwd (pad + grouped fc1 + swiglu + grouped fc2 + unpad)", "tokens": T, "topk": k,
+             "ms": ms, "tflops": flops / ms / 1e9, "frac_of_" + pk["kind"]: flops / ms / 1e9 / pk["bf16_tflops"]}]
+
+
+def bench_rmsnorm() -> List[dict]:
+    from cppmega_b200.ops import cuda as cu
+    pk = peaks()
+    rows, H = 65536, 4096
+    x = torch.randn(rows, H, device="cuda").bfloat16()
+    w = torch.ones(H, device="cuda").bfloat16()
+    with torch.no_grad():
+        ms = time_ms(lambda: cu.rmsnorm(x, w, 1e-5))
+    gbs = 2 * rows * H * 2 / ms / 1e6
+    return [{"kernel": "rmsnorm_fwd", "rows": rows, "H": H, "ms": ms, "GB/s": gbs,
+             "frac_of_" + pk["kind"]: gbs / pk["hbm_gbs"]}]
+
+
+def bench_ce() -> List[dict]:
+    from cppmega_b200.ops.cuda import extra
+    pk = peaks()
+    T, H, V = 16384, 4096, 131072
+    h = torch.randn(T, H, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(V, H, device="cuda") * 0.02).bfloat16().requires_grad_()
+    lab = torch.randint(0, V, (T,), device="cuda")
+    rw = torch.full((T,), 1.0 / T, device="cuda")
+    ms = time_ms(lambda: extra.linear_cross_entropy_weighted(h, w, lab, rw, -100), iters=3, warmup=1)
+    flops = 2.0 * T * H * V * 3
+    return [{"kernel": "linear_ce fwd+bwd (3 GEMMs + softmax)", "T": T, "V": V, "ms": ms, "tflops": flops / ms / 1e9,
+             "frac_of_" + pk["kind"]: flops / ms / 1e9 / pk["bf16_tflops"]}]
+
+
+CASES = {"gemm": bench_gemm, "grouped": bench_grouped, "rmsnorm": bench_rmsnorm, "ce": bench_ce}
+
+
+def register(name: str, fn: Callable[[], List[dict]]) -> None:
+    CASES[name] = fn
+
+
+def main(argv: List[str]) -> int:
+    out_path = None
+    names = []
+    it = iter(argv)
+    for a in it:
+        if a == "--out":
+            out_path = next(it)
+        else:
+            names.append(a)
+    try:
+        from . import kernel_bench_extra  # noqa: F401  (registers more cases)
+    except ImportError:
+        pass
+    names = names or list(CASES)
+    results = []
+    for n in names:
+        for rec in CASES[n]():
+            print(json.dumps(rec))
+            results.append(rec)
+    if out_path:
+        with open(out_path, "w") as f:
+            json.dump({"peaks": peaks(), "results": results}, f, indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1:]))

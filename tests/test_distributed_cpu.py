@@ -1,0 +1,46 @@
+"""Multi-process plumbing on CPU (gloo, world_size 2): every parallel layout must reproduce the
+single-process loss curve of the tiny NAM56R-pattern model for the same global batch."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(mode, world, steps=3, timeout=600):
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    if world == 1:
+        cmd = [sys.executable, os.path.join(HERE, "dist_worker.py"), mode, str(steps)]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+               os.path.join(HERE, "dist_worker.py"), mode, str(steps)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])["losses"]
+
+
+@pytest.fixture(scope="module")
+def baseline():
+    return _run("dp", 1)
+
+
+@pytest.mark.parametrize("mode", ["dp", "ep", "ep_nodistopt", "tp", "tp_sp", "pp"])
+def test_layout_matches_single_process(baseline, mode):
+    got = _run(mode, 2)
+    for step, (b, g) in enumerate(zip(baseline, got)):
+        assert abs(b[0] - g[0]) < 2e-3 * max(1.0, abs(b[0])), (mode, step, baseline, got)
+        assert abs(b[1] - g[1]) < 2e-3 * max(1.0, abs(b[1])), (mode, step, baseline, got)
+        if mode != "pp":
+            assert abs(b[2] - g[2]) < 2e-2 * max(1.0, abs(b[2])), (mode, step, baseline, got)
