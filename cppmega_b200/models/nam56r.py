@@ -244,7 +244,7 @@ class NAM56RModel(nn.Module):
                 mask_list.append(msk_d)
         w = self.output_weight()
         if pc.sequence_parallel:
-            hiddens = [gather_seq(h, pc) for h in hiddens]
+            hiddens = [gather_seq(h, pc, reduce_grad=False) for h in hiddens]   # CE all-reduces dh itself
         # one weighted cross-entropy over [main | depth 1 | ... | depth D]: the row weights carry the
         # loss mask, the per-head token count and the MTP depth scaling
         D = len(hiddens) - 1

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(CE_THREADS) ce_fwd_bwd_kernel(__nv_bfloat16* _
     }
     // block reduce (max, sum)
     float wm = warp_max(mx);
-    sm *= __expf(mx - wm);
+    sm = (mx == -INFINITY) ? 0.f : sm * __expf(mx - wm);     // lanes / warps that saw no element
     sm = warp_sum(sm);
     if (lane == 0) { s_max[warp] = wm; s_sum[warp] = sm; }
     __syncthreads();
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(CE_THREADS) ce_fwd_bwd_kernel(__nv_bfloat16* _
     for (int i = 1; i < CE_THREADS / 32; ++i) gm = fmaxf(gm, s_max[i]);
     float gs = 0.f;
 #pragma unroll
-    for (int i = 0; i < CE_THREADS / 32; ++i) gs += s_sum[i] * __expf(s_max[i] - gm);
+    for (int i = 0; i < CE_THREADS / 32; ++i) gs += (s_max[i] == -INFINITY) ? 0.f : s_sum[i] * __expf(s_max[i] - gm);
     const float lse = gm + __logf(gs);
     const float tgt = __bfloat162float(lr[label]);
     __syncthreads();          // everyone has read the target logit and the shared partials

@@ -1,0 +1,358 @@
+// M2RNN matrix-state recurrence, forward and backward.
+//
+//   a_t = h_{t-1} W + k_t (x) v_t ;  h_t = f_t h_{t-1} + (1 - f_t) tanh(a_t) ;  y_t = q_t . h_t
+//
+// One CTA per (batch, head).  The state h [KD x 16] lives in registers for the whole sequence:
+// thread (k, quad) owns h[k, 4*quad .. 4*quad+3]; the four threads of a row are adjacent lanes and
+// exchange their quads with shuffles for the 16x16 state transition.  Inputs are staged through
+// shared memory in blocks of 32 time steps (next block prefetched into registers while the
+// current one runs); y partial sums are reduced over k once per block.  The forward pass can
+// write the state history (fp32) that the backward pass replays in reverse; the backward pass
+// recomputes tanh(a_t) from h_{t-1}, keeps dh in registers, accumulates dW per thread over time
+// and reduces it once at the end.  q and k gradients are produced per head (the caller sums the
+// head axis when q/k are shared by all heads).
+// The reference runs this recurrence as Triton kernels with 64-token checkpoints
+// (cppmega/megatron/m2rnn_triton.py:243-415 forward, :662-758 backward).
+#include "common.cuh"
+
+namespace cm {
+
+constexpr int VD = 16;       // value head dim (fixed)
+constexpr int TB = 32;       // time steps per staging block (forward)
+constexpr int TBB = 16;      // backward (more staged arrays)
+
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int KD>
+__global__ void __launch_bounds__(KD * 4) m2rnn_fwd_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+    const __nv_bfloat16* __restrict__ W, const float* __restrict__ f, __nv_bfloat16* __restrict__ y,
+    float* __restrict__ hist, float* __restrict__ h_last, int S, int H, int Hq, int Hk) {
+  constexpr int NT = KD * 4;
+  constexpr int NW = NT / 32;
+  constexpr int QPT = TB * KD / NT;     // staged q (and k) elements per thread = 8
+  constexpr int VPT = TB * VD / NT;     // staged v elements per thread
+  __shared__ float Ws[VD][VD];
+  __shared__ float qs[TB][KD], ks[TB][KD], vs[TB][VD], fs[TB];
+  __shared__ float ypart[TB][NW][VD];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = tid >> 2, quad = tid & 3;
+  const int b = blockIdx.x / H, h = blockIdx.x % H;
+  const int hq = Hq == 1 ? 0 : h, hk = Hk == 1 ? 0 : h;
+  for (int i = tid; i < VD * VD; i += NT) Ws[i / VD][i % VD] = __bfloat162float(W[(size_t)h * VD * VD + i]);
+  float hreg[4] = {0.f, 0.f, 0.f, 0.f};
+  float pq[QPT], pk[QPT], pv[VPT], pf = 0.f;
+
+  auto prefetch = [&](int t0) {
+#pragma unroll
+    for (int i = 0; i < QPT; ++i) {
+      const int e = tid + i * NT, t = e / KD, c = e % KD;
+      const bool ok = t0 + t < S;
+      pq[i] = ok ? __bfloat162float(q[((size_t)(b * S + t0 + t) * Hq + hq) * KD + c]) : 0.f;
+      pk[i] = ok ? __bfloat162float(k[((size_t)(b * S + t0 + t) * Hk + hk) * KD + c]) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int e = tid + i * NT;
+      const int t = e / VD, c = e % VD;
+      pv[i] = (t0 + t < S) ? __bfloat162float(v[((size_t)(b * S + t0 + t) * H + h) * VD + c]) : 0.f;
+    }
+    if (tid < TB) pf = (t0 + tid < S) ? f[(size_t)(b * S + t0 + tid) * H + h] : 1.f;
+  };
+  auto commit = [&]() {
+#pragma unroll
+    for (int i = 0; i < QPT; ++i) {
+      const int e = tid + i * NT;
+      qs[e / KD][e % KD] = pq[i];
+      ks[e / KD][e % KD] = pk[i];
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int e = tid + i * NT;
+      vs[e / VD][e % VD] = pv[i];
+    }
+    if (tid < TB) fs[tid] = pf;
+  };
+
+  prefetch(0);
+  commit();
+  __syncthreads();
+  for (int t0 = 0; t0 < S; t0 += TB) {
+    if (t0 + TB < S) prefetch(t0 + TB);
+    const int nt = min(TB, S - t0);
+    for (int t = 0; t < nt; ++t) {
+      float hrow[VD];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) hrow[j * 4 + c] = __shfl_sync(0xffffffffu, hreg[c], (lane & ~3) + j);
+      const float kt = ks[t][row], qt = qs[t][row], ft = fs[t];
+      float a[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) a[c] = kt * vs[t][quad * 4 + c];
+#pragma unroll
+      for (int u = 0; u < VD; ++u) {
+        const float4 w = *reinterpret_cast<const float4*>(&Ws[u][quad * 4]);
+        a[0] += hrow[u] * w.x; a[1] += hrow[u] * w.y; a[2] += hrow[u] * w.z; a[3] += hrow[u] * w.w;
+      }
+      float yp[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        hreg[c] = ft * hreg[c] + (1.f - ft) * fast_tanh(a[c]);
+        yp[c] = qt * hreg[c];
+      }
+      if (hist) {
+        float4 o = make_float4(hreg[0], hreg[1], hreg[2], hreg[3]);
+        *reinterpret_cast<float4*>(hist + (((size_t)(b * H + h) * S + t0 + t) * KD + row) * VD + quad * 4) = o;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        yp[c] += __shfl_xor_sync(0xffffffffu, yp[c], 4);
+        yp[c] += __shfl_xor_sync(0xffffffffu, yp[c], 8);
+        yp[c] += __shfl_xor_sync(0xffffffffu, yp[c], 16);
+      }
+      if (lane < 4) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ypart[t][warp][quad * 4 + c] = yp[c];
+      }
+    }
+    __syncthreads();
+    for (int e = tid; e < nt * VD; e += NT) {
+      const int t = e / VD, c = e % VD;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) s += ypart[t][w][c];
+      y[((size_t)(b * S + t0 + t) * H + h) * VD + c] = __float2bfloat16(s);
+    }
+    if (t0 + TB < S) commit();
+    __syncthreads();
+  }
+  if (h_last) {
+    float4 o = make_float4(hreg[0], hreg[1], hreg[2], hreg[3]);
+    *reinterpret_cast<float4*>(h_last + ((size_t)(b * H + h) * KD + row) * VD + quad * 4) = o;
+  }
+}
+
+template <int KD>
+__global__ void __launch_bounds__(KD * 4) m2rnn_bwd_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+    const __nv_bfloat16* __restrict__ W, const float* __restrict__ f, const float* __restrict__ hist,
+    const __nv_bfloat16* __restrict__ dy, float* __restrict__ dq_h, float* __restrict__ dk_h,
+    float* __restrict__ dv, float* __restrict__ df, float* __restrict__ dW, int S, int H, int Hq, int Hk) {
+  constexpr int NT = KD * 4;
+  constexpr int NW = NT / 32;
+  constexpr int QPT = TBB * KD / NT;
+  __shared__ float Ws[VD][VD];          // W[u][v]
+  __shared__ float Wt[VD][VD];          // W^T: Wt[v][u]
+  __shared__ float qs[TBB][KD], ks[TBB][KD], vs[TBB][VD], gs[TBB][VD], fs[TBB];
+  __shared__ float dqs[TBB][KD], dks[TBB][KD], dvpart[TBB][NW][VD], dfpart[TBB][NW];
+  __shared__ float dWs[VD][VD];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = tid >> 2, quad = tid & 3;
+  const int b = blockIdx.x / H, h = blockIdx.x % H;
+  const int hq = Hq == 1 ? 0 : h, hk = Hk == 1 ? 0 : h;
+  for (int i = tid; i < VD * VD; i += NT) {
+    const float w = __bfloat162float(W[(size_t)h * VD * VD + i]);
+    Ws[i / VD][i % VD] = w;
+    Wt[i % VD][i / VD] = w;
+    dWs[i / VD][i % VD] = 0.f;
+  }
+  float dh[4] = {0.f, 0.f, 0.f, 0.f};
+  float P[4][VD];
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int j = 0; j < VD; ++j) P[c][j] = 0.f;
+  const float* hbase = hist + (size_t)(b * H + h) * S * KD * VD;
+  __syncthreads();
+
+  const int nblocks = (S + TBB - 1) / TBB;
+  for (int blk = nblocks - 1; blk >= 0; --blk) {
+    const int t0 = blk * TBB;
+    const int nt = min(TBB, S - t0);
+    // stage this block's inputs
+#pragma unroll
+    for (int i = 0; i < QPT; ++i) {
+      const int e = tid + i * NT, t = e / KD, c = e % KD;
+      const bool ok = t < nt;
+      qs[t][c] = ok ? __bfloat162float(q[((size_t)(b * S + t0 + t) * Hq + hq) * KD + c]) : 0.f;
+      ks[t][c] = ok ? __bfloat162float(k[((size_t)(b * S + t0 + t) * Hk + hk) * KD + c]) : 0.f;
+    }
+    for (int e = tid; e < TBB * VD; e += NT) {
+      const int t = e / VD, c = e % VD;
+      const bool ok = t < nt;
+      vs[t][c] = ok ? __bfloat162float(v[((size_t)(b * S + t0 + t) * H + h) * VD + c]) : 0.f;
+      gs[t][c] = ok ? __bfloat162float(dy[((size_t)(b * S + t0 + t) * H + h) * VD + c]) : 0.f;
+    }
+    if (tid < TBB) fs[tid] = (tid < nt) ? f[(size_t)(b * S + t0 + tid) * H + h] : 1.f;
+    __syncthreads();
+    for (int t = nt - 1; t >= 0; --t) {
+      const int tg = t0 + t;
+      // h_{t-1} full row and h_t own quad from the history
+      float hprev[VD];
+      if (tg > 0) {
+        const float4* hp = reinterpret_cast<const float4*>(hbase + ((size_t)(tg - 1) * KD + row) * VD);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 x = hp[j];
+          hprev[j * 4 + 0] = x.x; hprev[j * 4 + 1] = x.y; hprev[j * 4 + 2] = x.z; hprev[j * 4 + 3] = x.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < VD; ++j) hprev[j] = 0.f;
+      }
+      const float4 hc = *reinterpret_cast<const float4*>(hbase + ((size_t)tg * KD + row) * VD + quad * 4);
+      const float hcur[4] = {hc.x, hc.y, hc.z, hc.w};
+      const float kt = ks[t][row], qt = qs[t][row], ft = fs[t];
+      // dh_t += q_t (x) dy_t ; dq_t = h_t . dy_t
+      float dqp = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float g = gs[t][quad * 4 + c];
+        dh[c] += qt * g;
+        dqp += hcur[c] * g;
+      }
+      dqp += __shfl_xor_sync(0xffffffffu, dqp, 1);
+      dqp += __shfl_xor_sync(0xffffffffu, dqp, 2);
+      if (quad == 0) dqs[t][row] = dqp;
+      // recompute tanh(a_t) for own columns
+      float a[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) a[c] = kt * vs[t][quad * 4 + c];
+#pragma unroll
+      for (int u = 0; u < VD; ++u) {
+        const float4 w = *reinterpret_cast<const float4*>(&Ws[u][quad * 4]);
+        a[0] += hprev[u] * w.x; a[1] += hprev[u] * w.y; a[2] += hprev[u] * w.z; a[3] += hprev[u] * w.w;
+      }
+      float hown[4];                     // h_{t-1}[k, own quad], selected without dynamic indexing
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        hown[c] = quad == 0 ? hprev[c] : quad == 1 ? hprev[4 + c] : quad == 2 ? hprev[8 + c] : hprev[12 + c];
+      float da[4], dfp = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float hn = fast_tanh(a[c]);
+        dfp += dh[c] * (hown[c] - hn);
+        da[c] = dh[c] * (1.f - ft) * (1.f - hn * hn);
+      }
+      dfp = warp_sum(dfp);
+      if (lane == 0) dfpart[t][warp] = dfp;
+      // full da row of this k
+      float darow[VD];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) darow[j * 4 + c] = __shfl_sync(0xffffffffu, da[c], (lane & ~3) + j);
+      // dk_t[k] = da[k,:] . v_t
+      if (quad == 0) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < VD; ++j) s += darow[j] * vs[t][j];
+        dks[t][row] = s;
+      }
+      // dv_t[v] = sum_k da[k,v] k_t[k]  (own columns; reduce over the 8 rows of this warp)
+      float dvp[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        dvp[c] = da[c] * kt;
+        dvp[c] += __shfl_xor_sync(0xffffffffu, dvp[c], 4);
+        dvp[c] += __shfl_xor_sync(0xffffffffu, dvp[c], 8);
+        dvp[c] += __shfl_xor_sync(0xffffffffu, dvp[c], 16);
+      }
+      if (lane < 4) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dvpart[t][warp][quad * 4 + c] = dvp[c];
+      }
+      // dW[u,v] += h_{t-1}[k,u] da[k,v]  for own u = 4*quad + c
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float hu = hown[c];
+#pragma unroll
+        for (int j = 0; j < VD; ++j) P[c][j] += hu * darow[j];
+      }
+      // dh_{t-1}[k,u] = f dh_t[k,u] + sum_v da[k,v] W[u,v]   for own u
+#pragma unroll
+      for (int c = 0; c < 4; ++c) dh[c] *= ft;
+#pragma unroll
+      for (int j = 0; j < VD; ++j) {
+        const float4 w = *reinterpret_cast<const float4*>(&Wt[j][quad * 4]);   // W[u=4q..4q+3][v=j]
+        dh[0] += darow[j] * w.x; dh[1] += darow[j] * w.y; dh[2] += darow[j] * w.z; dh[3] += darow[j] * w.w;
+      }
+    }
+    __syncthreads();
+    // write this block's per-step gradients
+    for (int e = tid; e < nt * KD; e += NT) {
+      const int t = e / KD, c = e % KD;
+      dq_h[((size_t)(b * S + t0 + t) * H + h) * KD + c] = dqs[t][c];
+      dk_h[((size_t)(b * S + t0 + t) * H + h) * KD + c] = dks[t][c];
+    }
+    for (int e = tid; e < nt * VD; e += NT) {
+      const int t = e / VD, c = e % VD;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) s += dvpart[t][w][c];
+      dv[((size_t)(b * S + t0 + t) * H + h) * VD + c] = s;
+    }
+    if (tid < nt) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) s += dfpart[tid][w];
+      df[(size_t)(b * S + t0 + tid) * H + h] = s;
+    }
+    __syncthreads();
+  }
+  // reduce dW over the rows k of this CTA, then over batch with atomics
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int j = 0; j < VD; ++j) {
+      float s = P[c][j];
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s += __shfl_xor_sync(0xffffffffu, s, 8);
+      s += __shfl_xor_sync(0xffffffffu, s, 16);
+      if (lane < 4) atomicAdd(&dWs[quad * 4 + c][j], s);
+    }
+  __syncthreads();
+  for (int i = tid; i < VD * VD; i += NT) atomicAdd(dW + (size_t)h * VD * VD + i, dWs[i / VD][i % VD]);
+}
+
+}  // namespace cm
+
+using namespace cm;
+
+// q [B,S,Hq,KD], k [B,S,Hk,KD], v [B,S,H,16], W [H,16,16] (bf16); f [B,S,H] fp32.
+// y [B,S,H,16] bf16; hist (nullable) [B,H,S,KD,16] fp32; h_last (nullable) [B,H,KD,16] fp32.
+extern "C" int cm_m2rnn_fwd(const void* q, const void* k, const void* v, const void* W, const float* f, void* y,
+                            float* hist, float* h_last, int B, int S, int H, int Hq, int Hk, int KD, int VDim,
+                            cudaStream_t s) {
+  if (B <= 0 || S <= 0) return 0;
+  if (VDim != VD) return -10;
+  auto qp = (const __nv_bfloat16*)q; auto kp = (const __nv_bfloat16*)k; auto vp = (const __nv_bfloat16*)v;
+  auto wp = (const __nv_bfloat16*)W; auto yp = (__nv_bfloat16*)y;
+  const int grid = B * H;
+  if (KD == 64) m2rnn_fwd_kernel<64><<<grid, 256, 0, s>>>(qp, kp, vp, wp, f, yp, hist, h_last, S, H, Hq, Hk);
+  else if (KD == 32) m2rnn_fwd_kernel<32><<<grid, 128, 0, s>>>(qp, kp, vp, wp, f, yp, hist, h_last, S, H, Hq, Hk);
+  else if (KD == 16) m2rnn_fwd_kernel<16><<<grid, 64, 0, s>>>(qp, kp, vp, wp, f, yp, hist, h_last, S, H, Hq, Hk);
+  else return -10;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// dq_h, dk_h [B,S,H,KD] fp32 (per head); dv [B,S,H,16] fp32; df [B,S,H] fp32; dW [H,16,16] fp32 (accumulated, caller zeroes).
+extern "C" int cm_m2rnn_bwd(const void* q, const void* k, const void* v, const void* W, const float* f, const float* hist,
+                            const void* dy, float* dq_h, float* dk_h, float* dv, float* df, float* dW, int B, int S, int H,
+                            int Hq, int Hk, int KD, int VDim, cudaStream_t s) {
+  if (B <= 0 || S <= 0) return 0;
+  if (VDim != VD) return -10;
+  auto qp = (const __nv_bfloat16*)q; auto kp = (const __nv_bfloat16*)k; auto vp = (const __nv_bfloat16*)v;
+  auto wp = (const __nv_bfloat16*)W; auto gp = (const __nv_bfloat16*)dy;
+  const int grid = B * H;
+  if (KD == 64) m2rnn_bwd_kernel<64><<<grid, 256, 0, s>>>(qp, kp, vp, wp, f, hist, gp, dq_h, dk_h, dv, df, dW, S, H, Hq, Hk);
+  else if (KD == 32) m2rnn_bwd_kernel<32><<<grid, 128, 0, s>>>(qp, kp, vp, wp, f, hist, gp, dq_h, dk_h, dv, df, dW, S, H, Hq, Hk);
+  else if (KD == 16) m2rnn_bwd_kernel<16><<<grid, 64, 0, s>>>(qp, kp, vp, wp, f, hist, gp, dq_h, dk_h, dv, df, dW, S, H, Hq, Hk);
+  else return -10;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -155,6 +155,10 @@ def mimo_scan(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Psi, Zeta, Phi, angles, D,
     if fn is not None:
         return fn(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Psi, Zeta, Phi, angles, D, Z,
                   rotary_dim_divisor, chunk_size)
+    if V.is_cuda and None not in (Zeta, Phi, D, Z):
+        from .mimo_scan_lean import mimo_scan_lean     # PyTorch on GPU, one head group at a time
+        return mimo_scan_lean(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Psi, Zeta, Phi, angles, D, Z,
+                              rotary_dim_divisor, 64)
     return mimo_scan_ref.mimo_scan_chunked(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Psi, Zeta, Phi,
                                            angles, D, Z, rotary_dim_divisor, chunk_size)
 

@@ -126,8 +126,10 @@ def mimo_scan_chunked(
     Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Psi, Zeta, Phi, angles, D, Z,
     rotary_dim_divisor: int = 4, chunk_size: int = 16,
     initial_state: Optional[torch.Tensor] = None, return_state: bool = False,
+    mm_dtype: Optional[torch.dtype] = None,
 ):
-    """Block-parallel form of the same operator; differentiable."""
+    """Block-parallel form of the same operator; differentiable.  ``mm_dtype`` (e.g. bf16)
+    rounds the operands of the large contractions, as a tensor-core kernel would."""
     B, S, R, G, N = Q.shape
     H, P = V.shape[2], V.shape[3]
     L = min(chunk_size, S)
@@ -151,13 +153,18 @@ def mimo_scan_chunked(
     cs = torch.cumsum(adt.view(B, H, C, L), dim=-1)                       # inclusive
     tot = cs[..., -1]                                                     # [B,H,C]
     ks = kc * tsc[..., None, None]
+    if mm_dtype is not None:
+        def mm(eq, a, b):
+            return torch.einsum(eq, a.to(mm_dtype), b.to(mm_dtype)).float()
+    else:
+        mm = torch.einsum
     # intra-chunk, strictly causal in tokens
-    scores = torch.einsum("bhcirn,bhcjsn->bhcirjs", qc, ks)
+    scores = mm("bhcirn,bhcjsn->bhcirjs", qc, ks)
     seg = cs[..., :, None] - cs[..., None, :]                             # [B,H,C,L,L]
     mask = torch.ones(L, L, dtype=torch.bool, device=Q.device).tril(-1)
     decay = torch.where(mask, torch.exp(torch.where(mask, seg, torch.zeros_like(seg))), torch.zeros_like(seg))
     scores = scores * decay[..., :, None, :, None]
-    o = torch.einsum("bhcirjs,bhcjsp->bhcirp", scores, pc)
+    o = mm("bhcirjs,bhcjsp->bhcirp", scores, pc)
     # same-token term
     qk = torch.einsum("bhcirn,bhcisn->bhcirs", qc, kc)
     o = o + gam[..., None, None] * torch.einsum("bhcirs,bhcisp->bhcirp", qk, pc)
@@ -165,7 +172,7 @@ def mimo_scan_chunked(
         o = o + D.float()[None, :, None, None, None, None] * pc
     # chunk-local end states and recurrence over chunks
     w = torch.exp(tot[..., None] - cs)                                    # [B,H,C,L]
-    local = torch.einsum("bhcjrn,bhcjrp->bhcnp", ks * w[..., None, None], pc)
+    local = mm("bhcjrn,bhcjrp->bhcnp", ks * w[..., None, None], pc)
     state = (initial_state.float() if initial_state is not None
              else torch.zeros(B, H, N, P, dtype=torch.float32, device=Q.device))
     starts = []
@@ -174,7 +181,7 @@ def mimo_scan_chunked(
         starts.append(state)
         state = state * dec_c[:, :, c, None, None] + local[:, :, c]
     start = torch.stack(starts, dim=2)                                    # [B,H,C,N,P]
-    o = o + torch.exp(cs)[..., None, None] * torch.einsum("bhcirn,bhcnp->bhcirp", qc, start)
+    o = o + torch.exp(cs)[..., None, None] * mm("bhcirn,bhcnp->bhcirp", qc, start)
     o = o.permute(0, 2, 3, 1, 4, 5).reshape(B, Sp, H, R, P)[:, :S]
     y = _gate(o, Z, Zeta, Phi, V.dtype)
     return (y, state) if return_state else y

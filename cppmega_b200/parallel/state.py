@@ -77,6 +77,7 @@ class ParallelContext:
     ep_group: Optional[dist.ProcessGroup] = None
     edp_group: Optional[dist.ProcessGroup] = None
     world_group: Optional[dist.ProcessGroup] = None
+    embd_group: Optional[dist.ProcessGroup] = None     # first+last pipeline stage (embedding copies)
     tp_ranks: List[int] = field(default_factory=lambda: [0])
     pp_ranks: List[int] = field(default_factory=lambda: [0])
     dp_ranks: List[int] = field(default_factory=lambda: [0])
@@ -199,12 +200,19 @@ def initialize(cfg: ParallelConfig = ParallelConfig(), backend: Optional[str] = 
             if rank in ranks:
                 mine[kind] = ranks
                 groups[kind] = g
+    embd_group = None
+    if cfg.pp > 1:
+        for ranks in lists["pp"]:
+            pair = [ranks[0], ranks[-1]]
+            g = dist.new_group(ranks=pair, backend=backend)
+            if rank in pair:
+                embd_group = g
     tp_rank, ep_rank, edp_rank, dp_rank, pp_rank = rank_coordinates(rank, world, cfg)
     _CTX = ParallelContext(
         config=cfg, world_size=world, rank=rank, local_rank=local_rank,
         tp_rank=tp_rank, pp_rank=pp_rank, dp_rank=dp_rank, ep_rank=ep_rank, edp_rank=edp_rank,
         tp_group=groups["tp"], pp_group=groups["pp"], dp_group=groups["dp"],
-        ep_group=groups["ep"], edp_group=groups["edp"], world_group=dist.group.WORLD,
+        ep_group=groups["ep"], edp_group=groups["edp"], world_group=dist.group.WORLD, embd_group=embd_group,
         tp_ranks=mine["tp"], pp_ranks=mine["pp"], dp_ranks=mine["dp"],
         ep_ranks=mine["ep"], edp_ranks=mine["edp"],
     )

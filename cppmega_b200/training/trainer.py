@@ -63,7 +63,10 @@ class Trainer:
         self.device = device
         self.model = model or build_model(model_cfg, self.pc, dtype=train_cfg.torch_dtype(), seed=train_cfg.seed,
                                           recompute=train_cfg.recompute, device=device)
-        self.optimizer = DistributedOptimizer(self.model, train_cfg.optimizer, self.pc)
+        # with pipeline stages the embedding copies are summed before the data-parallel reduction,
+        # so the reduction cannot start from inside backward
+        self.optimizer = DistributedOptimizer(self.model, train_cfg.optimizer, self.pc,
+                                              overlap=False if self.pc.pp > 1 else None)
         if self.pc.world_size > 1 and device.type == "cuda" and self.pc.config.fused_collectives:
             self._attach_fused_paths()
         self.lr_schedule = train_cfg.lr_schedule or LRSchedule(lr=train_cfg.optimizer.lr, style="constant")
