@@ -175,8 +175,9 @@ def sparse_mla(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, scale: 
     B, S, Hq, Dq = q.shape
     valid = indices >= 0
     idx = indices.clamp(min=0).long()
-    g = torch.gather(kv.float().unsqueeze(1).expand(B, S, kv.shape[1], Dq), 2,
-                     idx.unsqueeze(-1).expand(B, S, idx.shape[-1], Dq))          # [B,S,T,D]
+    T = idx.shape[-1]
+    # gather rows of the (un-expanded) KV so that the backward scatter-adds into [B,Skv,D]
+    g = torch.gather(kv.float(), 1, idx.reshape(B, S * T, 1).expand(B, S * T, Dq)).view(B, S, T, Dq)
     s = torch.einsum("bshd,bstd->bsht", q.float(), g) * scale
     s = s.masked_fill(~valid.unsqueeze(2), float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
