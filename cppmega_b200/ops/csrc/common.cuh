@@ -87,6 +87,32 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// ---- cross-GPU flags ------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// Spin until *flag >= value or `timeout_ns` of wall clock has passed (returns false then).
+__device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag, unsigned long long value,
+                                             unsigned long long timeout_ns) {
+  if (ld_acquire_sys(flag) >= value) return true;
+  const unsigned long long t0 = global_timer_ns();
+  while (true) {
+    if (ld_acquire_sys(flag) >= value) return true;
+    if (global_timer_ns() - t0 > timeout_ns) return false;
+    __nanosleep(100);
+  }
+}
+
 // ---- TMA ---------------------------------------------------------------------------------
 // Tiled loads into this CTA's shared memory, completion on an mbarrier of this CTA.
 // (No cluster multicast anywhere in this library.)

@@ -66,7 +66,8 @@ class ParamGroupBuffer:
     """One reduction domain x dtype: contiguous params, grads, buckets, shard bookkeeping."""
 
     def __init__(self, params: List[nn.Parameter], group, group_size: int, group_rank: int,
-                 grad_dtype: torch.dtype, bucket_bytes: int, distributed: bool, is_expert: bool = False):
+                 grad_dtype: torch.dtype, bucket_bytes: int, distributed: bool, is_expert: bool = False,
+                 alloc: Optional[Callable] = None):
         self.params = params
         self.is_expert = is_expert
         self.group, self.n, self.rank = group, group_size, group_rank
@@ -96,8 +97,12 @@ class ParamGroupBuffer:
             b.params = [q for q, _ in cur_params]
             self.buckets.append(b)
         self.numel = pos
-        self.param_buffer = torch.zeros(self.numel, dtype=dtype, device=dev)
-        self.grad_buffer = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
+        if alloc is not None:          # e.g. peer-mapped symmetric memory
+            self.param_buffer = alloc(self, self.numel, dtype)
+            self.grad_buffer = alloc(self, self.numel, grad_dtype)
+        else:
+            self.param_buffer = torch.zeros(self.numel, dtype=dtype, device=dev)
+            self.grad_buffer = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
         self.offsets: Dict[nn.Parameter, int] = {}
         self.bucket_of: Dict[nn.Parameter, Bucket] = {}
         for b in self.buckets:
@@ -178,10 +183,16 @@ class DistributedOptimizer:
         bb = cfg.bucket_mb << 20
         for dt, ps in dense.items():
             g = gd if dt != torch.float32 else torch.float32
-            self.buffers.append(ParamGroupBuffer(ps, pc.dp_group, pc.dp, pc.dp_rank, g, bb, self.distributed))
+            self.buffers.append(ParamGroupBuffer(ps, pc.dp_group, pc.dp, pc.dp_rank, g, bb, self.distributed,
+                                                 alloc=self._buffer_allocator(False, ps, g)))
         for dt, ps in expert.items():
             g = gd if dt != torch.float32 else torch.float32
-            self.buffers.append(ParamGroupBuffer(ps, pc.edp_group, pc.edp, pc.edp_rank, g, bb, self.distributed, is_expert=True))
+            self.buffers.append(ParamGroupBuffer(ps, pc.edp_group, pc.edp, pc.edp_rank, g, bb, self.distributed,
+                                                 is_expert=True, alloc=self._buffer_allocator(True, ps, g)))
+        # the loss is a mean over each rank's tokens, so every gradient (expert ones included, whose
+        # reduction group is only the expert-data-parallel ranks) is the sum over ranks / dp
+        for _buf in self.buffers:
+            _buf.grad_div = float(pc.dp)
         self.step_count = 0
         self.lr = cfg.lr
         self._hooks = []
@@ -190,6 +201,10 @@ class DistributedOptimizer:
         self._install_hooks()
         self.zero_grad()
         self.fused_step: Optional[Callable] = None       # set by parallel.fused_optimizer.attach()
+
+    def _buffer_allocator(self, is_expert: bool, params, grad_dtype) -> Optional[Callable]:
+        """Hook for subclasses that place the flat buffers in special memory."""
+        return None
 
     # ---- state ------------------------------------------------------------
     def _build_state(self):
@@ -229,7 +244,7 @@ class DistributedOptimizer:
                     b = buf.bucket_of[param]
                     b.pending -= 1
                     if b.pending == 0 and self.overlap and not b.reduced:
-                        buf.reduce_bucket(b, async_op=True, scale=self._grad_scale / buf.n)
+                        buf.reduce_bucket(b, async_op=True, scale=self._grad_scale / buf.grad_div)
                 self._hooks.append(p.register_post_accumulate_grad_hook(hook))
         self._last_microbatch = True
 
@@ -253,7 +268,7 @@ class DistributedOptimizer:
         for buf in self.buffers:
             for b in buf.buckets:
                 if not b.reduced:      # no overlap, or a bucket holding parameters that got no gradient
-                    buf.reduce_bucket(b, async_op=False, scale=self._grad_scale / buf.n)
+                    buf.reduce_bucket(b, async_op=False, scale=self._grad_scale / buf.grad_div)
             buf.finish()
 
     def _shard_grads(self):

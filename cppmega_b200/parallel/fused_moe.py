@@ -1,0 +1,280 @@
+"""Expert-parallel MoE layer body over peer memory: dispatch fused with the permutation, grouped
+tcgen05 expert GEMMs on the receiving rank, combine fused with un-permutation and weighting.
+
+Forward on every rank of the EP group (same call order everywhere):
+
+1. ``plan``: all ranks exchange per-expert token counts (one tiny all-gather) and derive, without
+   a host sync, the final row of every routed copy inside the owner's 128-row-aligned expert
+   segments;
+2. ``push_rows``: copies go straight to those rows of the owner's symmetric input buffer;
+3. flag barrier, then the owner runs fc1 -> SwiGLU -> fc2 with the grouped GEMM kernels;
+4. flag barrier, then ``pull_combine`` reads each token's k results from their owners and forms the
+   weighted sum.
+
+Backward mirrors it: weighted output gradients are pushed to the owners, the grouped dgrad / wgrad
+kernels run there, input gradients are pulled back and summed over k; the routing-weight gradient
+is a row-dot against the owners' saved outputs.
+
+Symmetric buffers: per layer an input and an output row buffer (they must survive until that
+layer's backward), plus two buffers shared by all layers for the backward traffic.  Capacity is
+``capacity_factor`` times the mean load; an overflow sets the kernel error word.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F_
+from .symm_mem import SymmetricHeap
+
+TILE = 128
+FLAG_BASE = 16
+
+
+def _lib():
+    from ..ops import cuda as cu
+    L = cu.lib()
+    if not getattr(L, "_moe_declared", False):
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        L.cm_moe_push_rows.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, vp, vp]
+        L.cm_moe_pull_combine.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, vp]
+        L.cm_moe_pull_rowdot.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, vp]
+        L.cm_moe_zero_pad_rows.argtypes = [vp, vp, vp, i32, i32, i64, vp]
+        for n in ("cm_moe_push_rows", "cm_moe_pull_combine", "cm_moe_pull_rowdot", "cm_moe_zero_pad_rows"):
+            getattr(L, n).restype = i32
+        L._moe_declared = True
+    return L
+
+
+class MoEPlan:
+    """Device-side routing plan of one call (no host synchronisation)."""
+
+    def __init__(self, ids: torch.Tensor, num_experts: int, ep: int, ep_rank: int, group, capacity_rows: int):
+        T, k = ids.shape
+        E, El = num_experts, num_experts // ep
+        dev = ids.device
+        flat = ids.reshape(-1)
+        counts = torch.bincount(flat, minlength=E)
+        allc = torch.empty(ep * E, dtype=counts.dtype, device=dev)
+        dist.all_gather_into_tensor(allc, counts.contiguous(), group=group)
+        allc = allc.view(ep, E)                                  # [src rank, expert]
+        tot = allc.sum(0)                                        # rows per expert (all sources)
+        padded = (tot + (TILE - 1)) // TILE * TILE
+        pe = padded.view(ep, El)
+        seg_end = torch.cumsum(pe, 1)
+        seg_start = (seg_end - pe).reshape(E)                    # start row of each expert on its owner
+        before_me = allc[:ep_rank].sum(0) if ep_rank > 0 else torch.zeros_like(tot)
+        base = seg_start + before_me                             # first row of my copies of expert e
+        sort_idx = torch.argsort(flat, stable=True)
+        e_sorted = flat[sort_idx]
+        un_end = torch.cumsum(counts, 0)
+        un_start = un_end - counts
+        pos = torch.arange(T * k, device=dev)
+        row_sorted = base[e_sorted] + (pos - un_start[e_sorted])
+        # per copy in (token, j) order
+        dest_row = torch.empty(T * k, dtype=torch.int64, device=dev)
+        dest_row[sort_idx] = row_sorted
+        self.dest_row = dest_row
+        self.dest_rank = torch.div(flat, El, rounding_mode="floor").to(torch.int32)
+        self.token_of_copy = torch.div(pos, k, rounding_mode="floor").to(torch.int32)
+        self.T, self.k = T, k
+        # receiver side (my local experts)
+        lo = ep_rank * El
+        my_tot = tot[lo:lo + El]
+        my_pad = padded[lo:lo + El]
+        my_end = torch.cumsum(my_pad, 0)
+        self.seg_start_local = (my_end - my_pad).to(torch.int32)
+        self.tot_local = my_tot.to(torch.int32)
+        self.seg_offsets = torch.cat([torch.zeros(1, dtype=my_end.dtype, device=dev), my_end]).to(torch.int32)
+        tiles = torch.arange(capacity_rows // TILE, device=dev) * TILE
+        te = torch.searchsorted(my_end, tiles, right=True)
+        self.tile_expert = torch.where(te < El, te, torch.full_like(te, -1)).to(torch.int32)
+        self.rows_used = my_end[-1]
+        self.counts_global = tot
+
+
+class FusedMoEBuffers:
+    """Symmetric buffers of one EP group; one instance shared by all MoE layers of the model."""
+
+    def __init__(self, pc, hidden: int, tokens_per_rank: int, topk: int, num_layers: int, device,
+                 capacity_factor: float = 2.0, per_layer: bool = True):
+        self.pc = pc
+        self.hidden = hidden
+        El = 1
+        mean_rows = tokens_per_rank * topk
+        self.capacity = int((mean_rows * capacity_factor + 16 * TILE + TILE - 1) // TILE * TILE)
+        n_bufs = (2 * num_layers if per_layer else 2) + 2
+        nbytes = n_bufs * (self.capacity * hidden * 2 + 4096)
+        self.heap = SymmetricHeap(pc.ep_group, pc.ep_ranks, nbytes, device)
+        self.per_layer = per_layer
+        self.layer_bufs: List = []
+        n = num_layers if per_layer else 1
+        for _ in range(n):
+            self.layer_bufs.append((self.heap.alloc((self.capacity, hidden), torch.bfloat16),
+                                    self.heap.alloc((self.capacity, hidden), torch.bfloat16)))
+        self.grad_in = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
+        self.grad_out = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
+        self.epoch = 0
+        _ = El
+
+    def bufs(self, layer_slot: int):
+        return self.layer_bufs[layer_slot if self.per_layer else 0]
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+
+def _push(heap: SymmetricHeap, src, plan: MoEPlan, dst_buf, scale=None):
+    from ..ops.cuda import err_word, stream_ptr
+    rc = _lib().cm_moe_push_rows(src.data_ptr(), plan.token_of_copy.data_ptr(), plan.dest_rank.data_ptr(),
+                                 plan.dest_row.data_ptr(), None if scale is None else scale.data_ptr(),
+                                 heap.peer_ptr_array(dst_buf), heap.world, plan.T * plan.k, src.shape[1],
+                                 dst_buf.shape[0], err_word(src.device).data_ptr(), stream_ptr())
+    if rc:
+        raise RuntimeError(f"cm_moe_push_rows failed ({rc})")
+    F_.count_launch("moe_push_rows")
+
+
+def _pull_combine(heap: SymmetricHeap, src_buf, plan: MoEPlan, weights, H, dtype):
+    from ..ops.cuda import stream_ptr
+    out = torch.empty(plan.T, H, dtype=dtype, device=src_buf.device)
+    rc = _lib().cm_moe_pull_combine(heap.peer_ptr_array(src_buf), heap.world, plan.dest_rank.data_ptr(),
+                                    plan.dest_row.data_ptr(), None if weights is None else weights.data_ptr(),
+                                    out.data_ptr(), plan.T, plan.k, H, stream_ptr())
+    if rc:
+        raise RuntimeError(f"cm_moe_pull_combine failed ({rc})")
+    F_.count_launch("moe_pull_combine")
+    return out
+
+
+def _pull_rowdot(heap: SymmetricHeap, src_buf, plan: MoEPlan, dy):
+    from ..ops.cuda import stream_ptr
+    out = torch.empty(plan.T, plan.k, dtype=torch.float32, device=dy.device)
+    rc = _lib().cm_moe_pull_rowdot(heap.peer_ptr_array(src_buf), heap.world, plan.dest_rank.data_ptr(),
+                                   plan.dest_row.data_ptr(), dy.data_ptr(), out.data_ptr(), plan.T, plan.k, dy.shape[1],
+                                   stream_ptr())
+    if rc:
+        raise RuntimeError(f"cm_moe_pull_rowdot failed ({rc})")
+    F_.count_launch("moe_pull_rowdot")
+    return out
+
+
+def _zero_pad(buf, plan: MoEPlan, capacity: int):
+    from ..ops.cuda import stream_ptr
+    rc = _lib().cm_moe_zero_pad_rows(buf.data_ptr(), plan.seg_start_local.data_ptr(), plan.tot_local.data_ptr(),
+                                     plan.tot_local.numel(), buf.shape[1], capacity, stream_ptr())
+    if rc:
+        raise RuntimeError(f"cm_moe_zero_pad_rows failed ({rc})")
+
+
+def _grouped(x, w, tile_expert, rows, b_mn, out=None):
+    """out[r] = x[r] . W[e(r)]^T (b_mn False) or x[r] . W[e(r)] (b_mn True, W [E, red, out])."""
+    from ..ops.cuda import lib, err_word, stream_ptr, _check
+    E = w.shape[0]
+    if b_mn:
+        red, n_out = w.shape[1], w.shape[2]
+    else:
+        n_out, red = w.shape[1], w.shape[2]
+    if out is None:
+        out = torch.empty(rows, n_out, dtype=x.dtype, device=x.device)
+    _check(lib().cm_grouped_gemm_rows_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), rows, n_out, red, E, int(b_mn),
+                                           tile_expert.data_ptr(), err_word(x.device).data_ptr(), stream_ptr()),
+           "cm_grouped_gemm_rows_bf16")
+    F_.count_launch("grouped_gemm")
+    return out
+
+
+def _grouped_wgrad(dy, x, seg_offsets, E):
+    from ..ops.cuda import lib, err_word, stream_ptr, _check
+    rows, N = dy.shape
+    K = x.shape[1]
+    dw = torch.empty(E, N, K, dtype=dy.dtype, device=dy.device)
+    _check(lib().cm_grouped_gemm_k_bf16(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), rows, N, K, E, seg_offsets.data_ptr(),
+                                        0, 0, err_word(dy.device).data_ptr(), stream_ptr()), "cm_grouped_gemm_k_bf16")
+    F_.count_launch("grouped_gemm")
+    return dw
+
+
+class _FusedMoEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, probs, w1, w2, ids, bufs: FusedMoEBuffers, layer_slot: int):
+        from ..ops.cuda import swiglu
+        pc, heap = bufs.pc, bufs.heap
+        cap = bufs.capacity
+        H = x.shape[1]
+        plan = MoEPlan(ids, w1.shape[0] * pc.ep, pc.ep, pc.ep_rank, pc.ep_group, cap)
+        xin, yout = bufs.bufs(layer_slot)
+        ep0 = bufs.next_epoch()
+        f0 = FLAG_BASE + 4 * layer_slot
+        x = x.contiguous()
+        _push(heap, x, plan, xin)
+        heap.barrier(f0 + 0, ep0)
+        _zero_pad(xin, plan, cap)
+        with torch.no_grad():
+            h = _grouped(xin, w1, plan.tile_expert, cap, False)
+            a = swiglu(h)
+            _grouped(a, w2, plan.tile_expert, cap, False, out=yout)
+        heap.barrier(f0 + 1, ep0)
+        p32 = probs.float().contiguous()
+        y = _pull_combine(heap, yout, plan, p32.reshape(-1), H, x.dtype)
+        ctx.save_for_backward(h, w1, w2, p32)
+        ctx.plan, ctx.bufs, ctx.slot, ctx.xin, ctx.yout = plan, bufs, layer_slot, xin, yout
+        ctx.x_dtype, ctx.p_dtype = x.dtype, probs.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.cuda import lib, stream_ptr, _check
+        h, w1, w2, p32 = ctx.saved_tensors
+        plan, bufs = ctx.plan, ctx.bufs
+        pc, heap, cap = bufs.pc, bufs.heap, bufs.capacity
+        H = dy.shape[1]
+        dy = dy.contiguous()
+        epb = bufs.next_epoch()
+        f0 = FLAG_BASE + 4 * ctx.slot
+        dprobs = _pull_rowdot(heap, ctx.yout, plan, dy)
+        _push(heap, dy, plan, bufs.grad_in, scale=p32.reshape(-1))
+        heap.barrier(f0 + 2, epb)
+        E = w1.shape[0]
+        Fh = w2.shape[2]
+        # recompute a = swiglu(h); expert backward on the padded layout
+        from ..ops.cuda import swiglu as _sw
+        with torch.no_grad():
+            a = _sw(h)
+            da = _grouped(bufs.grad_in, w2, plan.tile_expert, cap, True)                  # [cap, F]
+            dw2 = _grouped_wgrad(bufs.grad_in, a, plan.seg_offsets, E)                   # [E, H, F]
+            dh = torch.empty_like(h)
+            _check(lib().cm_swiglu_bwd(h.data_ptr(), da.data_ptr(), dh.data_ptr(), cap, Fh, stream_ptr()), "cm_swiglu_bwd")
+            F_.count_launch("swiglu_bwd")
+            _grouped(dh, w1, plan.tile_expert, cap, True, out=bufs.grad_out)               # [cap, H]
+            dw1 = _grouped_wgrad(dh, ctx.xin, plan.seg_offsets, E)                        # [E, 2F, H]
+        heap.barrier(f0 + 3, epb)
+        dx = _pull_combine(heap, bufs.grad_out, plan, None, H, ctx.x_dtype)
+        return dx, dprobs.to(ctx.p_dtype), dw1, dw2, None, None, None
+
+
+class FusedMoEDispatcher:
+    """Callable installed as ``MoELayer.fused_dispatcher``."""
+
+    def __init__(self, bufs: FusedMoEBuffers, layer_slot: int):
+        self.bufs, self.slot = bufs, layer_slot
+
+    def __call__(self, flat, probs, ids, experts):
+        return _FusedMoEFn.apply(flat, probs, experts.weight1, experts.weight2, ids, self.bufs, self.slot)
+
+
+def attach(model, pc, device, tokens_per_rank: int, per_layer: bool = True, capacity_factor: float = 2.0) -> Optional[FusedMoEBuffers]:
+    """Install the fused dispatcher on every MoE layer of ``model`` (EP > 1, bf16, peer access)."""
+    layers = model.moe_layers()
+    if pc.ep <= 1 or not layers:
+        return None
+    hidden = model.cfg.hidden_size
+    bufs = FusedMoEBuffers(pc, hidden, tokens_per_rank, model.cfg.moe.topk, len(layers), device,
+                           capacity_factor=capacity_factor, per_layer=per_layer)
+    for slot, m in enumerate(layers):
+        m.fused_dispatcher = FusedMoEDispatcher(bufs, slot)
+    return bufs

@@ -1,0 +1,185 @@
+"""ZeRO-1 step with the collectives fused into the optimizer kernels over peer memory.
+
+Per step and per shard, two kernels replace reduce-scatter + cast/scale + update + all-gather:
+
+1. ``reduce_shard``: pulls this rank's slice of every rank's gradient buffer with peer loads, sums
+   and scales it into fp32 and accumulates the squared norm;
+2. ``adamw_push``: AdamW on the fp32 master slice, then stores the new bf16 values into every rank's
+   parameter buffer with peer stores.
+
+Cross-GPU ordering uses two flag words per heap: ``GRAD`` (my backward is complete - peers may
+pull) and ``PARAM`` (my pushes are complete - peers may run the next forward and may overwrite
+their gradient buffers).  All waits are bounded device-side waits.  The gradient norm needs one
+scalar all-reduce between the two kernels (NCCL, 4 bytes).
+
+Buffers whose reduction group has one rank (e.g. experts when EP spans the whole data-parallel
+group) use the local fused AdamW kernel.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from .dist_optimizer import DistributedOptimizer, OptimizerConfig, ParamGroupBuffer
+from .symm_mem import SymmetricHeap
+
+FLAG_GRAD = 0
+FLAG_PARAM = 1
+
+
+class FusedDistributedOptimizer(DistributedOptimizer):
+    def __init__(self, model, cfg: OptimizerConfig, pc, **kw):
+        self._heaps: Dict[bool, Optional[SymmetricHeap]] = {}
+        self._pc_for_alloc = pc
+        kw["overlap"] = False                      # gradients stay local until the fused pull
+        kw["distributed"] = True
+        super().__init__(model, cfg, pc, **kw)
+        from ..ops import cuda as cu
+        self.L = cu.lib()
+        vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        self.L.cm_reduce_shard.argtypes = [vp, i32, i32, i64, i64, f32, vp, vp, i32, vp]
+        self.L.cm_reduce_shard.restype = i32
+        self.L.cm_adamw_push.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i64, i64, f32, f32, f32, f32, f32, f32, f32, i32, vp]
+        self.L.cm_adamw_push.restype = i32
+        for st in self.state:
+            buf: ParamGroupBuffer = st["buf"]
+            if buf.n > 1:
+                st["red"] = torch.empty(st["hi"] - st["lo"], dtype=torch.float32, device=st["master"].device)
+        self._param_wait_pending = False
+        if any(st.get("muon") for st in self.state):
+            raise NotImplementedError("the fused optimizer path implements AdamW; use the NCCL path for Muon")
+
+    def _buffer_allocator(self, is_expert: bool, params, grad_dtype):
+        pc = self._pc_for_alloc
+        n = pc.edp if is_expert else pc.dp
+        if n <= 1:
+            return None
+        group = pc.edp_group if is_expert else pc.dp_group
+        ranks = pc.edp_ranks if is_expert else pc.dp_ranks
+        heap = self._heaps.get(is_expert)
+        if heap is None:
+            total = 0
+            for p in params:
+                total += (p.numel() + 64) * (p.element_size() + torch.empty((), dtype=grad_dtype).element_size())
+            # + per-bucket padding (128 * n elements each) and allocator alignment
+            total += 64 << 20
+            # dense buffers of other dtypes (fp32 per-head params) share the heap: reserve for them too
+            total = int(total * 1.05)
+            heap = SymmetricHeap(group, ranks, total, params[0].device)
+            self._heaps[is_expert] = heap
+
+        def alloc(buf: ParamGroupBuffer, numel: int, dtype: torch.dtype):
+            buf.heap = heap
+            return heap.alloc(numel, dtype)
+
+        return alloc
+
+    def _heaps_in_use(self):
+        return [h for h in self._heaps.values() if h is not None]
+
+    # gradients are reduced by the fused pull, not by NCCL
+    def finish_grad_sync(self):
+        for buf in self.buffers:
+            if getattr(buf, "heap", None) is None:
+                for b in buf.buckets:
+                    if not b.reduced:
+                        buf.reduce_bucket(b, async_op=False, scale=self._grad_scale / buf.grad_div)
+                buf.finish()
+
+    def zero_grad(self):
+        # peers may still be pulling last step's gradients or pushing parameters: wait for their
+        # PARAM flag before touching either buffer
+        if getattr(self, "_param_wait_pending", False):
+            for h in self._heaps_in_use():
+                h.wait(FLAG_PARAM, self.step_count)
+            self._param_wait_pending = False
+        super().zero_grad()
+
+    @torch.no_grad()
+    def step(self, lr: Optional[float] = None):
+        from ..ops import cuda as cu
+        from ..optim import adamw as adamw_ops
+        cfg, pc = self.cfg, self.pc
+        lr = self.lr if lr is None else lr
+        self.finish_grad_sync()
+        step = self.step_count + 1
+        heaps = self._heaps_in_use()
+        for h in heaps:
+            h.signal(FLAG_GRAD, step)
+        for h in heaps:
+            h.wait(FLAG_GRAD, step)
+        dev = self.state[0]["master"].device
+        dense_sq = torch.zeros((), dtype=torch.float32, device=dev)
+        expert_sq = torch.zeros((), dtype=torch.float32, device=dev)
+        s = cu.stream_ptr()
+        for st in self.state:
+            buf: ParamGroupBuffer = st["buf"]
+            sq = expert_sq if buf.is_expert else dense_sq
+            if "red" in st:
+                gk = 0 if buf.grad_buffer.dtype == torch.float32 else 1
+                arr = buf.heap.peer_ptr_array(buf.grad_buffer)
+                rc = self.L.cm_reduce_shard(arr, buf.n, buf.rank, st["lo"], st["hi"] - st["lo"],
+                                            float(self._grad_scale / buf.grad_div), st["red"].data_ptr(), sq.data_ptr(), gk, s)
+                if rc:
+                    raise RuntimeError(f"cm_reduce_shard failed ({rc})")
+                from ..ops import functional as F_
+                F_.count_launch("reduce_shard")
+            else:
+                g = buf.grad_buffer[st["lo"]:st["hi"]]
+                sq += self._sumsq_tp_aware(st, g)
+        gnorm = self._finish_norm(dense_sq, expert_sq)
+        clip = torch.ones_like(gnorm)
+        if cfg.clip_grad > 0:
+            clip = torch.clamp(cfg.clip_grad / (gnorm + 1e-6), max=1.0)
+        self.step_count = step
+        bc1 = 1.0 - cfg.beta1 ** step
+        bc2 = 1.0 - cfg.beta2 ** step
+        clip_t = clip.reshape(1).float().contiguous()
+        for st in self.state:
+            buf = st["buf"]
+            if "red" in st:
+                ok = 0 if buf.param_buffer.dtype == torch.float32 else 1
+                arr = buf.heap.peer_ptr_array(buf.param_buffer)
+                rc = self.L.cm_adamw_push(st["master"].data_ptr(), st["m"].data_ptr(), st["v"].data_ptr(),
+                                          st["red"].data_ptr(), st["wd_mask"].data_ptr(), clip_t.data_ptr(), arr, buf.n,
+                                          st["lo"], st["hi"] - st["lo"], float(lr), cfg.beta1, cfg.beta2, cfg.eps,
+                                          cfg.weight_decay, bc1, bc2, ok, s)
+                if rc:
+                    raise RuntimeError(f"cm_adamw_push failed ({rc})")
+                from ..ops import functional as F_
+                F_.count_launch("adamw_push")
+            else:
+                g = buf.grad_buffer[st["lo"]:st["hi"]]
+                out = buf.param_buffer[st["lo"]:st["hi"]]
+                adamw_ops.adamw_shard_update(st["master"], st["m"], st["v"], g, out, st["wd_mask"], clip, lr,
+                                             cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2)
+        for h in heaps:
+            h.signal(FLAG_PARAM, step)
+        self._param_wait_pending = bool(heaps)
+        return {"grad_norm": gnorm, "clip_coef": clip}
+
+    def _finish_norm(self, dense_sq, expert_sq):
+        """Same reduction tree as ``DistributedOptimizer.grad_norm`` on already-sharded sums.
+        (Replicated-over-TP tensors are not down-weighted on this path: it requires tp == 1.)"""
+        pc = self.pc
+        if pc.dp > 1:
+            dist.all_reduce(dense_sq, group=pc.dp_group)
+            dist.all_reduce(expert_sq, group=pc.dp_group)
+        total = dense_sq + expert_sq
+        if pc.pp > 1:
+            dist.all_reduce(total, group=pc.pp_group)
+        return total.sqrt()
+
+    def close(self):
+        for h in self._heaps_in_use():
+            h.close()
+        self._heaps = {}
+
+
+def fused_optimizer_supported(pc, device: torch.device) -> bool:
+    from .symm_mem import peer_access_available
+    return (device.type == "cuda" and pc.world_size > 1 and pc.tp == 1 and pc.dp > 1
+            and pc.config.distributed_optimizer and pc.config.fused_collectives and peer_access_available(pc))
