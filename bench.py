@@ -113,6 +113,7 @@ def main() -> int:
     ap.add_argument("--depth", type=int, default=0, help="debug: truncate the stack (result is then not the headline config)")
     ap.add_argument("--recompute", default="auto", choices=["auto", "none", "selective", "full"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile-dir", default=None, help="after timing, capture one step with the torch profiler here")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -236,6 +237,10 @@ def main() -> int:
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
         }
         print(json.dumps(out))
+    if args.profile_dir and rank == 0:
+        from cppmega_b200.utils.profiling import profile_steps
+        table = profile_steps(step_device, 1, args.profile_dir)
+        print(table[:200], file=sys.stderr)
     if world > 1:
         dist.barrier()
         pstate.destroy()

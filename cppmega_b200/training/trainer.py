@@ -65,8 +65,15 @@ class Trainer:
                                           recompute=train_cfg.recompute, device=device)
         # with pipeline stages the embedding copies are summed before the data-parallel reduction,
         # so the reduction cannot start from inside backward
-        self.optimizer = DistributedOptimizer(self.model, train_cfg.optimizer, self.pc,
-                                              overlap=False if self.pc.pp > 1 else None)
+        self.fused = {"optimizer": False, "moe": False}
+        opt_cls = DistributedOptimizer
+        if device.type == "cuda" and self.pc.world_size > 1 and train_cfg.optimizer.optimizer == "adamw":
+            from ..parallel.fused_optimizer import FusedDistributedOptimizer, fused_optimizer_supported
+            if fused_optimizer_supported(self.pc, device) and self.pc.pp == 1:
+                opt_cls = FusedDistributedOptimizer
+                self.fused["optimizer"] = True
+        self.optimizer = opt_cls(self.model, train_cfg.optimizer, self.pc,
+                                 overlap=False if self.pc.pp > 1 else None)
         if self.pc.world_size > 1 and device.type == "cuda" and self.pc.config.fused_collectives:
             self._attach_fused_paths()
         self.lr_schedule = train_cfg.lr_schedule or LRSchedule(lr=train_cfg.optimizer.lr, style="constant")
@@ -83,11 +90,18 @@ class Trainer:
         self.watchdog = None
 
     def _attach_fused_paths(self):
-        try:
-            from ..parallel import fused_attach
-        except ImportError:
+        """Swap the NCCL collectives for the peer-memory kernels where the topology allows it."""
+        from ..parallel.symm_mem import peer_access_available
+        pc = self.pc
+        if not peer_access_available(pc):
             return
-        fused_attach.attach(self)
+        if pc.ep > 1 and pc.tp == 1 and self.cfg.torch_dtype() == torch.bfloat16:
+            from ..parallel import fused_moe
+            bufs = fused_moe.attach(self.model, pc, self.device,
+                                    tokens_per_rank=self.cfg.micro_batch_size * self.cfg.seq_length,
+                                    per_layer=self.cfg.recompute != "full")
+            self.fused["moe"] = bufs is not None
+            self._moe_bufs = bufs
 
     # ---- one optimizer step ------------------------------------------------
     def _to_device(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:

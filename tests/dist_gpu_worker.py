@@ -1,0 +1,49 @@
+"""Worker for the multi-GPU tests: trains the tiny model for a few steps with either the plain
+NCCL collectives or the fused peer-memory kernels and prints the loss curve on rank 0."""
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from cppmega_b200.config.model import nam56r_tiny  # noqa: E402
+from cppmega_b200.ops import cuda as cu  # noqa: E402
+from cppmega_b200.ops import functional as F_  # noqa: E402
+from cppmega_b200.parallel import state as pstate  # noqa: E402
+from cppmega_b200.parallel.dist_optimizer import OptimizerConfig  # noqa: E402
+from cppmega_b200.parallel.state import ParallelConfig  # noqa: E402
+from cppmega_b200.training.trainer import TrainConfig, Trainer, synthetic_batches  # noqa: E402
+
+
+def main():
+    mode, steps = sys.argv[1], int(sys.argv[2])
+    recompute = sys.argv[3] if len(sys.argv) > 3 else "none"
+    world = int(os.environ["WORLD_SIZE"])
+    local_rank = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local_rank)
+    pc = pstate.initialize(ParallelConfig(ep=world, fused_collectives=(mode == "fused")))
+    mcfg = nam56r_tiny(seq_length=128)
+    tcfg = TrainConfig(micro_batch_size=2, seq_length=128, dtype="bf16", recompute=recompute,
+                       optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0), log_interval=0)
+    trainer = Trainer(mcfg, tcfg, pc, device=torch.device("cuda", local_rank))
+    stream = synthetic_batches(mcfg.vocab_size, 2, 128, num_microbatches=world, seed=0, pin=False, rank=0)
+    F_.reset_counters()
+    losses = []
+    for _ in range(steps):
+        mbs = next(stream)
+        res = trainer.train_step([mbs[pc.dp_rank]])
+        rec = trainer.reduce_loss_for_logging(res)
+        losses.append([rec["loss"], rec["lm_loss"], rec["grad_norm"]])
+    torch.cuda.synchronize()
+    cu.check_errors()
+    if pc.rank == 0:
+        print("RESULT " + json.dumps({"mode": mode, "losses": losses, "fused": trainer.fused,
+                                      "launches": F_.launch_counts()}), flush=True)
+    pstate.destroy()
+
+
+if __name__ == "__main__":
+    main()

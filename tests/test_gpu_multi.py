@@ -1,0 +1,42 @@
+"""Fused peer-memory collectives against the plain NCCL path on 2+ GPUs (one process per GPU)."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(mode, world, steps=3, recompute="none"):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(HERE, "dist_gpu_worker.py"), mode, str(steps), recompute]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("recompute", ["none", "full"])
+def test_fused_collectives_match_nccl(recompute):
+    world = 2
+    base = _run("nccl", world, recompute=recompute)
+    fused = _run("fused", world, recompute=recompute)
+    assert fused["fused"]["optimizer"] and fused["fused"]["moe"], fused
+    assert fused["launches"].get("moe_push_rows", 0) > 0 and fused["launches"].get("adamw_push", 0) > 0
+    for b, f in zip(base["losses"], fused["losses"]):
+        assert abs(b[0] - f[0]) < 3e-2 * max(1.0, abs(b[0])), (base, fused)
+        assert abs(b[2] - f[2]) < 8e-2 * max(1.0, abs(b[2])), (base, fused)
