@@ -1,0 +1,188 @@
+// Shared pieces of the Mamba3 MIMO scan kernels (forward and backward).
+//
+// Work decomposition (chunk-parallel): the sequence is cut into chunks of LT = 32 tokens; with MIMO
+// rank R = 4 a chunk is a tile of 128 "fused rows" i = 4*t + r, which is exactly one tcgen05 M=128
+// tile.  All heavy kernels run one CTA (128 threads, thread i <-> fused row i <-> TMEM lane i) per
+// (batch, head, chunk) with no loop-carried dependency; the only sequential part is an elementwise
+// recurrence over chunk states.  Per chunk (N = state dim, P = head dim = 64):
+//
+//   Qr, Kr [128,N]  = rot(Q + bias), bf16, 128-byte-swizzled shared memory tiles (K-major)
+//   PV [128,P]      = V[t] * Psi[r]
+//   S1 = Qr Kr^T ;  M[i,j] = ts_tj e^{cs_ti - cs_tj} (tj<ti) | gamma_ti (tj==ti) | 0 ;  Pm = S1 o M
+//   O  = Pm PV + e^{cs_ti} (Qr St) + D PV ;   y[t] = sum_r O[4t+r] * Phi[r] * silu(Z[t] Zeta[r])
+//   St_end = e^{tot} St + Kr^T (w o PV),  w_j = ts_tj e^{tot - cs_tj}
+//
+// with cs the inclusive within-chunk cumulative sum of A*dt, tot its last value, gamma/ts the
+// trapezoid coefficients.  The reference runs the same mathematics chunk by chunk inside one
+// TileLang kernel per (batch, head) (restated at cppmega/megatron/cute_dsl_mimo/cute_dsl_mimo_fwd.py:89-267).
+#pragma once
+#include "common.cuh"
+
+namespace cm {
+namespace mimo {
+
+constexpr int LT = 32;            // tokens per chunk
+constexpr int R = 4;              // MIMO rank
+constexpr int ROWS = LT * R;      // 128 fused rows
+constexpr int P = 64;             // head dim
+constexpr int THREADS = 128;
+constexpr int SLAB = ROWS * 128;  // bytes of one [128 rows x 64 bf16] swizzled slab
+
+// byte offset of logical 16-byte chunk `c` (0..7) of row `row` inside a 128B-swizzled slab
+__device__ __forceinline__ int sw_off(int row, int c) { return row * 128 + ((c ^ (row & 7)) << 4); }
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 t = __bfloat1622float2(b[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+  o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+  return o;
+}
+
+struct ChunkScalars {           // shared-memory block, one per CTA
+  float cs[LT];                 // inclusive cumsum of A*dt inside the chunk
+  float ts[LT];                 // trapezoid coefficient entering the state
+  float gam[LT];                // same-token coefficient
+  float tot;                    // cs[LT-1]
+};
+
+// Warp 0 computes the chunk scalars.  ADT/DT/Trap are [B,H,S] fp32; `base` = (b*H + h)*S + t0.
+__device__ __forceinline__ void compute_chunk_scalars(ChunkScalars* sc, const float* __restrict__ ADT,
+                                                      const float* __restrict__ DT, const float* __restrict__ Trap,
+                                                      size_t base, int t0, int S) {
+  const int lane = threadIdx.x & 31;
+  if ((threadIdx.x >> 5) != 0) return;
+  float a = ADT[base + lane];
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float n = __shfl_up_sync(0xffffffffu, a, o);
+    if (lane >= o) a += n;
+  }
+  const float dt = DT[base + lane], tr = Trap[base + lane];
+  const float g = dt / (1.f + __expf(-tr));
+  float nxt = 0.f;
+  if (t0 + lane + 1 < S) {
+    const float dt1 = DT[base + lane + 1], tr1 = Trap[base + lane + 1];
+    nxt = dt1 / (1.f + __expf(tr1));            // dt * sigmoid(-trap)
+  }
+  sc->cs[lane] = a;
+  sc->gam[lane] = g;
+  sc->ts[lane] = g + nxt;
+  if (lane == 31) sc->tot = a;
+}
+
+// cos/sin of the chunk's rotary angles into shared memory: cs_tab[t][a] (a < NROT).
+// angles [B,S,H,NROT] fp32 (already cumulative).  Each thread (t = i/4, r = i%4) fills a quarter row.
+template <int NROT>
+__device__ __forceinline__ void fill_sincos(float* cos_tab, float* sin_tab, const float* __restrict__ angles,
+                                            size_t b, int t0, int h, int S, int H) {
+  const int i = threadIdx.x, t = i >> 2, r = i & 3;
+  constexpr int PER = NROT / 4;
+  const float* a = angles + (((size_t)b * S + t0 + t) * H + h) * NROT + r * PER;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    float x = a[j];
+    x -= 6.283185307179586f * rintf(x * 0.15915494309189535f);     // range-reduce before the fast path
+    float s, c;
+    __sincosf(x, &s, &c);
+    cos_tab[t * NROT + r * PER + j] = c;
+    sin_tab[t * NROT + r * PER + j] = s;
+  }
+}
+
+// In-place transform of one operand tile (row i of this thread): x <- rot(x + bias[r]).
+// Tile = N/64 slabs of [128 x 64] bf16, swizzled.  bias [R,N] fp32 for this head.  Pairs (n, N/2 + n),
+// n < NROT, are rotated by the token's angle.
+template <int N, int NROT>
+__device__ __forceinline__ void transform_rows(uint8_t* tile, const float* __restrict__ bias, const float* cos_tab,
+                                               const float* sin_tab) {
+  const int i = threadIdx.x, t = i >> 2, r = i & 3;
+  const float* bb = bias + r * N;
+  constexpr int HALF = N / 2;
+  // rotated pairs: chunks [0, NROT/8) of the first half with the same chunks of the second half
+#pragma unroll
+  for (int c = 0; c < NROT / 8; ++c) {
+    const int colA = c * 8, colB = HALF + c * 8;
+    uint8_t* pa = tile + (colA / 64) * SLAB + sw_off(i, (colA % 64) / 8);
+    uint8_t* pb = tile + (colB / 64) * SLAB + sw_off(i, (colB % 64) / 8);
+    float fa[8], fb[8];
+    unpack8(*reinterpret_cast<uint4*>(pa), fa);
+    unpack8(*reinterpret_cast<uint4*>(pb), fb);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float xa = fa[j] + bb[colA + j], xb = fb[j] + bb[colB + j];
+      const float cs = cos_tab[t * NROT + colA + j], sn = sin_tab[t * NROT + colA + j];
+      fa[j] = cs * xa - sn * xb;
+      fb[j] = sn * xa + cs * xb;
+    }
+    *reinterpret_cast<uint4*>(pa) = pack8(fa);
+    *reinterpret_cast<uint4*>(pb) = pack8(fb);
+  }
+  // un-rotated remainder of both halves: bias only
+#pragma unroll
+  for (int hsel = 0; hsel < 2; ++hsel) {
+#pragma unroll
+    for (int c = NROT / 8; c < HALF / 8; ++c) {
+      const int col = hsel * HALF + c * 8;
+      uint8_t* p = tile + (col / 64) * SLAB + sw_off(i, (col % 64) / 8);
+      float f[8];
+      unpack8(*reinterpret_cast<uint4*>(p), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += bb[col + j];
+      *reinterpret_cast<uint4*>(p) = pack8(f);
+    }
+  }
+}
+
+// PV row of this thread: pv[p] = V[t,p] * Psi[r,p].  V [B,S,H,P] bf16, psi [R,P] fp32 (this head).
+__device__ __forceinline__ void load_pv_row(float (&pv)[P], const __nv_bfloat16* __restrict__ V, const float* __restrict__ psi,
+                                            size_t b, int t0, int h, int S, int H) {
+  const int i = threadIdx.x, t = i >> 2, r = i & 3;
+  const uint4* v = reinterpret_cast<const uint4*>(V + (((size_t)b * S + t0 + t) * H + h) * P);
+#pragma unroll
+  for (int c = 0; c < P / 8; ++c) {
+    float f[8];
+    unpack8(v[c], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) pv[c * 8 + j] = f[j] * psi[r * P + c * 8 + j];
+  }
+}
+
+// Store a [128 x 64] operand row (this thread's row, scaled) as bf16 into a swizzled slab.
+__device__ __forceinline__ void store_row64(uint8_t* slab, const float (&x)[P], float scale) {
+  const int i = threadIdx.x;
+#pragma unroll
+  for (int c = 0; c < P / 8; ++c) {
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = x[c * 8 + j] * scale;
+    *reinterpret_cast<uint4*>(slab + sw_off(i, c)) = pack8(f);
+  }
+}
+
+// 5-D tensor map over an operand stored [B, S, G, R, N] bf16; boxes are [32 tokens, 4 ranks, 64 cols].
+int make_tmap_qk(CUtensorMap* out, const void* base, int B, int S, int G, int N);
+// 2-D map over [rows, 64] bf16 with boxes of [128, 64].
+int make_tmap_rows64(CUtensorMap* out, const void* base, uint64_t rows);
+
+// UMMA descriptors for the tiles used here
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int kstep) {       // [128 x N] operand, K = N
+  return umma_desc_sw128(tile_addr + (kstep >> 2) * SLAB + (kstep & 3) * 32, 16, 1024);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor_rows(uint32_t slab_addr, int kstep) { // [rows(K) x 64] operand, one slab
+  return umma_desc_sw128(slab_addr + kstep * 2048, SLAB, 1024);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor_2slab(uint32_t tile_addr, int kstep) { // [rows(K) x 128(M)] operand
+  return umma_desc_sw128(tile_addr + kstep * 2048, SLAB, 1024);
+}
+
+}  // namespace mimo
+}  // namespace cm

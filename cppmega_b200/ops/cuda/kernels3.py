@@ -1,17 +1,96 @@
-"""Wrappers for the Mamba3 scan / sparse attention / indexer / embedding kernels."""
+"""Wrappers for the Mamba3 MIMO scan kernels."""
 from __future__ import annotations
 
 import ctypes
 
+import torch
+
 from .. import functional as F_
+
+LT = 32
 
 
 def declare(L: ctypes.CDLL) -> None:
-    pass
+    vp, i32 = ctypes.c_void_p, ctypes.c_int
+    fn = getattr(L, "cm_mimo_scan_fwd", None)
+    if fn is not None:
+        fn.argtypes = [vp] * 19 + [i32] * 5 + [vp, vp]
+        fn.restype = i32
+    fn = getattr(L, "cm_mimo_scan_bwd", None)
+    if fn is not None:
+        fn.argtypes = [vp] * 30 + [i32] * 5 + [vp, vp]
+        fn.restype = i32
+
+
+def supported(Q, K, V, Zeta, Phi, D, Z, div) -> bool:
+    B, S, R, G, N = Q.shape
+    H, P = V.shape[2], V.shape[3]
+    return (V.is_cuda and V.dtype == torch.bfloat16 and Q.dtype == torch.bfloat16 and K.dtype == torch.bfloat16
+            and R == 4 and N == 128 and P == 64 and div == 4 and S % LT == 0 and H % G == 0
+            and None not in (Zeta, Phi, D, Z) and Z.dtype == torch.bfloat16)
+
+
+def _as_bsgrn(x: torch.Tensor) -> torch.Tensor:
+    """[B,S,R,G,N] (possibly a permuted view) -> contiguous [B,S,G,R,N]."""
+    y = x.permute(0, 1, 3, 2, 4)
+    return y if y.is_contiguous() else y.contiguous()
+
+
+def mimo_fwd_raw(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, want_state: bool = False):
+    """Qn/Kn are [B,S,G,R,N] contiguous bf16.  Returns (y, states, tot[, final_state])."""
+    from . import lib, err_word, stream_ptr, _check
+    B, S, G, R, N = Qn.shape
+    H, P = V.shape[2], V.shape[3]
+    C = S // LT
+    dev = V.device
+    local = torch.empty(B, H, C, N, P, dtype=torch.float32, device=dev)
+    tot = torch.empty(B, H, C, dtype=torch.float32, device=dev)
+    states = torch.empty(B, H, C, N, P, dtype=torch.bfloat16, device=dev)
+    final = torch.empty(B, H, N, P, dtype=torch.float32, device=dev) if want_state else None
+    y = torch.empty(B, S, H, P, dtype=torch.bfloat16, device=dev)
+    f32 = lambda t: t.float().contiguous()
+    args = [Qn, Kn, V.contiguous(), Z.contiguous(), f32(ADT), f32(DT), f32(Trap), f32(Qb), f32(Kb), f32(Psi), f32(Zeta),
+            f32(Phi), f32(angles), f32(D)]
+    _check(lib().cm_mimo_scan_fwd(*[t.data_ptr() for t in args], local.data_ptr(), tot.data_ptr(), states.data_ptr(),
+                                  final.data_ptr() if want_state else None, y.data_ptr(), B, S, H, G, N,
+                                  err_word(dev).data_ptr(), stream_ptr()), "cm_mimo_scan_fwd")
+    F_.count_launch("mimo_scan_fwd", 3)
+    return (y, states, tot, final) if want_state else (y, states, tot)
+
+
+class MimoScanFn(torch.autograd.Function):
+    """Fused forward; the backward uses the fused backward kernels when the library has them and
+    otherwise recomputes group by group in PyTorch."""
+
+    @staticmethod
+    def forward(ctx, Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk):
+        Qn, Kn = _as_bsgrn(Q), _as_bsgrn(K)
+        y, states, tot = mimo_fwd_raw(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D)
+        ctx.save_for_backward(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z)
+        ctx.div, ctx.chunk = div, 64          # chunk length of the PyTorch recomputation, not of the kernel
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import lib
+        if getattr(lib(), "cm_mimo_scan_bwd", None) is not None:
+            from .mimo_bwd import mimo_bwd
+            return (*mimo_bwd(ctx.saved_tensors, dy), None, None)
+        from ..mimo_scan_lean import _LeanScan
+        F_._FALLBACKS["mimo_scan_bwd"] += 1
+        return _LeanScan.backward(ctx, dy)
+
+
+def mimo_scan(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk):
+    if not supported(Q, K, V, Zeta, Phi, D, Z, div):
+        from ..mimo_scan_lean import mimo_scan_lean
+        F_._FALLBACKS["mimo_scan"] += 1
+        if None in (Zeta, Phi, D, Z):
+            from .. import mimo_scan_ref as R
+            return R.mimo_scan_chunked(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk)
+        return mimo_scan_lean(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, 64)
+    return MimoScanFn.apply(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk)
 
 
 def register() -> None:
-    pass
-
-
-_ = F_
+    F_.register_cuda("mimo_scan", mimo_scan)

@@ -163,3 +163,33 @@ def main(argv: List[str]) -> int:
 
 if __name__ == "__main__":
     sys.exit(main(sys.argv[1:]))
+
+
+def bench_scan() -> List[dict]:
+    """Mamba3 MIMO scan forward at the NAM56R layer shape (B4 S4096 H128 G8 N128 P64 R4)."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import kernels3
+    pk = peaks()
+    B, S, H, G, N, P, R = 4, 4096, 128, 8, 128, 64, 4
+    dev = "cuda"
+    Qn = (torch.randn(B, S, G, R, N, device=dev) * 0.5).bfloat16()
+    Kn = (torch.randn(B, S, G, R, N, device=dev) * 0.5).bfloat16()
+    V = torch.randn(B, S, H, P, device=dev).bfloat16()
+    Z = torch.randn(B, S, H, P, device=dev).bfloat16()
+    DT = torch.rand(B, H, S, device=dev) * 0.1
+    ADT = -DT * torch.rand(B, H, S, device=dev)
+    Trap = torch.randn(B, H, S, device=dev)
+    Qb, Kb = torch.randn(H, R, N, device=dev), torch.randn(H, R, N, device=dev)
+    Psi, Zeta, Phi = (torch.randn(H, R, P, device=dev) for _ in range(3))
+    ang = torch.randn(B, S, H, N // 4, device=dev)
+    D = torch.randn(H, device=dev)
+    ms = time_ms(lambda: kernels3.mimo_fwd_raw(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D), iters=5)
+    cu.check_errors()
+    chunks = B * H * (S // 32)
+    flops = chunks * (2.0 * 128 * 128 * 128 + 3 * 2.0 * 128 * 64 * 128)
+    return [{"kernel": "mimo_scan_fwd (local_state + state_scan + chunk_out)", "B": B, "S": S, "H": H, "ms": ms,
+             "tflops": flops / ms / 1e9, "frac_of_" + pk["kind"]: flops / ms / 1e9 / pk["bf16_tflops"],
+             "tokens_per_s": B * S / ms * 1e3}]
+
+
+CASES["scan"] = bench_scan
