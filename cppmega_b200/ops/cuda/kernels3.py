@@ -66,19 +66,20 @@ class MimoScanFn(torch.autograd.Function):
     def forward(ctx, Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk):
         Qn, Kn = _as_bsgrn(Q), _as_bsgrn(K)
         y, states, tot = mimo_fwd_raw(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D)
-        ctx.save_for_backward(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z)
+        ctx.save_for_backward(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, states, tot)
         ctx.div, ctx.chunk = div, 64          # chunk length of the PyTorch recomputation, not of the kernel
         return y
 
     @staticmethod
     def backward(ctx, dy):
         from . import lib
-        if getattr(lib(), "cm_mimo_scan_bwd", None) is not None:
+        *saved, states, tot = ctx.saved_tensors
+        if getattr(lib(), "cm_mimo_scan_bwd", None) is not None and "mimo_scan_bwd" not in F_._DISABLED:
             from .mimo_bwd import mimo_bwd
-            return (*mimo_bwd(ctx.saved_tensors, dy), None, None)
-        from ..mimo_scan_lean import _LeanScan
+            return (*mimo_bwd(saved, dy, states, tot), None, None)
+        from ..mimo_scan_lean import lean_backward
         F_._FALLBACKS["mimo_scan_bwd"] += 1
-        return _LeanScan.backward(ctx, dy)
+        return lean_backward(saved, dy, ctx.div, ctx.chunk)
 
 
 def mimo_scan(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk):

@@ -32,7 +32,12 @@ class _LeanScan(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        saved = ctx.saved_tensors
+        return lean_backward(ctx.saved_tensors, dy, ctx.div, ctx.chunk)
+
+
+def lean_backward(saved, dy, div, chunk):
+    """Gradients of the scan by recomputing one head group at a time under autograd."""
+    if True:
         Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z = saved
         G = Q.shape[3]
         H = V.shape[2]
@@ -52,7 +57,7 @@ class _LeanScan(torch.autograd.Function):
                     p = t[tuple(idx)]
                 parts.append(p.detach().requires_grad_(True))
             with torch.enable_grad():
-                y = R.mimo_scan_chunked(*parts, ctx.div, ctx.chunk, mm_dtype=torch.bfloat16)
+                y = R.mimo_scan_chunked(*parts, div, chunk, mm_dtype=torch.bfloat16)
             gs = torch.autograd.grad(y, parts, dy[:, :, hs].to(y.dtype), allow_unused=True)
             for i, (gi, hd) in enumerate(zip(gs, head_dim)):
                 if gi is None:

@@ -353,6 +353,15 @@ class DistributedOptimizer:
         return {"grad_norm": gnorm, "clip_coef": clip}
 
     # ---- checkpoint -------------------------------------------------------
+    @torch.no_grad()
+    def reset_master_from_params(self) -> None:
+        """Re-seed the fp32 master shards from the (just loaded) low-precision parameters and clear
+        the moments; used when a checkpoint was written under a different parallel layout."""
+        for s in self.state:
+            s["master"].copy_(s["buf"].param_buffer[s["lo"]:s["hi"]].float())
+            s["m"].zero_()
+            s["v"].zero_()
+
     def state_dict(self) -> dict:
         return {
             "step": self.step_count, "lr": self.lr,

@@ -161,10 +161,6 @@ def main(argv: List[str]) -> int:
     return 0
 
 
-if __name__ == "__main__":
-    sys.exit(main(sys.argv[1:]))
-
-
 def bench_scan() -> List[dict]:
     """Mamba3 MIMO scan forward at the NAM56R layer shape (B4 S4096 H128 G8 N128 P64 R4)."""
     from cppmega_b200.ops import cuda as cu
@@ -193,3 +189,7 @@ def bench_scan() -> List[dict]:
 
 
 CASES["scan"] = bench_scan
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1:]))

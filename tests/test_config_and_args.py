@@ -1,0 +1,121 @@
+"""Pattern language, typed configs and the Megatron-style argument surface (pure Python)."""
+import dataclasses
+
+import pytest
+
+from cppmega_b200.config import pattern as P
+from cppmega_b200.config.model import (DSAConfig, MoEConfig, ModelConfig, Mamba3Config, get_preset, nam56r_full,
+                                       nam56r_tiny)
+from cppmega_b200.parallel.state import ParallelConfig, group_rank_lists, rank_coordinates
+from cppmega_b200.training.arguments import parse_args, render_args
+from cppmega_b200.training.trainer import TrainConfig
+
+
+def test_pattern_tiling_counts():
+    c = P.count_symbols("AEMEAEMEAEMR", 52)
+    assert c == {"A": 13, "E": 22, "M": 13, "R": 4}
+    plan = P.translate_pattern("AEMEAEMEAEMR", 52, mtp_depths=2)
+    assert plan.hybrid_pattern.startswith("*EME*EME*EMM*")
+    assert plan.full_pattern.endswith("/*-/*-")
+    assert plan.r_layer_numbers == (12, 24, 36, 48)
+    assert len(plan.attention_layer_numbers) == 13
+
+
+def test_pattern_rejects_bad_input():
+    with pytest.raises(P.PatternError):
+        P.expand_nam_pattern("AXM", 3)
+    with pytest.raises(P.PatternError):
+        P.expand_nam_pattern("AE|ME", 5)
+    with pytest.raises(P.PatternError):
+        P.expand_nam_pattern("", 4)
+    assert P.expand_nam_pattern("AE|ME", 4) == list("AEME")
+
+
+def test_pipeline_split():
+    assert P.split_pattern_for_pipeline("*" * 52, 2, 2) == "|".join(["*" * 13] * 4)
+    assert P.split_pattern_for_pipeline("MMMMMMMMMM", 4) == "MMM|MMM|MM|MM"
+    main, mtp, chunks = P.parse_hybrid_pattern("*EM|E*E/*-/*-")
+    assert main == list("*EME*E") and mtp == 2 and chunks == [3, 3]
+    with pytest.raises(P.PatternError):
+        P.parse_hybrid_pattern("*EM/*E")
+
+
+def test_int_list():
+    assert P.parse_int_list("1,2,5-7") == (1, 2, 5, 6, 7)
+    assert P.parse_int_list("") == ()
+    assert P.parse_int_list([3, 1, 3]) == (1, 3)
+
+
+def test_nam56r_layout_matches_reference_facts():
+    cfg = nam56r_full()
+    kinds = cfg.layer_kinds()
+    assert kinds.count("dsa") == 9 and kinds.count("mla") == 4
+    assert kinds.count("mamba3") == 13 and kinds.count("m2rnn") == 4 and kinds.count("moe") == 22
+    assert [i + 1 for i, k in enumerate(kinds) if k == "m2rnn"] == [12, 24, 36, 48]
+    assert sum(cfg.mamba3.in_proj_sizes(cfg.hidden_size)) == 24960
+    assert cfg.mamba3.num_rope_angles == 32 and cfg.mamba3.rotary_dim_divisor == 4
+    pc = cfg.param_count()
+    assert 7.5e9 < pc["total"] < 8.5e9 and pc["active"] < pc["total"]
+
+
+def test_config_validation():
+    with pytest.raises(ValueError):
+        Mamba3Config(rope_fraction=0.3)
+    with pytest.raises(ValueError):
+        MoEConfig(dispatcher="ring")
+    with pytest.raises(ValueError):
+        DSAConfig(indexer_dtype="fp8")
+    with pytest.raises(ValueError):
+        ModelConfig(mamba_variant="s4")
+    with pytest.raises(KeyError):
+        get_preset("nope")
+    with pytest.raises(ValueError):
+        Mamba3Config().in_proj_sizes(4096, tp=3)
+
+
+def test_tp_partition_sizes():
+    m3 = Mamba3Config()
+    full = m3.in_proj_sizes(4096, 1)
+    half = m3.in_proj_sizes(4096, 2)
+    assert all(f == 2 * h for f, h in zip(full, half))
+    assert half == (4096, 4096, 2048, 2048, 64, 64, 64)
+
+
+@pytest.mark.parametrize("preset", ["nam56r", "nam56r_tiny"])
+def test_args_round_trip(preset):
+    m = get_preset(preset)
+    p = ParallelConfig(pp=2, ep=2, tp=1, distributed_optimizer=True, overlap_grad_reduce=True)
+    t = TrainConfig(seq_length=m.seq_length, recompute="selective")
+    argv = render_args(m, p, t, mock_data=True, save="/tmp/x", save_interval=10)
+    m2, p2, t2, ex = parse_args(argv + ["--model-preset", preset])
+    assert m2.layer_kinds() == m.layer_kinds()
+    assert dataclasses.replace(m2, pattern=m.pattern) == m
+    assert (p2.pp, p2.ep, p2.tp, p2.distributed_optimizer) == (2, 2, 1, True)
+    assert t2.recompute == "selective" and ex["save"] == "/tmp/x" and ex["mock_data"]
+    assert "--hybrid-layer-pattern" in argv and "--use-distributed-optimizer" in argv
+    assert "--expert-model-parallel-size" in argv
+
+
+def test_args_reject_unsupported():
+    with pytest.raises(ValueError):
+        parse_args(["--context-parallel-size", "2"])
+    with pytest.raises(ValueError):
+        parse_args(["--moe-token-dispatcher-type", "flex"])
+    with pytest.raises(P.PatternError):
+        parse_args(["--hybrid-layer-pattern", "*EM", "--r-layer-indices", "1"])
+
+
+def test_rank_groups():
+    cfg = ParallelConfig(tp=2, pp=2, ep=2)
+    lists = group_rank_lists(16, cfg)
+    assert [0, 1] in lists["tp"] and [0, 8] in lists["pp"]
+    assert [0, 2, 4, 6] in lists["dp"] and [0, 2] in lists["ep"] and [0, 4] in lists["edp"]
+    for kind, groups in lists.items():
+        flat = sorted(r for g in groups for r in g)
+        assert flat == list(range(16)), kind
+    assert rank_coordinates(13, 16, cfg) == (1, 0, 1, 2, 1)
+    with pytest.raises(ValueError):
+        ParallelConfig(tp=3).dp(8)
+    with pytest.raises(ValueError):
+        ParallelConfig(cp=2)
+    assert nam56r_tiny().plan().needs_mamba3
