@@ -76,11 +76,28 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 
 // Bounded wait.  Returns false (after recording `code`) if the barrier never flips or if
 // another role of this CTA has already aborted.
+// The bound is wall clock (CM_WAIT_NS, default 2 s): a try_wait poll may itself suspend for an
+// implementation-defined time, so counting polls does not bound anything.  A kernel-wide error word that
+// is already set (another CTA gave up) ends the wait at once, so a broken launch drains quickly.
+#ifndef CM_WAIT_NS
+#define CM_WAIT_NS 2000000000ull
+#endif
+__device__ __forceinline__ unsigned long long cm_globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* err_word, int code) {
-  for (uint32_t i = 0; i < CM_WAIT_LIMIT; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = cm_globaltimer();
+  for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (err_word && *reinterpret_cast<volatile int*>(err_word) != 0) { *abort_flag = 1; return false; }
+      if (cm_globaltimer() - t0 > CM_WAIT_NS) break;
+    }
   }
   *abort_flag = 1;
   if (err_word) atomicCAS(err_word, 0, code);

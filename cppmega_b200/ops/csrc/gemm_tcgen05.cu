@@ -67,6 +67,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  if (args.err && *reinterpret_cast<volatile int*>(args.err) != 0) return;   // an earlier kernel gave up: drain
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 

@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(THREADS) mimo_grad_state_kernel(const __grid_c
   uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 1);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
   int b, g, c, h;
   decode_block_b(a, b, g, c, h);
   const int t0 = c * LT;
@@ -225,6 +226,7 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
   float* colsum = reinterpret_cast<float*>(tmem_slot + 4);          // [4 warps][2][32]
   GradScratch* gs = reinterpret_cast<GradScratch*>(sPm);            // aliases Pm: used only after phase 2 has read it
 
+  if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
   int b, g, c, h;
   decode_block_b(a, b, g, c, h);
   const int t0 = c * LT;

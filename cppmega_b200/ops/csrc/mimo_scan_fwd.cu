@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(THREADS) mimo_local_state_kernel(const __grid_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
   int b, g, c, h;
   decode_block(a, b, g, c, h);
   const int t0 = c * LT;
@@ -203,6 +204,7 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_out_kernel(const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
   int b, g, c, h;
   decode_block(a, b, g, c, h);
   const int t0 = c * LT;
