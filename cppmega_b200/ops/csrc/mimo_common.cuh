@@ -47,12 +47,14 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return o;
 }
 
-struct ChunkScalars {           // shared-memory block, one per CTA
-  float cs[LT];                 // inclusive cumsum of A*dt inside the chunk
-  float ts[LT];                 // trapezoid coefficient entering the state
-  float gam[LT];                // same-token coefficient
-  float tot;                    // cs[LT-1]
+struct alignas(16) ChunkScalars {   // shared-memory block, one per CTA; the mbarriers are placed right after it,
+  float cs[LT];                     // so its size must keep them 8-byte aligned
+  float ts[LT];                     // trapezoid coefficient entering the state
+  float gam[LT];                    // same-token coefficient
+  float tot;                        // cs[LT-1]
+  float pad_[3];
 };
+static_assert(sizeof(ChunkScalars) % 16 == 0, "mbarriers follow this block and need 8-byte alignment");
 
 // Warp 0 computes the chunk scalars.  ADT/DT/Trap are [B,H,S] fp32; `base` = (b*H + h)*S + t0.
 __device__ __forceinline__ void compute_chunk_scalars(ChunkScalars* sc, const float* __restrict__ ADT,
