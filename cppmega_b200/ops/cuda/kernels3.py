@@ -18,7 +18,7 @@ def declare(L: ctypes.CDLL) -> None:
         fn.restype = i32
     fn = getattr(L, "cm_mimo_scan_bwd", None)
     if fn is not None:
-        fn.argtypes = [vp] * 30 + [i32] * 5 + [vp, vp]
+        fn.argtypes = [vp] * 31 + [i32] * 5 + [vp, vp]
         fn.restype = i32
 
 
