@@ -249,7 +249,7 @@ class NAM56RModel(nn.Module):
         # loss mask, the per-head token count and the MTP depth scaling
         D = len(hiddens) - 1
         counts = [m.sum().clamp_min(1.0) for m in mask_list]
-        scales = [1.0] + [cfg.mtp.loss_scaling_factor / D] * D
+        scales = [1.0] + [cfg.mtp.loss_scaling_factor / max(D, 1)] * D
         row_w = torch.cat([(m * (sc / n)).reshape(-1) for m, sc, n in zip(mask_list, scales, counts)])
         if cfg.mtp.fused_with_main_ce or D == 0:
             hcat = torch.cat([h.reshape(B * S, -1) for h in hiddens], dim=0) if D else hiddens[0].reshape(B * S, -1)

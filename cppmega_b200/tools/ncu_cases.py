@@ -1,0 +1,113 @@
+"""Small, self-terminating workloads for Nsight Compute captures of single kernels.
+
+    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,ce,rmsnorm}
+
+Each case launches its kernel three times on inputs that exceed the 126 MB L2 but hold at most a few GB, so a
+``--set full`` capture of one launch finishes in a minute or two:
+
+    ncu --set full --clock-control none -k regex:<kernel> -s 1 -c 1 -o out python -m cppmega_b200.tools.ncu_cases <case>
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+
+def case_gemm(a_mn=False, b_mn=False):
+    from cppmega_b200.ops import cuda as cu
+    M = N = K = 8192
+    A = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+    B = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+    C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        cu.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=C)
+    torch.cuda.synchronize()
+    cu.check_errors()
+
+
+def _scan_inputs(B=1, S=4096, H=32, G=2, N=128, P=64, R=4):
+    dev = "cuda"
+    Qn = (torch.randn(B, S, G, R, N, device=dev) * 0.5).bfloat16()
+    Kn = (torch.randn(B, S, G, R, N, device=dev) * 0.5).bfloat16()
+    V = torch.randn(B, S, H, P, device=dev).bfloat16()
+    Z = torch.randn(B, S, H, P, device=dev).bfloat16()
+    DT = torch.rand(B, H, S, device=dev) * 0.1
+    ADT = -DT * torch.rand(B, H, S, device=dev)
+    Trap = torch.randn(B, H, S, device=dev)
+    Qb, Kb = torch.randn(H, R, N, device=dev), torch.randn(H, R, N, device=dev)
+    Psi, Zeta, Phi = (torch.randn(H, R, P, device=dev) for _ in range(3))
+    ang = torch.randn(B, S, H, N // 4, device=dev)
+    D = torch.randn(H, device=dev)
+    return Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D
+
+
+def case_scan_fwd():
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import kernels3
+    args = _scan_inputs()
+    for _ in range(3):
+        kernels3.mimo_fwd_raw(*args)
+    torch.cuda.synchronize()
+    cu.check_errors()
+
+
+def case_scan_bwd():
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import kernels3
+    from cppmega_b200.ops.cuda.mimo_bwd import mimo_bwd
+    Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D = _scan_inputs()
+    y, states, tot = kernels3.mimo_fwd_raw(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D)
+    saved = [Qn.permute(0, 1, 3, 2, 4), Kn.permute(0, 1, 3, 2, 4), V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D, Z]
+    dy = torch.randn_like(y)
+    for _ in range(3):
+        mimo_bwd(saved, dy, states, tot)
+    torch.cuda.synchronize()
+    cu.check_errors()
+
+
+def case_m2rnn():
+    from cppmega_b200.ops.cuda import kernels2
+    B, S, H = 4, 4096, 51
+    q = torch.randn(B, S, 1, 64, device="cuda").bfloat16()
+    k = torch.randn(B, S, 1, 64, device="cuda").bfloat16()
+    v = torch.randn(B, S, H, 16, device="cuda").bfloat16()
+    W = torch.eye(16, device="cuda").repeat(H, 1, 1).bfloat16()
+    f = torch.rand(B, S, H, device="cuda")
+    with torch.no_grad():
+        for _ in range(3):
+            kernels2.m2rnn_scan(q, k, v, W, f)
+    torch.cuda.synchronize()
+
+
+def case_ce():
+    from cppmega_b200.ops.cuda import extra
+    T, H, V = 4096, 4096, 131072
+    h = torch.randn(T, H, device="cuda").bfloat16()
+    w = (torch.randn(V, H, device="cuda") * 0.02).bfloat16()
+    lab = torch.randint(0, V, (T,), device="cuda")
+    rw = torch.full((T,), 1.0 / T, device="cuda")
+    for _ in range(2):
+        extra.linear_cross_entropy_weighted(h, w, lab, rw, -100)
+    torch.cuda.synchronize()
+
+
+def case_rmsnorm():
+    from cppmega_b200.ops import cuda as cu
+    x = torch.randn(65536, 4096, device="cuda").bfloat16()
+    w = torch.ones(4096, device="cuda").bfloat16()
+    with torch.no_grad():
+        for _ in range(3):
+            cu.rmsnorm(x, w, 1e-5)
+    torch.cuda.synchronize()
+
+
+CASES = {"gemm": case_gemm, "gemm_wgrad": lambda: case_gemm(True, True), "scan_fwd": case_scan_fwd,
+         "scan_bwd": case_scan_bwd, "m2rnn": case_m2rnn, "ce": case_ce, "rmsnorm": case_rmsnorm}
+
+if __name__ == "__main__":
+    name = sys.argv[1] if len(sys.argv) > 1 else ""
+    if name not in CASES:
+        raise SystemExit(f"usage: python -m cppmega_b200.tools.ncu_cases {{{','.join(CASES)}}}")
+    CASES[name]()
+    print(f"{name}: done")
