@@ -391,3 +391,51 @@ extern "C" int cm_mimo_scan_fwd(const void* Qn, const void* Kn, const void* V, c
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ------------------------------------------------------------------------------------------
+// Variant with the work buffers in a fixed device array (see mimo_scan_static.h for the contract).
+// ------------------------------------------------------------------------------------------
+#include <cstdio>
+
+#include "mimo_scan_static.h"
+
+static __device__ __align__(256) unsigned char cm_mimo_static_scratch[CM_MIMO_STATIC_BYTES];
+
+extern "C" int cm_mimo_scan_fwd_static(const void* Qn, const void* Kn, const void* V, const void* Z, const float* ADT,
+                                       const float* DT, const float* Trap, const float* Qb, const float* Kb,
+                                       const float* Psi, const float* Zeta, const float* Phi, const float* angles,
+                                       const float* Dskip, float* final_state, void* y, int B, int S, int H, int G, int N,
+                                       int* err, cudaStream_t stream) {
+  if (B <= 0 || S <= 0) return 0;
+  if (S % LT || N != 128 || H <= 0 || G <= 0 || H % G) return -10;
+  const long long chunks = (long long)B * H * (S / LT);
+  if (chunks > CM_MIMO_STATIC_MAX_CHUNKS) {
+    fprintf(stderr,
+            "cm_mimo_scan_fwd_static: B*H*S/32 = %lld chunks exceeds the fixed work array (%d chunks, %zu bytes); "
+            "use cm_mimo_scan_fwd with caller-provided scratch for this size\n",
+            chunks, CM_MIMO_STATIC_MAX_CHUNKS, (size_t)CM_MIMO_STATIC_BYTES);
+    return CM_MIMO_STATIC_E_TOO_LARGE;
+  }
+  constexpr int MAX_DEV = 64;
+  static unsigned char* base[MAX_DEV] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return CM_MIMO_STATIC_E_DEVICE;
+  if (base[dev] == nullptr) {
+    unsigned char* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&p, cm_mimo_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "cm_mimo_scan_fwd_static: cudaGetSymbolAddress failed on device %d: %s\n", dev, cudaGetErrorString(e));
+      return CM_MIMO_STATIC_E_SYMBOL;
+    }
+    base[dev] = p;
+  }
+  // carve: local fp32 | start states bf16 | tot fp32 (each offset a multiple of 256 bytes)
+  unsigned char* p = base[dev];
+  float* local = reinterpret_cast<float*>(p);
+  p += (size_t)CM_MIMO_STATIC_MAX_CHUNKS * CM_MIMO_STATIC_STATE_ELEMS * 4;
+  void* states = p;
+  p += (size_t)CM_MIMO_STATIC_MAX_CHUNKS * CM_MIMO_STATIC_STATE_ELEMS * 2;
+  float* tot = reinterpret_cast<float*>(p);
+  return cm_mimo_scan_fwd(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, Dskip, local, tot, states,
+                          final_state, y, B, S, H, G, N, err, stream);
+}
