@@ -1,0 +1,137 @@
+// Cumulative rotary angles of the Mamba3 mixer and their backward.
+//
+//   out[b,t,h,a] = sum_{s<=t} raw[b,s,a] * dt[b,h,s]                      (fp32, a < A <= 32)
+//
+// The reference builds this with a broadcast multiply and a sequence cumsum in PyTorch
+// (cppmega/megatron/noconv_mamba_mixer.py:326-333), i.e. three passes over a [B,S,H,A] fp32 tensor forward and
+// five backward.  Here: one pass forward (a warp owns a (b, h, sequence segment); lanes are the angles, so every
+// store is one 128-byte line) and two passes backward (suffix sums, then the two reductions over heads / angles).
+#include "common.cuh"
+
+namespace cm {
+
+constexpr int ANG_SEG = 512;
+
+// grid: ceil(B*H*nseg / 4) blocks of 128 threads.  Warps with the longest read-only prefix come first.
+__global__ void __launch_bounds__(128) angle_cumsum_fwd_kernel(const float* __restrict__ raw, const float* __restrict__ dt,
+                                                               long long dsb, long long dsh, long long dss,
+                                                               float* __restrict__ out, int B, int S, int H, int A, int nseg) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const long long BH = (long long)B * H;
+  if (w >= BH * nseg) return;
+  const int seg = nseg - 1 - (int)(w / BH);
+  const int bh = (int)(w % BH);
+  const int b = bh / H, h = bh % H;
+  const bool on = lane < A;
+  const float* rp = raw + (size_t)b * S * A + (on ? lane : 0);
+  const float* dp = dt + b * dsb + h * dsh;
+  float acc = 0.f;
+  const int t0 = seg * ANG_SEG;
+  const int t1 = min(S, t0 + ANG_SEG);
+#pragma unroll 8
+  for (int t = 0; t < t0; ++t) acc = fmaf(rp[(size_t)t * A], dp[t * dss], acc);
+  float* op = out + ((size_t)b * S * H + h) * A + lane;
+#pragma unroll 8
+  for (int t = t0; t < t1; ++t) {
+    acc = fmaf(rp[(size_t)t * A], dp[t * dss], acc);
+    if (on) op[(size_t)t * H * A] = acc;
+  }
+}
+
+// segsum[b,h,seg,a] = sum over the segment of g[b,t,h,a]
+__global__ void __launch_bounds__(128) angle_segsum_kernel(const float* __restrict__ g, float* __restrict__ segsum, int B, int S, int H,
+                                                           int A, int nseg) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (w >= (long long)B * H * nseg) return;
+  const int seg = (int)(w % nseg);
+  const int bh = (int)(w / nseg);
+  const int b = bh / H, h = bh % H;
+  if (lane >= A) return;
+  const float* gp = g + ((size_t)b * S * H + h) * A + lane;
+  const int t0 = seg * ANG_SEG, t1 = min(S, t0 + ANG_SEG);
+  float acc = 0.f;
+#pragma unroll 8
+  for (int t = t0; t < t1; ++t) acc += gp[(size_t)t * H * A];
+  segsum[w * A + lane] = acc;
+}
+
+// suffix sums in place: g[b,t,h,a] <- sum_{s>=t} g[b,s,h,a]
+__global__ void __launch_bounds__(128) angle_suffix_kernel(float* __restrict__ g, const float* __restrict__ segsum, int B, int S, int H,
+                                                           int A, int nseg) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (w >= (long long)B * H * nseg) return;
+  const int seg = (int)(w % nseg);
+  const int bh = (int)(w / nseg);
+  const int b = bh / H, h = bh % H;
+  if (lane >= A) return;
+  float acc = 0.f;
+  for (int s2 = nseg - 1; s2 > seg; --s2) acc += segsum[((size_t)bh * nseg + s2) * A + lane];
+  float* gp = g + ((size_t)b * S * H + h) * A + lane;
+  const int t0 = seg * ANG_SEG, t1 = min(S, t0 + ANG_SEG);
+#pragma unroll 8
+  for (int t = t1 - 1; t >= t0; --t) {
+    acc += gp[(size_t)t * H * A];
+    gp[(size_t)t * H * A] = acc;
+  }
+}
+
+// one block per token: draw[b,t,a] = sum_h g*dt ; ddt[b,h,t] = sum_a g*raw     (g holds the suffix sums)
+__global__ void __launch_bounds__(256) angle_reduce_kernel(const float* __restrict__ g, const float* __restrict__ raw,
+                                                           const float* __restrict__ dt, long long dsb, long long dsh, long long dss,
+                                                           float* __restrict__ draw, float* __restrict__ ddt, int B, int S, int H, int A) {
+  __shared__ float red[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long tok = blockIdx.x;
+  const int b = (int)(tok / S), t = (int)(tok % S);
+  const bool on = lane < A;
+  const float rv = on ? raw[tok * A + lane] : 0.f;
+  const float* gp = g + (size_t)tok * H * A;
+  float acc = 0.f;
+  for (int h = warp; h < H; h += 8) {
+    const float gv = on ? gp[(size_t)h * A + lane] : 0.f;
+    acc = fmaf(gv, dt[b * dsb + h * dsh + t * dss], acc);
+    const float s = warp_sum(gv * rv);
+    if (lane == 0) ddt[((size_t)b * H + h) * S + t] = s;
+  }
+  red[warp][lane] = acc;
+  __syncthreads();
+  if (warp == 0 && on) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += red[i][lane];
+    draw[tok * A + lane] = s;
+  }
+}
+
+}  // namespace cm
+
+using namespace cm;
+
+// raw [B,S,A] fp32 contiguous; dt addressed as dt[b*dsb + h*dsh + t*dss] (element strides); out [B,S,H,A] fp32.
+extern "C" int cm_angle_cumsum_fwd(const float* raw, const float* dt, long long dsb, long long dsh, long long dss, float* out,
+                                   int B, int S, int H, int A, cudaStream_t s) {
+  if (B <= 0 || S <= 0 || H <= 0) return 0;
+  if (A <= 0 || A > 32) return -10;
+  const int nseg = (S + ANG_SEG - 1) / ANG_SEG;
+  const long long warps = (long long)B * H * nseg;
+  angle_cumsum_fwd_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, s>>>(raw, dt, dsb, dsh, dss, out, B, S, H, A, nseg);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// g [B,S,H,A] fp32: gradient of `out` on entry, overwritten with its suffix sums.  segsum: [B*H*nseg*A] fp32 scratch.
+// draw [B,S,A] fp32, ddt [B,H,S] fp32 contiguous.
+extern "C" int cm_angle_cumsum_bwd(float* g, const float* raw, const float* dt, long long dsb, long long dsh, long long dss,
+                                   float* segsum, float* draw, float* ddt, int B, int S, int H, int A, cudaStream_t s) {
+  if (B <= 0 || S <= 0 || H <= 0) return 0;
+  if (A <= 0 || A > 32) return -10;
+  const int nseg = (S + ANG_SEG - 1) / ANG_SEG;
+  const long long warps = (long long)B * H * nseg;
+  const unsigned grid = (unsigned)((warps + 3) / 4);
+  angle_segsum_kernel<<<grid, 128, 0, s>>>(g, segsum, B, S, H, A, nseg);
+  angle_suffix_kernel<<<grid, 128, 0, s>>>(g, segsum, B, S, H, A, nseg);
+  angle_reduce_kernel<<<(unsigned)((long long)B * S), 256, 0, s>>>(g, raw, dt, dsb, dsh, dss, draw, ddt, B, S, H, A);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -28,6 +28,20 @@ constexpr int P = 64;             // head dim
 constexpr int THREADS = 128;
 constexpr int SLAB = ROWS * 128;  // bytes of one [128 rows x 64 bf16] swizzled slab
 
+// Optional phase timestamps (compile with -DCM_MIMO_TIMING): thread 0 of the first 1024 CTAs records the SM clock at
+// numbered points of a kernel; cm_mimo_read_stamps copies them out.  Compiled out by default.
+#ifdef CM_MIMO_TIMING
+static __device__ unsigned long long cm_mimo_stamps[1024 * 16];
+#define CM_STAMP(k)                                                                                      \
+  do {                                                                                                   \
+    if (threadIdx.x == 0 && blockIdx.x < 1024) cm_mimo_stamps[blockIdx.x * 16 + (k)] = (unsigned long long)clock64(); \
+  } while (0)
+#else
+#define CM_STAMP(k) \
+  do {              \
+  } while (0)
+#endif
+
 // byte offset of logical 16-byte chunk `c` (0..7) of row `row` inside a 128B-swizzled slab
 __device__ __forceinline__ int sw_off(int row, int c) { return row * 128 + ((c ^ (row & 7)) << 4); }
 
@@ -83,35 +97,46 @@ __device__ __forceinline__ void compute_chunk_scalars(ChunkScalars* sc, const fl
 
 // cos/sin of the chunk's rotary angles into shared memory: cs_tab[t][a] (a < NROT).
 // angles [B,S,H,NROT] fp32 (already cumulative).  Each thread (t = i/4, r = i%4) fills a quarter row.
+// Table rows are NROT + 1 floats apart so that the eight tokens a warp touches at once fall into different banks.
+// NWG = warpgroups (of 128 threads) in the CTA; the work of a row is split between them.
 template <int NROT>
+constexpr int tab_stride() { return NROT + 1; }
+template <int NROT>
+constexpr int tab_floats() { return LT * (NROT + 1); }   // one table; (32 * 33 * 4) bytes keeps 16-byte alignment
+
+template <int NROT, int NWG = 1>
 __device__ __forceinline__ void fill_sincos(float* cos_tab, float* sin_tab, const float* __restrict__ angles,
                                             size_t b, int t0, int h, int S, int H) {
-  const int i = threadIdx.x, t = i >> 2, r = i & 3;
-  constexpr int PER = NROT / 4;
-  const float* a = angles + (((size_t)b * S + t0 + t) * H + h) * NROT + r * PER;
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3;
+  constexpr int PER = NROT / 4 / NWG;
+  constexpr int TS = tab_stride<NROT>();
+  const int off = (r * NWG + wg) * PER;
+  const float* a = angles + (((size_t)b * S + t0 + t) * H + h) * NROT + off;
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     float x = a[j];
     x -= 6.283185307179586f * rintf(x * 0.15915494309189535f);     // range-reduce before the fast path
     float s, c;
     __sincosf(x, &s, &c);
-    cos_tab[t * NROT + r * PER + j] = c;
-    sin_tab[t * NROT + r * PER + j] = s;
+    cos_tab[t * TS + off + j] = c;
+    sin_tab[t * TS + off + j] = s;
   }
 }
 
 // In-place transform of one operand tile (row i of this thread): x <- rot(x + bias[r]).
 // Tile = N/64 slabs of [128 x 64] bf16, swizzled.  bias [R,N] fp32 for this head.  Pairs (n, N/2 + n),
 // n < NROT, are rotated by the token's angle.
-template <int N, int NROT>
+template <int N, int NROT, int NWG = 1>
 __device__ __forceinline__ void transform_rows(uint8_t* tile, const float* __restrict__ bias, const float* cos_tab,
                                                const float* sin_tab) {
-  const int i = threadIdx.x, t = i >> 2, r = i & 3;
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3;
   const float* bb = bias + r * N;
   constexpr int HALF = N / 2;
+  constexpr int TS = tab_stride<NROT>();
   // rotated pairs: chunks [0, NROT/8) of the first half with the same chunks of the second half
 #pragma unroll
-  for (int c = 0; c < NROT / 8; ++c) {
+  for (int c0 = 0; c0 < NROT / 8; c0 += NWG) {
+    const int c = c0 + wg;
     const int colA = c * 8, colB = HALF + c * 8;
     uint8_t* pa = tile + (colA / 64) * SLAB + sw_off(i, (colA % 64) / 8);
     uint8_t* pb = tile + (colB / 64) * SLAB + sw_off(i, (colB % 64) / 8);
@@ -121,7 +146,7 @@ __device__ __forceinline__ void transform_rows(uint8_t* tile, const float* __res
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float xa = fa[j] + bb[colA + j], xb = fb[j] + bb[colB + j];
-      const float cs = cos_tab[t * NROT + colA + j], sn = sin_tab[t * NROT + colA + j];
+      const float cs = cos_tab[t * TS + colA + j], sn = sin_tab[t * TS + colA + j];
       fa[j] = cs * xa - sn * xb;
       fb[j] = sn * xa + cs * xb;
     }
@@ -132,7 +157,8 @@ __device__ __forceinline__ void transform_rows(uint8_t* tile, const float* __res
 #pragma unroll
   for (int hsel = 0; hsel < 2; ++hsel) {
 #pragma unroll
-    for (int c = NROT / 8; c < HALF / 8; ++c) {
+    for (int c0 = NROT / 8; c0 < HALF / 8; c0 += NWG) {
+      const int c = c0 + wg;
       const int col = hsel * HALF + c * 8;
       uint8_t* p = tile + (col / 64) * SLAB + sw_off(i, (col % 64) / 8);
       float f[8];
@@ -155,6 +181,56 @@ __device__ __forceinline__ void load_pv_row(float (&pv)[P], const __nv_bfloat16*
     unpack8(v[c], f);
 #pragma unroll
     for (int j = 0; j < 8; ++j) pv[c * 8 + j] = f[j] * psi[r * P + c * 8 + j];
+  }
+}
+
+// Two-warpgroup form: this thread owns columns [wg*32, wg*32 + 32) of row i.  `psi` may point to shared memory.
+__device__ __forceinline__ void load_pv_half(float (&pv)[P / 2], const __nv_bfloat16* __restrict__ V, const float* psi,
+                                             size_t b, int t0, int h, int S, int H) {
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3;
+  const uint4* v = reinterpret_cast<const uint4*>(V + (((size_t)b * S + t0 + t) * H + h) * P + wg * 32);
+#pragma unroll
+  for (int c = 0; c < P / 16; ++c) {
+    float f[8];
+    unpack8(v[c], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) pv[c * 8 + j] = f[j] * psi[r * P + wg * 32 + c * 8 + j];
+  }
+}
+__device__ __forceinline__ void store_half64(uint8_t* slab, const float (&x)[P / 2], float scale) {
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7;
+#pragma unroll
+  for (int c = 0; c < P / 16; ++c) {
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = x[c * 8 + j] * scale;
+    *reinterpret_cast<uint4*>(slab + sw_off(i, wg * 4 + c)) = pack8(f);
+  }
+}
+
+// Per-head constants staged in shared memory (fp32): Q/K bias [R,N] and the three [R,P] MIMO vectors.
+template <int N>
+struct HeadBias {
+  float qb[R * N];
+  float kb[R * N];
+};
+struct HeadVecs {
+  float psi[R * P];
+  float zeta[R * P];
+  float phi[R * P];
+};
+template <int N>
+__device__ __forceinline__ void load_head_consts(HeadBias<N>* hb, HeadVecs* hv, const float* __restrict__ Qb,
+                                                 const float* __restrict__ Kb, const float* __restrict__ Psi,
+                                                 const float* __restrict__ Zeta, const float* __restrict__ Phi, int h) {
+  for (int x = threadIdx.x; x < R * N; x += blockDim.x) {
+    if (Qb) hb->qb[x] = Qb[(size_t)h * R * N + x];
+    hb->kb[x] = Kb[(size_t)h * R * N + x];
+  }
+  for (int x = threadIdx.x; x < R * P; x += blockDim.x) {
+    hv->psi[x] = Psi[(size_t)h * R * P + x];
+    if (Zeta) hv->zeta[x] = Zeta[(size_t)h * R * P + x];
+    if (Phi) hv->phi[x] = Phi[(size_t)h * R * P + x];
   }
 }
 

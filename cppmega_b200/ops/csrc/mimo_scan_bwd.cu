@@ -81,19 +81,36 @@ __device__ __forceinline__ void load_row_bf16(float (&x)[P], const __nv_bfloat16
   }
 }
 
+// this thread's half row (columns [wg*32, wg*32+32)) of a [.., P] bf16 tensor; `base` points at the row start
+__device__ __forceinline__ void load_half_bf16(float (&x)[P / 2], const __nv_bfloat16* __restrict__ base) {
+  const uint4* v = reinterpret_cast<const uint4*>(base + (threadIdx.x >> 7) * 32);
+#pragma unroll
+  for (int c = 0; c < P / 16; ++c) {
+    float f[8];
+    unpack8(v[c], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[c * 8 + j] = f[j];
+  }
+}
+
+constexpr int NROT_MAX = 32;
+constexpr int THREADS2 = 256;      // two warpgroups: thread (i = tid & 127, wg = tid >> 7) owns half of fused row i
+
 // ------------------------------------------------------------------------------------------
 // grad_state: Gc[n,p] = sum_i Qr[i,n] e^{cs_ti} dO[i,p]
 // ------------------------------------------------------------------------------------------
 template <int N, int NROT>
-__global__ void __launch_bounds__(THREADS) mimo_grad_state_kernel(const __grid_constant__ CUtensorMap tmQ, const BwdArgs a) {
+__global__ void __launch_bounds__(THREADS2) mimo_grad_state_kernel(const __grid_constant__ CUtensorMap tmQ, const BwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int QT = (N / 64) * SLAB;
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + QT;
   float* cos_tab = reinterpret_cast<float*>(sdO + SLAB);
-  float* sin_tab = cos_tab + LT * NROT;
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sin_tab + LT * NROT);
+  float* sin_tab = cos_tab + tab_floats<NROT>();
+  HeadBias<N>* hb = reinterpret_cast<HeadBias<N>*>(sin_tab + tab_floats<NROT>());
+  HeadVecs* hv = reinterpret_cast<HeadVecs*>(hb + 1);
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(hv + 1);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 1);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -101,8 +118,8 @@ __global__ void __launch_bounds__(THREADS) mimo_grad_state_kernel(const __grid_c
   int b, g, c, h;
   decode_block_b(a, b, g, c, h);
   const int t0 = c * LT;
-  const int i = threadIdx.x, t = i >> 2, r = i & 3, warp = i >> 5;
-  if (i == 0) {
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
     *abort_flag = 0;
@@ -113,34 +130,35 @@ __global__ void __launch_bounds__(THREADS) mimo_grad_state_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (i == 0) {
+  if (threadIdx.x == 0) {
     mbar_expect_tx(&bars[0], QT);
 #pragma unroll
     for (int s = 0; s < N / 64; ++s) tma_load_5d_b(sQ + s * SLAB, &tmQ, &bars[0], s * 64, 0, g, t0, b);
   }
   compute_chunk_scalars(sc, a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
-  fill_sincos<NROT>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
+  fill_sincos<NROT, 2>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
+  load_head_consts<N>(hb, hv, a.Qb, a.Qb, a.Phi, a.Zeta, a.Phi, h);
   __syncthreads();
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
   if (ok) {
-    transform_rows<N, NROT>(sQ, a.Qb + (size_t)h * R * N, cos_tab, sin_tab);
+    transform_rows<N, NROT, 2>(sQ, hb->qb, cos_tab, sin_tab);
     const size_t rowoff = (((size_t)b * a.S + t0 + t) * a.H + h) * P;
-    float dy[P], z[P];
-    load_row_bf16(dy, a.dY + rowoff);
-    load_row_bf16(z, a.Z + rowoff);
-    const float* zeta = a.Zeta + ((size_t)h * R + r) * P;
-    const float* phi = a.Phi + ((size_t)h * R + r) * P;
+    float dy[P / 2], z[P / 2];
+    load_half_bf16(dy, a.dY + rowoff);
+    load_half_bf16(z, a.Z + rowoff);
+    const float* zeta = hv->zeta + r * P + wg * 32;
+    const float* phi = hv->phi + r * P + wg * 32;
     const float e = __expf(sc->cs[t]);
 #pragma unroll
-    for (int p = 0; p < P; ++p) {
+    for (int p = 0; p < P / 2; ++p) {
       const float zz = z[p] * zeta[p];
       dy[p] = dy[p] * phi[p] * (zz / (1.f + __expf(-zz)));
     }
-    store_row64(sdO, dy, e);
+    store_half64(sdO, dy, e);
     fence_proxy_async_smem();
   }
   __syncthreads();
-  if (i == 0 && !*abort_flag) {
+  if (threadIdx.x == 0 && !*abort_flag) {
     constexpr uint32_t idesc = umma_idesc_bf16(N, P, true, true);
     const uint32_t aQ = smem_u32(sQ), aO = smem_u32(sdO);
 #pragma unroll
@@ -150,17 +168,14 @@ __global__ void __launch_bounds__(THREADS) mimo_grad_state_kernel(const __grid_c
   ok = mbar_wait(&bars[1], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL);
   tc_fence_after();
   if (ok) {
-    float* dst = a.gbuf + ((((size_t)b * a.H + h) * a.C + c) * N + i) * P;
+    float* dst = a.gbuf + ((((size_t)b * a.H + h) * a.C + c) * N + i) * P + wg * 32;
+    uint32_t rr[32];
+    tmem_ld_32x32(tmem + (uint32_t((warp & 3) * 32) << 16) + wg * 32, rr);
+    tmem_ld_wait();
 #pragma unroll
-    for (int cc = 0; cc < P / 32; ++cc) {
-      uint32_t rr[32];
-      tmem_ld_32x32(tmem + (uint32_t(warp * 32) << 16) + cc * 32, rr);
-      tmem_ld_wait();
-#pragma unroll
-      for (int v = 0; v < 8; ++v)
-        reinterpret_cast<float4*>(dst + cc * 32)[v] = make_float4(__uint_as_float(rr[4 * v]), __uint_as_float(rr[4 * v + 1]),
-                                                                  __uint_as_float(rr[4 * v + 2]), __uint_as_float(rr[4 * v + 3]));
-    }
+    for (int v = 0; v < 8; ++v)
+      reinterpret_cast<float4*>(dst)[v] = make_float4(__uint_as_float(rr[4 * v]), __uint_as_float(rr[4 * v + 1]),
+                                                      __uint_as_float(rr[4 * v + 2]), __uint_as_float(rr[4 * v + 3]));
   }
   tc_fence_before();
   __syncthreads();
@@ -197,15 +212,17 @@ struct GradScratch {
   float dgam[LT];
   float dtot;
   float dD;
-  float par[3][4][R][P];     // per-warp partials of dPsi, dZeta, dPhi
+  float par[3][4][R][P];     // per-lane-quarter partials of dPsi, dZeta, dPhi (each warpgroup fills its own columns)
+  float dang[LT][NROT_MAX];  // K-side d(angle) partials handed from warpgroup 1 to warpgroup 0
 };
 
 template <int N, int NROT>
-__global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_constant__ CUtensorMap tmQ,
-                                                                  const __grid_constant__ CUtensorMap tmK,
-                                                                  const __grid_constant__ CUtensorMap tmS,
-                                                                  const __grid_constant__ CUtensorMap tmE, const BwdArgs a) {
+__global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                      const __grid_constant__ CUtensorMap tmK,
+                                                                      const __grid_constant__ CUtensorMap tmS,
+                                                                      const __grid_constant__ CUtensorMap tmE, const BwdArgs a) {
   static_assert(N == 128, "chunk_grad is written for a 128-wide state");
+  static_assert(NROT <= NROT_MAX && NROT / 8 == R, "rank r writes the r-th group of eight angles");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                    // 32 KB
@@ -218,20 +235,24 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
   uint8_t* sdS = sPm + 2 * SLAB;         // 32 KB
   uint8_t* sPVw = sdS + 2 * SLAB;        // 16 KB
   float* cos_tab = reinterpret_cast<float*>(sPVw + SLAB);
-  float* sin_tab = cos_tab + LT * NROT;
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sin_tab + LT * NROT);
+  float* sin_tab = cos_tab + tab_floats<NROT>();
+  HeadVecs* hv = reinterpret_cast<HeadVecs*>(sin_tab + tab_floats<NROT>());
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(hv + 1);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 1);             // tma, ph1, ph2, ph3
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* colsum = reinterpret_cast<float*>(tmem_slot + 4);          // [4 warps][2][32]
+  float* colsum = reinterpret_cast<float*>(tmem_slot + 4);          // [8 warps][2][16]
+  HeadBias<N>* hb = reinterpret_cast<HeadBias<N>*>(sPm);            // aliases Pm: biases die before phase A writes Pm
   GradScratch* gs = reinterpret_cast<GradScratch*>(sPm);            // aliases Pm: used only after phase 2 has read it
+  static_assert(sizeof(GradScratch) <= 2 * SLAB && sizeof(HeadBias<N>) <= 2 * SLAB, "scratch must fit the Pm tile");
 
   if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
   int b, g, c, h;
   decode_block_b(a, b, g, c, h);
   const int t0 = c * LT;
-  const int i = threadIdx.x, t = i >> 2, r = i & 3, warp = i >> 5, lane = i & 31;
-  if (i == 0) {
+  const int tid = threadIdx.x;
+  const int i = tid & 127, wg = tid >> 7, t = i >> 2, r = i & 3, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
     for (int q = 0; q < 4; ++q) mbar_init(&bars[q], 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -241,12 +262,12 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+  const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
   // phase 1 accumulators                      phase 2 / 3 accumulators
   const uint32_t tS1 = tmem, tdPm = tmem + 128, tO2 = tmem + 256, tX = tmem + 320, tdQb = tmem + 384;
   const uint32_t tO1 = tmem, tdPV1 = tmem + 64, tdQ = tmem + 128, tdK = tmem + 256;
 
-  if (i == 0) {
+  if (tid == 0) {
     mbar_expect_tx(&bars[0], 4 * SLAB + 2 * SLAB);
     for (int s = 0; s < 2; ++s) {
       tma_load_5d_b(sQ + s * SLAB, &tmQ, &bars[0], s * 64, 0, g, t0, b);
@@ -257,12 +278,13 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
     tma_load_2d(sdE, &tmE, &bars[0], 0, srow);
   }
   compute_chunk_scalars(sc, a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
-  fill_sincos<NROT>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
+  fill_sincos<NROT, 2>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
+  load_head_consts<N>(hb, hv, a.Qb, a.Kb, a.Psi, a.Zeta, a.Phi, h);
   __syncthreads();
-  const size_t rowoff = (((size_t)b * a.S + t0 + t) * a.H + h) * P;
-  const float* zeta = a.Zeta + ((size_t)h * R + r) * P;
-  const float* phi = a.Phi + ((size_t)h * R + r) * P;
-  const float* psi = a.Psi + (size_t)h * R * P;
+  const size_t rowoff = (((size_t)b * a.S + t0 + t) * a.H + h) * P + wg * 32;     // this thread's half row
+  const float* zeta = hv->zeta + r * P + wg * 32;
+  const float* phi = hv->phi + r * P + wg * 32;
+  const float* psi = hv->psi + r * P + wg * 32;
   const float csi = sc->cs[t], gi = sc->gam[t], tsi = sc->ts[t], tot = sc->tot;
   const float ei = __expf(csi);
   const float wi = tsi * __expf(tot - csi);
@@ -270,21 +292,21 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
 
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
   if (ok) {
-    transform_rows<N, NROT>(sQ, a.Qb + (size_t)h * R * N, cos_tab, sin_tab);
-    transform_rows<N, NROT>(sK, a.Kb + (size_t)h * R * N, cos_tab, sin_tab);
-    float pv[P];
-    load_pv_row(pv, a.V, psi, b, t0, h, a.S, a.H);
-    store_row64(sPV, pv, 1.f);
-    store_row64(sPVw, pv, wi);
-    float dy[P], z[P];
-    load_row_bf16(dy, a.dY + rowoff);
-    load_row_bf16(z, a.Z + rowoff);
+    transform_rows<N, NROT, 2>(sQ, hb->qb, cos_tab, sin_tab);
+    transform_rows<N, NROT, 2>(sK, hb->kb, cos_tab, sin_tab);
+    float pv[P / 2];
+    load_pv_half(pv, a.V, hv->psi, b, t0, h, a.S, a.H);
+    store_half64(sPV, pv, 1.f);
+    store_half64(sPVw, pv, wi);
+    float dy[P / 2], z[P / 2];
+    load_half_bf16(dy, a.dY + rowoff - wg * 32);
+    load_half_bf16(z, a.Z + rowoff - wg * 32);
 #pragma unroll
-    for (int p = 0; p < P; ++p) {
+    for (int p = 0; p < P / 2; ++p) {
       const float zz = z[p] * zeta[p];
       dy[p] = dy[p] * phi[p] * (zz / (1.f + __expf(-zz)));
     }
-    store_row64(sdO, dy, 1.f);
+    store_half64(sdO, dy, 1.f);
     fence_proxy_async_smem();
   }
   __syncthreads();
@@ -295,7 +317,7 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
   constexpr uint32_t id_64_mm = umma_idesc_bf16(ROWS, P, true, true);
   constexpr uint32_t id_128_km = umma_idesc_bf16(ROWS, 128, false, true);
   constexpr uint32_t id_128_mm = umma_idesc_bf16(ROWS, 128, true, true);
-  if (i == 0 && !*abort_flag) {
+  if (tid == 0 && !*abort_flag) {
 #pragma unroll
     for (int k = 0; k < 8; ++k) umma_f16(tS1, desc_kmajor(aQ, k), desc_kmajor(aK, k), id_128_kk, k != 0);
 #pragma unroll
@@ -308,11 +330,12 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
     for (int k = 0; k < 4; ++k) umma_f16(tdQb, desc_kmajor(adO, k), desc_kmajor(aSt, k), id_128_kk, k != 0);
     umma_commit(&bars[1]);
   }
-  // while the tensor core works: d tot from the state decay, e^{tot} * <dEnd, St> (each thread one state row n = i)
+  // while the tensor core works: d tot from the state decay, e^{tot} * <dEnd, St> (state row n = i, half of its columns)
   float dtot_part = 0.f;
   if (ok) {
 #pragma unroll
-    for (int cidx = 0; cidx < 8; ++cidx) {
+    for (int c2 = 0; c2 < 4; ++c2) {
+      const int cidx = wg * 4 + c2;
       float s8[8], e8[8];
       unpack8(*reinterpret_cast<const uint4*>(sSt + sw_off(i, cidx)), s8);
       unpack8(*reinterpret_cast<const uint4*>(sdE + sw_off(i, cidx)), e8);
@@ -325,11 +348,13 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
   tc_fence_after();
 
   // ---------------- phase A: masks, Pm, dS1, scalar gradients from dM = dPm o S1 ----------------
+  // this warpgroup's key tokens: [16 wg, 16 wg + 16)
   float rowR = 0.f, dgam_i = 0.f;
-  float colC[LT], colT[LT];
+  float colC[LT / 2], colT[LT / 2];
   if (ok) {
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
+    for (int c2 = 0; c2 < 2; ++c2) {
+      const int cc = wg * 2 + c2;
       uint32_t s1[32], dp[32];
       tmem_ld_32x32(tS1 + lane_addr + cc * 32, s1);
       tmem_ld_32x32(tdPm + lane_addr + cc * 32, dp);
@@ -339,7 +364,8 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
         float fp[8], fd[8];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-          const int tj = cc * 8 + q * 2 + u;
+          const int tl = c2 * 8 + q * 2 + u;          // local key-token index, 0..15
+          const int tj = wg * 16 + tl;
           float ex = 0.f, m = 0.f;
           if (tj < t) { ex = __expf(csi - sc->cs[tj]); m = sc->ts[tj] * ex; }
           else if (tj == t) m = gi;
@@ -354,11 +380,11 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
           }
           if (tj < t) {
             rowR += dmsum * m;
-            colC[tj] = dmsum * m;
-            colT[tj] = dmsum * ex;
+            colC[tl] = dmsum * m;
+            colT[tl] = dmsum * ex;
           } else {
-            colC[tj] = 0.f;
-            colT[tj] = 0.f;
+            colC[tl] = 0.f;
+            colT[tl] = 0.f;
             if (tj == t) dgam_i += dmsum;
           }
         }
@@ -371,7 +397,7 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
   }
   tc_fence_before();
   __syncthreads();
-  if (i == 0 && !*abort_flag) {
+  if (tid == 0 && !*abort_flag) {
     tc_fence_after();
 #pragma unroll
     for (int k = 0; k < 8; ++k) umma_f16(tO1, desc_kmajor(aPm, k), desc_mnmajor_rows(aPV, k), id_64_km, k != 0);
@@ -384,113 +410,106 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
   // column sums over the rows of this warp while phase 2 runs
   if (ok) {
 #pragma unroll
-    for (int tj = 0; tj < LT; ++tj) {
-      const float c_ = warp_sum(colC[tj]);
-      const float t_ = warp_sum(colT[tj]);
-      if (lane == tj) { colsum[(warp * 2 + 0) * LT + tj] = c_; colsum[(warp * 2 + 1) * LT + tj] = t_; }
+    for (int tl = 0; tl < LT / 2; ++tl) {
+      const float c_ = warp_sum(colC[tl]);
+      const float t_ = warp_sum(colT[tl]);
+      if (lane == tl) { colsum[(warp * 2 + 0) * (LT / 2) + tl] = c_; colsum[(warp * 2 + 1) * (LT / 2) + tl] = t_; }
     }
   }
   ok = __syncthreads_and(mbar_wait(&bars[2], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
   tc_fence_after();
   // Pm has been consumed by phase 2: its space becomes the reduction scratch
-  if (i < LT) { gs->dcs[i] = 0.f; gs->dts[i] = 0.f; gs->dgam[i] = 0.f; }
-  if (i == 0) { gs->dtot = 0.f; gs->dD = 0.f; }
+  if (tid < LT) { gs->dcs[tid] = 0.f; gs->dts[tid] = 0.f; gs->dgam[tid] = 0.f; }
+  if (tid == 0) { gs->dtot = 0.f; gs->dD = 0.f; }
   __syncthreads();
 
-  // ---------------- epilogue B: gating gradients, dPV, dw, de ----------------
+  // ---------------- epilogue B: gating gradients, dPV, dw, de (this warpgroup's 32 columns) ----------------
   float dw_i = 0.f, de_i = 0.f;
   if (ok) {
     const uint4* vrow = reinterpret_cast<const uint4*>(a.V + rowoff);
     const uint4* yrow = reinterpret_cast<const uint4*>(a.dY + rowoff);
     const uint4* zrow = reinterpret_cast<const uint4*>(a.Z + rowoff);
+    const int wq = warp & 3;
     float dD_part = 0.f;
-#pragma unroll 1
-    for (int cc = 0; cc < 2; ++cc) {
-      float dvrow[32];
-      {   // pass 1: O = O1 + e O2 + D PV  ->  dPhi, dZeta, dZ, de, dD and the D dO part of dPV
-        uint32_t o1[32], o2[32];
-        tmem_ld_32x32(tO1 + lane_addr + cc * 32, o1);
-        tmem_ld_32x32(tO2 + lane_addr + cc * 32, o2);
-        tmem_ld_wait();
-        float dzrow[32];
+    float dvrow[32];
+    {   // pass 1: O = O1 + e O2 + D PV  ->  dPhi, dZeta, dZ, de, dD and the D dO part of dPV
+      uint32_t o1[32], o2[32];
+      tmem_ld_32x32(tO1 + lane_addr + wg * 32, o1);
+      tmem_ld_32x32(tO2 + lane_addr + wg * 32, o2);
+      tmem_ld_wait();
+      float mz[8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          float vf[8], yf[8], zf[8];
-          unpack8(vrow[cc * 4 + q], vf);
-          unpack8(yrow[cc * 4 + q], yf);
-          unpack8(zrow[cc * 4 + q], zf);
+      for (int q = 0; q < 4; ++q) {
+        float vf[8], yf[8], zf[8];
+        unpack8(vrow[q], vf);
+        unpack8(yrow[q], yf);
+        unpack8(zrow[q], zf);
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const int p = cc * 32 + q * 8 + v;
-            const int e = q * 8 + v;
-            const float pvv = vf[v] * psi[r * P + p];
-            const float o2v = __uint_as_float(o2[e]);
-            const float o = __uint_as_float(o1[e]) + ei * o2v + dsk * pvv;
-            const float zz = zf[v] * zeta[p];
-            const float sg = 1.f / (1.f + __expf(-zz));
-            const float sil = zz * sg;
-            const float dO = yf[v] * phi[p] * sil;
-            const float dgate = yf[v] * o;
-            const float dzz = dgate * phi[p] * sg * (1.f + zz * (1.f - sg));
-            float pphi = dgate * sil, pzeta = dzz * zf[v], ppsi = dsk * dO * vf[v];
-            de_i += dO * o2v;
-            dD_part += dO * pvv;
-            dzrow[e] = dzz * zeta[p];
-            dvrow[e] = dsk * dO * psi[r * P + p];
+        for (int v = 0; v < 8; ++v) {
+          const int e = q * 8 + v;
+          const float pvv = vf[v] * psi[e];
+          const float o2v = __uint_as_float(o2[e]);
+          const float o = __uint_as_float(o1[e]) + ei * o2v + dsk * pvv;
+          const float zz = zf[v] * zeta[e];
+          const float sg = 1.f / (1.f + __expf(-zz));
+          const float sil = zz * sg;
+          const float dO = yf[v] * phi[e] * sil;
+          const float dgate = yf[v] * o;
+          const float dzz = dgate * phi[e] * sg * (1.f + zz * (1.f - sg));
+          float pphi = dgate * sil, pzeta = dzz * zf[v], ppsi = dsk * dO * vf[v];
+          de_i += dO * o2v;
+          dD_part += dO * pvv;
+          float dzv = dzz * zeta[e];
+          dvrow[e] = dsk * dO * psi[e];
 #pragma unroll
-            for (int o_ = 4; o_ < 32; o_ <<= 1) {
-              pphi += __shfl_xor_sync(0xffffffffu, pphi, o_);
-              pzeta += __shfl_xor_sync(0xffffffffu, pzeta, o_);
-              ppsi += __shfl_xor_sync(0xffffffffu, ppsi, o_);
-            }
-            if (lane < 4) {
-              gs->par[0][warp][r][p] = ppsi;
-              gs->par[1][warp][r][p] = pzeta;
-              gs->par[2][warp][r][p] = pphi;
-            }
-            dzrow[e] += __shfl_xor_sync(0xffffffffu, dzrow[e], 1);
-            dzrow[e] += __shfl_xor_sync(0xffffffffu, dzrow[e], 2);
+          for (int o_ = 4; o_ < 32; o_ <<= 1) {
+            pphi += __shfl_xor_sync(0xffffffffu, pphi, o_);
+            pzeta += __shfl_xor_sync(0xffffffffu, pzeta, o_);
+            ppsi += __shfl_xor_sync(0xffffffffu, ppsi, o_);
           }
-        }
-        float mz[8];
-#pragma unroll
-        for (int v = 0; v < 8; ++v) mz[v] = r == 0 ? dzrow[v] : r == 1 ? dzrow[8 + v] : r == 2 ? dzrow[16 + v] : dzrow[24 + v];
-        *reinterpret_cast<uint4*>(a.dZ + rowoff + cc * 32 + r * 8) = pack8(mz);
-      }
-      {   // pass 2: dPV = dPV1 + w X (+ D dO from pass 1)  ->  dV, dPsi, dw
-        uint32_t d1[32], xx[32];
-        tmem_ld_32x32(tdPV1 + lane_addr + cc * 32, d1);
-        tmem_ld_32x32(tX + lane_addr + cc * 32, xx);
-        tmem_ld_wait();
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          float vf[8];
-          unpack8(vrow[cc * 4 + q], vf);
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const int p = cc * 32 + q * 8 + v;
-            const int e = q * 8 + v;
-            const float xv = __uint_as_float(xx[e]);
-            const float dpv = __uint_as_float(d1[e]) + wi * xv;
-            dw_i += vf[v] * psi[r * P + p] * xv;
-            float ppsi = dpv * vf[v];
-            dvrow[e] += dpv * psi[r * P + p];
-#pragma unroll
-            for (int o_ = 4; o_ < 32; o_ <<= 1) ppsi += __shfl_xor_sync(0xffffffffu, ppsi, o_);
-            if (lane < 4) gs->par[0][warp][r][p] += ppsi;
-            dvrow[e] += __shfl_xor_sync(0xffffffffu, dvrow[e], 1);
-            dvrow[e] += __shfl_xor_sync(0xffffffffu, dvrow[e], 2);
+          if (lane < 4) {
+            gs->par[0][wq][r][wg * 32 + e] = ppsi;
+            gs->par[1][wq][r][wg * 32 + e] = pzeta;
+            gs->par[2][wq][r][wg * 32 + e] = pphi;
           }
+          dzv += __shfl_xor_sync(0xffffffffu, dzv, 1);
+          dzv += __shfl_xor_sync(0xffffffffu, dzv, 2);
+          if (q == r) mz[v] = dzv;
         }
-        float mv[8];
-#pragma unroll
-        for (int v = 0; v < 8; ++v) mv[v] = r == 0 ? dvrow[v] : r == 1 ? dvrow[8 + v] : r == 2 ? dvrow[16 + v] : dvrow[24 + v];
-        *reinterpret_cast<uint4*>(a.dV + rowoff + cc * 32 + r * 8) = pack8(mv);
       }
+      *reinterpret_cast<uint4*>(a.dZ + rowoff + r * 8) = pack8(mz);
+    }
+    {   // pass 2: dPV = dPV1 + w X (+ D dO from pass 1)  ->  dV, dPsi, dw
+      uint32_t d1[32], xx[32];
+      tmem_ld_32x32(tdPV1 + lane_addr + wg * 32, d1);
+      tmem_ld_32x32(tX + lane_addr + wg * 32, xx);
+      tmem_ld_wait();
+      float mv[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float vf[8];
+        unpack8(vrow[q], vf);
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const int e = q * 8 + v;
+          const float xv = __uint_as_float(xx[e]);
+          const float dpv = __uint_as_float(d1[e]) + wi * xv;
+          dw_i += vf[v] * psi[e] * xv;
+          float ppsi = dpv * vf[v];
+          float dvv = dvrow[e] + dpv * psi[e];
+#pragma unroll
+          for (int o_ = 4; o_ < 32; o_ <<= 1) ppsi += __shfl_xor_sync(0xffffffffu, ppsi, o_);
+          if (lane < 4) gs->par[0][wq][r][wg * 32 + e] += ppsi;
+          dvv += __shfl_xor_sync(0xffffffffu, dvv, 1);
+          dvv += __shfl_xor_sync(0xffffffffu, dvv, 2);
+          if (q == r) mv[v] = dvv;
+        }
+      }
+      *reinterpret_cast<uint4*>(a.dV + rowoff + r * 8) = pack8(mv);
     }
     dD_part = warp_sum(dD_part);
     if (lane == 0) atomicAdd(&gs->dD, dD_part);
-    // per-token scalar gradients
+    // per-token scalar gradients (each warpgroup adds the part that comes from its columns)
     //   cs_ti:  + rowR + e_i de_i - w_i dw_i         ts_ti: + dw_i e^{tot-cs_ti}       gamma_ti: + dgam_i
     const float ewi = __expf(tot - csi);
     float dcs_row = rowR + ei * de_i - wi * dw_i;
@@ -507,14 +526,16 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
       atomicAdd(&gs->dgam[t], dgm_row);
     }
     if (lane == 0) atomicAdd(&gs->dtot, dtot_row);
-    // column sums from phase A: lane tj of every warp adds its key token's totals
-    atomicAdd(&gs->dcs[lane], -colsum[(warp * 2 + 0) * LT + lane]);
-    atomicAdd(&gs->dts[lane], colsum[(warp * 2 + 1) * LT + lane]);
+    // column sums from phase A: lane tl of every warp adds the totals of key token 16 wg + tl
+    if (lane < LT / 2) {
+      atomicAdd(&gs->dcs[wg * 16 + lane], -colsum[(warp * 2 + 0) * (LT / 2) + lane]);
+      atomicAdd(&gs->dts[wg * 16 + lane], colsum[(warp * 2 + 1) * (LT / 2) + lane]);
+    }
   }
   tc_fence_before();
   __syncthreads();
   // ---------------- phase 3: dK ----------------
-  if (i == 0 && !*abort_flag) {
+  if (tid == 0 && !*abort_flag) {
     tc_fence_after();
 #pragma unroll
     for (int k = 0; k < 8; ++k) umma_f16(tdK, desc_mnmajor_2slab(adS, k), desc_mnmajor_2slab(aQ, k), id_128_mm, k != 0);
@@ -537,7 +558,8 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
       a.dTs[sb] = gs->dts[lane];
       a.dGam[sb] = gs->dgam[lane];
     }
-    for (int e = i; e < R * P; e += THREADS) {
+    {
+      const int e = tid;                                   // R * P == 256 == THREADS2
       const int rr = e / P, pp = e % P;
       float s0 = 0.f, s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -546,80 +568,81 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
       atomicAdd(a.dZeta + (size_t)h * R * P + e, s1);
       atomicAdd(a.dPhi + (size_t)h * R * P + e, s2);
     }
-    if (i == 0) atomicAdd(a.dD + h, gs->dD);
+    if (tid == 0) atomicAdd(a.dD + h, gs->dD);
   }
   ok = __syncthreads_and(mbar_wait(&bars[3], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
   tc_fence_after();
-  // ---------------- epilogue C: dQr = dQ + e dQb, dKr; inverse rotation; d(angles) ----------------
+  // ---------------- epilogue C: dQr = dQ + e dQb (warpgroup 0), dKr (warpgroup 1); inverse rotation; d(angles) ----
+  float dang[NROT / 8][8];
   if (ok) {
     constexpr int HALF = N / 2;
-    float dang[NROT / 8][8];
 #pragma unroll
     for (int x = 0; x < NROT / 8; ++x)
 #pragma unroll
       for (int j = 0; j < 8; ++j) dang[x][j] = 0.f;
-    __nv_bfloat16* dqrow = a.dQh + ((((size_t)b * a.S + t0 + t) * a.H + h) * R + r) * N;
-    __nv_bfloat16* dkrow = a.dKh + ((((size_t)b * a.S + t0 + t) * a.H + h) * R + r) * N;
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {           // 0: Q, 1: K
-      const uint8_t* tile = which == 0 ? sQ : sK;        // rotated operand rows (bf16) for d(angle)
-      __nv_bfloat16* drow = which == 0 ? dqrow : dkrow;
-      // columns [0,32) pair with [64,96); [32,64) and [96,128) are not rotated
-      uint32_t lo[32], hi[32], lob[32], hib[32];
-      if (which == 0) {
-        tmem_ld_32x32(tdQ + lane_addr + 0, lo);
-        tmem_ld_32x32(tdQ + lane_addr + HALF, hi);
-        tmem_ld_32x32(tdQb + lane_addr + 0, lob);
-        tmem_ld_32x32(tdQb + lane_addr + HALF, hib);
-      } else {
-        tmem_ld_32x32(tdK + lane_addr + 0, lo);
-        tmem_ld_32x32(tdK + lane_addr + HALF, hi);
-      }
+    const bool isq = wg == 0;
+    const uint8_t* tile = isq ? sQ : sK;                 // rotated operand rows (bf16) for d(angle)
+    __nv_bfloat16* drow = (isq ? a.dQh : a.dKh) + ((((size_t)b * a.S + t0 + t) * a.H + h) * R + r) * N;
+    const uint32_t tacc = isq ? tdQ : tdK;
+    // columns [0,32) pair with [64,96); [32,64) and [96,128) are not rotated
+    uint32_t lo[32], hi[32];
+    tmem_ld_32x32(tacc + lane_addr + 0, lo);
+    tmem_ld_32x32(tacc + lane_addr + HALF, hi);
+    tmem_ld_wait();
+    if (isq) {
+      uint32_t lob[32], hib[32];
+      tmem_ld_32x32(tdQb + lane_addr + 0, lob);
+      tmem_ld_32x32(tdQb + lane_addr + HALF, hib);
       tmem_ld_wait();
 #pragma unroll
-      for (int x = 0; x < NROT / 8; ++x) {
-        float xa[8], xb[8], ga[8], gb[8];
-        unpack8(*reinterpret_cast<const uint4*>(tile + sw_off(i, x)), xa);                 // rotated values, cols 8x..
-        unpack8(*reinterpret_cast<const uint4*>(tile + SLAB + sw_off(i, x)), xb);          // cols 64+8x..
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float da = __uint_as_float(lo[x * 8 + j]), db = __uint_as_float(hi[x * 8 + j]);
-          if (which == 0) { da += ei * __uint_as_float(lob[x * 8 + j]); db += ei * __uint_as_float(hib[x * 8 + j]); }
-          const float cs_ = cos_tab[t * NROT + x * 8 + j], sn_ = sin_tab[t * NROT + x * 8 + j];
-          dang[x][j] += db * xa[j] - da * xb[j];
-          ga[j] = cs_ * da + sn_ * db;
-          gb[j] = -sn_ * da + cs_ * db;
-        }
-        *reinterpret_cast<uint4*>(drow + x * 8) = pack8(ga);
-        *reinterpret_cast<uint4*>(drow + HALF + x * 8) = pack8(gb);
-      }
-      // un-rotated halves
-      uint32_t lo2[32], hi2[32], lob2[32], hib2[32];
-      if (which == 0) {
-        tmem_ld_32x32(tdQ + lane_addr + NROT, lo2);
-        tmem_ld_32x32(tdQ + lane_addr + HALF + NROT, hi2);
-        tmem_ld_32x32(tdQb + lane_addr + NROT, lob2);
-        tmem_ld_32x32(tdQb + lane_addr + HALF + NROT, hib2);
-      } else {
-        tmem_ld_32x32(tdK + lane_addr + NROT, lo2);
-        tmem_ld_32x32(tdK + lane_addr + HALF + NROT, hi2);
-      }
-      tmem_ld_wait();
-#pragma unroll
-      for (int x = 0; x < (HALF - NROT) / 8; ++x) {
-        float ga[8], gb[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          ga[j] = __uint_as_float(lo2[x * 8 + j]);
-          gb[j] = __uint_as_float(hi2[x * 8 + j]);
-          if (which == 0) { ga[j] += ei * __uint_as_float(lob2[x * 8 + j]); gb[j] += ei * __uint_as_float(hib2[x * 8 + j]); }
-        }
-        *reinterpret_cast<uint4*>(drow + NROT + x * 8) = pack8(ga);
-        *reinterpret_cast<uint4*>(drow + HALF + NROT + x * 8) = pack8(gb);
+      for (int e = 0; e < 32; ++e) {
+        lo[e] = __float_as_uint(__uint_as_float(lo[e]) + ei * __uint_as_float(lob[e]));
+        hi[e] = __float_as_uint(__uint_as_float(hi[e]) + ei * __uint_as_float(hib[e]));
       }
     }
-    // d(angle)[t, a] = sum over the four ranks
-    float* darow = a.dAngles + (((size_t)b * a.S + t0 + t) * a.H + h) * NROT;
+#pragma unroll
+    for (int x = 0; x < NROT / 8; ++x) {
+      float xa[8], xb[8], ga[8], gb[8];
+      unpack8(*reinterpret_cast<const uint4*>(tile + sw_off(i, x)), xa);                 // rotated values, cols 8x..
+      unpack8(*reinterpret_cast<const uint4*>(tile + SLAB + sw_off(i, x)), xb);          // cols 64+8x..
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float da = __uint_as_float(lo[x * 8 + j]), db = __uint_as_float(hi[x * 8 + j]);
+        const float cs_ = cos_tab[t * tab_stride<NROT>() + x * 8 + j], sn_ = sin_tab[t * tab_stride<NROT>() + x * 8 + j];
+        dang[x][j] += db * xa[j] - da * xb[j];
+        ga[j] = cs_ * da + sn_ * db;
+        gb[j] = -sn_ * da + cs_ * db;
+      }
+      *reinterpret_cast<uint4*>(drow + x * 8) = pack8(ga);
+      *reinterpret_cast<uint4*>(drow + HALF + x * 8) = pack8(gb);
+    }
+    // un-rotated halves
+    tmem_ld_32x32(tacc + lane_addr + NROT, lo);
+    tmem_ld_32x32(tacc + lane_addr + HALF + NROT, hi);
+    tmem_ld_wait();
+    if (isq) {
+      uint32_t lob[32], hib[32];
+      tmem_ld_32x32(tdQb + lane_addr + NROT, lob);
+      tmem_ld_32x32(tdQb + lane_addr + HALF + NROT, hib);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        lo[e] = __float_as_uint(__uint_as_float(lo[e]) + ei * __uint_as_float(lob[e]));
+        hi[e] = __float_as_uint(__uint_as_float(hi[e]) + ei * __uint_as_float(hib[e]));
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < (HALF - NROT) / 8; ++x) {
+      float ga[8], gb[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        ga[j] = __uint_as_float(lo[x * 8 + j]);
+        gb[j] = __uint_as_float(hi[x * 8 + j]);
+      }
+      *reinterpret_cast<uint4*>(drow + NROT + x * 8) = pack8(ga);
+      *reinterpret_cast<uint4*>(drow + HALF + NROT + x * 8) = pack8(gb);
+    }
+    // sum over the four ranks; warpgroup 1 (K side) hands its part over through shared memory
 #pragma unroll
     for (int x = 0; x < NROT / 8; ++x) {
 #pragma unroll
@@ -629,19 +652,36 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_grad_kernel(const __grid_c
         v += __shfl_xor_sync(0xffffffffu, v, 2);
         dang[x][j] = v;
       }
-      if (x == r) {       // NROT/8 == 4 == R: rank r writes the r-th group of 8 angles
-        reinterpret_cast<float4*>(darow + x * 8)[0] = make_float4(dang[x][0], dang[x][1], dang[x][2], dang[x][3]);
-        reinterpret_cast<float4*>(darow + x * 8)[1] = make_float4(dang[x][4], dang[x][5], dang[x][6], dang[x][7]);
+      if (!isq && x == r) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gs->dang[t][x * 8 + j] = dang[x][j];
       }
     }
   }
   tc_fence_before();
   __syncthreads();
+  if (ok && wg == 0) {
+    float* darow = a.dAngles + (((size_t)b * a.S + t0 + t) * a.H + h) * NROT;
+#pragma unroll
+    for (int x = 0; x < NROT / 8; ++x) {
+      if (x == r) {       // NROT/8 == 4 == R: rank r writes the r-th group of 8 angles
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = dang[x][j] + gs->dang[t][x * 8 + j];
+        reinterpret_cast<float4*>(darow + x * 8)[0] = make_float4(o[0], o[1], o[2], o[3]);
+        reinterpret_cast<float4*>(darow + x * 8)[1] = make_float4(o[4], o[5], o[6], o[7]);
+      }
+    }
+  }
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
-constexpr int grad_state_smem() { return 2 * SLAB + SLAB + 2 * LT * 32 * 4 + (int)sizeof(ChunkScalars) + 64 + 1024; }
-constexpr int chunk_grad_smem() { return 13 * SLAB + 2 * LT * 32 * 4 + (int)sizeof(ChunkScalars) + 64 + 1024 + 1024; }
+constexpr int grad_state_smem() {
+  return 2 * SLAB + SLAB + 2 * tab_floats<32>() * 4 + (int)sizeof(HeadBias<128>) + (int)sizeof(HeadVecs) + (int)sizeof(ChunkScalars) + 64 + 1024;
+}
+constexpr int chunk_grad_smem() {
+  return 13 * SLAB + 2 * tab_floats<32>() * 4 + (int)sizeof(HeadVecs) + (int)sizeof(ChunkScalars) + 64 + 1024 + 1024;
+}
 
 }  // namespace mimo
 }  // namespace cm
@@ -685,9 +725,9 @@ extern "C" int cm_mimo_scan_bwd(const void* Qn, const void* Kn, const void* V, c
     cfg = true;
   }
   const int grid = B * H * C;
-  k0<<<grid, THREADS, grad_state_smem(), stream>>>(tmQ, a);
+  k0<<<grid, THREADS2, grad_state_smem(), stream>>>(tmQ, a);
   dim3 g2(B * H, (128 * P + 1023) / 1024);
   mimo_state_scan_rev_kernel<<<g2, 256, 0, stream>>>(gbuf, tot, (__nv_bfloat16*)dend, C, 128 * P);
-  k2<<<grid, THREADS, chunk_grad_smem(), stream>>>(tmQ, tmK, tmS, tmE, a);
+  k2<<<grid, THREADS2, chunk_grad_smem(), stream>>>(tmQ, tmK, tmS, tmE, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

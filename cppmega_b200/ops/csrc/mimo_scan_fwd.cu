@@ -75,17 +75,22 @@ __device__ __forceinline__ void decode_block(const FwdArgs& a, int& b, int& g, i
 
 // ------------------------------------------------------------------------------------------
 // local_state: Lc[n,p] = sum_j Kr[j,n] * w_j * PV[j,p]
+// 256 threads: thread (i = tid & 127, wg = tid >> 7) owns fused row i and half of its columns.
 // ------------------------------------------------------------------------------------------
+constexpr int THREADS2 = 256;
+
 template <int N, int NROT>
-__global__ void __launch_bounds__(THREADS) mimo_local_state_kernel(const __grid_constant__ CUtensorMap tmK, const FwdArgs a) {
+__global__ void __launch_bounds__(THREADS2) mimo_local_state_kernel(const __grid_constant__ CUtensorMap tmK, const FwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int KT = (N / 64) * SLAB;
   uint8_t* sK = smem;
   uint8_t* sPVw = sK + KT;
   float* cos_tab = reinterpret_cast<float*>(sPVw + SLAB);
-  float* sin_tab = cos_tab + LT * NROT;
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sin_tab + LT * NROT);
+  float* sin_tab = cos_tab + tab_floats<NROT>();
+  HeadBias<N>* hb = reinterpret_cast<HeadBias<N>*>(sin_tab + tab_floats<NROT>());
+  HeadVecs* hv = reinterpret_cast<HeadVecs*>(hb + 1);
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(hv + 1);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 1);            // [0] tma, [1] mma
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -94,7 +99,7 @@ __global__ void __launch_bounds__(THREADS) mimo_local_state_kernel(const __grid_
   int b, g, c, h;
   decode_block(a, b, g, c, h);
   const int t0 = c * LT;
-  const int warp = threadIdx.x >> 5;
+  const int warp = threadIdx.x >> 5, i = threadIdx.x & 127, wg = threadIdx.x >> 7;
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -112,15 +117,16 @@ __global__ void __launch_bounds__(THREADS) mimo_local_state_kernel(const __grid_
     for (int s = 0; s < N / 64; ++s) tma_load_5d(sK + s * SLAB, &tmK, &bars[0], s * 64, 0, g, t0, b);
   }
   compute_chunk_scalars(sc, a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
-  fill_sincos<NROT>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
+  fill_sincos<NROT, 2>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
+  load_head_consts<N>(hb, hv, nullptr, a.Kb, a.Psi, nullptr, nullptr, h);
   __syncthreads();
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
   if (ok) {
-    transform_rows<N, NROT>(sK, a.Kb + (size_t)h * R * N, cos_tab, sin_tab);
-    float pv[P];
-    load_pv_row(pv, a.V, a.Psi + (size_t)h * R * P, b, t0, h, a.S, a.H);
-    const int t = threadIdx.x >> 2;
-    store_row64(sPVw, pv, sc->ts[t] * __expf(sc->tot - sc->cs[t]));
+    transform_rows<N, NROT, 2>(sK, hb->kb, cos_tab, sin_tab);
+    float pv[P / 2];
+    load_pv_half(pv, a.V, hv->psi, b, t0, h, a.S, a.H);
+    const int t = i >> 2;
+    store_half64(sPVw, pv, sc->ts[t] * __expf(sc->tot - sc->cs[t]));
     fence_proxy_async_smem();
   }
   __syncthreads();
@@ -134,18 +140,15 @@ __global__ void __launch_bounds__(THREADS) mimo_local_state_kernel(const __grid_
   }
   ok = mbar_wait(&bars[1], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL);
   tc_fence_after();
-  if (ok && threadIdx.x < N) {
-    float* dst = a.local + ((((size_t)b * a.H + h) * a.C + c) * N + threadIdx.x) * P;
+  if (ok) {
+    float* dst = a.local + ((((size_t)b * a.H + h) * a.C + c) * N + i) * P + wg * 32;
+    uint32_t r[32];
+    tmem_ld_32x32(tmem + (uint32_t((warp & 3) * 32) << 16) + wg * 32, r);
+    tmem_ld_wait();
 #pragma unroll
-    for (int cc = 0; cc < P / 32; ++cc) {
-      uint32_t r[32];
-      tmem_ld_32x32(tmem + (uint32_t(warp * 32) << 16) + cc * 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int v = 0; v < 8; ++v)
-        reinterpret_cast<float4*>(dst + cc * 32)[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                                                  __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-    }
+    for (int v = 0; v < 8; ++v)
+      reinterpret_cast<float4*>(dst)[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                      __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
   }
   if (threadIdx.x == 0) a.tot[((size_t)b * a.H + h) * a.C + c] = sc->tot;
   tc_fence_before();
@@ -182,12 +185,12 @@ __global__ void __launch_bounds__(256) mimo_state_scan_kernel(const float* __res
 }
 
 // ------------------------------------------------------------------------------------------
-// chunk_out
+// chunk_out (256 threads, two warpgroups splitting the columns of every row-wise phase)
 // ------------------------------------------------------------------------------------------
 template <int N, int NROT>
-__global__ void __launch_bounds__(THREADS) mimo_chunk_out_kernel(const __grid_constant__ CUtensorMap tmQ,
-                                                                 const __grid_constant__ CUtensorMap tmK,
-                                                                 const __grid_constant__ CUtensorMap tmS, const FwdArgs a) {
+__global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                     const __grid_constant__ CUtensorMap tmK,
+                                                                     const __grid_constant__ CUtensorMap tmS, const FwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int QT = (N / 64) * SLAB;            // Q tile bytes (also K tile bytes)
@@ -198,19 +201,23 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_out_kernel(const __grid_co
   uint8_t* sPV = sK + QT;
   uint8_t* sSt = sPV + SLAB;                     // start state [N x 64] bf16
   float* cos_tab = reinterpret_cast<float*>(sSt + (N / 128 > 0 ? N : 128) * 128);
-  float* sin_tab = cos_tab + LT * NROT;
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sin_tab + LT * NROT);
+  float* sin_tab = cos_tab + tab_floats<NROT>();
+  HeadBias<N>* hb = reinterpret_cast<HeadBias<N>*>(sPV);      // biases die before PV is written (barrier between)
+  static_assert(sizeof(HeadBias<N>) <= SLAB, "bias block must fit the PV slab it borrows");
+  HeadVecs* hv = reinterpret_cast<HeadVecs*>(sin_tab + tab_floats<NROT>());
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(hv + 1);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 1);            // [0] tma, [1] S1+O2, [2] O1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
+  CM_STAMP(0);
   int b, g, c, h;
   decode_block(a, b, g, c, h);
   const int t0 = c * LT;
-  const int i = threadIdx.x, t = i >> 2, r = i & 3;
-  const int warp = i >> 5;
-  if (i == 0) {
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
     mbar_init(&bars[2], 1);
@@ -221,9 +228,10 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_out_kernel(const __grid_co
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  CM_STAMP(1);
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS1 = tmem, tO2 = tmem + 128, tO1 = tmem + 192;
-  if (i == 0) {
+  if (threadIdx.x == 0) {
     mbar_expect_tx(&bars[0], 2 * QT + N * 128);
 #pragma unroll
     for (int s = 0; s < N / 64; ++s) {
@@ -233,19 +241,32 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_out_kernel(const __grid_co
     tma_load_2d(sSt, &tmS, &bars[0], 0, (int)((((size_t)b * a.H + h) * a.C + c) * N));
   }
   compute_chunk_scalars(sc, a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
-  fill_sincos<NROT>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
+  fill_sincos<NROT, 2>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
+  load_head_consts<N>(hb, hv, a.Qb, a.Kb, a.Psi, a.Zeta, a.Phi, h);
+  // this thread's gate inputs, fetched early so the latency hides behind the products
+  const uint4* zrow = reinterpret_cast<const uint4*>(a.Z + (((size_t)b * a.S + t0 + t) * a.H + h) * P + wg * 32);
+  uint4 zraw[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) zraw[q] = zrow[q];
+  const float dsk = a.Dskip[h];
   __syncthreads();
+  CM_STAMP(2);
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
-  float pv[P];
+  CM_STAMP(3);
+  float pv[P / 2];
   if (ok) {
-    transform_rows<N, NROT>(sQ, a.Qb + (size_t)h * R * N, cos_tab, sin_tab);
-    transform_rows<N, NROT>(sK, a.Kb + (size_t)h * R * N, cos_tab, sin_tab);
-    load_pv_row(pv, a.V, a.Psi + (size_t)h * R * P, b, t0, h, a.S, a.H);
-    store_row64(sPV, pv, 1.f);
+    transform_rows<N, NROT, 2>(sQ, hb->qb, cos_tab, sin_tab);
+    transform_rows<N, NROT, 2>(sK, hb->kb, cos_tab, sin_tab);
+    load_pv_half(pv, a.V, hv->psi, b, t0, h, a.S, a.H);
+  }
+  CM_STAMP(4);
+  __syncthreads();                               // every thread is done with the biases stored in the PV slab
+  if (ok) {
+    store_half64(sPV, pv, 1.f);
     fence_proxy_async_smem();
   }
   __syncthreads();
-  if (i == 0 && !*abort_flag) {
+  if (threadIdx.x == 0 && !*abort_flag) {
     constexpr uint32_t id_s1 = umma_idesc_bf16(ROWS, ROWS, false, false);
     constexpr uint32_t id_o = umma_idesc_bf16(ROWS, P, false, true);
     const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aSt = smem_u32(sSt);
@@ -255,14 +276,17 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_out_kernel(const __grid_co
     for (int k = 0; k < N / 16; ++k) umma_f16(tO2, desc_kmajor(aQ, k), desc_mnmajor_rows(aSt, k), id_o, k != 0);
     umma_commit(&bars[1]);
   }
+  CM_STAMP(5);
   ok = mbar_wait(&bars[1], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL);
   tc_fence_after();
+  CM_STAMP(6);
+  const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
   if (ok) {
     // mask the scores of this row and store them as the A operand of the second product
     const float csi = sc->cs[t], gi = sc->gam[t];
-    const uint32_t lane_addr = uint32_t(warp * 32) << 16;
-#pragma unroll 1
-    for (int cc = 0; cc < 4; ++cc) {            // 32 columns = 8 key tokens per pass
+#pragma unroll
+    for (int c2 = 0; c2 < 2; ++c2) {            // 32 columns = 8 key tokens per pass; this warpgroup's two passes
+      const int cc = wg * 2 + c2;
       uint32_t rr[32];
       tmem_ld_32x32(tS1 + lane_addr + cc * 32, rr);
       tmem_ld_wait();
@@ -286,7 +310,7 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_out_kernel(const __grid_co
   }
   tc_fence_before();
   __syncthreads();
-  if (i == 0 && !*abort_flag) {
+  if (threadIdx.x == 0 && !*abort_flag) {
     tc_fence_after();
     constexpr uint32_t id_o = umma_idesc_bf16(ROWS, P, false, true);
     const uint32_t aPm = smem_u32(sQ), aPV = smem_u32(sPV);
@@ -294,57 +318,53 @@ __global__ void __launch_bounds__(THREADS) mimo_chunk_out_kernel(const __grid_co
     for (int k = 0; k < ROWS / 16; ++k) umma_f16(tO1, desc_kmajor(aPm, k), desc_mnmajor_rows(aPV, k), id_o, k != 0);
     umma_commit(&bars[2]);
   }
+  CM_STAMP(7);
   ok = mbar_wait(&bars[2], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL);
   tc_fence_after();
+  CM_STAMP(8);
   if (ok) {
     const float ecs = __expf(sc->cs[t]);
-    const float dsk = a.Dskip[h];
-    const uint32_t lane_addr = uint32_t(warp * 32) << 16;
-    const uint4* zrow = reinterpret_cast<const uint4*>(a.Z + (((size_t)b * a.S + t0 + t) * a.H + h) * P);
-    const float* zeta = a.Zeta + ((size_t)h * R + r) * P;
-    const float* phi = a.Phi + ((size_t)h * R + r) * P;
-    __nv_bfloat16* yrow = a.y + (((size_t)b * a.S + t0 + t) * a.H + h) * P;
+    const float* zeta = hv->zeta + r * P + wg * 32;
+    const float* phi = hv->phi + r * P + wg * 32;
+    __nv_bfloat16* yrow = a.y + (((size_t)b * a.S + t0 + t) * a.H + h) * P + wg * 32;
+    uint32_t o1[32], o2[32];
+    tmem_ld_32x32(tO1 + lane_addr + wg * 32, o1);
+    tmem_ld_32x32(tO2 + lane_addr + wg * 32, o2);
+    tmem_ld_wait();
+    float mine[8];
 #pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-      uint32_t o1[32], o2[32];
-      tmem_ld_32x32(tO1 + lane_addr + cc * 32, o1);
-      tmem_ld_32x32(tO2 + lane_addr + cc * 32, o2);
-      tmem_ld_wait();
-      float out[32];
+    for (int q = 0; q < 4; ++q) {
+      float zf[8];
+      unpack8(zraw[q], zf);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float zf[8];
-        unpack8(zrow[cc * 4 + q], zf);
-#pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const int p = cc * 32 + q * 8 + v;
-          const float o = __uint_as_float(o1[q * 8 + v]) + ecs * __uint_as_float(o2[q * 8 + v]) + dsk * pv[p];
-          const float zz = zf[v] * zeta[p];
-          float val = o * phi[p] * (zz / (1.f + __expf(-zz)));
-          val += __shfl_xor_sync(0xffffffffu, val, 1);
-          val += __shfl_xor_sync(0xffffffffu, val, 2);
-          out[q * 8 + v] = val;
-        }
+      for (int v = 0; v < 8; ++v) {
+        const int p = q * 8 + v;
+        const float o = __uint_as_float(o1[p]) + ecs * __uint_as_float(o2[p]) + dsk * pv[p];
+        const float zz = zf[v] * zeta[p];
+        float val = o * phi[p] * (zz / (1.f + __expf(-zz)));
+        val += __shfl_xor_sync(0xffffffffu, val, 1);
+        val += __shfl_xor_sync(0xffffffffu, val, 2);
+        if (q == r) mine[v] = val;
       }
-      // the four lanes of a token hold the same sums; lane r writes columns [cc*32 + 8r, +8)
-      float mine[8];
-#pragma unroll
-      for (int v = 0; v < 8; ++v)
-        mine[v] = r == 0 ? out[v] : r == 1 ? out[8 + v] : r == 2 ? out[16 + v] : out[24 + v];
-      *reinterpret_cast<uint4*>(yrow + cc * 32 + r * 8) = pack8(mine);
     }
+    // the four lanes of a token hold the same sums; lane r writes columns [8r, 8r + 8) of this warpgroup's half
+    *reinterpret_cast<uint4*>(yrow + r * 8) = pack8(mine);
   }
+  CM_STAMP(9);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, 256); }
+  CM_STAMP(10);
 }
 
 template <int N>
-constexpr int local_state_smem() { return (N / 64) * SLAB + SLAB + 2 * LT * (N / 4) * 4 + sizeof(ChunkScalars) + 64 + 1024; }
+constexpr int local_state_smem() {
+  return (N / 64) * SLAB + SLAB + 2 * tab_floats<N / 4>() * 4 + sizeof(HeadBias<N>) + sizeof(HeadVecs) + sizeof(ChunkScalars) + 64 + 1024;
+}
 template <int N>
 constexpr int chunk_out_smem() {
   return ((N / 64) * SLAB > 2 * SLAB ? (N / 64) * SLAB : 2 * SLAB) + (N / 64) * SLAB + SLAB + (N > 128 ? N : 128) * 128 +
-         2 * LT * (N / 4) * 4 + sizeof(ChunkScalars) + 64 + 1024;
+         2 * tab_floats<N / 4>() * 4 + sizeof(HeadVecs) + sizeof(ChunkScalars) + 64 + 1024;
 }
 
 }  // namespace mimo
@@ -384,13 +404,19 @@ extern "C" int cm_mimo_scan_fwd(const void* Qn, const void* Kn, const void* V, c
       if (cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, chunk_out_smem<128>()) != cudaSuccess) return -2;
       cfg = true;
     }
-    k1<<<grid, THREADS, local_state_smem<128>(), stream>>>(tmK, a);
+    k1<<<grid, THREADS2, local_state_smem<128>(), stream>>>(tmK, a);
     dim3 g2(B * H, (128 * P + 1023) / 1024);
     mimo_state_scan_kernel<<<g2, 256, 0, stream>>>(local, tot, (__nv_bfloat16*)states, final_state, C, 128 * P);
-    k3<<<grid, THREADS, chunk_out_smem<128>(), stream>>>(tmQ, tmK, tmS, a);
+    k3<<<grid, THREADS2, chunk_out_smem<128>(), stream>>>(tmQ, tmK, tmS, a);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+#ifdef CM_MIMO_TIMING
+extern "C" int cm_mimo_read_stamps(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, cm_mimo_stamps, sizeof(cm_mimo_stamps)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 // ------------------------------------------------------------------------------------------
 // Variant with the work buffers in a fixed device array (see mimo_scan_static.h for the contract).

@@ -57,8 +57,9 @@ def _declare(L: ctypes.CDLL) -> None:
         if fn is not None:
             fn.argtypes = args
             fn.restype = i32
-    from . import extra
+    from . import extra, kernels4
     extra.declare(L)
+    kernels4.declare(L)
 
 
 def stream_ptr() -> int:
@@ -257,8 +258,9 @@ def _register() -> None:
     F_.register_cuda("rmsnorm", rmsnorm)
     F_.register_cuda("swiglu", swiglu)
     F_.register_cuda("adamw_shard", adamw_shard)
-    from . import extra
+    from . import extra, kernels4
     extra.register()
+    kernels4.register()
 
 
 if torch.cuda.is_available():

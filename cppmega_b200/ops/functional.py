@@ -164,6 +164,11 @@ def mimo_scan(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Psi, Zeta, Phi, angles, D,
 
 
 def angle_cumsum(angles_raw, dt):
+    fn = _cuda("angle_cumsum", angles_raw)
+    if fn is not None:
+        out = fn(angles_raw, dt)
+        if out is not None:
+            return out
     return mimo_scan_ref.angle_cumsum(angles_raw, dt)
 
 

@@ -58,9 +58,12 @@ class MoEPlan:
         dev = ids.device
         flat = ids.reshape(-1)
         counts = torch.bincount(flat, minlength=E)
-        allc = torch.empty(ep * E, dtype=counts.dtype, device=dev)
-        dist.all_gather_into_tensor(allc, counts.contiguous(), group=group)
-        allc = allc.view(ep, E)                                  # [src rank, expert]
+        if ep > 1:
+            allc = torch.empty(ep * E, dtype=counts.dtype, device=dev)
+            dist.all_gather_into_tensor(allc, counts.contiguous(), group=group)
+            allc = allc.view(ep, E)                              # [src rank, expert]
+        else:
+            allc = counts.view(1, E)
         tot = allc.sum(0)                                        # rows per expert (all sources)
         padded = (tot + (TILE - 1)) // TILE * TILE
         pe = padded.view(ep, El)
@@ -115,13 +118,60 @@ class FusedMoEBuffers:
         for _ in range(n):
             self.layer_bufs.append((self.heap.alloc((self.capacity, hidden), torch.bfloat16),
                                     self.heap.alloc((self.capacity, hidden), torch.bfloat16)))
-        self.grad_in = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
-        self.grad_out = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
+        self.grad_in_ = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
+        self.grad_out_ = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
         self.epoch = 0
         _ = El
 
-    def bufs(self, layer_slot: int):
+    def capacity_for(self, ncopies: int) -> int:
+        return self.capacity
+
+    def bufs(self, layer_slot: int, cap: int):
         return self.layer_bufs[layer_slot if self.per_layer else 0]
+
+    def grad_bufs(self, cap: int):
+        return self.grad_in_, self.grad_out_
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+
+class _LocalHeap:
+    """Stand-in for the symmetric heap when all experts live on this GPU: one "peer", no flags."""
+
+    world = 1
+
+    @staticmethod
+    def peer_ptr_array(t: torch.Tensor):
+        return (ctypes.c_void_p * 1)(t.data_ptr())
+
+    @staticmethod
+    def barrier(*_args) -> None:
+        return None
+
+
+class LocalMoEBuffers:
+    """EP = 1: the same permute-fused kernels on ordinary (caching-allocator) buffers.  Row buffers are exact-size
+    (every copy lands here, so T*k rows plus at most 127 padding rows per expert) and live as long as autograd needs
+    them, which with layer recomputation is one layer at a time."""
+
+    def __init__(self, pc, hidden: int, num_experts: int, device):
+        self.pc, self.hidden, self.num_experts, self.device = pc, hidden, num_experts, device
+        self.heap = _LocalHeap()
+        self.epoch = 0
+
+    def capacity_for(self, ncopies: int) -> int:
+        return (ncopies + self.num_experts * (TILE - 1) + TILE - 1) // TILE * TILE
+
+    def _row_buf(self, cap: int):
+        return torch.empty(cap, self.hidden, dtype=torch.bfloat16, device=self.device)
+
+    def bufs(self, layer_slot: int, cap: int):
+        return self._row_buf(cap), self._row_buf(cap)
+
+    def grad_bufs(self, cap: int):
+        return self._row_buf(cap), self._row_buf(cap)
 
     def next_epoch(self) -> int:
         self.epoch += 1
@@ -204,10 +254,10 @@ class _FusedMoEFn(torch.autograd.Function):
     def forward(ctx, x, probs, w1, w2, ids, bufs: FusedMoEBuffers, layer_slot: int):
         from ..ops.cuda import swiglu
         pc, heap = bufs.pc, bufs.heap
-        cap = bufs.capacity
+        cap = bufs.capacity_for(ids.numel())
         H = x.shape[1]
         plan = MoEPlan(ids, w1.shape[0] * pc.ep, pc.ep, pc.ep_rank, pc.ep_group, cap)
-        xin, yout = bufs.bufs(layer_slot)
+        xin, yout = bufs.bufs(layer_slot, cap)
         ep0 = bufs.next_epoch()
         f0 = FLAG_BASE + 4 * layer_slot
         x = x.contiguous()
@@ -221,39 +271,42 @@ class _FusedMoEFn(torch.autograd.Function):
         heap.barrier(f0 + 1, ep0)
         p32 = probs.float().contiguous()
         y = _pull_combine(heap, yout, plan, p32.reshape(-1), H, x.dtype)
-        ctx.save_for_backward(h, w1, w2, p32)
-        ctx.plan, ctx.bufs, ctx.slot, ctx.xin, ctx.yout = plan, bufs, layer_slot, xin, yout
+        # xin / yout go through save_for_backward as well: activation checkpointing only drops what it sees there
+        ctx.save_for_backward(h, w1, w2, p32, xin, yout)
+        ctx.plan, ctx.bufs, ctx.slot, ctx.cap = plan, bufs, layer_slot, cap
         ctx.x_dtype, ctx.p_dtype = x.dtype, probs.dtype
         return y
 
     @staticmethod
     def backward(ctx, dy):
         from ..ops.cuda import lib, stream_ptr, _check
-        h, w1, w2, p32 = ctx.saved_tensors
+        h, w1, w2, p32, xin, yout = ctx.saved_tensors
         plan, bufs = ctx.plan, ctx.bufs
-        pc, heap, cap = bufs.pc, bufs.heap, bufs.capacity
+        pc, heap, cap = bufs.pc, bufs.heap, ctx.cap
+        grad_in, grad_out = bufs.grad_bufs(cap)
         H = dy.shape[1]
         dy = dy.contiguous()
         epb = bufs.next_epoch()
         f0 = FLAG_BASE + 4 * ctx.slot
-        dprobs = _pull_rowdot(heap, ctx.yout, plan, dy)
-        _push(heap, dy, plan, bufs.grad_in, scale=p32.reshape(-1))
+        dprobs = _pull_rowdot(heap, yout, plan, dy)
+        _push(heap, dy, plan, grad_in, scale=p32.reshape(-1))
         heap.barrier(f0 + 2, epb)
+        _zero_pad(grad_in, plan, cap)      # padding rows feed the wgrad products: 0 * stale NaN would poison them
         E = w1.shape[0]
         Fh = w2.shape[2]
         # recompute a = swiglu(h); expert backward on the padded layout
         from ..ops.cuda import swiglu as _sw
         with torch.no_grad():
             a = _sw(h)
-            da = _grouped(bufs.grad_in, w2, plan.tile_expert, cap, True)                  # [cap, F]
-            dw2 = _grouped_wgrad(bufs.grad_in, a, plan.seg_offsets, E)                   # [E, H, F]
+            da = _grouped(grad_in, w2, plan.tile_expert, cap, True)                  # [cap, F]
+            dw2 = _grouped_wgrad(grad_in, a, plan.seg_offsets, E)                   # [E, H, F]
             dh = torch.empty_like(h)
             _check(lib().cm_swiglu_bwd(h.data_ptr(), da.data_ptr(), dh.data_ptr(), cap, Fh, stream_ptr()), "cm_swiglu_bwd")
             F_.count_launch("swiglu_bwd")
-            _grouped(dh, w1, plan.tile_expert, cap, True, out=bufs.grad_out)               # [cap, H]
-            dw1 = _grouped_wgrad(dh, ctx.xin, plan.seg_offsets, E)                        # [E, 2F, H]
+            _grouped(dh, w1, plan.tile_expert, cap, True, out=grad_out)               # [cap, H]
+            dw1 = _grouped_wgrad(dh, xin, plan.seg_offsets, E)                        # [E, 2F, H]
         heap.barrier(f0 + 3, epb)
-        dx = _pull_combine(heap, bufs.grad_out, plan, None, H, ctx.x_dtype)
+        dx = _pull_combine(heap, grad_out, plan, None, H, ctx.x_dtype)
         return dx, dprobs.to(ctx.p_dtype), dw1, dw2, None, None, None
 
 
@@ -270,9 +323,14 @@ class FusedMoEDispatcher:
 def attach(model, pc, device, tokens_per_rank: int, per_layer: bool = True, capacity_factor: float = 2.0) -> Optional[FusedMoEBuffers]:
     """Install the fused dispatcher on every MoE layer of ``model`` (EP > 1, bf16, peer access)."""
     layers = model.moe_layers()
-    if pc.ep <= 1 or not layers:
+    if not layers:
         return None
     hidden = model.cfg.hidden_size
+    if pc.ep <= 1:
+        local = LocalMoEBuffers(pc, hidden, model.cfg.moe.num_experts, device)
+        for slot, m in enumerate(layers):
+            m.fused_dispatcher = FusedMoEDispatcher(local, slot)
+        return local
     bufs = FusedMoEBuffers(pc, hidden, tokens_per_rank, model.cfg.moe.topk, len(layers), device,
                            capacity_factor=capacity_factor, per_layer=per_layer)
     for slot, m in enumerate(layers):

@@ -76,6 +76,11 @@ class Trainer:
                                  overlap=False if self.pc.pp > 1 else None)
         if self.pc.world_size > 1 and device.type == "cuda" and self.pc.config.fused_collectives:
             self._attach_fused_paths()
+        if (device.type == "cuda" and self.pc.ep == 1 and self.pc.tp == 1 and self.pc.config.fused_collectives
+                and train_cfg.torch_dtype() == torch.bfloat16 and model_cfg.hidden_size % 8 == 0):
+            from ..parallel import fused_moe          # permute-fused MoE kernels on local buffers
+            self._moe_bufs = fused_moe.attach(self.model, self.pc, device, tokens_per_rank=0)
+            self.fused["moe"] = self._moe_bufs is not None
         self.lr_schedule = train_cfg.lr_schedule or LRSchedule(lr=train_cfg.optimizer.lr, style="constant")
         self.step = 0
         dp = self.pc.dp
