@@ -41,7 +41,7 @@ class Router(nn.Module):
             self.expert_bias = None
 
     def forward(self, x: torch.Tensor):
-        logits = torch.nn.functional.linear(x.float(), self.weight)
+        logits = F_.linear_fp32out(x, self.weight)
         probs, ids, scores = F_.router_topk(logits, self.cfg.topk, self.cfg.score_function,
                                             self.expert_bias, self.cfg.norm_topk_prob)
         if self.expert_bias is not None and self.training:

@@ -132,7 +132,7 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag, uns
 
 // ---- TMA ---------------------------------------------------------------------------------
 // Tiled loads into this CTA's shared memory, completion on an mbarrier of this CTA.
-// (No cluster multicast anywhere in this library.)
+// Every load in this library targets exactly one CTA.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

@@ -151,6 +151,43 @@ def linear(x: torch.Tensor, w: torch.Tensor):
     return LinearFn.apply(x, w)
 
 
+class LinearFp32OutFn(torch.autograd.Function):
+    """``y = x W^T`` with bf16 operands on the tensor cores and an fp32 result, for fp32 parameters whose
+    consumers want fp32 (router logits).  ``w`` is the fp32 parameter; it is rounded to bf16 for the products and
+    receives an fp32 gradient."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        wb = w.to(torch.bfloat16)
+        ctx.save_for_backward(x2, wb)
+        ctx.xshape = x.shape
+        y = gemm(x2, wb, out_dtype=torch.float32)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, wb = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, wb, b_mn=True).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        return dx, dw
+
+
+def linear_fp32out(x: torch.Tensor, w: torch.Tensor):
+    if (x.dtype != torch.bfloat16 or w.dtype != torch.float32 or w.dim() != 2 or x.shape[-1] % 8 or w.shape[0] % 8
+            or x.numel() == 0):
+        return None
+    return LinearFp32OutFn.apply(x, w)
+
+
 # ---------------------------------------------------------------------------
 # RMSNorm / SwiGLU
 # ---------------------------------------------------------------------------
@@ -255,6 +292,7 @@ def sumsq(g: torch.Tensor, out: torch.Tensor) -> None:
 
 def _register() -> None:
     F_.register_cuda("linear", linear)
+    F_.register_cuda("linear_fp32out", linear_fp32out)
     F_.register_cuda("rmsnorm", rmsnorm)
     F_.register_cuda("swiglu", swiglu)
     F_.register_cuda("adamw_shard", adamw_shard)

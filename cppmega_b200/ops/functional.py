@@ -91,6 +91,17 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return F.linear(x, w.to(x.dtype) if w.dtype != x.dtype else w)
 
 
+def linear_fp32out(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """fp32 ``x @ weight.T`` for an fp32 parameter.  On the GPU with bf16 activations the products run on the tensor
+    cores (bf16 operands, fp32 accumulation and output); elsewhere plain fp32."""
+    fn = _cuda("linear_fp32out", x) if x.is_cuda and x.dtype == torch.bfloat16 else None
+    if fn is not None:
+        y = fn(x, weight)
+        if y is not None:
+            return y
+    return F.linear(x.float(), weight.float())
+
+
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, counts_host=None) -> torch.Tensor:
     """Rows of x sorted by expert; w [E, out, in]; counts [E] rows per expert."""
     fn = _cuda("grouped_linear", x)

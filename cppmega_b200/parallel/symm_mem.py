@@ -9,8 +9,8 @@ flag words; ``signal`` stores a value into one word on every peer (release), ``w
 local words with a wall-clock bound and reports a timeout through the kernel error word instead
 of hanging.
 
-The kernels that use these pointers issue plain peer loads and stores; nothing here uses NVLS
-multicast, so a rank that exits between steps leaves its peers' memory mappings valid.
+The kernels that use these pointers issue plain peer loads and stores; nothing here binds memory
+to a switch-side reduction object, so a rank that exits between steps leaves its peers' memory mappings valid.
 """
 from __future__ import annotations
 

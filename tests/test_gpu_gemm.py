@@ -87,3 +87,23 @@ def test_grouped_experts(cu, counts):
     assert _rel(x.grad, xr.grad) < 1.5e-2
     assert _rel(w1.grad, w1r.grad) < 1.5e-2
     assert _rel(w2.grad, w2r.grad) < 1.5e-2
+
+
+def test_linear_fp32out_router_shape():
+    from cppmega_b200.ops import cuda as cu
+    torch.manual_seed(0)
+    x = (torch.randn(3000, 512, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(16, 512, device="cuda") * 0.05).requires_grad_()
+    y = cu.linear_fp32out(x, w)
+    assert y.dtype == torch.float32
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().clone().requires_grad_()
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(g)
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(y, yr) < 1e-2
+    assert rel(x.grad, xr.grad) < 2e-2
+    assert rel(w.grad, wr.grad) < 2e-2
+    assert w.grad.dtype == torch.float32
