@@ -305,6 +305,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 static EncodeTiledFn g_encode = nullptr;
 EncodeTiledFn get_encode_tiled() {
+  // The encode call is a driver entry point and wants the device's primary context current on the calling thread.
+  // A thread that has made no runtime call yet (an autograd worker running its first backward) has none bound:
+  // one no-op runtime call binds it.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   if (g_encode) return g_encode;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult q;

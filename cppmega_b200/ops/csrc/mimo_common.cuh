@@ -70,29 +70,47 @@ struct alignas(16) ChunkScalars {   // shared-memory block, one per CTA; the mba
 };
 static_assert(sizeof(ChunkScalars) % 16 == 0, "mbarriers follow this block and need 8-byte alignment");
 
-// Warp 0 computes the chunk scalars.  ADT/DT/Trap are [B,H,S] fp32; `base` = (b*H + h)*S + t0.
-__device__ __forceinline__ void compute_chunk_scalars(ChunkScalars* sc, const float* __restrict__ ADT,
-                                                      const float* __restrict__ DT, const float* __restrict__ Trap,
-                                                      size_t base, int t0, int S) {
+// Chunk scalars in two steps so that the global loads can be issued at the top of a kernel and consumed later.
+// ADT/DT/Trap are [B,H,S] fp32; `base` = (b*H + h)*S + t0.  Only warp 0 takes part.
+struct ScalarLoads {
+  float a, dt, tr, dt1, tr1;
+};
+__device__ __forceinline__ ScalarLoads load_chunk_scalars(const float* __restrict__ ADT, const float* __restrict__ DT,
+                                                          const float* __restrict__ Trap, size_t base, int t0, int S) {
+  ScalarLoads l{0.f, 0.f, 0.f, 0.f, 0.f};
+  if ((threadIdx.x >> 5) != 0) return l;
+  const int lane = threadIdx.x & 31;
+  l.a = ADT[base + lane];
+  l.dt = DT[base + lane];
+  l.tr = Trap[base + lane];
+  if (t0 + lane + 1 < S) {
+    l.dt1 = DT[base + lane + 1];
+    l.tr1 = Trap[base + lane + 1];
+  }
+  return l;
+}
+__device__ __forceinline__ void finish_chunk_scalars(ChunkScalars* sc, const ScalarLoads& l, int t0, int S) {
   const int lane = threadIdx.x & 31;
   if ((threadIdx.x >> 5) != 0) return;
-  float a = ADT[base + lane];
+  float a = l.a;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const float n = __shfl_up_sync(0xffffffffu, a, o);
     if (lane >= o) a += n;
   }
-  const float dt = DT[base + lane], tr = Trap[base + lane];
-  const float g = dt / (1.f + __expf(-tr));
+  const float g = __fdividef(l.dt, 1.f + __expf(-l.tr));
   float nxt = 0.f;
-  if (t0 + lane + 1 < S) {
-    const float dt1 = DT[base + lane + 1], tr1 = Trap[base + lane + 1];
-    nxt = dt1 / (1.f + __expf(tr1));            // dt * sigmoid(-trap)
-  }
+  if (t0 + lane + 1 < S) nxt = __fdividef(l.dt1, 1.f + __expf(l.tr1));            // dt * sigmoid(-trap)
   sc->cs[lane] = a;
   sc->gam[lane] = g;
   sc->ts[lane] = g + nxt;
   if (lane == 31) sc->tot = a;
+}
+__device__ __forceinline__ void compute_chunk_scalars(ChunkScalars* sc, const float* __restrict__ ADT,
+                                                      const float* __restrict__ DT, const float* __restrict__ Trap,
+                                                      size_t base, int t0, int S) {
+  const ScalarLoads l = load_chunk_scalars(ADT, DT, Trap, base, t0, S);
+  finish_chunk_scalars(sc, l, t0, S);
 }
 
 // cos/sin of the chunk's rotary angles into shared memory: cs_tab[t][a] (a < NROT).
@@ -116,6 +134,30 @@ __device__ __forceinline__ void fill_sincos(float* cos_tab, float* sin_tab, cons
   for (int j = 0; j < PER; ++j) {
     float x = a[j];
     x -= 6.283185307179586f * rintf(x * 0.15915494309189535f);     // range-reduce before the fast path
+    float s, c;
+    __sincosf(x, &s, &c);
+    cos_tab[t * TS + off + j] = c;
+    sin_tab[t * TS + off + j] = s;
+  }
+}
+
+// Two-warpgroup form with the four angles of this thread already in registers (NROT == 32: PER == 4).
+template <int NROT>
+__device__ __forceinline__ float4 load_angles4(const float* __restrict__ angles, size_t b, int t0, int h, int S, int H) {
+  static_assert(NROT == 32, "one float4 per thread");
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3;
+  return *reinterpret_cast<const float4*>(angles + (((size_t)b * S + t0 + t) * H + h) * NROT + (r * 2 + wg) * 4);
+}
+template <int NROT>
+__device__ __forceinline__ void fill_sincos4(float* cos_tab, float* sin_tab, const float4& a4) {
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3;
+  constexpr int TS = tab_stride<NROT>();
+  const int off = (r * 2 + wg) * 4;
+  const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float x = av[j];
+    x -= 6.283185307179586f * rintf(x * 0.15915494309189535f);
     float s, c;
     __sincosf(x, &s, &c);
     cos_tab[t * TS + off + j] = c;
@@ -197,6 +239,36 @@ __device__ __forceinline__ void load_pv_half(float (&pv)[P / 2], const __nv_bflo
     for (int j = 0; j < 8; ++j) pv[c * 8 + j] = f[j] * psi[r * P + wg * 32 + c * 8 + j];
   }
 }
+// raw 64-byte half row (columns [wg*32, +32)) of a [B,S,H,P] bf16 tensor for this thread's token
+struct HalfRowRaw {
+  uint4 v[4];
+};
+__device__ __forceinline__ HalfRowRaw load_half_raw(const __nv_bfloat16* __restrict__ X, size_t b, int t0, int h, int S, int H) {
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2;
+  const uint4* p = reinterpret_cast<const uint4*>(X + (((size_t)b * S + t0 + t) * H + h) * P + wg * 32);
+  HalfRowRaw o;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) o.v[c] = p[c];
+  return o;
+}
+__device__ __forceinline__ void half_raw_to_float(float (&x)[P / 2], const HalfRowRaw& raw) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float f[8];
+    unpack8(raw.v[c], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[c * 8 + j] = f[j];
+  }
+}
+// pv = V * psi for this thread's half row; psi -> [R,P] in shared memory
+__device__ __forceinline__ void pv_from_raw(float (&pv)[P / 2], const HalfRowRaw& raw, const float* psi) {
+  const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, r = i & 3;
+  half_raw_to_float(pv, raw);
+#pragma unroll
+  for (int e = 0; e < P / 2; ++e) pv[e] *= psi[r * P + wg * 32 + e];
+}
+__device__ __forceinline__ float fast_silu(float zz) { return __fdividef(zz, 1.f + __expf(-zz)); }
+
 __device__ __forceinline__ void store_half64(uint8_t* slab, const float (&x)[P / 2], float scale) {
   const int i = threadIdx.x & 127, wg = threadIdx.x >> 7;
 #pragma unroll

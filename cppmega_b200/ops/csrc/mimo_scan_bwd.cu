@@ -119,6 +119,11 @@ __global__ void __launch_bounds__(THREADS2) mimo_grad_state_kernel(const __grid_
   decode_block_b(a, b, g, c, h);
   const int t0 = c * LT;
   const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3, warp = threadIdx.x >> 5;
+  // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
+  const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
+  const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
+  const HalfRowRaw yraw = load_half_raw(a.dY, b, t0, h, a.S, a.H);
+  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.H);
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -135,25 +140,21 @@ __global__ void __launch_bounds__(THREADS2) mimo_grad_state_kernel(const __grid_
 #pragma unroll
     for (int s = 0; s < N / 64; ++s) tma_load_5d_b(sQ + s * SLAB, &tmQ, &bars[0], s * 64, 0, g, t0, b);
   }
-  compute_chunk_scalars(sc, a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
-  fill_sincos<NROT, 2>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
   load_head_consts<N>(hb, hv, a.Qb, a.Qb, a.Phi, a.Zeta, a.Phi, h);
+  finish_chunk_scalars(sc, sl, t0, a.S);
+  fill_sincos4<NROT>(cos_tab, sin_tab, ang4);
   __syncthreads();
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
   if (ok) {
     transform_rows<N, NROT, 2>(sQ, hb->qb, cos_tab, sin_tab);
-    const size_t rowoff = (((size_t)b * a.S + t0 + t) * a.H + h) * P;
     float dy[P / 2], z[P / 2];
-    load_half_bf16(dy, a.dY + rowoff);
-    load_half_bf16(z, a.Z + rowoff);
+    half_raw_to_float(dy, yraw);
+    half_raw_to_float(z, zraw);
     const float* zeta = hv->zeta + r * P + wg * 32;
     const float* phi = hv->phi + r * P + wg * 32;
     const float e = __expf(sc->cs[t]);
 #pragma unroll
-    for (int p = 0; p < P / 2; ++p) {
-      const float zz = z[p] * zeta[p];
-      dy[p] = dy[p] * phi[p] * (zz / (1.f + __expf(-zz)));
-    }
+    for (int p = 0; p < P / 2; ++p) dy[p] = dy[p] * phi[p] * fast_silu(z[p] * zeta[p]);
     store_half64(sdO, dy, e);
     fence_proxy_async_smem();
   }
@@ -252,6 +253,12 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   const int t0 = c * LT;
   const int tid = threadIdx.x;
   const int i = tid & 127, wg = tid >> 7, t = i >> 2, r = i & 3, warp = tid >> 5, lane = tid & 31;
+  // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
+  const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
+  const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
+  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.H);
+  const HalfRowRaw yraw = load_half_raw(a.dY, b, t0, h, a.S, a.H);
+  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.H);
   if (tid == 0) {
     for (int q = 0; q < 4; ++q) mbar_init(&bars[q], 1);
     *abort_flag = 0;
@@ -277,9 +284,9 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
     tma_load_2d(sSt, &tmS, &bars[0], 0, srow);
     tma_load_2d(sdE, &tmE, &bars[0], 0, srow);
   }
-  compute_chunk_scalars(sc, a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
-  fill_sincos<NROT, 2>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
   load_head_consts<N>(hb, hv, a.Qb, a.Kb, a.Psi, a.Zeta, a.Phi, h);
+  finish_chunk_scalars(sc, sl, t0, a.S);
+  fill_sincos4<NROT>(cos_tab, sin_tab, ang4);
   __syncthreads();
   const size_t rowoff = (((size_t)b * a.S + t0 + t) * a.H + h) * P + wg * 32;     // this thread's half row
   const float* zeta = hv->zeta + r * P + wg * 32;
@@ -294,19 +301,20 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   if (ok) {
     transform_rows<N, NROT, 2>(sQ, hb->qb, cos_tab, sin_tab);
     transform_rows<N, NROT, 2>(sK, hb->kb, cos_tab, sin_tab);
-    float pv[P / 2];
-    load_pv_half(pv, a.V, hv->psi, b, t0, h, a.S, a.H);
-    store_half64(sPV, pv, 1.f);
-    store_half64(sPVw, pv, wi);
-    float dy[P / 2], z[P / 2];
-    load_half_bf16(dy, a.dY + rowoff - wg * 32);
-    load_half_bf16(z, a.Z + rowoff - wg * 32);
-#pragma unroll
-    for (int p = 0; p < P / 2; ++p) {
-      const float zz = z[p] * zeta[p];
-      dy[p] = dy[p] * phi[p] * (zz / (1.f + __expf(-zz)));
+    {
+      float pv[P / 2];
+      pv_from_raw(pv, vraw, hv->psi);
+      store_half64(sPV, pv, 1.f);
+      store_half64(sPVw, pv, wi);
     }
-    store_half64(sdO, dy, 1.f);
+    {
+      float dy[P / 2], z[P / 2];
+      half_raw_to_float(dy, yraw);
+      half_raw_to_float(z, zraw);
+#pragma unroll
+      for (int p = 0; p < P / 2; ++p) dy[p] = dy[p] * phi[p] * fast_silu(z[p] * zeta[p]);
+      store_half64(sdO, dy, 1.f);
+    }
     fence_proxy_async_smem();
   }
   __syncthreads();
@@ -426,9 +434,9 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   // ---------------- epilogue B: gating gradients, dPV, dw, de (this warpgroup's 32 columns) ----------------
   float dw_i = 0.f, de_i = 0.f;
   if (ok) {
-    const uint4* vrow = reinterpret_cast<const uint4*>(a.V + rowoff);
-    const uint4* yrow = reinterpret_cast<const uint4*>(a.dY + rowoff);
-    const uint4* zrow = reinterpret_cast<const uint4*>(a.Z + rowoff);
+    const uint4* vrow = vraw.v;
+    const uint4* yrow = yraw.v;
+    const uint4* zrow = zraw.v;
     const int wq = warp & 3;
     float dD_part = 0.f;
     float dvrow[32];
@@ -451,7 +459,7 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
           const float o2v = __uint_as_float(o2[e]);
           const float o = __uint_as_float(o1[e]) + ei * o2v + dsk * pvv;
           const float zz = zf[v] * zeta[e];
-          const float sg = 1.f / (1.f + __expf(-zz));
+          const float sg = __fdividef(1.f, 1.f + __expf(-zz));
           const float sil = zz * sg;
           const float dO = yf[v] * phi[e] * sil;
           const float dgate = yf[v] * o;

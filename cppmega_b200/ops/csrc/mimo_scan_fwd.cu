@@ -100,6 +100,10 @@ __global__ void __launch_bounds__(THREADS2) mimo_local_state_kernel(const __grid
   decode_block(a, b, g, c, h);
   const int t0 = c * LT;
   const int warp = threadIdx.x >> 5, i = threadIdx.x & 127, wg = threadIdx.x >> 7;
+  // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
+  const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
+  const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
+  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.H);
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -116,15 +120,15 @@ __global__ void __launch_bounds__(THREADS2) mimo_local_state_kernel(const __grid
 #pragma unroll
     for (int s = 0; s < N / 64; ++s) tma_load_5d(sK + s * SLAB, &tmK, &bars[0], s * 64, 0, g, t0, b);
   }
-  compute_chunk_scalars(sc, a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
-  fill_sincos<NROT, 2>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
   load_head_consts<N>(hb, hv, nullptr, a.Kb, a.Psi, nullptr, nullptr, h);
+  finish_chunk_scalars(sc, sl, t0, a.S);
+  fill_sincos4<NROT>(cos_tab, sin_tab, ang4);
   __syncthreads();
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
   if (ok) {
     transform_rows<N, NROT, 2>(sK, hb->kb, cos_tab, sin_tab);
     float pv[P / 2];
-    load_pv_half(pv, a.V, hv->psi, b, t0, h, a.S, a.H);
+    pv_from_raw(pv, vraw, hv->psi);
     const int t = i >> 2;
     store_half64(sPVw, pv, sc->ts[t] * __expf(sc->tot - sc->cs[t]));
     fence_proxy_async_smem();
@@ -217,6 +221,12 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   const int t0 = c * LT;
   const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3;
   const int warp = threadIdx.x >> 5;
+  // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
+  const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
+  const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
+  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.H);
+  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.H);
+  const float dsk = a.Dskip[h];
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -240,15 +250,9 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
     }
     tma_load_2d(sSt, &tmS, &bars[0], 0, (int)((((size_t)b * a.H + h) * a.C + c) * N));
   }
-  compute_chunk_scalars(sc, a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
-  fill_sincos<NROT, 2>(cos_tab, sin_tab, a.angles, b, t0, h, a.S, a.H);
   load_head_consts<N>(hb, hv, a.Qb, a.Kb, a.Psi, a.Zeta, a.Phi, h);
-  // this thread's gate inputs, fetched early so the latency hides behind the products
-  const uint4* zrow = reinterpret_cast<const uint4*>(a.Z + (((size_t)b * a.S + t0 + t) * a.H + h) * P + wg * 32);
-  uint4 zraw[4];
-#pragma unroll
-  for (int q = 0; q < 4; ++q) zraw[q] = zrow[q];
-  const float dsk = a.Dskip[h];
+  finish_chunk_scalars(sc, sl, t0, a.S);
+  fill_sincos4<NROT>(cos_tab, sin_tab, ang4);
   __syncthreads();
   CM_STAMP(2);
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
@@ -257,7 +261,7 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   if (ok) {
     transform_rows<N, NROT, 2>(sQ, hb->qb, cos_tab, sin_tab);
     transform_rows<N, NROT, 2>(sK, hb->kb, cos_tab, sin_tab);
-    load_pv_half(pv, a.V, hv->psi, b, t0, h, a.S, a.H);
+    pv_from_raw(pv, vraw, hv->psi);
   }
   CM_STAMP(4);
   __syncthreads();                               // every thread is done with the biases stored in the PV slab
@@ -335,13 +339,13 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float zf[8];
-      unpack8(zraw[q], zf);
+      unpack8(zraw.v[q], zf);
 #pragma unroll
       for (int v = 0; v < 8; ++v) {
         const int p = q * 8 + v;
         const float o = __uint_as_float(o1[p]) + ecs * __uint_as_float(o2[p]) + dsk * pv[p];
         const float zz = zf[v] * zeta[p];
-        float val = o * phi[p] * (zz / (1.f + __expf(-zz)));
+        float val = o * phi[p] * fast_silu(zz);
         val += __shfl_xor_sync(0xffffffffu, val, 1);
         val += __shfl_xor_sync(0xffffffffu, val, 2);
         if (q == r) mine[v] = val;

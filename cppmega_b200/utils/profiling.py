@@ -38,9 +38,9 @@ def install_layer_nvtx(model) -> None:
 
 def profile_steps(step_fn: Callable[[int], None], steps: int, out_dir: Optional[str] = None, row_limit: int = 60) -> str:
     """Run ``step_fn(i)`` for ``steps`` iterations under the torch profiler; returns the kernel table
-    sorted by device time and writes ``kernel_table.txt`` / ``trace.json`` into ``out_dir``."""
+    sorted by device time and writes ``kernel_table.txt`` / ``by_shape.txt`` into ``out_dir``."""
     from torch.profiler import ProfilerActivity, profile
-    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=True, with_stack=True) as prof:
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=True) as prof:
         for i in range(steps):
             step_fn(i)
         torch.cuda.synchronize()
@@ -49,11 +49,11 @@ def profile_steps(step_fn: Callable[[int], None], steps: int, out_dir: Optional[
         os.makedirs(out_dir, exist_ok=True)
         with open(os.path.join(out_dir, "kernel_table.txt"), "w") as f:
             f.write(table)
-        try:      # the same device time attributed to the Python source lines that launched it
-            by_src = prof.key_averages(group_by_stack_n=8).table(sort_by="self_cuda_time_total", row_limit=120,
-                                                                 max_name_column_width=60, max_src_column_width=110)
-            with open(os.path.join(out_dir, "by_source.txt"), "w") as f:
-                f.write(by_src)
+        try:      # the same device time split by operand shapes, which identifies the call sites of the glue ops
+            by_shape = prof.key_averages(group_by_input_shape=True).table(
+                sort_by="self_cuda_time_total", row_limit=150, max_name_column_width=50, max_shapes_column_width=120)
+            with open(os.path.join(out_dir, "by_shape.txt"), "w") as f:
+                f.write(by_shape)
         except Exception:
             pass
     return table
