@@ -36,8 +36,12 @@ class M2RNNMixer(nn.Module):
         name = f"decoder.layers.{layer_number - 1}.mixer"
         gen = torch.Generator(device="cpu")
         gen.manual_seed(seed_for(name, seed))
-        w_in = torch.empty(self.conv_dim + H + self.g_dim, hidden).normal_(0, init_std, generator=gen)
-        self.input_projection = nn.Linear(hidden, self.conv_dim + H + self.g_dim, bias=False, dtype=dtype)
+        self.in_dim = self.conv_dim + H + self.g_dim
+        # rows padded to a multiple of 8 (zero, never read) so that the projection is a tensor-core GEMM shape
+        self.in_dim_padded = (self.in_dim + 7) // 8 * 8
+        w_in = torch.zeros(self.in_dim_padded, hidden)
+        w_in[:self.in_dim].normal_(0, init_std, generator=gen)
+        self.input_projection = nn.Linear(hidden, self.in_dim_padded, bias=False, dtype=dtype)
         self.output_projection = nn.Linear(self.g_dim, hidden, bias=False, dtype=dtype)
         with torch.no_grad():
             self.input_projection.weight.copy_(w_in.to(dtype))
@@ -66,7 +70,7 @@ class M2RNNMixer(nn.Module):
         B, S, _ = x.shape
         H = self.num_heads
         proj = F_.linear(x, self.input_projection.weight)
-        conv_in, f_in, g = proj.split((self.conv_dim, H, self.g_dim), dim=-1)
+        conv_in, f_in, g = proj[..., :self.in_dim].split((self.conv_dim, H, self.g_dim), dim=-1)
         f = torch.exp(-torch.exp(self.A_log) * F.softplus(f_in.float() + self.dt_bias))       # [B,S,H] fp32
         if self.conv1d is not None:
             c = self.conv1d(conv_in.transpose(1, 2))[..., :S]

@@ -237,6 +237,44 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Transposing all-reduce: every lane holds 32 values; lane l returns the reduction over the 32 lanes of element l
+template <bool IS_MAX>
+__device__ __forceinline__ float xreduce32(const float (&v)[32], int lane) {
+  float a16[16], a8[8], a4[4], a2[2];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const bool up = lane & 16;
+    const float keep = up ? v[i + 16] : v[i], send = up ? v[i] : v[i + 16];
+    const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
+    a16[i] = IS_MAX ? fmaxf(keep, recv) : keep + recv;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const bool up = lane & 8;
+    const float keep = up ? a16[i + 8] : a16[i], send = up ? a16[i] : a16[i + 8];
+    const float recv = __shfl_xor_sync(0xffffffffu, send, 8);
+    a8[i] = IS_MAX ? fmaxf(keep, recv) : keep + recv;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const bool up = lane & 4;
+    const float keep = up ? a8[i + 4] : a8[i], send = up ? a8[i] : a8[i + 4];
+    const float recv = __shfl_xor_sync(0xffffffffu, send, 4);
+    a4[i] = IS_MAX ? fmaxf(keep, recv) : keep + recv;
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const bool up = lane & 2;
+    const float keep = up ? a4[i + 2] : a4[i], send = up ? a4[i] : a4[i + 2];
+    const float recv = __shfl_xor_sync(0xffffffffu, send, 2);
+    a2[i] = IS_MAX ? fmaxf(keep, recv) : keep + recv;
+  }
+  const bool up = lane & 1;
+  const float keep = up ? a2[1] : a2[0], send = up ? a2[0] : a2[1];
+  const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+  return IS_MAX ? fmaxf(keep, recv) : keep + recv;
+}
+
 // ---- host: tensor-map encoding through the runtime's driver entry point -----------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

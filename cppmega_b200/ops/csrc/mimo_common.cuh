@@ -243,9 +243,10 @@ __device__ __forceinline__ void load_pv_half(float (&pv)[P / 2], const __nv_bflo
 struct HalfRowRaw {
   uint4 v[4];
 };
-__device__ __forceinline__ HalfRowRaw load_half_raw(const __nv_bfloat16* __restrict__ X, size_t b, int t0, int h, int S, int H) {
+// `ld` = elements between consecutive tokens (H*P for a packed tensor; larger for a column slice of a wider matrix)
+__device__ __forceinline__ HalfRowRaw load_half_raw(const __nv_bfloat16* __restrict__ X, size_t b, int t0, int h, int S, long long ld) {
   const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2;
-  const uint4* p = reinterpret_cast<const uint4*>(X + (((size_t)b * S + t0 + t) * H + h) * P + wg * 32);
+  const uint4* p = reinterpret_cast<const uint4*>(X + ((size_t)b * S + t0 + t) * ld + h * P + wg * 32);
   HalfRowRaw o;
 #pragma unroll
   for (int c = 0; c < 4; ++c) o.v[c] = p[c];

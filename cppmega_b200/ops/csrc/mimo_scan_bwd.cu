@@ -56,6 +56,7 @@ struct BwdArgs {
   float* dPhi;
   float* dD;                    // [H]
   int B, S, H, G, C;
+  long long ldV, ldZ;           // token strides of V and Z in elements
   int* err;
 };
 
@@ -122,8 +123,8 @@ __global__ void __launch_bounds__(THREADS2) mimo_grad_state_kernel(const __grid_
   // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
   const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
   const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
-  const HalfRowRaw yraw = load_half_raw(a.dY, b, t0, h, a.S, a.H);
-  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.H);
+  const HalfRowRaw yraw = load_half_raw(a.dY, b, t0, h, a.S, (long long)a.H * P);
+  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.ldZ);
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -256,9 +257,9 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
   const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
   const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
-  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.H);
-  const HalfRowRaw yraw = load_half_raw(a.dY, b, t0, h, a.S, a.H);
-  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.H);
+  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.ldV);
+  const HalfRowRaw yraw = load_half_raw(a.dY, b, t0, h, a.S, (long long)a.H * P);
+  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.ldZ);
   if (tid == 0) {
     for (int q = 0; q < 4; ++q) mbar_init(&bars[q], 1);
     *abort_flag = 0;
@@ -708,9 +709,10 @@ extern "C" int cm_mimo_scan_bwd(const void* Qn, const void* Kn, const void* V, c
                                 const float* Dskip, const void* states, const float* tot, float* gbuf, void* dend,
                                 void* dQh, void* dKh, void* dV, void* dZ, float* dAngles, float* dADT, float* dTs,
                                 float* dGam, float* dPsi, float* dZeta, float* dPhi, float* dD_, int B, int S, int H, int G,
-                                int N, int* err, cudaStream_t stream) {
+                                int N, long long ldV, long long ldZ, int* err, cudaStream_t stream) {
   if (B <= 0 || S <= 0) return 0;
   if (S % LT || N != 128 || H % G) return -10;
+  if (ldV < (long long)H * P || ldZ < (long long)H * P || ldV % 8 || ldZ % 8) return -11;
   const int C = S / LT;
   CUtensorMap tmQ, tmK, tmS, tmE;
   int rc = make_tmap_qk(&tmQ, Qn, B, S, G, N);
@@ -723,7 +725,7 @@ extern "C" int cm_mimo_scan_bwd(const void* Qn, const void* Kn, const void* V, c
   if (rc) return rc;
   BwdArgs a{(const __nv_bfloat16*)V, (const __nv_bfloat16*)Z, (const __nv_bfloat16*)dY, ADT, DT, Trap, Qb, Kb, Psi, Zeta,
             Phi, angles, Dskip, gbuf, (__nv_bfloat16*)dQh, (__nv_bfloat16*)dKh, (__nv_bfloat16*)dV, (__nv_bfloat16*)dZ,
-            dAngles, dADT, dTs, dGam, dPsi, dZeta, dPhi, dD_, B, S, H, G, C, err};
+            dAngles, dADT, dTs, dGam, dPsi, dZeta, dPhi, dD_, B, S, H, G, C, ldV, ldZ, err};
   auto k0 = mimo_grad_state_kernel<128, 32>;
   auto k2 = mimo_chunk_grad_kernel<128, 32>;
   static bool cfg = false;

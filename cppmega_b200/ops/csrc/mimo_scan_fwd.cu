@@ -59,6 +59,7 @@ struct FwdArgs {
   float* tot;                  // [B,H,C]
   __nv_bfloat16* y;            // [B,S,H,P]
   int B, S, H, G, C;
+  long long ldV, ldZ;          // token strides of V and Z in elements
   int* err;
 };
 
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(THREADS2) mimo_local_state_kernel(const __grid
   // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
   const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
   const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
-  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.H);
+  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.ldV);
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -224,8 +225,8 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
   const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
   const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
-  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.H);
-  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.H);
+  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.ldV);
+  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.ldZ);
   const float dsk = a.Dskip[h];
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
@@ -381,13 +382,16 @@ using namespace cm::mimo;
 // Qb, Kb: [H,R,N] fp32; Psi, Zeta, Phi: [H,R,P] fp32; angles: [B,S,H,N/4] fp32 cumulative; D: [H] fp32.
 // Scratch: local [B,H,C,N,P] fp32, tot [B,H,C] fp32, states [B,H,C,N,P] bf16 (start state of every chunk).
 // Output y [B,S,H,P] bf16.  S % 32 == 0, P == 64, R == 4, N == 128, rotary divisor 4.
+// ldV / ldZ: elements between consecutive tokens of V / Z (H*P when packed; V and Z may be column slices of a wider
+// [B*S, W] matrix, in which case the batch stride must be S*ld).
 extern "C" int cm_mimo_scan_fwd(const void* Qn, const void* Kn, const void* V, const void* Z, const float* ADT,
                                 const float* DT, const float* Trap, const float* Qb, const float* Kb, const float* Psi,
                                 const float* Zeta, const float* Phi, const float* angles, const float* Dskip, float* local,
                                 float* tot, void* states, float* final_state, void* y, int B, int S, int H, int G, int N,
-                                int* err, cudaStream_t stream) {
+                                long long ldV, long long ldZ, int* err, cudaStream_t stream) {
   if (B <= 0 || S <= 0) return 0;
   if (S % LT || N != 128 || H % G) return -10;   // M = 64 accumulators use a different TMEM lane map
+  if (ldV < (long long)H * P || ldZ < (long long)H * P || ldV % 8 || ldZ % 8) return -11;   // 16-byte row loads
   const int C = S / LT;
   CUtensorMap tmQ, tmK, tmS;
   int rc = make_tmap_qk(&tmQ, Qn, B, S, G, N);
@@ -397,7 +401,7 @@ extern "C" int cm_mimo_scan_fwd(const void* Qn, const void* Kn, const void* V, c
   rc = make_tmap_2d_bf16(&tmS, states, (uint64_t)B * H * C * N, 64, 64, 128, 64);
   if (rc) return rc;
   FwdArgs a{(const __nv_bfloat16*)V, (const __nv_bfloat16*)Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, Dskip,
-            local, tot, (__nv_bfloat16*)y, B, S, H, G, C, err};
+            local, tot, (__nv_bfloat16*)y, B, S, H, G, C, ldV, ldZ, err};
   const int grid = B * H * C;
   if (N == 128) {
     auto k1 = mimo_local_state_kernel<128, 32>;
@@ -467,5 +471,5 @@ extern "C" int cm_mimo_scan_fwd_static(const void* Qn, const void* Kn, const voi
   p += (size_t)CM_MIMO_STATIC_MAX_CHUNKS * CM_MIMO_STATIC_STATE_ELEMS * 2;
   float* tot = reinterpret_cast<float*>(p);
   return cm_mimo_scan_fwd(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, Dskip, local, tot, states,
-                          final_state, y, B, S, H, G, N, err, stream);
+                          final_state, y, B, S, H, G, N, (long long)H * P, (long long)H * P, err, stream);
 }

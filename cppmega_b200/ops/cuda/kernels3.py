@@ -11,14 +11,14 @@ LT = 32
 
 
 def declare(L: ctypes.CDLL) -> None:
-    vp, i32 = ctypes.c_void_p, ctypes.c_int
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     fn = getattr(L, "cm_mimo_scan_fwd", None)
     if fn is not None:
-        fn.argtypes = [vp] * 19 + [i32] * 5 + [vp, vp]
+        fn.argtypes = [vp] * 19 + [i32] * 5 + [i64, i64] + [vp, vp]
         fn.restype = i32
     fn = getattr(L, "cm_mimo_scan_bwd", None)
     if fn is not None:
-        fn.argtypes = [vp] * 31 + [i32] * 5 + [vp, vp]
+        fn.argtypes = [vp] * 31 + [i32] * 5 + [i64, i64] + [vp, vp]
         fn.restype = i32
 
 
@@ -36,6 +36,17 @@ def _as_bsgrn(x: torch.Tensor) -> torch.Tensor:
     return y if y.is_contiguous() else y.contiguous()
 
 
+def token_strided(x: torch.Tensor):
+    """(tensor, token stride) for a [B,S,H,P] bf16 operand that the kernels can read in place: the last two dims packed,
+    batch stride = S * token stride, 16-byte aligned rows.  Anything else is copied to a packed tensor."""
+    B, S, H, P = x.shape
+    sb, ss, sh, sp = x.stride()
+    if sp == 1 and sh == P and sb == S * ss and ss >= H * P and ss % 8 == 0 and x.data_ptr() % 16 == 0:
+        return x, ss
+    x = x.contiguous()
+    return x, H * P
+
+
 def mimo_fwd_raw(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, want_state: bool = False):
     """Qn/Kn are [B,S,G,R,N] contiguous bf16.  Returns (y, states, tot[, final_state])."""
     from . import lib, err_word, stream_ptr, _check
@@ -49,10 +60,12 @@ def mimo_fwd_raw(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D,
     final = torch.empty(B, H, N, P, dtype=torch.float32, device=dev) if want_state else None
     y = torch.empty(B, S, H, P, dtype=torch.bfloat16, device=dev)
     f32 = lambda t: t.float().contiguous()
-    args = [Qn, Kn, V.contiguous(), Z.contiguous(), f32(ADT), f32(DT), f32(Trap), f32(Qb), f32(Kb), f32(Psi), f32(Zeta),
+    Vs, ldV = token_strided(V)
+    Zs, ldZ = token_strided(Z)
+    args = [Qn, Kn, Vs, Zs, f32(ADT), f32(DT), f32(Trap), f32(Qb), f32(Kb), f32(Psi), f32(Zeta),
             f32(Phi), f32(angles), f32(D)]
     _check(lib().cm_mimo_scan_fwd(*[t.data_ptr() for t in args], local.data_ptr(), tot.data_ptr(), states.data_ptr(),
-                                  final.data_ptr() if want_state else None, y.data_ptr(), B, S, H, G, N,
+                                  final.data_ptr() if want_state else None, y.data_ptr(), B, S, H, G, N, ldV, ldZ,
                                   err_word(dev).data_ptr(), stream_ptr()), "cm_mimo_scan_fwd")
     F_.count_launch("mimo_scan_fwd", 3)
     return (y, states, tot, final) if want_state else (y, states, tot)

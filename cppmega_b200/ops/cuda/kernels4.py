@@ -16,6 +16,11 @@ def declare(L: ctypes.CDLL) -> None:
         "cm_angle_cumsum_fwd": [vp, vp, i64, i64, i64, vp, i32, i32, i32, i32, vp],
         "cm_angle_cumsum_bwd": [vp, vp, vp, i64, i64, i64, vp, vp, vp, i32, i32, i32, i32, vp],
     }
+    f32 = ctypes.c_float
+    sig["cm_sparse_mla_fwd"] = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp]
+    sig["cm_sparse_mla_bwd"] = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp]
+    sig["cm_indexer_scores"] = [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
+    sig["cm_indexer_topk"] = [vp, vp, i32, i32, i32, vp]
     for name, args in sig.items():
         fn = getattr(L, name, None)
         if fn is not None:
@@ -68,5 +73,69 @@ def angle_cumsum(raw, dt):
     return AngleCumsumFn.apply(raw, dt)
 
 
+class SparseMLAFn(torch.autograd.Function):
+    """Sparse latent attention on the tcgen05 kernels: q [B,S,32,128], kv [B,Skv,128] bf16, idx [B,S,256] int32."""
+
+    @staticmethod
+    def forward(ctx, q, kv, idx, scale, d_v):
+        from . import lib, err_word, stream_ptr, _check
+        B, S, Hq, Dq = q.shape
+        Skv, topk = kv.shape[1], idx.shape[-1]
+        q, kv = q.contiguous(), kv.contiguous()
+        idx = idx.to(torch.int32).contiguous()
+        out = torch.empty(B, S, Hq, d_v, dtype=torch.bfloat16, device=q.device)
+        lse = torch.empty(B, S, Hq, dtype=torch.float32, device=q.device)
+        _check(lib().cm_sparse_mla_fwd(q.data_ptr(), kv.data_ptr(), idx.data_ptr(), out.data_ptr(), lse.data_ptr(), B, S, Skv,
+                                       Hq, Dq, topk, d_v, float(scale), err_word(q.device).data_ptr(), stream_ptr()),
+               "cm_sparse_mla_fwd")
+        F_.count_launch("sparse_mla")
+        ctx.save_for_backward(q, kv, idx, out, lse)
+        ctx.scale, ctx.d_v = float(scale), d_v
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from . import lib, err_word, stream_ptr, _check
+        q, kv, idx, out, lse = ctx.saved_tensors
+        B, S, Hq, Dq = q.shape
+        Skv, topk = kv.shape[1], idx.shape[-1]
+        dout = dout.to(torch.bfloat16).contiguous()
+        dq = torch.empty_like(q)
+        dkv = torch.zeros(B, Skv, Dq, dtype=torch.float32, device=q.device)
+        _check(lib().cm_sparse_mla_bwd(q.data_ptr(), kv.data_ptr(), idx.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                                       lse.data_ptr(), dq.data_ptr(), dkv.data_ptr(), B, S, Skv, Hq, Dq, topk, ctx.d_v,
+                                       ctx.scale, err_word(q.device).data_ptr(), stream_ptr()), "cm_sparse_mla_bwd")
+        F_.count_launch("sparse_mla_bwd")
+        return dq, dkv.to(kv.dtype), None, None, None
+
+
+def sparse_mla(q, kv, idx, scale, d_v):
+    if (q.dtype != torch.bfloat16 or kv.dtype != torch.bfloat16 or q.dim() != 4 or q.shape[2] != 32 or q.shape[3] != 128
+            or kv.shape[-1] != 128 or idx.shape[-1] != 256 or d_v != 64):
+        return None
+    return SparseMLAFn.apply(q, kv, idx, scale, d_v)
+
+
+def indexer_topk(q_idx, k_idx, w, topk: int):
+    """Causal top-k key positions per query (int32 [B,S,topk], unordered, -1 padded) on the indexer kernels."""
+    if (q_idx.dtype != torch.bfloat16 or k_idx.dtype != torch.bfloat16 or q_idx.dim() != 4 or q_idx.shape[2] != 32
+            or q_idx.shape[3] != 64 or q_idx.shape[1] % 4 or q_idx.shape[1] > 8192 or k_idx.shape[1] != q_idx.shape[1]
+            or topk > 2048):
+        return None
+    from . import lib, err_word, stream_ptr, _check
+    B, S = q_idx.shape[:2]
+    q, k = q_idx.contiguous(), k_idx.contiguous()
+    wf = w.float().contiguous()
+    scores = torch.empty(B, S, S, dtype=torch.float32, device=q.device)
+    out = torch.empty(B, S, topk, dtype=torch.int32, device=q.device)
+    _check(lib().cm_indexer_scores(q.data_ptr(), k.data_ptr(), wf.data_ptr(), scores.data_ptr(), B, S, 32, 64,
+                                   err_word(q.device).data_ptr(), stream_ptr()), "cm_indexer_scores")
+    _check(lib().cm_indexer_topk(scores.data_ptr(), out.data_ptr(), B, S, topk, stream_ptr()), "cm_indexer_topk")
+    F_.count_launch("indexer_topk", 2)
+    return out
+
+
 def register() -> None:
+    F_.register_cuda("indexer_topk", indexer_topk)
     F_.register_cuda("angle_cumsum", angle_cumsum)
+    F_.register_cuda("sparse_mla", sparse_mla)

@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import functional as F_
-from .kernels3 import LT, _as_bsgrn
+from .kernels3 import LT, _as_bsgrn, token_strided
 
 
 def mimo_bwd(saved, dy, states, tot):
@@ -34,10 +34,12 @@ def mimo_bwd(saved, dy, states, tot):
     dZeta = torch.zeros(H, R, P, dtype=torch.float32, device=dev)
     dPhi = torch.zeros(H, R, P, dtype=torch.float32, device=dev)
     dD = torch.zeros(H, dtype=torch.float32, device=dev)
-    ins = [Qn, Kn, V.contiguous(), Z.contiguous(), dyc, ADTf, DTf, Trapf, f32(Qb), f32(Kb), f32(Psi), f32(Zeta), f32(Phi),
+    Vs, ldV = token_strided(V)
+    Zs, ldZ = token_strided(Z)
+    ins = [Qn, Kn, Vs, Zs, dyc, ADTf, DTf, Trapf, f32(Qb), f32(Kb), f32(Psi), f32(Zeta), f32(Phi),
            f32(angles), f32(D), states, tot]
     outs = [gbuf, dend, dQh, dKh, dV, dZ, dAng, dADT, dTs, dGam, dPsi, dZeta, dPhi, dD]
-    _check(lib().cm_mimo_scan_bwd(*[t.data_ptr() for t in ins], *[t.data_ptr() for t in outs], B, S, H, G, N,
+    _check(lib().cm_mimo_scan_bwd(*[t.data_ptr() for t in ins], *[t.data_ptr() for t in outs], B, S, H, G, N, ldV, ldZ,
                                   err_word(dev).data_ptr(), stream_ptr()), "cm_mimo_scan_bwd")
     F_.count_launch("mimo_scan_bwd", 3)
     del gbuf, dend

@@ -195,7 +195,11 @@ def m2rnn_scan(q, k, v, W, f):
 def indexer_topk(q_idx, k_idx, w, topk: int):
     fn = _cuda("indexer_topk", q_idx)
     if fn is not None:
-        return fn(q_idx, k_idx, w, topk)
+        with torch.no_grad():
+            out = fn(q_idx, k_idx, w, topk)
+        if out is not None:
+            return out
+        _FALLBACKS["indexer_topk(shape)"] += 1
     with torch.no_grad():
         return ref.indexer_topk(q_idx, k_idx, w, topk)
 
@@ -203,7 +207,10 @@ def indexer_topk(q_idx, k_idx, w, topk: int):
 def sparse_mla(q, kv, indices, scale: float, d_v: int):
     fn = _cuda("sparse_mla", q)
     if fn is not None:
-        return fn(q, kv, indices, scale, d_v)
+        out = fn(q, kv, indices, scale, d_v)
+        if out is not None:
+            return out
+        _FALLBACKS["sparse_mla(shape)"] += 1
     return ref.sparse_mla(q, kv, indices, scale, d_v)[0]
 
 

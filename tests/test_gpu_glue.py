@@ -62,3 +62,82 @@ def test_local_fused_moe_matches_plain_dispatch():
     assert set(g0) == set(g1)
     for n in g0:
         assert _rel(g1[n], g0[n]) < 4e-2, n
+
+
+@pytest.mark.parametrize("B,S,Skv", [(1, 300, 300), (2, 520, 520)])
+def test_sparse_mla_kernels(B, S, Skv):
+    from cppmega_b200.ops import reference as ref
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import kernels4
+    torch.manual_seed(0)
+    Hq, D, TK, DV = 32, 128, 256, 64
+    q = (torch.randn(B, S, Hq, D, device="cuda") * 0.5).bfloat16().requires_grad_()
+    kv = (torch.randn(B, Skv, D, device="cuda") * 0.5).bfloat16().requires_grad_()
+    # causal random selections: query s may pick keys <= s; the first positions see fewer than TK keys (-1 padding)
+    idx = torch.full((B, S, TK), -1, dtype=torch.int32, device="cuda")
+    for b in range(B):
+        for s in range(S):
+            n = min(TK, s + 1)
+            perm = torch.randperm(s + 1, device="cuda")[:n]
+            idx[b, s, :n] = perm.to(torch.int32)
+    scale = D ** -0.5
+    out = kernels4.sparse_mla(q, kv, idx, scale, DV)
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    cu.check_errors()
+    q2 = q.detach().float().requires_grad_()
+    kv2 = kv.detach().float().requires_grad_()
+    ref_out, _ = ref.sparse_mla(q2, kv2, idx, scale, DV)
+    ref_out.backward(g.float())
+    assert torch.isfinite(out.float()).all()
+    assert _rel(out, ref_out) < 2e-2
+    assert _rel(q.grad, q2.grad) < 3e-2
+    assert _rel(kv.grad, kv2.grad) < 3e-2
+
+
+def test_mimo_scan_reads_column_slices_in_place():
+    """V and Z given as column slices of one wide projection output give the same result as packed copies."""
+    from cppmega_b200.ops.cuda import kernels3
+    from cppmega_b200.tools.ncu_cases import _scan_inputs
+    B, S, H, G = 2, 128, 4, 2
+    Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D = _scan_inputs(B, S, H, G)
+    wide = torch.zeros(B, S, 2 * H * 64 + 72, dtype=torch.bfloat16, device="cuda")
+    wide[..., :H * 64] = Z.reshape(B, S, -1)
+    wide[..., H * 64:2 * H * 64] = V.reshape(B, S, -1)
+    Zs = wide[..., :H * 64].view(B, S, H, 64)
+    Vs = wide[..., H * 64:2 * H * 64].view(B, S, H, 64)
+    assert not Vs.is_contiguous() and kernels3.token_strided(Vs)[1] == wide.shape[-1]
+    y0, _, _ = kernels3.mimo_fwd_raw(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D)
+    y1, _, _ = kernels3.mimo_fwd_raw(Qn, Kn, Vs, Zs, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D)
+    torch.cuda.synchronize()
+    assert torch.equal(y0, y1)
+
+
+@pytest.mark.parametrize("B,S,topk", [(2, 512, 256), (1, 1100, 256)])
+def test_indexer_topk_kernels(B, S, topk):
+    from cppmega_b200.ops import reference as ref
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import kernels4
+    torch.manual_seed(0)
+    q = torch.randn(B, S, 32, 64, device="cuda").bfloat16()
+    k = torch.randn(B, S, 64, device="cuda").bfloat16()
+    w = torch.randn(B, S, 32, device="cuda") * 0.1
+    idx = kernels4.indexer_topk(q, k, w, topk)
+    torch.cuda.synchronize()
+    cu.check_errors()
+    sc = ref.indexer_scores(q, k, w)
+    causal = torch.ones(S, S, dtype=torch.bool, device="cuda").tril()
+    sc = sc.masked_fill(~causal, float("-inf"))
+    ref_idx = ref.indexer_topk(q, k, w, topk)
+    for b in range(B):
+        for i in (0, 1, topk - 2, topk - 1, topk, topk + 1, S // 2, S - 1):
+            got = idx[b, i]
+            got_valid = got[got >= 0]
+            n = min(i + 1, topk)
+            assert got_valid.numel() == n and got_valid.unique().numel() == n and int(got_valid.max()) <= i
+            # same selection up to ties: the smallest selected score is not below the largest rejected one
+            sel = sc[b, i, got_valid.long()]
+            want = sc[b, i, ref_idx[b, i][ref_idx[b, i] >= 0].long()]
+            assert abs(sel.min().item() - want.min().item()) <= 2e-2 * max(1.0, abs(want.min().item()))
+            assert abs(sel.sum().item() - want.sum().item()) <= 2e-2 * max(1.0, abs(want.sum().item()))
