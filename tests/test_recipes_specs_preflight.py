@@ -1,0 +1,152 @@
+"""Recipes, stack specs, launch preflight and the host-side failure detection."""
+import threading
+import time
+
+import pytest
+import torch
+
+from cppmega_b200.config import recipes as R
+from cppmega_b200.config.model import nam56r_full, nam56r_tiny
+from cppmega_b200.models import specs as S
+from cppmega_b200.utils import preflight as PF
+from cppmega_b200.utils.deprecated import DeprecatedPathError
+from cppmega_b200.utils.watchdog import DictStore, RankHeartbeat, StepWatchdog
+
+
+def test_recipes_render_and_refuse_mock_data():
+    r = R.get_recipe("native_pretrain")
+    with pytest.raises(ValueError, match="refuses mock data"):
+        r.to_args(mock_data=True, data_path=None)
+    argv = r.to_args(data_path="/data/corpus")
+    assert "--expert-model-parallel-size" in argv and argv[argv.index("--expert-model-parallel-size") + 1] == "8"
+    assert "/data/corpus" in argv
+    env = r.to_env_dict()
+    assert env["NCCL_NVLS_ENABLE"] == "0"
+    assert R.get_recipe("mamba3_native").to_env_dict()["CUDA_DEVICE_MAX_CONNECTIONS"] == "1"     # TP overlap ordering
+    assert R.get_recipe("smoke_test").to_args()                                                   # synthetic data allowed
+    assert "torch.distributed.run" in R.get_recipe("smoke_test").shell()
+    with pytest.raises(DeprecatedPathError):
+        R.get_recipe("mamba3_te")
+    assert R.get_recipe("mamba3_te", ack=True).profile.model.mamba_variant == "ssd"
+    with pytest.raises(KeyError):
+        R.get_recipe("nope")
+
+
+def test_recipe_argv_round_trips_through_the_parser():
+    from cppmega_b200.training.arguments import parse_args
+    r = R.get_recipe("noconv")
+    mcfg, pcfg, tcfg, extras = parse_args(r.to_args(data_path="/d/x"))
+    assert mcfg.mamba_variant == "noconv_ssd" and pcfg.ep == 8 and tcfg.micro_batch_size == 4
+    assert extras["data_path"] == "/d/x" and not extras["mock_data"]
+
+
+def test_moe_flag_validation():
+    import dataclasses
+    from cppmega_b200.parallel.state import ParallelConfig
+    cfg = nam56r_full()
+    bad = dataclasses.replace(cfg, moe=dataclasses.replace(cfg.moe, dispatcher="flex"))
+    with pytest.raises(ValueError, match="expert parallelism"):
+        R.validate_moe_flags(bad, ParallelConfig(ep=1))
+    R.validate_moe_flags(bad, ParallelConfig(ep=8))
+
+
+def test_stack_specs():
+    cfg = nam56r_full()
+    full = S.apply_spec(cfg, S.get_spec("nam56r_full"))
+    idx = S.custom_layer_indices(full)
+    assert len(idx["dsa"]) == 9 and len(idx["mla"]) == 4 and idx["m2rnn"] == [12, 24, 36, 48]
+    lite = S.apply_spec(cfg, S.get_spec("nam56r_lite"))
+    assert "dsa" not in S.custom_layer_indices(lite) and "m2rnn" not in S.custom_layer_indices(lite)
+    local = S.apply_spec(cfg, S.get_spec("mamba_local"))
+    kinds = set(local.layer_kinds())
+    assert kinds == {"mla", "mlp", "mamba3"} and local.mtp.num_layers == 0 and local.mamba_variant == "ssd"
+    desc = S.describe_stack(S.apply_spec(cfg, S.get_spec("nam56r_noconv")))
+    assert any("SSDMixer[noconv_ssd]" in d[2] for d in desc) and len(desc) == 52
+    with pytest.raises(KeyError):
+        S.get_spec("x")
+
+
+def test_every_spec_builds_and_runs_tiny():
+    from cppmega_b200.models.nam56r import build_model
+    for name in S.SPECS:
+        cfg = S.apply_spec(nam56r_tiny(seq_length=32), S.get_spec(name))
+        model = build_model(cfg)
+        ids = torch.randint(0, cfg.vocab_size, (1, 32))
+        out = model(ids, ids)
+        assert torch.isfinite(out["loss"]), name
+
+
+def test_preflight_parses_ptxas_and_flags_violations(tmp_path):
+    text = """ptxas info    : Compiling entry function '_Z4kernA' for 'sm_100a'
+ptxas info    : Function properties for _Z4kernA
+    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
+ptxas info    : Used 96 registers, used 1 barriers, 1024 bytes smem
+ptxas info    : Compiling entry function '_Z4kernB' for 'sm_100a'
+ptxas info    : Function properties for _Z4kernB
+    400 bytes stack frame, 380 bytes spill stores, 400 bytes spill loads
+ptxas info    : Used 255 registers, used 1 barriers, 60000 bytes smem
+"""
+    ks = PF.parse_ptxas(text)
+    assert [k.name for k in ks] == ["_Z4kernA", "_Z4kernB"] and ks[0].registers == 96 and ks[1].spill_stores == 380
+    (tmp_path / "x.ptxas.txt").write_text(text)
+    rep = PF.static_check(tmp_path)
+    assert not rep.ok and any("static shared memory" in p for p in rep.problems)
+    assert any("spills" in w for w in rep.warnings)
+    src = tmp_path / "src"
+    src.mkdir()
+    (src / "k.cu").write_text("tmem_alloc(slot, 768);\n tmem_alloc(slot, 256);")
+    rep2 = PF.source_check(src)
+    assert len(rep2.problems) == 1 and "768" in rep2.problems[0]
+    assert PF.source_check().ok and "preflight" in PF.run_all().render()
+
+
+def test_step_watchdog_fires_only_without_progress():
+    fired = []
+    wd = StepWatchdog(0.3, rank=0, on_timeout=lambda idle, step: fired.append((idle, step)), poll_s=0.05).start()
+    for s in range(5):
+        time.sleep(0.1)
+        wd.beat(s)
+    assert not fired
+    time.sleep(0.6)
+    wd.stop()
+    assert fired and fired[0][1] == 4 and wd.fired
+
+
+def test_rank_heartbeat_reports_dead_and_lagging_ranks():
+    store = DictStore()
+    now = [100.0]
+    hbs = [RankHeartbeat(store, r, 3, limit_s=5.0, clock=lambda: now[0]) for r in range(3)]
+    for h in hbs:
+        h.beat(10)
+    assert hbs[0].dead_ranks() == []
+    now[0] = 104.0
+    hbs[0].beat(12)
+    hbs[1].beat(12)                 # rank 2 stopped: raised, exited, or never joined this step
+    now[0] = 107.0
+    assert hbs[0].dead_ranks() == [2] and hbs[1].dead_ranks() == [2]
+    assert hbs[0].lagging_ranks(max_lag_steps=1) == [2]
+    fresh = RankHeartbeat(DictStore(), 0, 2, limit_s=1.0)
+    fresh.beat(0)
+    assert fresh.dead_ranks() == [1]          # a rank that never wrote a heartbeat counts as missing
+
+
+def test_heartbeat_threads_share_a_store():
+    store = DictStore()
+    stop = threading.Event()
+
+    def worker(rank):
+        hb = RankHeartbeat(store, rank, 2, limit_s=0.5)
+        step = 0
+        while not stop.is_set() and step < 50:
+            hb.beat(step)
+            step += 1
+            time.sleep(0.01)
+
+    ts = [threading.Thread(target=worker, args=(r,)) for r in range(2)]
+    for t in ts:
+        t.start()
+    time.sleep(0.1)
+    assert RankHeartbeat(store, 0, 2, limit_s=0.5).dead_ranks() == []
+    stop.set()
+    for t in ts:
+        t.join()
