@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 import torch.distributed as dist
 import torch.nn as nn
-from torch.utils.checkpoint import checkpoint
+from ..utils.recompute import checkpoint
 
 from ..config.model import ModelConfig
 from ..ops import functional as F_
@@ -187,9 +187,9 @@ class NAM56RModel(nn.Module):
                 # pick the indices once, outside the checkpoint, so the recomputation in
                 # backward replays the layer with the same selection
                 idx = layer.select_indices(x, cache)
-                x = checkpoint(layer, x, None, idx, use_reentrant=False)
+                x = checkpoint(layer, x, None, idx)
             elif ck:
-                x = checkpoint(layer, x, None, None, use_reentrant=False)
+                x = checkpoint(layer, x, None, None)
             else:
                 x = layer(x, cache)
         return x

@@ -141,8 +141,22 @@ class LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).view(ctx.xshape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+            dw = wgrad_into_main_grad(w, lambda out, acc: gemm(dy2, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
         return dx, dw
+
+
+def wgrad_into_main_grad(w: torch.Tensor, run):
+    """Weight gradient either as a fresh tensor or, when the optimizer asked for it (``w.fuse_wgrad_accumulation``),
+    accumulated by the GEMM epilogue straight into the parameter's slice of the flat gradient buffer.  In the fused
+    case autograd still gets a tensor of the right shape (uninitialised, never read): the optimizer's hook sees
+    ``grad_added_to_main_grad`` and drops it.  ``run(out, accumulate)`` launches the GEMM."""
+    mg = getattr(w, "main_grad", None)
+    if (mg is not None and getattr(w, "fuse_wgrad_accumulation", False) and mg.dtype in (torch.bfloat16, torch.float32)
+            and mg.is_contiguous() and mg.shape == w.shape):
+        run(mg, True)
+        w.grad_added_to_main_grad = True
+        return torch.empty(w.shape, dtype=w.dtype, device=w.device)
+    return run(None, False)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor):

@@ -84,11 +84,16 @@ class GroupedLinearFn(torch.autograd.Function):
                    "cm_grouped_gemm_rows_bf16(dgrad)")
             F_.count_launch("grouped_gemm")
         if ctx.needs_input_grad[1]:
-            dw = torch.empty_like(w)
-            _check(lib().cm_grouped_gemm_k_bf16(dy.data_ptr(), xp.data_ptr(), dw.data_ptr(), rows, N, K, E,
-                                                seg_offsets.data_ptr(), 0, 0, err, stream_ptr()),
-                   "cm_grouped_gemm_k_bf16")
-            F_.count_launch("grouped_gemm")
+            from . import wgrad_into_main_grad
+
+            def run(out, acc):
+                out = torch.empty_like(w) if out is None else out
+                _check(lib().cm_grouped_gemm_k_bf16(dy.data_ptr(), xp.data_ptr(), out.data_ptr(), rows, N, K, E,
+                                                    seg_offsets.data_ptr(), int(out.dtype == torch.float32), int(acc), err,
+                                                    stream_ptr()), "cm_grouped_gemm_k_bf16")
+                F_.count_launch("grouped_gemm")
+                return out
+            dw = wgrad_into_main_grad(w, run)
         return dx, dw, None, None
 
 

@@ -76,9 +76,10 @@ class MimoScanFn(torch.autograd.Function):
     otherwise recomputes group by group in PyTorch."""
 
     @staticmethod
-    def forward(ctx, Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk):
-        Qn, Kn = _as_bsgrn(Q), _as_bsgrn(K)
-        y, states, tot = mimo_fwd_raw(Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D)
+    def forward(ctx, Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk, precomputed=None):
+        if precomputed is None:
+            precomputed = mimo_fwd_raw(_as_bsgrn(Q), _as_bsgrn(K), V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D)
+        y, states, tot = precomputed
         ctx.save_for_backward(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, states, tot)
         ctx.div, ctx.chunk = div, 64          # chunk length of the PyTorch recomputation, not of the kernel
         return y
@@ -89,10 +90,10 @@ class MimoScanFn(torch.autograd.Function):
         *saved, states, tot = ctx.saved_tensors
         if getattr(lib(), "cm_mimo_scan_bwd", None) is not None and "mimo_scan_bwd" not in F_._DISABLED:
             from .mimo_bwd import mimo_bwd
-            return (*mimo_bwd(saved, dy, states, tot), None, None)
+            return (*mimo_bwd(saved, dy, states, tot), None, None, None)
         from ..mimo_scan_lean import lean_backward
         F_._FALLBACKS["mimo_scan_bwd"] += 1
-        return lean_backward(saved, dy, ctx.div, ctx.chunk)
+        return (*lean_backward(saved, dy, ctx.div, ctx.chunk), None)
 
 
 def mimo_scan(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk):
@@ -103,7 +104,12 @@ def mimo_scan(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div,
             from .. import mimo_scan_ref as R
             return R.mimo_scan_chunked(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk)
         return mimo_scan_lean(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, 64)
-    return MimoScanFn.apply(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk)
+    from ...utils.recompute import stashed_call
+    # inside a recomputed layer the three forward kernels run once: the replay picks up (y, chunk states, totals)
+    return stashed_call(
+        "mimo_scan",
+        lambda: mimo_fwd_raw(_as_bsgrn(Q), _as_bsgrn(K), V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D),
+        lambda res: MimoScanFn.apply(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk, res))
 
 
 def register() -> None:

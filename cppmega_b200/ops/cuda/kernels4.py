@@ -73,22 +73,29 @@ def angle_cumsum(raw, dt):
     return AngleCumsumFn.apply(raw, dt)
 
 
+def sparse_mla_fwd_raw(q, kv, idx, scale, d_v):
+    from . import lib, err_word, stream_ptr, _check
+    B, S, Hq, Dq = q.shape
+    Skv, topk = kv.shape[1], idx.shape[-1]
+    q, kv = q.contiguous(), kv.contiguous()
+    idx = idx.to(torch.int32).contiguous()
+    out = torch.empty(B, S, Hq, d_v, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(B, S, Hq, dtype=torch.float32, device=q.device)
+    _check(lib().cm_sparse_mla_fwd(q.data_ptr(), kv.data_ptr(), idx.data_ptr(), out.data_ptr(), lse.data_ptr(), B, S, Skv,
+                                   Hq, Dq, topk, d_v, float(scale), err_word(q.device).data_ptr(), stream_ptr()),
+           "cm_sparse_mla_fwd")
+    F_.count_launch("sparse_mla")
+    return out, lse
+
+
 class SparseMLAFn(torch.autograd.Function):
     """Sparse latent attention on the tcgen05 kernels: q [B,S,32,128], kv [B,Skv,128] bf16, idx [B,S,256] int32."""
 
     @staticmethod
-    def forward(ctx, q, kv, idx, scale, d_v):
-        from . import lib, err_word, stream_ptr, _check
-        B, S, Hq, Dq = q.shape
-        Skv, topk = kv.shape[1], idx.shape[-1]
+    def forward(ctx, q, kv, idx, scale, d_v, precomputed=None):
         q, kv = q.contiguous(), kv.contiguous()
         idx = idx.to(torch.int32).contiguous()
-        out = torch.empty(B, S, Hq, d_v, dtype=torch.bfloat16, device=q.device)
-        lse = torch.empty(B, S, Hq, dtype=torch.float32, device=q.device)
-        _check(lib().cm_sparse_mla_fwd(q.data_ptr(), kv.data_ptr(), idx.data_ptr(), out.data_ptr(), lse.data_ptr(), B, S, Skv,
-                                       Hq, Dq, topk, d_v, float(scale), err_word(q.device).data_ptr(), stream_ptr()),
-               "cm_sparse_mla_fwd")
-        F_.count_launch("sparse_mla")
+        out, lse = precomputed if precomputed is not None else sparse_mla_fwd_raw(q, kv, idx, scale, d_v)
         ctx.save_for_backward(q, kv, idx, out, lse)
         ctx.scale, ctx.d_v = float(scale), d_v
         return out
@@ -106,14 +113,16 @@ class SparseMLAFn(torch.autograd.Function):
                                        lse.data_ptr(), dq.data_ptr(), dkv.data_ptr(), B, S, Skv, Hq, Dq, topk, ctx.d_v,
                                        ctx.scale, err_word(q.device).data_ptr(), stream_ptr()), "cm_sparse_mla_bwd")
         F_.count_launch("sparse_mla_bwd")
-        return dq, dkv.to(kv.dtype), None, None, None
+        return dq, dkv.to(kv.dtype), None, None, None, None
 
 
 def sparse_mla(q, kv, idx, scale, d_v):
     if (q.dtype != torch.bfloat16 or kv.dtype != torch.bfloat16 or q.dim() != 4 or q.shape[2] != 32 or q.shape[3] != 128
             or kv.shape[-1] != 128 or idx.shape[-1] != 256 or d_v != 64):
         return None
-    return SparseMLAFn.apply(q, kv, idx, scale, d_v)
+    from ...utils.recompute import stashed_call
+    return stashed_call("sparse_mla", lambda: sparse_mla_fwd_raw(q.detach(), kv.detach(), idx, scale, d_v),
+                        lambda res: SparseMLAFn.apply(q, kv, idx, scale, d_v, res))
 
 
 def indexer_topk(q_idx, k_idx, w, topk: int):

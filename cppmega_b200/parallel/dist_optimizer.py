@@ -236,7 +236,10 @@ class DistributedOptimizer:
         for buf in self.buffers:
             for p in buf.params:
                 def hook(param, buf=buf):
-                    if param.grad is not None:
+                    if getattr(param, "grad_added_to_main_grad", False):
+                        param.grad_added_to_main_grad = False      # the wgrad GEMM accumulated in place
+                        param.grad = None
+                    elif param.grad is not None:
                         param.main_grad.add_(param.grad.view_as(param.main_grad))
                         param.grad = None
                     if not self._last_microbatch:
@@ -246,6 +249,8 @@ class DistributedOptimizer:
                     if b.pending == 0 and self.overlap and not b.reduced:
                         buf.reduce_bucket(b, async_op=True, scale=self._grad_scale / buf.grad_div)
                 self._hooks.append(p.register_post_accumulate_grad_hook(hook))
+                # GEMM epilogues may add weight gradients directly into the flat buffer (CUDA, 2-D/3-D bf16 weights)
+                p.fuse_wgrad_accumulation = bool(p.is_cuda and p.dim() >= 2 and p.dtype == torch.bfloat16)
         self._last_microbatch = True
 
     def set_microbatch(self, is_last: bool, grad_scale: float = 1.0):

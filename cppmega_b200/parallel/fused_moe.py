@@ -238,15 +238,20 @@ def _grouped(x, w, tile_expert, rows, b_mn, out=None):
     return out
 
 
-def _grouped_wgrad(dy, x, seg_offsets, E):
-    from ..ops.cuda import lib, err_word, stream_ptr, _check
+def _grouped_wgrad(dy, x, seg_offsets, E, w=None):
+    """dW[e] = dy_e^T x_e per expert segment; accumulated into ``w.main_grad`` when the optimizer allows it."""
+    from ..ops.cuda import lib, err_word, stream_ptr, _check, wgrad_into_main_grad
     rows, N = dy.shape
     K = x.shape[1]
-    dw = torch.empty(E, N, K, dtype=dy.dtype, device=dy.device)
-    _check(lib().cm_grouped_gemm_k_bf16(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), rows, N, K, E, seg_offsets.data_ptr(),
-                                        0, 0, err_word(dy.device).data_ptr(), stream_ptr()), "cm_grouped_gemm_k_bf16")
-    F_.count_launch("grouped_gemm")
-    return dw
+
+    def run(out, acc):
+        out = torch.empty(E, N, K, dtype=dy.dtype, device=dy.device) if out is None else out
+        _check(lib().cm_grouped_gemm_k_bf16(dy.data_ptr(), x.data_ptr(), out.data_ptr(), rows, N, K, E, seg_offsets.data_ptr(),
+                                            int(out.dtype == torch.float32), int(acc), err_word(dy.device).data_ptr(),
+                                            stream_ptr()), "cm_grouped_gemm_k_bf16")
+        F_.count_launch("grouped_gemm")
+        return out
+    return run(None, False) if w is None else wgrad_into_main_grad(w, run)
 
 
 class _FusedMoEFn(torch.autograd.Function):
@@ -299,12 +304,12 @@ class _FusedMoEFn(torch.autograd.Function):
         with torch.no_grad():
             a = _sw(h)
             da = _grouped(grad_in, w2, plan.tile_expert, cap, True)                  # [cap, F]
-            dw2 = _grouped_wgrad(grad_in, a, plan.seg_offsets, E)                   # [E, H, F]
+            dw2 = _grouped_wgrad(grad_in, a, plan.seg_offsets, E, w2)                   # [E, H, F]
             dh = torch.empty_like(h)
             _check(lib().cm_swiglu_bwd(h.data_ptr(), da.data_ptr(), dh.data_ptr(), cap, Fh, stream_ptr()), "cm_swiglu_bwd")
             F_.count_launch("swiglu_bwd")
             _grouped(dh, w1, plan.tile_expert, cap, True, out=grad_out)               # [cap, H]
-            dw1 = _grouped_wgrad(dh, xin, plan.seg_offsets, E)                        # [E, 2F, H]
+            dw1 = _grouped_wgrad(dh, xin, plan.seg_offsets, E, w1)                        # [E, 2F, H]
         heap.barrier(f0 + 3, epb)
         dx = _pull_combine(heap, grad_out, plan, None, H, ctx.x_dtype)
         return dx, dprobs.to(ctx.p_dtype), dw1, dw2, None, None, None
