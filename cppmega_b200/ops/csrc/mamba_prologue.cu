@@ -106,9 +106,60 @@ __global__ void __launch_bounds__(256) angle_reduce_kernel(const float* __restri
   }
 }
 
+// Per-head operand gradients of the scan -> gradients of the group-shared operand and of the per-head bias:
+//   dgrp[t, g, c]  = sum_{h in group g} dh[t, h, c]            (bf16 out)
+//   dbias[h, c]   += sum_t dh[t, h, c]                          (fp32, atomically accumulated; caller zeroes)
+// dh [T, H, C] bf16 with C = R * N columns.  One block covers TT tokens of one group; a thread owns two columns.
+constexpr int HR_TT = 64;
+template <int HPG>
+__global__ void __launch_bounds__(256) head_reduce_kernel(const __nv_bfloat16* __restrict__ dh, __nv_bfloat16* __restrict__ dgrp,
+                                                          float* __restrict__ dbias, long long T, int H, int C) {
+  const int g = blockIdx.y, G = H / HPG;
+  const long long t0 = (long long)blockIdx.x * HR_TT;
+  const long long t1 = t0 + HR_TT < T ? t0 + HR_TT : T;
+  for (int c2 = threadIdx.x; c2 < C / 2; c2 += blockDim.x) {
+    float bx[HPG], by[HPG];
+#pragma unroll
+    for (int j = 0; j < HPG; ++j) { bx[j] = 0.f; by[j] = 0.f; }
+    for (long long t = t0; t < t1; ++t) {
+      const __nv_bfloat162* row = reinterpret_cast<const __nv_bfloat162*>(dh + ((size_t)t * H + (size_t)g * HPG) * C) + c2;
+      float sx = 0.f, sy = 0.f;
+#pragma unroll
+      for (int j = 0; j < HPG; ++j) {
+        const float2 v = __bfloat1622float2(row[(size_t)j * (C / 2)]);
+        bx[j] += v.x; by[j] += v.y;
+        sx += v.x; sy += v.y;
+      }
+      reinterpret_cast<__nv_bfloat162*>(dgrp + ((size_t)t * G + g) * C)[c2] = __floats2bfloat162_rn(sx, sy);
+    }
+#pragma unroll
+    for (int j = 0; j < HPG; ++j) {
+      float* d = dbias + ((size_t)g * HPG + j) * C + 2 * c2;
+      atomicAdd(d, bx[j]);
+      atomicAdd(d + 1, by[j]);
+    }
+  }
+}
+
 }  // namespace cm
 
 using namespace cm;
+
+extern "C" int cm_head_reduce(const void* dh, void* dgrp, float* dbias, long long T, int H, int G, int C, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (C % 2 || H % G) return -10;
+  dim3 grid((unsigned)((T + HR_TT - 1) / HR_TT), G);
+  const int hpg = H / G;
+  auto a = (const __nv_bfloat16*)dh;
+  auto o = (__nv_bfloat16*)dgrp;
+  if (hpg == 16) head_reduce_kernel<16><<<grid, 256, 0, s>>>(a, o, dbias, T, H, C);
+  else if (hpg == 8) head_reduce_kernel<8><<<grid, 256, 0, s>>>(a, o, dbias, T, H, C);
+  else if (hpg == 4) head_reduce_kernel<4><<<grid, 256, 0, s>>>(a, o, dbias, T, H, C);
+  else if (hpg == 2) head_reduce_kernel<2><<<grid, 256, 0, s>>>(a, o, dbias, T, H, C);
+  else if (hpg == 1) head_reduce_kernel<1><<<grid, 256, 0, s>>>(a, o, dbias, T, H, C);
+  else return -12;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
 
 // raw [B,S,A] fp32 contiguous; dt addressed as dt[b*dsb + h*dsh + t*dss] (element strides); out [B,S,H,A] fp32.
 extern "C" int cm_angle_cumsum_fwd(const float* raw, const float* dt, long long dsb, long long dsh, long long dss, float* out,

@@ -115,12 +115,13 @@ __device__ __forceinline__ void compute_chunk_scalars(ChunkScalars* sc, const fl
 
 // cos/sin of the chunk's rotary angles into shared memory: cs_tab[t][a] (a < NROT).
 // angles [B,S,H,NROT] fp32 (already cumulative).  Each thread (t = i/4, r = i%4) fills a quarter row.
-// Table rows are NROT + 1 floats apart so that the eight tokens a warp touches at once fall into different banks.
+// Table rows are NROT + 4 floats apart: 16-byte aligned for vector loads, and the tokens a warp touches at once fall
+// into different banks.
 // NWG = warpgroups (of 128 threads) in the CTA; the work of a row is split between them.
 template <int NROT>
-constexpr int tab_stride() { return NROT + 1; }
+constexpr int tab_stride() { return NROT + 4; }   // 16-byte aligned rows; 4-bank skew per row keeps 128-bit loads conflict-free
 template <int NROT>
-constexpr int tab_floats() { return LT * (NROT + 1); }   // one table; (32 * 33 * 4) bytes keeps 16-byte alignment
+constexpr int tab_floats() { return LT * (NROT + 4); }   // one table
 
 template <int NROT, int NWG = 1>
 __device__ __forceinline__ void fill_sincos(float* cos_tab, float* sin_tab, const float* __restrict__ angles,
@@ -154,25 +155,32 @@ __device__ __forceinline__ void fill_sincos4(float* cos_tab, float* sin_tab, con
   constexpr int TS = tab_stride<NROT>();
   const int off = (r * 2 + wg) * 4;
   const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+  float cv[4], sv[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     float x = av[j];
     x -= 6.283185307179586f * rintf(x * 0.15915494309189535f);
-    float s, c;
-    __sincosf(x, &s, &c);
-    cos_tab[t * TS + off + j] = c;
-    sin_tab[t * TS + off + j] = s;
+    __sincosf(x, &sv[j], &cv[j]);
   }
+  *reinterpret_cast<float4*>(cos_tab + t * TS + off) = make_float4(cv[0], cv[1], cv[2], cv[3]);
+  *reinterpret_cast<float4*>(sin_tab + t * TS + off) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+}
+
+__device__ __forceinline__ void ld8(float (&o)[8], const float* p) {        // two 128-bit shared/global loads
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
 }
 
 // In-place transform of one operand tile (row i of this thread): x <- rot(x + bias[r]).
 // Tile = N/64 slabs of [128 x 64] bf16, swizzled.  bias [R,N] fp32 for this head.  Pairs (n, N/2 + n),
 // n < NROT, are rotated by the token's angle.
-template <int N, int NROT, int NWG = 1>
+// BLD = floats between the bias rows of consecutive ranks (N when read from global memory; N + 4 in the padded
+// shared-memory copy, which puts the four ranks a warp reads at once into different banks).
+template <int N, int NROT, int NWG = 1, int BLD = N>
 __device__ __forceinline__ void transform_rows(uint8_t* tile, const float* __restrict__ bias, const float* cos_tab,
                                                const float* sin_tab) {
   const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, t = i >> 2, r = i & 3;
-  const float* bb = bias + r * N;
+  const float* bb = bias + r * BLD;
   constexpr int HALF = N / 2;
   constexpr int TS = tab_stride<NROT>();
   // rotated pairs: chunks [0, NROT/8) of the first half with the same chunks of the second half
@@ -185,12 +193,16 @@ __device__ __forceinline__ void transform_rows(uint8_t* tile, const float* __res
     float fa[8], fb[8];
     unpack8(*reinterpret_cast<uint4*>(pa), fa);
     unpack8(*reinterpret_cast<uint4*>(pb), fb);
+    float ba[8], bbv[8], cs8[8], sn8[8];
+    ld8(ba, bb + colA);
+    ld8(bbv, bb + colB);
+    ld8(cs8, cos_tab + t * TS + colA);
+    ld8(sn8, sin_tab + t * TS + colA);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float xa = fa[j] + bb[colA + j], xb = fb[j] + bb[colB + j];
-      const float cs = cos_tab[t * TS + colA + j], sn = sin_tab[t * TS + colA + j];
-      fa[j] = cs * xa - sn * xb;
-      fb[j] = sn * xa + cs * xb;
+      const float xa = fa[j] + ba[j], xb = fb[j] + bbv[j];
+      fa[j] = cs8[j] * xa - sn8[j] * xb;
+      fb[j] = sn8[j] * xa + cs8[j] * xb;
     }
     *reinterpret_cast<uint4*>(pa) = pack8(fa);
     *reinterpret_cast<uint4*>(pb) = pack8(fb);
@@ -205,8 +217,10 @@ __device__ __forceinline__ void transform_rows(uint8_t* tile, const float* __res
       uint8_t* p = tile + (col / 64) * SLAB + sw_off(i, (col % 64) / 8);
       float f[8];
       unpack8(*reinterpret_cast<uint4*>(p), f);
+      float bv[8];
+      ld8(bv, bb + col);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] += bb[col + j];
+      for (int j = 0; j < 8; ++j) f[j] += bv[j];
       *reinterpret_cast<uint4*>(p) = pack8(f);
     }
   }
@@ -268,6 +282,92 @@ __device__ __forceinline__ void pv_from_raw(float (&pv)[P / 2], const HalfRowRaw
 #pragma unroll
   for (int e = 0; e < P / 2; ++e) pv[e] *= psi[r * P + wg * 32 + e];
 }
+// Sum 32 per-thread values over the four lanes of a token (lanes that differ in their two low bits); lane r ends up
+// with the totals of columns [8r, 8r + 8).  24 shuffles instead of 64.
+__device__ __forceinline__ void reduce4_keep8(const float (&v)[32], float (&out)[8]) {
+  const int lane = threadIdx.x & 31;
+  float a16[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const bool up = lane & 2;
+    const float keep = up ? v[i + 16] : v[i], send = up ? v[i] : v[i + 16];
+    a16[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const bool up = lane & 1;
+    const float keep = up ? a16[i + 8] : a16[i], send = up ? a16[i] : a16[i + 8];
+    out[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+  }
+}
+// Sum 32 per-thread values over the eight lanes of a warp that share a rank (lanes that differ in bits 2..4); the lane
+// with bits (b4 b3 b2) ends up with the totals of columns [16 b4 + 8 b3 + 4 b2, +4).  28 shuffles instead of 96.
+__device__ __forceinline__ void reduce8_keep4(const float (&v)[32], float (&out)[4]) {
+  const int lane = threadIdx.x & 31;
+  float a16[16], a8[8];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const bool up = lane & 16;
+    const float keep = up ? v[i + 16] : v[i], send = up ? v[i] : v[i + 16];
+    a16[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const bool up = lane & 8;
+    const float keep = up ? a16[i + 8] : a16[i], send = up ? a16[i] : a16[i + 8];
+    a8[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const bool up = lane & 4;
+    const float keep = up ? a8[i + 4] : a8[i], send = up ? a8[i] : a8[i + 4];
+    out[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+}
+
+// 16-value forms of the two reductions above (used where 32-value arrays would not fit the register budget).
+// reduce4_keep4_of16: lane r keeps columns [4r, 4r + 4).  reduce8_keep2_of16: the lane with bits (b4 b3 b2) keeps
+// columns 8 b4 + 4 b3 + 2 b2 + {0, 1}.
+__device__ __forceinline__ void reduce4_keep4_of16(const float (&v)[16], float (&out)[4]) {
+  const int lane = threadIdx.x & 31;
+  float a8[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const bool up = lane & 2;
+    const float keep = up ? v[i + 8] : v[i], send = up ? v[i] : v[i + 8];
+    a8[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const bool up = lane & 1;
+    const float keep = up ? a8[i + 4] : a8[i], send = up ? a8[i] : a8[i + 4];
+    out[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+  }
+}
+__device__ __forceinline__ void reduce8_keep2_of16(const float (&v)[16], float (&out)[2]) {
+  const int lane = threadIdx.x & 31;
+  float a8[8], a4[4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const bool up = lane & 16;
+    const float keep = up ? v[i + 8] : v[i], send = up ? v[i] : v[i + 8];
+    a8[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const bool up = lane & 8;
+    const float keep = up ? a8[i + 4] : a8[i], send = up ? a8[i] : a8[i + 4];
+    a4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const bool up = lane & 4;
+    const float keep = up ? a4[i + 2] : a4[i], send = up ? a4[i] : a4[i + 2];
+    out[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+}
+__device__ __forceinline__ int reduce8_first_col(int lane) { return ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2; }
+
 __device__ __forceinline__ float fast_silu(float zz) { return __fdividef(zz, 1.f + __expf(-zz)); }
 
 __device__ __forceinline__ void store_half64(uint8_t* slab, const float (&x)[P / 2], float scale) {
@@ -284,8 +384,9 @@ __device__ __forceinline__ void store_half64(uint8_t* slab, const float (&x)[P /
 // Per-head constants staged in shared memory (fp32): Q/K bias [R,N] and the three [R,P] MIMO vectors.
 template <int N>
 struct HeadBias {
-  float qb[R * N];
-  float kb[R * N];
+  static constexpr int LD = N + 4;           // padded rank stride (see transform_rows)
+  float qb[R * LD];
+  float kb[R * LD];
 };
 struct HeadVecs {
   float psi[R * P];
@@ -297,8 +398,9 @@ __device__ __forceinline__ void load_head_consts(HeadBias<N>* hb, HeadVecs* hv, 
                                                  const float* __restrict__ Kb, const float* __restrict__ Psi,
                                                  const float* __restrict__ Zeta, const float* __restrict__ Phi, int h) {
   for (int x = threadIdx.x; x < R * N; x += blockDim.x) {
-    if (Qb) hb->qb[x] = Qb[(size_t)h * R * N + x];
-    hb->kb[x] = Kb[(size_t)h * R * N + x];
+    const int dst = (x / N) * HeadBias<N>::LD + (x % N);
+    if (Qb) hb->qb[dst] = Qb[(size_t)h * R * N + x];
+    hb->kb[dst] = Kb[(size_t)h * R * N + x];
   }
   for (int x = threadIdx.x; x < R * P; x += blockDim.x) {
     hv->psi[x] = Psi[(size_t)h * R * P + x];

@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(THREADS2) mimo_grad_state_kernel(const __grid_
   __syncthreads();
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
   if (ok) {
-    transform_rows<N, NROT, 2>(sQ, hb->qb, cos_tab, sin_tab);
+    transform_rows<N, NROT, 2, HeadBias<N>::LD>(sQ, hb->qb, cos_tab, sin_tab);
     float dy[P / 2], z[P / 2];
     half_raw_to_float(dy, yraw);
     half_raw_to_float(z, zraw);
@@ -300,8 +300,8 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
 
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
   if (ok) {
-    transform_rows<N, NROT, 2>(sQ, hb->qb, cos_tab, sin_tab);
-    transform_rows<N, NROT, 2>(sK, hb->kb, cos_tab, sin_tab);
+    transform_rows<N, NROT, 2, HeadBias<N>::LD>(sQ, hb->qb, cos_tab, sin_tab);
+    transform_rows<N, NROT, 2, HeadBias<N>::LD>(sK, hb->kb, cos_tab, sin_tab);
     {
       float pv[P / 2];
       pv_from_raw(pv, vraw, hv->psi);
@@ -441,79 +441,88 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
     const int wq = warp & 3;
     float dD_part = 0.f;
     float dvrow[32];
+    const int pcol = reduce8_first_col(lane);         // first of the two columns (per 16) this lane owns after reduce8
     {   // pass 1: O = O1 + e O2 + D PV  ->  dPhi, dZeta, dZ, de, dD and the D dO part of dPV
       uint32_t o1[32], o2[32];
       tmem_ld_32x32(tO1 + lane_addr + wg * 32, o1);
       tmem_ld_32x32(tO2 + lane_addr + wg * 32, o2);
       tmem_ld_wait();
-      float mz[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float vf[8], yf[8], zf[8];
-        unpack8(vrow[q], vf);
-        unpack8(yrow[q], yf);
-        unpack8(zrow[q], zf);
+      for (int half = 0; half < 2; ++half) {
+        float aphi[16], azeta[16], apsi[16], adz[16];
 #pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const int e = q * 8 + v;
-          const float pvv = vf[v] * psi[e];
-          const float o2v = __uint_as_float(o2[e]);
-          const float o = __uint_as_float(o1[e]) + ei * o2v + dsk * pvv;
-          const float zz = zf[v] * zeta[e];
-          const float sg = __fdividef(1.f, 1.f + __expf(-zz));
-          const float sil = zz * sg;
-          const float dO = yf[v] * phi[e] * sil;
-          const float dgate = yf[v] * o;
-          const float dzz = dgate * phi[e] * sg * (1.f + zz * (1.f - sg));
-          float pphi = dgate * sil, pzeta = dzz * zf[v], ppsi = dsk * dO * vf[v];
-          de_i += dO * o2v;
-          dD_part += dO * pvv;
-          float dzv = dzz * zeta[e];
-          dvrow[e] = dsk * dO * psi[e];
+        for (int q2 = 0; q2 < 2; ++q2) {
+          const int q = half * 2 + q2;
+          float vf[8], yf[8], zf[8];
+          unpack8(vrow[q], vf);
+          unpack8(yrow[q], yf);
+          unpack8(zrow[q], zf);
 #pragma unroll
-          for (int o_ = 4; o_ < 32; o_ <<= 1) {
-            pphi += __shfl_xor_sync(0xffffffffu, pphi, o_);
-            pzeta += __shfl_xor_sync(0xffffffffu, pzeta, o_);
-            ppsi += __shfl_xor_sync(0xffffffffu, ppsi, o_);
+          for (int v = 0; v < 8; ++v) {
+            const int e = q * 8 + v, c = q2 * 8 + v;
+            const float pvv = vf[v] * psi[e];
+            const float o2v = __uint_as_float(o2[e]);
+            const float o = __uint_as_float(o1[e]) + ei * o2v + dsk * pvv;
+            const float zz = zf[v] * zeta[e];
+            const float sg = __fdividef(1.f, 1.f + __expf(-zz));
+            const float sil = zz * sg;
+            const float dO = yf[v] * phi[e] * sil;
+            const float dgate = yf[v] * o;
+            const float dzz = dgate * phi[e] * sg * (1.f + zz * (1.f - sg));
+            aphi[c] = dgate * sil;
+            azeta[c] = dzz * zf[v];
+            apsi[c] = dsk * dO * vf[v];
+            adz[c] = dzz * zeta[e];
+            de_i += dO * o2v;
+            dD_part += dO * pvv;
+            dvrow[e] = dsk * dO * psi[e];
           }
-          if (lane < 4) {
-            gs->par[0][wq][r][wg * 32 + e] = ppsi;
-            gs->par[1][wq][r][wg * 32 + e] = pzeta;
-            gs->par[2][wq][r][wg * 32 + e] = pphi;
-          }
-          dzv += __shfl_xor_sync(0xffffffffu, dzv, 1);
-          dzv += __shfl_xor_sync(0xffffffffu, dzv, 2);
-          if (q == r) mz[v] = dzv;
         }
+        float r2[2], mz[4];
+        const int col = wg * 32 + half * 16 + pcol;
+        reduce8_keep2_of16(apsi, r2);
+        gs->par[0][wq][r][col] = r2[0]; gs->par[0][wq][r][col + 1] = r2[1];
+        reduce8_keep2_of16(azeta, r2);
+        gs->par[1][wq][r][col] = r2[0]; gs->par[1][wq][r][col + 1] = r2[1];
+        reduce8_keep2_of16(aphi, r2);
+        gs->par[2][wq][r][col] = r2[0]; gs->par[2][wq][r][col + 1] = r2[1];
+        reduce4_keep4_of16(adz, mz);
+        uint2 oz;
+        oz.x = pack_bf16(mz[0], mz[1]);
+        oz.y = pack_bf16(mz[2], mz[3]);
+        *reinterpret_cast<uint2*>(a.dZ + rowoff + half * 16 + r * 4) = oz;
       }
-      *reinterpret_cast<uint4*>(a.dZ + rowoff + r * 8) = pack8(mz);
     }
     {   // pass 2: dPV = dPV1 + w X (+ D dO from pass 1)  ->  dV, dPsi, dw
       uint32_t d1[32], xx[32];
       tmem_ld_32x32(tdPV1 + lane_addr + wg * 32, d1);
       tmem_ld_32x32(tX + lane_addr + wg * 32, xx);
       tmem_ld_wait();
-      float mv[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float vf[8];
-        unpack8(vrow[q], vf);
+      for (int half = 0; half < 2; ++half) {
+        float apsi[16];
 #pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const int e = q * 8 + v;
-          const float xv = __uint_as_float(xx[e]);
-          const float dpv = __uint_as_float(d1[e]) + wi * xv;
-          dw_i += vf[v] * psi[e] * xv;
-          float ppsi = dpv * vf[v];
-          float dvv = dvrow[e] + dpv * psi[e];
+        for (int q2 = 0; q2 < 2; ++q2) {
+          const int q = half * 2 + q2;
+          float vf[8];
+          unpack8(vrow[q], vf);
 #pragma unroll
-          for (int o_ = 4; o_ < 32; o_ <<= 1) ppsi += __shfl_xor_sync(0xffffffffu, ppsi, o_);
-          if (lane < 4) gs->par[0][wq][r][wg * 32 + e] += ppsi;
-          dvv += __shfl_xor_sync(0xffffffffu, dvv, 1);
-          dvv += __shfl_xor_sync(0xffffffffu, dvv, 2);
-          if (q == r) mv[v] = dvv;
+          for (int v = 0; v < 8; ++v) {
+            const int e = q * 8 + v;
+            const float xv = __uint_as_float(xx[e]);
+            const float dpv = __uint_as_float(d1[e]) + wi * xv;
+            dw_i += vf[v] * psi[e] * xv;
+            apsi[q2 * 8 + v] = dpv * vf[v];
+            dvrow[e] += dpv * psi[e];
+          }
         }
+        float r2[2];
+        const int col = wg * 32 + half * 16 + pcol;
+        reduce8_keep2_of16(apsi, r2);                 // same lane owns the same columns as in pass 1
+        gs->par[0][wq][r][col] += r2[0]; gs->par[0][wq][r][col + 1] += r2[1];
       }
+      float mv[8];
+      reduce4_keep8(dvrow, mv);
       *reinterpret_cast<uint4*>(a.dV + rowoff + r * 8) = pack8(mv);
     }
     dD_part = warp_sum(dD_part);

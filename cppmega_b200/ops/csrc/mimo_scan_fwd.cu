@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(THREADS2) mimo_local_state_kernel(const __grid
   __syncthreads();
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
   if (ok) {
-    transform_rows<N, NROT, 2>(sK, hb->kb, cos_tab, sin_tab);
+    transform_rows<N, NROT, 2, HeadBias<N>::LD>(sK, hb->kb, cos_tab, sin_tab);
     float pv[P / 2];
     pv_from_raw(pv, vraw, hv->psi);
     const int t = i >> 2;
@@ -209,8 +209,11 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   float* sin_tab = cos_tab + tab_floats<NROT>();
   HeadBias<N>* hb = reinterpret_cast<HeadBias<N>*>(sPV);      // biases die before PV is written (barrier between)
   static_assert(sizeof(HeadBias<N>) <= SLAB, "bias block must fit the PV slab it borrows");
-  HeadVecs* hv = reinterpret_cast<HeadVecs*>(sin_tab + tab_floats<NROT>());
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(hv + 1);
+  float* psi_s = sin_tab + tab_floats<NROT>();                 // [R, P]
+  float* zeta_s = cos_tab;                                      // zeta / phi move into the sin/cos tables once the
+  float* phi_s = cos_tab + R * P;                               // rotations are done (registers hold them until then)
+  static_assert(2 * R * P <= 2 * tab_floats<NROT>(), "zeta and phi must fit the retired tables");
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(psi_s + R * P);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 1);            // [0] tma, [1] S1+O2, [2] O1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -228,6 +231,9 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.ldV);
   const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.ldZ);
   const float dsk = a.Dskip[h];
+  static_assert(R * P == THREADS2, "one zeta / phi / psi element per thread");
+  const float zeta_v = a.Zeta[(size_t)h * R * P + threadIdx.x], phi_v = a.Phi[(size_t)h * R * P + threadIdx.x];
+  const float psi_v = a.Psi[(size_t)h * R * P + threadIdx.x];
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -251,7 +257,12 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
     }
     tma_load_2d(sSt, &tmS, &bars[0], 0, (int)((((size_t)b * a.H + h) * a.C + c) * N));
   }
-  load_head_consts<N>(hb, hv, a.Qb, a.Kb, a.Psi, a.Zeta, a.Phi, h);
+  for (int x = threadIdx.x; x < R * N; x += THREADS2) {
+    const int dst = (x / N) * HeadBias<N>::LD + (x % N);
+    hb->qb[dst] = a.Qb[(size_t)h * R * N + x];
+    hb->kb[dst] = a.Kb[(size_t)h * R * N + x];
+  }
+  psi_s[threadIdx.x] = psi_v;
   finish_chunk_scalars(sc, sl, t0, a.S);
   fill_sincos4<NROT>(cos_tab, sin_tab, ang4);
   __syncthreads();
@@ -260,12 +271,14 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   CM_STAMP(3);
   float pv[P / 2];
   if (ok) {
-    transform_rows<N, NROT, 2>(sQ, hb->qb, cos_tab, sin_tab);
-    transform_rows<N, NROT, 2>(sK, hb->kb, cos_tab, sin_tab);
-    pv_from_raw(pv, vraw, hv->psi);
+    transform_rows<N, NROT, 2, HeadBias<N>::LD>(sQ, hb->qb, cos_tab, sin_tab);
+    transform_rows<N, NROT, 2, HeadBias<N>::LD>(sK, hb->kb, cos_tab, sin_tab);
+    pv_from_raw(pv, vraw, psi_s);
   }
   CM_STAMP(4);
-  __syncthreads();                               // every thread is done with the biases stored in the PV slab
+  __syncthreads();                               // every thread is done with the biases stored in the PV slab and the tables
+  zeta_s[threadIdx.x] = zeta_v;
+  phi_s[threadIdx.x] = phi_v;
   if (ok) {
     store_half64(sPV, pv, 1.f);
     fence_proxy_async_smem();
@@ -329,14 +342,14 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   CM_STAMP(8);
   if (ok) {
     const float ecs = __expf(sc->cs[t]);
-    const float* zeta = hv->zeta + r * P + wg * 32;
-    const float* phi = hv->phi + r * P + wg * 32;
+    const float* zeta = zeta_s + r * P + wg * 32;
+    const float* phi = phi_s + r * P + wg * 32;
     __nv_bfloat16* yrow = a.y + (((size_t)b * a.S + t0 + t) * a.H + h) * P + wg * 32;
     uint32_t o1[32], o2[32];
     tmem_ld_32x32(tO1 + lane_addr + wg * 32, o1);
     tmem_ld_32x32(tO2 + lane_addr + wg * 32, o2);
     tmem_ld_wait();
-    float mine[8];
+    float val[32];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float zf[8];
@@ -345,14 +358,12 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
       for (int v = 0; v < 8; ++v) {
         const int p = q * 8 + v;
         const float o = __uint_as_float(o1[p]) + ecs * __uint_as_float(o2[p]) + dsk * pv[p];
-        const float zz = zf[v] * zeta[p];
-        float val = o * phi[p] * fast_silu(zz);
-        val += __shfl_xor_sync(0xffffffffu, val, 1);
-        val += __shfl_xor_sync(0xffffffffu, val, 2);
-        if (q == r) mine[v] = val;
+        val[p] = o * phi[p] * fast_silu(zf[v] * zeta[p]);
       }
     }
-    // the four lanes of a token hold the same sums; lane r writes columns [8r, 8r + 8) of this warpgroup's half
+    float mine[8];
+    reduce4_keep8(val, mine);
+    // lane r holds the sums over the four ranks for columns [8r, 8r + 8) of this warpgroup's half
     *reinterpret_cast<uint4*>(yrow + r * 8) = pack8(mine);
   }
   CM_STAMP(9);
@@ -369,7 +380,7 @@ constexpr int local_state_smem() {
 template <int N>
 constexpr int chunk_out_smem() {
   return ((N / 64) * SLAB > 2 * SLAB ? (N / 64) * SLAB : 2 * SLAB) + (N / 64) * SLAB + SLAB + (N > 128 ? N : 128) * 128 +
-         2 * tab_floats<N / 4>() * 4 + sizeof(HeadVecs) + sizeof(ChunkScalars) + 64 + 1024;
+         2 * tab_floats<N / 4>() * 4 + R * P * 4 + sizeof(ChunkScalars) + 64 + 1024;
 }
 
 }  // namespace mimo

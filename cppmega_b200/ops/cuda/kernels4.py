@@ -19,6 +19,7 @@ def declare(L: ctypes.CDLL) -> None:
     f32 = ctypes.c_float
     sig["cm_sparse_mla_fwd"] = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp]
     sig["cm_sparse_mla_bwd"] = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp]
+    sig["cm_head_reduce"] = [vp, vp, vp, i64, i32, i32, i32, vp]
     sig["cm_indexer_scores"] = [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
     sig["cm_indexer_topk"] = [vp, vp, i32, i32, i32, vp]
     for name, args in sig.items():
@@ -123,6 +124,18 @@ def sparse_mla(q, kv, idx, scale, d_v):
     from ...utils.recompute import stashed_call
     return stashed_call("sparse_mla", lambda: sparse_mla_fwd_raw(q.detach(), kv.detach(), idx, scale, d_v),
                         lambda res: SparseMLAFn.apply(q, kv, idx, scale, d_v, res))
+
+
+def head_reduce(dh: torch.Tensor, G: int):
+    """dh [B,S,H,R,N] bf16 -> (sum over the heads of each group [B,S,G,R,N] bf16, sum over tokens [H,R,N] fp32)."""
+    from . import lib, stream_ptr, _check
+    B, S, H, R, N = dh.shape
+    dgrp = torch.empty(B, S, G, R, N, dtype=torch.bfloat16, device=dh.device)
+    dbias = torch.zeros(H, R, N, dtype=torch.float32, device=dh.device)
+    _check(lib().cm_head_reduce(dh.data_ptr(), dgrp.data_ptr(), dbias.data_ptr(), B * S, H, G, R * N, stream_ptr()),
+           "cm_head_reduce")
+    F_.count_launch("head_reduce")
+    return dgrp, dbias
 
 
 def indexer_topk(q_idx, k_idx, w, topk: int):

@@ -43,11 +43,17 @@ def mimo_bwd(saved, dy, states, tot):
                                   err_word(dev).data_ptr(), stream_ptr()), "cm_mimo_scan_bwd")
     F_.count_launch("mimo_scan_bwd", 3)
     del gbuf, dend
-    # heads -> groups (Q/K are shared by the heads of a group) and per-head biases
-    dQ = dQh.view(B, S, G, hpg, R, N).sum(3, dtype=torch.float32).permute(0, 1, 3, 2, 4)
-    dK = dKh.view(B, S, G, hpg, R, N).sum(3, dtype=torch.float32).permute(0, 1, 3, 2, 4)
-    dQb = dQh.sum((0, 1), dtype=torch.float32)
-    dKb = dKh.sum((0, 1), dtype=torch.float32)
+    # heads -> groups (Q/K are shared by the heads of a group) and per-head biases, one pass per tensor
+    from .kernels4 import head_reduce
+    if hpg in (1, 2, 4, 8, 16):
+        dQg, dQb = head_reduce(dQh, G)
+        dKg, dKb = head_reduce(dKh, G)
+        dQ, dK = dQg.permute(0, 1, 3, 2, 4), dKg.permute(0, 1, 3, 2, 4)
+    else:
+        dQ = dQh.view(B, S, G, hpg, R, N).sum(3, dtype=torch.float32).permute(0, 1, 3, 2, 4)
+        dK = dKh.view(B, S, G, hpg, R, N).sum(3, dtype=torch.float32).permute(0, 1, 3, 2, 4)
+        dQb = dQh.sum((0, 1), dtype=torch.float32)
+        dKb = dKh.sum((0, 1), dtype=torch.float32)
     del dQh, dKh
     # trapezoid coefficients: gamma_t = DT_t sig(Trap_t), ts_t = gamma_t + DT_{t+1} sig(-Trap_{t+1})
     sg = torch.sigmoid(Trapf)

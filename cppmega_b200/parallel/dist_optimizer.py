@@ -315,6 +315,11 @@ class DistributedOptimizer:
         """Sum of squares of a shard; tensors replicated over TP contribute 1/tp so the later
         TP all-reduce counts them once."""
         tp = self.pc.tp
+        if tp == 1 and g.is_cuda and g.dtype in (torch.float32, torch.bfloat16) and g.is_contiguous():
+            from ..ops import cuda as cu           # one pass over the shard, no fp32 copy
+            out = torch.zeros((), dtype=torch.float32, device=g.device)
+            cu.sumsq(g, out)
+            return out
         gf = g.float()
         if tp == 1:
             return (gf * gf).sum()
