@@ -20,7 +20,7 @@ from ..config.model import Mamba3Config
 from ..ops import functional as F_
 from ..parallel.state import ParallelContext
 from ..parallel.tensor_parallel import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear, gather_seq
-from .common import RMSNorm, fp32_param, seed_for
+from .common import RMSNorm, fp32_param, seed_for, split_last_dim
 
 
 class Mamba3Mixer(nn.Module):
@@ -77,7 +77,7 @@ class Mamba3Mixer(nn.Module):
             angles_raw = gather_seq(angles_raw, pc, reduce_grad=True)
         packed = self.in_proj(x)                                    # [B,S,sum(sizes_local)]
         Bsz, S = packed.shape[:2]
-        z, xv, Bm, Cm, dd_dt, dd_A, trap = torch.split(packed, list(self.sizes_local), dim=-1)
+        z, xv, Bm, Cm, dd_dt, dd_A, trap = split_last_dim(packed, self.sizes_local)
         z = z.reshape(Bsz, S, Hl, P)
         xv = xv.reshape(Bsz, S, Hl, P)
         Bm = self.B_norm(Bm.reshape(Bsz, S, Gl, R, N)).permute(0, 1, 3, 2, 4)     # [B,S,R,G,N]
