@@ -354,9 +354,41 @@ __global__ void __launch_bounds__(256) sumsq_kernel(const T* __restrict__ g, lon
   }
 }
 
+// out[i] = sum over slots of stage[slot * n + i]   (bf16 in, fp32 accumulation, bf16 out; 8 values per thread)
+__global__ void __launch_bounds__(256) sum_slots_kernel(const __nv_bfloat16* __restrict__ stage, __nv_bfloat16* __restrict__ out,
+                                                        int n_slots, long long n) {
+  const long long nvec = n / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < n_slots; ++s) {
+      const uint4 v = reinterpret_cast<const uint4*>(stage + (size_t)s * n)[i];
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(b[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
 }  // namespace cm
 
 using namespace cm;
+
+extern "C" int cm_sum_slots(const void* stage, void* out, int n_slots, long long n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (n % 8 || n_slots <= 0) return -10;
+  long long blocks = (n / 8 + 255) / 256;
+  int grid = (int)(blocks < (long long)sm_count() * 16 ? blocks : (long long)sm_count() * 16);
+  sum_slots_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)stage, (__nv_bfloat16*)out, n_slots, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
 
 extern "C" int cm_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int H, float eps,
                               cudaStream_t s) {

@@ -30,7 +30,26 @@ constexpr int BK = 64;           // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
 
-enum GemmMode : int { DENSE = 0, GROUPED_ROWS = 1, GROUPED_K = 2 };
+// PEER_A: the rows of A live in the symmetric buffers of `n_peers` GPUs (sequence-parallel all-gather fused into the
+//         operand loads: row block m0 belongs to segment m0 / rows_per_seg = (batch, peer));
+// PEER_C: every output tile is stored into the staging slot `my_slot` of the GPU that owns its rows (the scatter half
+//         of a reduce-scatter fused into the epilogue; the owner sums the slots afterwards).
+enum GemmMode : int { DENSE = 0, GROUPED_ROWS = 1, GROUPED_K = 2, PEER_A = 3, PEER_C = 4 };
+constexpr int MAX_TP_PEERS = 8;
+struct PeerMaps {
+  CUtensorMap m[MAX_TP_PEERS];
+};
+struct NoPeerMaps {
+  char unused;
+};
+template <int MODE>
+struct PeerParam {
+  using type = NoPeerMaps;
+};
+template <>
+struct PeerParam<PEER_A> {
+  using type = PeerMaps;
+};
 
 struct GemmArgs {
   int M, N, K;             // DENSE: problem; GROUPED_ROWS: M = allocated rows, N,K per expert;
@@ -40,6 +59,12 @@ struct GemmArgs {
   const int* tile_expert;  // GROUPED_ROWS: [M/128]
   const int* seg_offsets;  // GROUPED_K: [E+1], multiples of BK
   int* err;
+  // PEER_A / PEER_C
+  int rows_per_seg;        // rows of one (batch, peer) segment; a multiple of BM
+  int n_peers;
+  int my_slot;             // PEER_C: staging slot this rank writes on every peer
+  long long local_rows;    // PEER_C: rows of one staging slot (= batch * rows_per_seg)
+  void* c_peers[MAX_TP_PEERS];   // PEER_C: staging buffers [n_peers slots, local_rows, N]
 };
 
 template <int BN>
@@ -56,7 +81,7 @@ struct SmemLayout {
 template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACC, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ C,
-                 const GemmArgs args) {
+                 const GemmArgs args, const __grid_constant__ typename PeerParam<MODE>::type peer_maps) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -146,7 +171,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sb = sa + L::A_BYTES;
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           const int k0 = (kb0 + kb) * BK;
-          if (!A_MN) {
+          if constexpr (MODE == PEER_A) {
+            // plain (single-CTA) tiled load from the peer that holds this row segment
+            const int seg = m0 / args.rows_per_seg;
+            const int src_row = (seg / args.n_peers) * args.rows_per_seg + (m0 - seg * args.rows_per_seg);
+            tma_load_2d(sa, &peer_maps.m[seg % args.n_peers], &full_bar[stage], k0, src_row);
+          } else if (!A_MN) {
             tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);                       // box [128 rows, 64 k]
           } else {
 #pragma unroll
@@ -215,6 +245,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < args.M;
       OutT* crow = C + (MODE == GROUPED_K ? (long long)e * args.M * args.ldc : 0ll) + (long long)row * args.ldc;
+      if constexpr (MODE == PEER_C) {
+        const int seg = m0 / args.rows_per_seg;
+        const long long dst_row = (long long)args.my_slot * args.local_rows + (long long)(seg / args.n_peers) * args.rows_per_seg +
+                                  (row - seg * args.rows_per_seg);
+        crow = reinterpret_cast<OutT*>(args.c_peers[seg % args.n_peers]) + dst_row * args.ldc;
+      }
       if (nkb == 0) {
         if (MODE == GROUPED_K && !ACC && row_ok) {
           for (int c = n0; c < min(n0 + BN, args.N); ++c) crow[c] = OutT(0.f);
@@ -373,7 +409,23 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, OutT* C, const
   }
   int grid = total_tiles < sm_count() ? total_tiles : sm_count();
   if (grid <= 0) return 0;
-  kern<<<grid, GEMM_THREADS, SmemLayout<BN>::TOTAL, stream>>>(tmA, tmB, C, args);
+  kern<<<grid, GEMM_THREADS, SmemLayout<BN>::TOTAL, stream>>>(tmA, tmB, C, args, NoPeerMaps{});
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+template <int BN, bool B_MN>
+static int launch_peer_a(const PeerMaps& pm, const CUtensorMap& tmB, __nv_bfloat16* C, const GemmArgs& args, int total_tiles,
+                         cudaStream_t stream) {
+  auto kern = gemm_bf16_kernel<BN, false, B_MN, __nv_bfloat16, false, PEER_A>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL) != cudaSuccess)
+      return -2;
+    configured = true;
+  }
+  int grid = total_tiles < sm_count() ? total_tiles : sm_count();
+  if (grid <= 0) return 0;
+  kern<<<grid, GEMM_THREADS, SmemLayout<BN>::TOTAL, stream>>>(pm.m[0], tmB, C, args, pm);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -406,7 +458,7 @@ extern "C" int cm_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   constexpr int BN = 256;
   rc = b_mn ? make_tmap_2d_bf16(&tmB, B, K, N, ldb, 64) : make_tmap_2d_bf16(&tmB, B, N, K, ldb, BN);
   if (rc) return rc;
-  GemmArgs args{M, N, K, ldc, 1, nullptr, nullptr, err};
+  GemmArgs args{M, N, K, ldc, 1, nullptr, nullptr, err, 0, 0, 0, 0, {}};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   if (out_fp32) {
     if (accumulate) return dispatch_layout<BN, float, true, DENSE>(a_mn, b_mn, tmA, tmB, (float*)C, args, tiles, stream);
@@ -432,7 +484,7 @@ extern "C" int cm_grouped_gemm_rows_bf16(const void* A, const void* W, void* C, 
   if (rc) return rc;
   rc = b_mn ? make_tmap_3d_bf16(&tmB, W, num_experts, K, N, N, 64) : make_tmap_3d_bf16(&tmB, W, num_experts, N, K, K, BN);
   if (rc) return rc;
-  GemmArgs args{rows, N, K, N, num_experts, tile_expert, nullptr, err};
+  GemmArgs args{rows, N, K, N, num_experts, tile_expert, nullptr, err, 0, 0, 0, 0, {}};
   const int tiles = (rows / BM) * ((N + BN - 1) / BN);
   if (b_mn) return launch<BN, false, true, __nv_bfloat16, false, GROUPED_ROWS>(tmA, tmB, (__nv_bfloat16*)C, args, tiles, stream);
   return launch<BN, false, false, __nv_bfloat16, false, GROUPED_ROWS>(tmA, tmB, (__nv_bfloat16*)C, args, tiles, stream);
@@ -451,7 +503,7 @@ extern "C" int cm_grouped_gemm_k_bf16(const void* A, const void* B, void* C, int
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&tmB, B, rows, N, N, 64);
   if (rc) return rc;
-  GemmArgs args{M, N, 0, N, num_experts, nullptr, seg_offsets, err};
+  GemmArgs args{M, N, 0, N, num_experts, nullptr, seg_offsets, err, 0, 0, 0, 0, {}};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * num_experts;
   if (out_fp32) {
     if (accumulate) return launch<BN, true, true, float, true, GROUPED_K>(tmA, tmB, (float*)C, args, tiles, stream);
@@ -459,4 +511,56 @@ extern "C" int cm_grouped_gemm_k_bf16(const void* A, const void* B, void* C, int
   }
   if (accumulate) return launch<BN, true, true, __nv_bfloat16, true, GROUPED_K>(tmA, tmB, (__nv_bfloat16*)C, args, tiles, stream);
   return launch<BN, true, true, __nv_bfloat16, false, GROUPED_K>(tmA, tmB, (__nv_bfloat16*)C, args, tiles, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Tensor parallelism with sequence parallelism, fused with the GEMMs (peer memory; plain single-CTA TMA loads and
+// ordinary stores only).  Rows are tokens; M = batch * n_peers * rows_per_seg, and global row block
+// (b, p, r) = b * n_peers * rows_per_seg + p * rows_per_seg + r belongs to peer p, local row b * rows_per_seg + r.
+// ---------------------------------------------------------------------------------------------------------
+
+// all-gather -> GEMM:  C[M, N] = gather(A)[M, K] . op(B);  a_ptrs[p] = peer p's shard [batch * rows_per_seg, K] bf16.
+// Callers make sure (flag barrier) that every peer's shard is complete before the launch and is not overwritten
+// until every rank's kernel has finished.
+extern "C" int cm_gemm_bf16_peer_a(void* const* a_ptrs, int n_peers, int rows_per_seg, int batch, const void* B, void* C, int N,
+                                   int K, long long ldb, long long ldc, int b_mn, int* err, cudaStream_t stream) {
+  if (n_peers <= 0 || n_peers > MAX_TP_PEERS || batch <= 0 || rows_per_seg <= 0) return -10;
+  if (rows_per_seg % BM || (K % 8) || (ldb % 8)) return -10;
+  const int M = batch * n_peers * rows_per_seg;
+  PeerMaps pm;
+  for (int p = 0; p < n_peers; ++p) {
+    if (reinterpret_cast<uintptr_t>(a_ptrs[p]) & 15) return -10;
+    int rc = make_tmap_2d_bf16(&pm.m[p], a_ptrs[p], (uint64_t)batch * rows_per_seg, K, K, BM);
+    if (rc) return rc;
+  }
+  for (int p = n_peers; p < MAX_TP_PEERS; ++p) pm.m[p] = pm.m[0];
+  constexpr int BN = 256;
+  CUtensorMap tmB;
+  int rc = b_mn ? make_tmap_2d_bf16(&tmB, B, K, N, ldb, 64) : make_tmap_2d_bf16(&tmB, B, N, K, ldb, BN);
+  if (rc) return rc;
+  GemmArgs args{M, N, K, ldc, 1, nullptr, nullptr, err, rows_per_seg, n_peers, 0, 0, {}};
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  if (b_mn) return launch_peer_a<BN, true>(pm, tmB, (__nv_bfloat16*)C, args, tiles, stream);
+  return launch_peer_a<BN, false>(pm, tmB, (__nv_bfloat16*)C, args, tiles, stream);
+}
+
+// GEMM -> scatter:  partial[M, N] = A[M, K] . op(B), every tile stored into slot `my_slot` of the staging buffer of the
+// peer that owns its rows; c_ptrs[p] = peer p's staging buffer [n_peers, batch * rows_per_seg, N] bf16.
+extern "C" int cm_gemm_bf16_peer_c(const void* A, const void* B, void* const* c_ptrs, int n_peers, int my_slot, int rows_per_seg,
+                                   int batch, int N, int K, long long lda, long long ldb, int b_mn, int* err,
+                                   cudaStream_t stream) {
+  if (n_peers <= 0 || n_peers > MAX_TP_PEERS || batch <= 0 || rows_per_seg <= 0 || my_slot < 0 || my_slot >= n_peers) return -10;
+  if (rows_per_seg % BM || (lda % 8) || (ldb % 8) || (N % 8)) return -10;
+  const int M = batch * n_peers * rows_per_seg;
+  constexpr int BN = 256;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d_bf16(&tmA, A, M, K, lda, BM);
+  if (rc) return rc;
+  rc = b_mn ? make_tmap_2d_bf16(&tmB, B, K, N, ldb, 64) : make_tmap_2d_bf16(&tmB, B, N, K, ldb, BN);
+  if (rc) return rc;
+  GemmArgs args{M, N, K, N, 1, nullptr, nullptr, err, rows_per_seg, n_peers, my_slot, (long long)batch * rows_per_seg, {}};
+  for (int p = 0; p < n_peers; ++p) args.c_peers[p] = c_ptrs[p];
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  if (b_mn) return launch<BN, false, true, __nv_bfloat16, false, PEER_C>(tmA, tmB, (__nv_bfloat16*)nullptr, args, tiles, stream);
+  return launch<BN, false, false, __nv_bfloat16, false, PEER_C>(tmA, tmB, (__nv_bfloat16*)nullptr, args, tiles, stream);
 }

@@ -81,8 +81,31 @@ def _cuda(name: str, *tensors) -> Optional[Callable]:
 
 # ---- dense ---------------------------------------------------------------
 
+_PRECISION_RECIPE = "bf16"
+
+
+def set_precision_recipe(name: str) -> None:
+    """``bf16`` or ``mxfp8``: with ``mxfp8`` every eligible linear layer (2-D bf16 weight, all three dims multiples
+    of 32) rounds its operands to MXFP8 along the reduced dimension and saves its activation as an MXFP8 tensor."""
+    global _PRECISION_RECIPE
+    if name not in ("bf16", "mxfp8"):
+        raise ValueError(f"unknown precision recipe {name!r}")
+    _PRECISION_RECIPE = name
+
+
+def precision_recipe() -> str:
+    return _PRECISION_RECIPE
+
+
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``x @ w^T``; w is [out, in]."""
+    if _PRECISION_RECIPE == "mxfp8" and x.is_cuda:
+        _ensure_ext()
+        from .cuda import mxfp8
+        y = mxfp8.linear(x, w)
+        if y is not None:
+            return y
+        _FALLBACKS["mxfp8_linear(shape)"] += 1
     fn = _cuda("linear", x)
     if fn is not None:
         y = fn(x, w)

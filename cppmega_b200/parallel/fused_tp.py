@@ -1,0 +1,204 @@
+"""Tensor-parallel linears with the sequence-parallel collectives fused into the GEMMs, over peer memory.
+
+* ``ag_gemm``  (column-parallel forward, row-parallel dgrad):  ``y = gather_seq(x) . op(W)``.  Every rank copies its
+  sequence shard into its symmetric buffer, the ranks meet at a flag barrier, and the GEMM's TMA producer then reads
+  each 128-row block of A straight from the peer that holds it, so the gather is hidden under the tensor-core main
+  loop tile by tile and the gathered activation is never materialised.
+* ``gemm_rs``  (row-parallel forward, column-parallel dgrad):  ``y_shard = reduce_scatter_seq(x . op(W))``.  The GEMM
+  epilogue stores every output tile into a staging slot on the rank that owns those rows; after a flag barrier the
+  owner sums its ``tp`` slots (one pass, fp32 accumulation).
+
+Both need ``(S / tp) % 128 == 0`` (row blocks must not straddle ranks), bf16, and peer access; otherwise the NCCL
+mappings in :mod:`cppmega_b200.parallel.tensor_parallel` are used.  The weight gradient still needs the gathered
+operand as a whole and takes it through one library all-gather.  This is the replacement for the reference's
+Megatron column/row linears with ``--sequence-parallel`` (cppmega/megatron/cppmega_mamba3_tp_mixer.py:217-229,363-375)
+and its TP communication overlap flags (cppmega/recipes/nam56r_nemo_recipe.py:429-443).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F_
+from .symm_mem import SymmetricHeap
+
+FLAG_AG, FLAG_AG_DONE, FLAG_RS, FLAG_RS_DONE = 0, 1, 2, 3      # this heap belongs to the TP group alone
+
+
+def _lib():
+    from ..ops import cuda as cu
+    L = cu.lib()
+    if not getattr(L, "_tp_declared", False):
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        L.cm_gemm_bf16_peer_a.argtypes = [vp, i32, i32, i32, vp, vp, i32, i32, i64, i64, i32, vp, vp]
+        L.cm_gemm_bf16_peer_c.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i64, i64, i32, vp, vp]
+        L.cm_sum_slots.argtypes = [vp, vp, i32, i64, vp]
+        for n in ("cm_gemm_bf16_peer_a", "cm_gemm_bf16_peer_c", "cm_sum_slots"):
+            getattr(L, n).restype = i32
+        L._tp_declared = True
+    return L
+
+
+class FusedTP:
+    """Symmetric buffers of one TP group, shared by all layers (one transfer in flight at a time per kind)."""
+
+    def __init__(self, pc, device, max_local_rows: int, max_width: int):
+        self.pc, self.device = pc, device
+        self.tp = pc.tp
+        self.max_elems = max_local_rows * max_width
+        nbytes = self.max_elems * 2 * (1 + self.tp) + 8192
+        self.heap = SymmetricHeap(pc.tp_group, pc.tp_ranks, nbytes, device)
+        self.xbuf = self.heap.alloc((self.max_elems,), torch.bfloat16)                 # all-gather source
+        self.stage = self.heap.alloc((self.tp * self.max_elems,), torch.bfloat16)      # reduce-scatter slots
+        self.ag_epoch = 0
+        self.rs_epoch = 0
+
+    def supported(self, batch: int, rows_per_seg: int, width_in: int, width_out: int) -> bool:
+        return (rows_per_seg % 128 == 0 and batch * rows_per_seg * max(width_in, width_out) <= self.max_elems
+                and width_in % 8 == 0 and width_out % 8 == 0)
+
+    # ---- all-gather -> GEMM ------------------------------------------------------------------
+    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
+        """x_local [B, S/tp, K] bf16 -> [B, S, N];  w is [N, K] (b_mn False) or [K, N] (b_mn True)."""
+        from ..ops.cuda import err_word, stream_ptr
+        B, Sl, K = x_local.shape
+        N = w.shape[1] if b_mn else w.shape[0]
+        self.ag_epoch += 1
+        src = self.xbuf[:B * Sl * K].view(B * Sl, K)
+        self.heap.wait(FLAG_AG_DONE, self.ag_epoch - 1)          # every rank has finished reading the previous contents
+        src.copy_(x_local.reshape(B * Sl, K))
+        self.heap.barrier(FLAG_AG, self.ag_epoch)                # all shards are in place
+        out = torch.empty(B, self.tp * Sl, N, dtype=torch.bfloat16, device=x_local.device)
+        rc = _lib().cm_gemm_bf16_peer_a(self.heap.peer_ptr_array(src), self.tp, Sl, B, w.data_ptr(), out.data_ptr(), N, K,
+                                        w.stride(0), N, int(b_mn), err_word(self.device).data_ptr(), stream_ptr())
+        if rc:
+            raise RuntimeError(f"cm_gemm_bf16_peer_a failed ({rc})")
+        self.heap.signal(FLAG_AG_DONE, self.ag_epoch)
+        F_.count_launch("tp_ag_gemm")
+        return out
+
+    # ---- GEMM -> reduce-scatter --------------------------------------------------------------
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
+        """x [B, S, K] bf16 (K = this rank's slice of the reduction) -> [B, S/tp, N] summed over the TP group."""
+        from ..ops.cuda import err_word, stream_ptr
+        B, S, K = x.shape
+        Sl = S // self.tp
+        N = w.shape[1] if b_mn else w.shape[0]
+        self.rs_epoch += 1
+        x2 = x.reshape(B * S, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        n_local = B * Sl * N
+        stage = self.stage[:self.tp * n_local]
+        self.heap.wait(FLAG_RS_DONE, self.rs_epoch - 1)          # owners have consumed the previous slots
+        rc = _lib().cm_gemm_bf16_peer_c(x2.data_ptr(), w.data_ptr(), self.heap.peer_ptr_array(stage), self.tp, self.heap.me,
+                                        Sl, B, N, K, x2.stride(0), w.stride(0), int(b_mn),
+                                        err_word(self.device).data_ptr(), stream_ptr())
+        if rc:
+            raise RuntimeError(f"cm_gemm_bf16_peer_c failed ({rc})")
+        self.heap.barrier(FLAG_RS, self.rs_epoch)                # every rank's partial tiles have landed here
+        out = torch.empty(B, Sl, N, dtype=torch.bfloat16, device=x.device)
+        rc = _lib().cm_sum_slots(stage.data_ptr(), out.data_ptr(), self.tp, n_local, stream_ptr())
+        if rc:
+            raise RuntimeError(f"cm_sum_slots failed ({rc})")
+        self.heap.signal(FLAG_RS_DONE, self.rs_epoch)
+        F_.count_launch("tp_gemm_rs")
+        return out
+
+
+_STATE: Optional[FusedTP] = None
+
+
+def install(pc, device, max_local_rows: int, max_width: int) -> Optional[FusedTP]:
+    """Create the TP buffers (collective over the TP group).  Returns None when the topology does not allow it."""
+    global _STATE
+    from .symm_mem import peer_access_available
+    if pc.tp <= 1 or not pc.sequence_parallel or not peer_access_available(pc):
+        _STATE = None
+        return None
+    _STATE = FusedTP(pc, device, max_local_rows, max_width)
+    return _STATE
+
+
+def uninstall() -> None:
+    global _STATE
+    _STATE = None
+
+
+def current() -> Optional[FusedTP]:
+    return _STATE
+
+
+def _gather_seq_nccl(x: torch.Tensor, group) -> torch.Tensor:
+    parts = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return torch.cat(parts, dim=1)
+
+
+class ColumnLinearSPFn(torch.autograd.Function):
+    """y = gather_seq(x) W^T with W [N_local, K]."""
+
+    @staticmethod
+    def forward(ctx, x_local, w, tp: FusedTP):
+        ctx.tp = tp
+        ctx.save_for_backward(x_local, w)
+        return tp.ag_gemm(x_local, w, b_mn=False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.cuda import gemm, wgrad_into_main_grad
+        x_local, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = tp.gemm_rs(dy, w, b_mn=True)                                   # [B,S,N_l] . W[N_l,K] -> scatter
+        if ctx.needs_input_grad[1]:
+            xg = _gather_seq_nccl(x_local, tp.pc.tp_group)
+            dy2, x2 = dy.reshape(-1, dy.shape[-1]), xg.reshape(-1, xg.shape[-1])
+            dw = wgrad_into_main_grad(w, lambda out, acc: gemm(dy2, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
+        return dx, dw, None
+
+
+class RowLinearSPFn(torch.autograd.Function):
+    """y_shard = reduce_scatter_seq(x W^T) with W [N, K_local]."""
+
+    @staticmethod
+    def forward(ctx, x, w, tp: FusedTP):
+        ctx.tp = tp
+        ctx.save_for_backward(x, w)
+        return tp.gemm_rs(x, w, b_mn=False)
+
+    @staticmethod
+    def backward(ctx, dy_local):
+        from ..ops.cuda import gemm, wgrad_into_main_grad
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy_local = dy_local.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = tp.ag_gemm(dy_local, w, b_mn=True)                             # gather(dy)[B,S,N] . W[N,K_l]
+        if ctx.needs_input_grad[1]:
+            dyg = _gather_seq_nccl(dy_local, tp.pc.tp_group)
+            dy2, x2 = dyg.reshape(-1, dyg.shape[-1]), x.reshape(-1, x.shape[-1])
+            dw = wgrad_into_main_grad(w, lambda out, acc: gemm(dy2, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
+        return dx, dw, None
+
+
+def column_linear(x_local: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+    tp = _STATE
+    if (tp is None or x_local.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x_local.dim() != 3
+            or not tp.supported(x_local.shape[0], x_local.shape[1], x_local.shape[2], w.shape[0])):
+        return None
+    return ColumnLinearSPFn.apply(x_local.contiguous(), w, tp)
+
+
+def row_linear(x: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+    tp = _STATE
+    if (tp is None or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 3 or x.shape[1] % tp.tp
+            or not tp.supported(x.shape[0], x.shape[1] // tp.tp, x.shape[2], w.shape[0])):
+        return None
+    return RowLinearSPFn.apply(x, w, tp)

@@ -123,6 +123,8 @@ class SymmetricHeap:
         """After all work queued so far on the current stream, store ``value`` into flag word
         ``index * world + me`` of every peer."""
         from ..ops.cuda import stream_ptr
+        if not 0 <= (index + 1) * self.world <= FLAG_WORDS:
+            raise IndexError(f"flag index {index} out of range for {self.world} ranks ({FLAG_WORDS} words)")
         rc = self.L.cm_signal_peers(self._flag_ptrs.data_ptr(), self.world, index * self.world + self.me, value,
                                     stream_ptr())
         if rc:
@@ -131,6 +133,8 @@ class SymmetricHeap:
     def wait(self, index: int, value: int, timeout_ns: Optional[int] = None) -> None:
         """Queue a bounded device-side wait until every rank has signalled ``value`` on ``index``."""
         from ..ops.cuda import err_word, stream_ptr
+        if not 0 <= (index + 1) * self.world <= FLAG_WORDS:
+            raise IndexError(f"flag index {index} out of range for {self.world} ranks ({FLAG_WORDS} words)")
         rc = self.L.cm_wait_flags(self.flags.data_ptr(), index * self.world, self.world, value,
                                   self.timeout_ns if timeout_ns is None else timeout_ns,
                                   err_word(self.device).data_ptr(), stream_ptr())

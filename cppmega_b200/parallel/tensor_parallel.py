@@ -214,9 +214,14 @@ class ColumnParallelLinear(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         from ..ops import functional as F_
         pc = self.pc
-        if pc.tp > 1:
-            x = gather_seq(x, pc) if (pc.sequence_parallel and self.sp_input) else copy_to_tp(x, pc)
-        y = F_.linear(x, self.weight)
+        y = None
+        if pc.tp > 1 and pc.sequence_parallel and self.sp_input and x.is_cuda:
+            from . import fused_tp
+            y = fused_tp.column_linear(x, self.weight)          # all-gather fused into the GEMM's operand loads
+        if y is None:
+            if pc.tp > 1:
+                x = gather_seq(x, pc) if (pc.sequence_parallel and self.sp_input) else copy_to_tp(x, pc)
+            y = F_.linear(x, self.weight)
         if self.gather_output:
             y = gather_last_dim(y, pc)
         return y
@@ -246,6 +251,11 @@ class RowParallelLinear(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         from ..ops import functional as F_
         pc = self.pc
+        if pc.tp > 1 and pc.sequence_parallel and self.sp_output and x.is_cuda:
+            from . import fused_tp
+            y = fused_tp.row_linear(x, self.weight)             # reduce-scatter fused into the GEMM's epilogue
+            if y is not None:
+                return y
         y = F_.linear(x, self.weight)
         if pc.tp > 1:
             y = reduce_scatter_seq(y, pc) if (pc.sequence_parallel and self.sp_output) else reduce_from_tp(y, pc)

@@ -65,6 +65,8 @@ class Trainer:
                                           recompute=train_cfg.recompute, device=device)
         # with pipeline stages the embedding copies are summed before the data-parallel reduction,
         # so the reduction cannot start from inside backward
+        from ..ops import functional as F_
+        F_.set_precision_recipe("mxfp8" if train_cfg.precision_recipe == "mxfp8" else "bf16")
         self.fused = {"optimizer": False, "moe": False}
         opt_cls = DistributedOptimizer
         if device.type == "cuda" and self.pc.world_size > 1 and train_cfg.optimizer.optimizer == "adamw":
@@ -100,6 +102,16 @@ class Trainer:
         pc = self.pc
         if not peer_access_available(pc):
             return
+        if pc.tp > 1 and pc.sequence_parallel and self.cfg.torch_dtype() == torch.bfloat16:
+            from ..parallel import fused_tp
+            from ..parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+            width = self.model_cfg.hidden_size
+            for m in self.model.modules():
+                if isinstance(m, (ColumnParallelLinear, RowParallelLinear)):
+                    width = max(width, m.weight.shape[0], m.weight.shape[1])
+            rows = self.cfg.micro_batch_size * (self.cfg.seq_length // pc.tp)
+            self._tp_bufs = fused_tp.install(pc, self.device, rows, width)
+            self.fused["tp"] = self._tp_bufs is not None
         if pc.ep > 1 and pc.tp == 1 and self.cfg.torch_dtype() == torch.bfloat16:
             from ..parallel import fused_moe
             bufs = fused_moe.attach(self.model, pc, self.device,

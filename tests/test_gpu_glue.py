@@ -141,3 +141,49 @@ def test_indexer_topk_kernels(B, S, topk):
             want = sc[b, i, ref_idx[b, i][ref_idx[b, i] >= 0].long()]
             assert abs(sel.min().item() - want.min().item()) <= 2e-2 * max(1.0, abs(want.min().item()))
             assert abs(sel.sum().item() - want.sum().item()) <= 2e-2 * max(1.0, abs(want.sum().item()))
+
+
+def test_mxfp8_quantize_kernels_match_reference():
+    from cppmega_b200.ops import reference as ref
+    from cppmega_b200.ops.cuda import mxfp8
+    torch.manual_seed(0)
+    x = (torch.randn(96, 256, device="cuda") * torch.logspace(-3, 2, 256, device="cuda")).bfloat16()
+    x[5, 32:64] = 0                                             # an all-zero block takes the neutral scale
+    r = mxfp8.quantize_rowwise(x)
+    pay_ref, sc_ref = ref.mxfp8_quantize(x, axis=-1)
+    assert torch.equal(r.scales, sc_ref)
+    assert torch.equal(r.payload, pay_ref.view(torch.uint8))
+    c = mxfp8.quantize_colwise(x)
+    pay_c, sc_c = ref.mxfp8_quantize(x, axis=0)                 # blocks along rows, [rows, cols] / [rows/32, cols]
+    assert torch.equal(c.scales, sc_c.t().contiguous())
+    assert torch.equal(c.payload, pay_c.view(torch.uint8).t().contiguous())
+    deq = mxfp8.dequantize(r)
+    torch.testing.assert_close(deq.float(), ref.mxfp8_dequantize(pay_ref, sc_ref).bfloat16().float(), rtol=0, atol=0)
+    assert ((deq.float() - x.float()).abs() <= 0.07 * x.float().abs() + 1e-6).all()       # 3 mantissa bits
+    sw = mxfp8.swizzle_scales(r.scales)
+    assert torch.equal(sw, ref.swizzle_scales_128x4(r.scales))
+
+
+def test_mxfp8_linear_matches_quantised_reference():
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.ops import reference as ref
+    torch.manual_seed(1)
+    x = (torch.randn(4, 64, 256, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(128, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    F_.set_precision_recipe("mxfp8")
+    try:
+        y = F_.linear(x, w)
+        g = torch.randn_like(y)
+        y.backward(g)
+    finally:
+        F_.set_precision_recipe("bf16")
+    q = lambda t, ax: ref.mxfp8_dequantize(*ref.mxfp8_quantize(t, axis=ax), axis=ax)
+    x2, g2 = x.detach().reshape(-1, 256), g.reshape(-1, 128)
+    y_ref = q(x2, -1) @ q(w.detach(), -1).t()
+    dx_ref = q(g2, -1) @ q(w.detach(), 0)
+    dw_ref = q(g2, 0).t() @ q(x2, 0)
+    assert _rel(y.reshape(-1, 128), y_ref) < 1e-2
+    assert _rel(x.grad.reshape(-1, 256), dx_ref) < 1e-2
+    assert _rel(w.grad, dw_ref) < 1e-2
+    # and it stays close to the unquantised product
+    assert _rel(y.reshape(-1, 128), x2.float() @ w.detach().float().t()) < 6e-2

@@ -40,3 +40,19 @@ def test_fused_collectives_match_nccl(recompute):
     for b, f in zip(base["losses"], fused["losses"]):
         assert abs(b[0] - f[0]) < 3e-2 * max(1.0, abs(b[0])), (base, fused)
         assert abs(b[2] - f[2]) < 8e-2 * max(1.0, abs(b[2])), (base, fused)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tensor_parallel_linears_match_nccl():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(HERE, "dist_gpu_worker_tp.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    outs = json.loads(line[len("RESULT "):])
+    for o in outs:
+        assert all(v < 2e-2 for v in o["rel"]), outs
+        assert o["launches"].get("tp_ag_gemm", 0) == 2 and o["launches"].get("tp_gemm_rs", 0) == 2, outs
+        assert "tp_ag_gemm" not in o["base_launches"]
