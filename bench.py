@@ -112,6 +112,8 @@ def main() -> int:
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--depth", type=int, default=0, help="debug: truncate the stack (result is then not the headline config)")
     ap.add_argument("--recompute", default="auto", choices=["auto", "none", "selective", "full"])
+    ap.add_argument("--keep-last", type=int, default=-1,
+                    help="layers at the end of the stack whose activations are kept instead of recomputed (-1: auto)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--profile-dir", default=None, help="after timing, capture one step with the torch profiler here")
     args = ap.parse_args()
@@ -152,7 +154,13 @@ def main() -> int:
         # per-layer recomputation leaves room for activations.  With experts and optimizer
         # state sharded over >= 4 ranks the activations fit without recomputation.
         recompute = "full" if world < 4 else "selective"
+    keep_last = args.keep_last
+    if keep_last < 0:
+        # spare memory on a single GPU (180 GB minus parameters, optimizer state and the scan stash) pays for keeping the
+        # activations of a few layers; with more ranks "selective" already keeps most of them
+        keep_last = 6 if (world == 1 and recompute == "full" and args.depth is None) else 0
     tcfg = TrainConfig(micro_batch_size=args.micro_batch, seq_length=args.seq, dtype="bf16", recompute=recompute,
+                       recompute_keep_last=keep_last,
                        optimizer=OptimizerConfig(lr=1e-5, weight_decay=0.1, grad_dtype="bf16" if world < 4 else "fp32"),
                        log_interval=0)
     trainer = Trainer(mcfg, tcfg, pc, device=device)
@@ -228,7 +236,7 @@ def main() -> int:
                                 f"{mcfg.depth} layers {mcfg.pattern}, hidden {mcfg.hidden_size}, vocab {mcfg.vocab_size}, MTP {mcfg.mtp.num_layers}",
                        "global_batch": args.micro_batch * world, "micro_batch": args.micro_batch, "seq_len": args.seq,
                        "parallelism": f"ep{ep}dp{world}" if world > 1 else "single GPU (16 local experts)",
-                       "distributed_optimizer": True, "recompute": recompute,
+                       "distributed_optimizer": True, "recompute": recompute, "recompute_keep_last": keep_last,
                        "l2": "weights + activations per step are far larger than the 126 MB L2",
                        "headline_config": not args.depth and args.seq == 4096 and args.micro_batch == 4},
             "clocks": sampler.summary() if rank == 0 else None,

@@ -126,7 +126,7 @@ class NAM56RModel(nn.Module):
     def __init__(self, cfg: ModelConfig, pc: Optional[ParallelContext] = None, *, dtype=torch.float32,
                  seed: int = 1234, layer_numbers: Optional[Sequence[int]] = None,
                  pre_process: bool = True, post_process: bool = True,
-                 recompute: str = "none", device=None):
+                 recompute: str = "none", device=None, recompute_keep_last: int = 0):
         """``layer_numbers`` (1-indexed) selects the layers of this pipeline stage; ``recompute``
         is ``none`` | ``full`` (checkpoint every layer) | ``selective`` (checkpoint the
         mixer layers only, cppmega/megatron/mamba_recompute_patch.py:41-118)."""
@@ -135,6 +135,7 @@ class NAM56RModel(nn.Module):
         self.cfg, self.pc, self.dtype = cfg, pc, dtype
         self.pre_process, self.post_process = pre_process, post_process
         self.recompute = recompute
+        self.recompute_keep_last = recompute_keep_last      # the last K layers of this stage keep their activations
         kinds = cfg.layer_kinds()
         dsa_ranks = cfg.dsa_rank_of_layer()
         self.layer_numbers = list(layer_numbers) if layer_numbers is not None else list(range(1, cfg.depth + 1))
@@ -178,9 +179,12 @@ class NAM56RModel(nn.Module):
     def run_layers(self, x: torch.Tensor, index_cache: Optional[IndexCacheState] = None) -> torch.Tensor:
         cache = index_cache if index_cache is not None else IndexCacheState()
         self.index_cache = cache
-        for key, layer in self.decoder.layers.items():
+        n_layers = len(self.decoder.layers)
+        for pos, (key, layer) in enumerate(self.decoder.layers.items()):
             ck = self.training and (self.recompute == "full" or
                                     (self.recompute == "selective" and layer.kind in ("mamba3", "m2rnn")))
+            if pos >= n_layers - self.recompute_keep_last:
+                ck = False
             if ck and layer.kind == "dsa" and self.cfg.dsa.indexer_loss_coeff > 0:
                 ck = False      # the indexer loss needs the layer's own graph
             if ck and layer.kind == "dsa":
@@ -302,16 +306,17 @@ class NAM56RModel(nn.Module):
 
 
 def build_model(cfg: ModelConfig, pc: Optional[ParallelContext] = None, *, dtype=torch.float32,
-                seed: int = 1234, recompute: str = "none", device=None) -> NAM56RModel:
+                seed: int = 1234, recompute: str = "none", device=None, recompute_keep_last: int = 0) -> NAM56RModel:
     """Build the model chunk of this rank's pipeline stage."""
     pc = pc or get_context()
     if pc.pp == 1:
-        return NAM56RModel(cfg, pc, dtype=dtype, seed=seed, recompute=recompute, device=device)
+        return NAM56RModel(cfg, pc, dtype=dtype, seed=seed, recompute=recompute, device=device,
+                           recompute_keep_last=recompute_keep_last)
     from ..parallel.pipeline import stage_layer_numbers
     layers = stage_layer_numbers(cfg.depth, pc.pp, pc.pp_rank)
     return NAM56RModel(cfg, pc, dtype=dtype, seed=seed, layer_numbers=layers,
                        pre_process=pc.is_first_pp, post_process=pc.is_last_pp,
-                       recompute=recompute, device=device)
+                       recompute=recompute, device=device, recompute_keep_last=recompute_keep_last)
 
 
 _ = dist

@@ -27,39 +27,62 @@ __device__ __forceinline__ float fast_tanh(float x) {
   return y;
 }
 
+// Forward.  One CTA owns RS = min(KD, 32) state rows of one (batch, head): 4 * RS threads, thread (row, quad) holds
+// h[row, 4 quad .. 4 quad + 3].  The 16 x 16 transition matrix sits in registers, arranged per thread in the order in
+// which the row's other three quads arrive by shuffle ("rotation d" brings quad (quad + d) % 4), so a step costs
+// 12 shuffles for the matvec and 4 for the reduction of y over the rows of a warp.  With KD = 64 a head is split
+// over two CTAs; each writes an fp32 partial y and a small kernel adds the halves.
 template <int KD>
-__global__ void __launch_bounds__(KD * 4) m2rnn_fwd_kernel(
+struct M2Split {
+  static constexpr int RS = KD < 32 ? KD : 32;
+  static constexpr int SPLITS = KD / RS;
+  static constexpr int NT = RS * 4;
+};
+
+template <int KD>
+__global__ void __launch_bounds__(M2Split<KD>::NT) m2rnn_fwd_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-    const __nv_bfloat16* __restrict__ W, const float* __restrict__ f, __nv_bfloat16* __restrict__ y,
-    float* __restrict__ hist, float* __restrict__ h_last, int S, int H, int Hq, int Hk) {
-  constexpr int NT = KD * 4;
+    const __nv_bfloat16* __restrict__ W, const float* __restrict__ f, __nv_bfloat16* __restrict__ y, float* __restrict__ y_part,
+    float* __restrict__ hist, float* __restrict__ h_last, int B, int S, int H, int Hq, int Hk) {
+  constexpr int RS = M2Split<KD>::RS, SPLITS = M2Split<KD>::SPLITS, NT = M2Split<KD>::NT;
   constexpr int NW = NT / 32;
-  constexpr int QPT = TB * KD / NT;     // staged q (and k) elements per thread = 8
-  constexpr int VPT = TB * VD / NT;     // staged v elements per thread
-  __shared__ float Ws[VD][VD];
-  __shared__ float qs[TB][KD], ks[TB][KD], vs[TB][VD], fs[TB];
+  constexpr int QPT = TB * RS / NT;     // staged q (and k) elements per thread = 8
+  constexpr int VPT = (TB * VD + NT - 1) / NT;
+  __shared__ float qs[TB][RS], ks[TB][RS], fs[TB];
+  __shared__ __align__(16) float vs[TB][VD];
   __shared__ float ypart[TB][NW][VD];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int row = tid >> 2, quad = tid & 3;
-  const int b = blockIdx.x / H, h = blockIdx.x % H;
+  const int lrow = tid >> 2, quad = tid & 3;
+  const int sp = blockIdx.x % SPLITS;
+  const int bh = blockIdx.x / SPLITS;
+  const int b = bh / H, h = bh % H;
+  const int row = sp * RS + lrow;
   const int hq = Hq == 1 ? 0 : h, hk = Hk == 1 ? 0 : h;
-  for (int i = tid; i < VD * VD; i += NT) Ws[i / VD][i % VD] = __bfloat162float(W[(size_t)h * VD * VD + i]);
+  // wrot[d][u][c] = W[4 * ((quad + d) % 4) + u][4 * quad + c]
+  float wrot[4][4][4];
+#pragma unroll
+  for (int d = 0; d < 4; ++d)
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        wrot[d][u][c] = __bfloat162float(W[(size_t)h * VD * VD + (4 * ((quad + d) & 3) + u) * VD + 4 * quad + c]);
   float hreg[4] = {0.f, 0.f, 0.f, 0.f};
   float pq[QPT], pk[QPT], pv[VPT], pf = 0.f;
 
   auto prefetch = [&](int t0) {
 #pragma unroll
     for (int i = 0; i < QPT; ++i) {
-      const int e = tid + i * NT, t = e / KD, c = e % KD;
+      const int e = tid + i * NT, t = e / RS, c = e % RS;
       const bool ok = t0 + t < S;
-      pq[i] = ok ? __bfloat162float(q[((size_t)(b * S + t0 + t) * Hq + hq) * KD + c]) : 0.f;
-      pk[i] = ok ? __bfloat162float(k[((size_t)(b * S + t0 + t) * Hk + hk) * KD + c]) : 0.f;
+      pq[i] = ok ? __bfloat162float(q[((size_t)(b * S + t0 + t) * Hq + hq) * KD + sp * RS + c]) : 0.f;
+      pk[i] = ok ? __bfloat162float(k[((size_t)(b * S + t0 + t) * Hk + hk) * KD + sp * RS + c]) : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int e = tid + i * NT;
       const int t = e / VD, c = e % VD;
-      pv[i] = (t0 + t < S) ? __bfloat162float(v[((size_t)(b * S + t0 + t) * H + h) * VD + c]) : 0.f;
+      pv[i] = (e < TB * VD && t0 + t < S) ? __bfloat162float(v[((size_t)(b * S + t0 + t) * H + h) * VD + c]) : 0.f;
     }
     if (tid < TB) pf = (t0 + tid < S) ? f[(size_t)(b * S + t0 + tid) * H + h] : 1.f;
   };
@@ -67,13 +90,13 @@ __global__ void __launch_bounds__(KD * 4) m2rnn_fwd_kernel(
 #pragma unroll
     for (int i = 0; i < QPT; ++i) {
       const int e = tid + i * NT;
-      qs[e / KD][e % KD] = pq[i];
-      ks[e / KD][e % KD] = pk[i];
+      qs[e / RS][e % RS] = pq[i];
+      ks[e / RS][e % RS] = pk[i];
     }
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int e = tid + i * NT;
-      vs[e / VD][e % VD] = pv[i];
+      if (e < TB * VD) vs[e / VD][e % VD] = pv[i];
     }
     if (tid < TB) fs[tid] = pf;
   };
@@ -81,23 +104,22 @@ __global__ void __launch_bounds__(KD * 4) m2rnn_fwd_kernel(
   prefetch(0);
   commit();
   __syncthreads();
+  const int src_base = lane & ~3;
   for (int t0 = 0; t0 < S; t0 += TB) {
     if (t0 + TB < S) prefetch(t0 + TB);
     const int nt = min(TB, S - t0);
     for (int t = 0; t < nt; ++t) {
-      float hrow[VD];
+      const float kt = ks[t][lrow], qt = qs[t][lrow], ft = fs[t];
+      const float4 vq = *reinterpret_cast<const float4*>(&vs[t][quad * 4]);
+      float a[4] = {kt * vq.x, kt * vq.y, kt * vq.z, kt * vq.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int d = 0; d < 4; ++d) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) hrow[j * 4 + c] = __shfl_sync(0xffffffffu, hreg[c], (lane & ~3) + j);
-      const float kt = ks[t][row], qt = qs[t][row], ft = fs[t];
-      float a[4];
+        for (int u = 0; u < 4; ++u) {
+          const float hv = d == 0 ? hreg[u] : __shfl_sync(0xffffffffu, hreg[u], src_base | ((quad + d) & 3));
 #pragma unroll
-      for (int c = 0; c < 4; ++c) a[c] = kt * vs[t][quad * 4 + c];
-#pragma unroll
-      for (int u = 0; u < VD; ++u) {
-        const float4 w = *reinterpret_cast<const float4*>(&Ws[u][quad * 4]);
-        a[0] += hrow[u] * w.x; a[1] += hrow[u] * w.y; a[2] += hrow[u] * w.z; a[3] += hrow[u] * w.w;
+          for (int c = 0; c < 4; ++c) a[c] = fmaf(hv, wrot[d][u][c], a[c]);
+        }
       }
       float yp[4];
 #pragma unroll
@@ -109,15 +131,17 @@ __global__ void __launch_bounds__(KD * 4) m2rnn_fwd_kernel(
         float4 o = make_float4(hreg[0], hreg[1], hreg[2], hreg[3]);
         *reinterpret_cast<float4*>(hist + (((size_t)(b * H + h) * S + t0 + t) * KD + row) * VD + quad * 4) = o;
       }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        yp[c] += __shfl_xor_sync(0xffffffffu, yp[c], 4);
-        yp[c] += __shfl_xor_sync(0xffffffffu, yp[c], 8);
-        yp[c] += __shfl_xor_sync(0xffffffffu, yp[c], 16);
-      }
-      if (lane < 4) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) ypart[t][warp][quad * 4 + c] = yp[c];
+      // sum over the 8 rows of this warp (lanes that differ in bits 2..4): 4 shuffles, halving the values kept
+      {
+        const bool u4 = lane & 16, u3 = lane & 8;
+        const float k0 = u4 ? yp[2] : yp[0], k1 = u4 ? yp[3] : yp[1];
+        const float s0 = u4 ? yp[0] : yp[2], s1 = u4 ? yp[1] : yp[3];
+        const float a0 = k0 + __shfl_xor_sync(0xffffffffu, s0, 16);
+        const float a1 = k1 + __shfl_xor_sync(0xffffffffu, s1, 16);
+        const float kk = u3 ? a1 : a0, ss = u3 ? a0 : a1;
+        float r = kk + __shfl_xor_sync(0xffffffffu, ss, 8);
+        r += __shfl_xor_sync(0xffffffffu, r, 4);
+        if ((lane & 4) == 0) ypart[t][warp][quad * 4 + (u4 ? 2 : 0) + (u3 ? 1 : 0)] = r;
       }
     }
     __syncthreads();
@@ -126,7 +150,9 @@ __global__ void __launch_bounds__(KD * 4) m2rnn_fwd_kernel(
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < NW; ++w) s += ypart[t][w][c];
-      y[((size_t)(b * S + t0 + t) * H + h) * VD + c] = __float2bfloat16(s);
+      const size_t o = ((size_t)(b * S + t0 + t) * H + h) * VD + c;
+      if (SPLITS == 1) y[o] = __float2bfloat16(s);
+      else y_part[(size_t)sp * B * S * H * VD + o] = s;
     }
     if (t0 + TB < S) commit();
     __syncthreads();
@@ -134,6 +160,15 @@ __global__ void __launch_bounds__(KD * 4) m2rnn_fwd_kernel(
   if (h_last) {
     float4 o = make_float4(hreg[0], hreg[1], hreg[2], hreg[3]);
     *reinterpret_cast<float4*>(h_last + ((size_t)(b * H + h) * KD + row) * VD + quad * 4) = o;
+  }
+}
+
+__global__ void __launch_bounds__(256) m2rnn_sum_parts_kernel(const float* __restrict__ parts, __nv_bfloat16* __restrict__ y, int nparts,
+                                                              long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float s = 0.f;
+    for (int p = 0; p < nparts; ++p) s += parts[(size_t)p * n + i];
+    y[i] = __float2bfloat16(s);
   }
 }
 
@@ -325,19 +360,30 @@ __global__ void __launch_bounds__(KD * 4) m2rnn_bwd_kernel(
 using namespace cm;
 
 // q [B,S,Hq,KD], k [B,S,Hk,KD], v [B,S,H,16], W [H,16,16] (bf16); f [B,S,H] fp32.
-// y [B,S,H,16] bf16; hist (nullable) [B,H,S,KD,16] fp32; h_last (nullable) [B,H,KD,16] fp32.
+// y [B,S,H,16] bf16; y_part: fp32 scratch [2,B,S,H,16] (needed for KD = 64, may be null otherwise);
+// hist (nullable) [B,H,S,KD,16] fp32; h_last (nullable) [B,H,KD,16] fp32.
 extern "C" int cm_m2rnn_fwd(const void* q, const void* k, const void* v, const void* W, const float* f, void* y,
-                            float* hist, float* h_last, int B, int S, int H, int Hq, int Hk, int KD, int VDim,
+                            float* y_part, float* hist, float* h_last, int B, int S, int H, int Hq, int Hk, int KD, int VDim,
                             cudaStream_t s) {
   if (B <= 0 || S <= 0) return 0;
   if (VDim != VD) return -10;
   auto qp = (const __nv_bfloat16*)q; auto kp = (const __nv_bfloat16*)k; auto vp = (const __nv_bfloat16*)v;
   auto wp = (const __nv_bfloat16*)W; auto yp = (__nv_bfloat16*)y;
-  const int grid = B * H;
-  if (KD == 64) m2rnn_fwd_kernel<64><<<grid, 256, 0, s>>>(qp, kp, vp, wp, f, yp, hist, h_last, S, H, Hq, Hk);
-  else if (KD == 32) m2rnn_fwd_kernel<32><<<grid, 128, 0, s>>>(qp, kp, vp, wp, f, yp, hist, h_last, S, H, Hq, Hk);
-  else if (KD == 16) m2rnn_fwd_kernel<16><<<grid, 64, 0, s>>>(qp, kp, vp, wp, f, yp, hist, h_last, S, H, Hq, Hk);
-  else return -10;
+  const int bh = B * H;
+  if (KD == 64) {
+    if (!y_part) return -10;          // two CTAs per head: needs the [2, B, S, H, 16] fp32 partial buffer
+    m2rnn_fwd_kernel<64><<<bh * 2, 128, 0, s>>>(qp, kp, vp, wp, f, yp, y_part, hist, h_last, B, S, H, Hq, Hk);
+    const long long n = (long long)B * S * H * VD;
+    long long blocks = (n + 255) / 256;
+    const int grid = (int)(blocks < (long long)sm_count() * 8 ? blocks : (long long)sm_count() * 8);
+    m2rnn_sum_parts_kernel<<<grid, 256, 0, s>>>(y_part, yp, 2, n);
+  } else if (KD == 32) {
+    m2rnn_fwd_kernel<32><<<bh, 128, 0, s>>>(qp, kp, vp, wp, f, yp, y_part, hist, h_last, B, S, H, Hq, Hk);
+  } else if (KD == 16) {
+    m2rnn_fwd_kernel<16><<<bh, 64, 0, s>>>(qp, kp, vp, wp, f, yp, y_part, hist, h_last, B, S, H, Hq, Hk);
+  } else {
+    return -10;
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

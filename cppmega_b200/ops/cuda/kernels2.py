@@ -11,7 +11,7 @@ from .. import functional as F_
 def declare(L: ctypes.CDLL) -> None:
     vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
     sig = {
-        "cm_m2rnn_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
+        "cm_m2rnn_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
         "cm_m2rnn_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
     }
     for name, args in sig.items():
@@ -40,8 +40,10 @@ class M2RNNFn(torch.autograd.Function):
         need = any(ctx.needs_input_grad)
         y = torch.empty(B, S, H, VD, dtype=torch.bfloat16, device=v.device)
         hist = torch.empty(B, H, S, KD, VD, dtype=torch.float32, device=v.device) if need else None
+        ypart = torch.empty(2, B, S, H, VD, dtype=torch.float32, device=v.device) if KD == 64 else None
         _check(lib().cm_m2rnn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), W.data_ptr(), f.data_ptr(), y.data_ptr(),
-                                  hist.data_ptr() if need else None, None, B, S, H, Hq, Hk, KD, VD, stream_ptr()),
+                                  None if ypart is None else ypart.data_ptr(), hist.data_ptr() if need else None, None,
+                                  B, S, H, Hq, Hk, KD, VD, stream_ptr()),
                "cm_m2rnn_fwd")
         F_.count_launch("m2rnn_fwd")
         if need:

@@ -19,6 +19,11 @@ def declare(L: ctypes.CDLL) -> None:
     f32 = ctypes.c_float
     sig["cm_sparse_mla_fwd"] = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp]
     sig["cm_sparse_mla_bwd"] = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp]
+    sig["cm_router_topk_fwd"] = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp]
+    sig["cm_router_topk_bwd"] = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp]
+    sig["cm_ngram_embed_fwd"] = [vp] * 8 + [i32] * 6 + [vp]
+    sig["cm_ngram_embed_bwd"] = [vp] * 8 + [i32] * 6 + [vp]
+    sig["cm_rope"] = [vp, vp, vp, vp, i64, i32, i32, i32, i64, i64, ctypes.c_float, vp]
     sig["cm_head_reduce"] = [vp, vp, vp, i64, i32, i32, i32, vp]
     sig["cm_indexer_scores"] = [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
     sig["cm_indexer_topk"] = [vp, vp, i32, i32, i32, vp]
@@ -157,7 +162,147 @@ def indexer_topk(q_idx, k_idx, w, topk: int):
     return out
 
 
+class RouterTopkFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, bias, topk, sigmoid, norm):
+        from . import lib, stream_ptr, _check
+        T, E = logits.shape
+        lf = logits.float().contiguous()
+        probs = torch.empty(T, topk, dtype=torch.float32, device=logits.device)
+        ids = torch.empty(T, topk, dtype=torch.int64, device=logits.device)
+        scores = torch.empty(T, E, dtype=torch.float32, device=logits.device)
+        bf = None if bias is None else bias.float().contiguous()
+        _check(lib().cm_router_topk_fwd(lf.data_ptr(), None if bf is None else bf.data_ptr(), probs.data_ptr(), ids.data_ptr(),
+                                        scores.data_ptr(), T, E, topk, int(sigmoid), int(norm), stream_ptr()),
+               "cm_router_topk_fwd")
+        F_.count_launch("router_topk")
+        ctx.save_for_backward(scores, ids)
+        ctx.cfg = (topk, sigmoid, norm, logits.dtype)
+        ctx.mark_non_differentiable(ids)
+        return probs, ids, scores
+
+    @staticmethod
+    def backward(ctx, dprobs, _dids, dscores):
+        from . import lib, stream_ptr, _check
+        scores, ids = ctx.saved_tensors
+        topk, sigmoid, norm, dtype = ctx.cfg
+        T, E = scores.shape
+        dp = None if dprobs is None else dprobs.float().contiguous()
+        dsc = None if dscores is None else dscores.float().contiguous()
+        dl = torch.empty(T, E, dtype=torch.float32, device=scores.device)
+        _check(lib().cm_router_topk_bwd(scores.data_ptr(), ids.data_ptr(), None if dp is None else dp.data_ptr(),
+                                        None if dsc is None else dsc.data_ptr(), dl.data_ptr(), T, E, topk, int(sigmoid),
+                                        int(norm), stream_ptr()), "cm_router_topk_bwd")
+        F_.count_launch("router_topk_bwd")
+        return dl.to(dtype), None, None, None, None
+
+
+def router_topk(logits, topk, score_function, expert_bias, norm_topk_prob):
+    if logits.dim() != 2 or logits.shape[1] > 64 or topk > 8 or score_function not in ("sigmoid", "softmax"):
+        return None
+    return RouterTopkFn.apply(logits, expert_bias, topk, score_function == "sigmoid", bool(norm_topk_prob))
+
+
+class NgramEmbedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, table, token_ids, mults, bias, sizes, offsets, order):
+        from . import lib, stream_ptr, _check
+        B, S = token_ids.shape
+        NT, max_order = mults.shape
+        D = table.shape[1]
+        tok = token_ids.long().contiguous()
+        tab = table.contiguous()
+        consts = [t.long().contiguous() for t in (mults, bias, sizes, offsets, order)]
+        out = torch.empty(B, S, NT * D, dtype=table.dtype, device=table.device)
+        kind = 0 if table.dtype == torch.float32 else 1
+        _check(lib().cm_ngram_embed_fwd(tok.data_ptr(), tab.data_ptr(), *[c.data_ptr() for c in consts], out.data_ptr(),
+                                        B, S, NT, D, max_order, kind, stream_ptr()), "cm_ngram_embed_fwd")
+        F_.count_launch("ngram_hash_embed")
+        ctx.save_for_backward(tok, *consts)
+        ctx.meta = (table.shape, table.dtype, kind)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from . import lib, stream_ptr, _check
+        tok, *consts = ctx.saved_tensors
+        shape, dtype, kind = ctx.meta
+        B, S = tok.shape
+        NT, max_order = consts[0].shape
+        dtable = torch.zeros(shape, dtype=torch.float32, device=dout.device)
+        dout = dout.to(dtype).contiguous()
+        _check(lib().cm_ngram_embed_bwd(tok.data_ptr(), dout.data_ptr(), *[c.data_ptr() for c in consts], dtable.data_ptr(),
+                                        B, S, NT, shape[1], max_order, kind, stream_ptr()), "cm_ngram_embed_bwd")
+        F_.count_launch("ngram_hash_embed_bwd")
+        return dtable.to(dtype), None, None, None, None, None, None
+
+
+def ngram_hash_embed(token_ids, table, mults, bias, sizes, offsets, order):
+    if table.dtype not in (torch.float32, torch.bfloat16) or token_ids.dim() != 2:
+        return None
+    return NgramEmbedFn.apply(table, token_ids, mults, bias, sizes, offsets, order)
+
+
+class RopeFn(torch.autograd.Function):
+    """Rotate-half RoPE on the last dim of a bf16 tensor [B, S, ..., D] whose last dim is contiguous and whose rows
+    (everything but the last dim) are evenly strided, e.g. a column slice of a wider head vector."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        return _rope_launch(x, cos, sin, 1.0)
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        return _rope_launch(g, cos, sin, -1.0), None, None
+
+
+def _row_stride(x: torch.Tensor):
+    """Element stride between consecutive rows when ``x`` can be read as [rows, D] with one stride, else None."""
+    D = x.shape[-1]
+    if x.stride(-1) != 1:
+        return None
+    st = None
+    expect = None
+    for size, stride in zip(reversed(x.shape[:-1]), reversed(x.stride()[:-1])):
+        if size == 1:
+            continue
+        if st is None:
+            st, expect = stride, stride * size
+        elif stride != expect:
+            return None
+        else:
+            expect = stride * size
+    return D if st is None else st
+
+
+def _rope_launch(x, cos, sin, sign):
+    from . import lib, stream_ptr, _check
+    ld = _row_stride(x)
+    if ld is None or ld < x.shape[-1]:
+        x = x.contiguous()
+        ld = x.shape[-1]
+    B, S, D = x.shape[0], x.shape[1], x.shape[-1]
+    rows = x.numel() // D
+    R = rows // (B * S)
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    _check(lib().cm_rope(x.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), rows, S, R, D, ld, D, sign, stream_ptr()),
+           "cm_rope")
+    F_.count_launch("rope")
+    return out
+
+
+def apply_rope(x, cos, sin):
+    if x.dtype != torch.bfloat16 or x.dim() < 3 or x.shape[-1] % 2 or cos.shape != (x.shape[1], x.shape[-1] // 2):
+        return None
+    return RopeFn.apply(x, cos.float().contiguous(), sin.float().contiguous())
+
+
 def register() -> None:
+    F_.register_cuda("router_topk", router_topk)
+    F_.register_cuda("ngram_hash_embed", ngram_hash_embed)
+    F_.register_cuda("apply_rope", apply_rope)
     F_.register_cuda("indexer_topk", indexer_topk)
     F_.register_cuda("angle_cumsum", angle_cumsum)
     F_.register_cuda("sparse_mla", sparse_mla)

@@ -169,6 +169,11 @@ def swiglu(gate_up):
 
 
 def apply_rope(x, cos, sin):
+    fn = _cuda("apply_rope", x)
+    if fn is not None:
+        y = fn(x, cos, sin)
+        if y is not None:
+            return y
     return ref.apply_rope(x, cos, sin)
 
 
@@ -177,7 +182,9 @@ def apply_rope(x, cos, sin):
 def ngram_hash_embed(token_ids, table, mults, bias, table_sizes, table_offsets, order_of_table):
     fn = _cuda("ngram_hash_embed", table)
     if fn is not None:
-        return fn(token_ids, table, mults, bias, table_sizes, table_offsets, order_of_table)
+        out = fn(token_ids, table, mults, bias, table_sizes, table_offsets, order_of_table)
+        if out is not None:
+            return out
     return ref.ngram_hash_embed(token_ids, table, mults, bias, table_sizes, table_offsets, order_of_table)
 
 
@@ -277,5 +284,7 @@ def linear_cross_entropy_weighted(hidden, weight, labels, row_weights, ignore_in
 def router_topk(logits, topk, score_function="sigmoid", expert_bias=None, norm_topk_prob=True):
     fn = _cuda("router_topk", logits)
     if fn is not None:
-        return fn(logits, topk, score_function, expert_bias, norm_topk_prob)
+        out = fn(logits, topk, score_function, expert_bias, norm_topk_prob)
+        if out is not None:
+            return out
     return ref.router_topk(logits, topk, score_function, expert_bias, norm_topk_prob)

@@ -34,6 +34,7 @@ class TrainConfig:
     seq_length: int = 4096
     dtype: str = "bf16"                          # bf16 | fp32
     recompute: str = "none"                      # none | selective | full
+    recompute_keep_last: int = 0                 # the last K layers of a stage are not recomputed (spend spare memory)
     seed: int = 1234
     log_interval: int = 1
     check_finite: bool = True
@@ -62,7 +63,8 @@ class Trainer:
                       else torch.device("cpu"))
         self.device = device
         self.model = model or build_model(model_cfg, self.pc, dtype=train_cfg.torch_dtype(), seed=train_cfg.seed,
-                                          recompute=train_cfg.recompute, device=device)
+                                          recompute=train_cfg.recompute, device=device,
+                                          recompute_keep_last=train_cfg.recompute_keep_last)
         # with pipeline stages the embedding copies are summed before the data-parallel reduction,
         # so the reduction cannot start from inside backward
         from ..ops import functional as F_
@@ -116,7 +118,7 @@ class Trainer:
             from ..parallel import fused_moe
             bufs = fused_moe.attach(self.model, pc, self.device,
                                     tokens_per_rank=self.cfg.micro_batch_size * self.cfg.seq_length,
-                                    per_layer=self.cfg.recompute != "full")
+                                    per_layer=self.cfg.recompute != "full" or self.cfg.recompute_keep_last > 0)
             self.fused["moe"] = bufs is not None
             self._moe_bufs = bufs
 

@@ -187,3 +187,62 @@ def test_mxfp8_linear_matches_quantised_reference():
     assert _rel(w.grad, dw_ref) < 1e-2
     # and it stays close to the unquantised product
     assert _rel(y.reshape(-1, 128), x2.float() @ w.detach().float().t()) < 6e-2
+
+
+@pytest.mark.parametrize("score_fn,norm", [("sigmoid", True), ("softmax", True), ("softmax", False)])
+def test_router_topk_kernel(score_fn, norm):
+    from cppmega_b200.ops import reference as ref
+    from cppmega_b200.ops.cuda import kernels4
+    torch.manual_seed(0)
+    T, E, K = 777, 16, 4
+    logits = torch.randn(T, E, device="cuda").requires_grad_()
+    bias = torch.randn(E, device="cuda") * 0.1
+    probs, ids, scores = kernels4.router_topk(logits, K, score_fn, bias, norm)
+    gp, gs = torch.randn_like(probs), torch.randn_like(scores) * 0.1
+    (probs * gp).sum().add((scores * gs).sum()).backward()
+    l2 = logits.detach().clone().requires_grad_()
+    p2, i2, s2 = ref.router_topk(l2, K, score_fn, bias, norm)
+    (p2 * gp).sum().add((s2 * gs).sum()).backward()
+    assert torch.equal(ids.sort(-1).values, i2.sort(-1).values)
+    torch.testing.assert_close(scores, s2, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(probs.sort(-1).values, p2.sort(-1).values, rtol=1e-4, atol=1e-6)
+    assert _rel(logits.grad, l2.grad) < 1e-3
+
+
+def test_ngram_hash_embed_kernel():
+    from cppmega_b200.config.model import nam56r_tiny
+    from cppmega_b200.models.embedding import NgramHashEmbedding
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.ops import reference as ref
+    cfg = nam56r_tiny()
+    torch.manual_seed(0)
+    emb = NgramHashEmbedding(cfg.hidden_size, cfg.ngram_hash, dtype=torch.bfloat16).cuda()
+    ids = torch.randint(0, cfg.vocab_size, (3, 50), device="cuda")
+    args = (emb.hash_mults, emb.hash_bias, emb.table_sizes_t, emb.table_offsets, emb.order_for_table)
+    table = emb.unified_table.weight
+    out = F_.ngram_hash_embed(ids, table, *args)
+    want = ref.ngram_hash_embed(ids, table, *args)
+    assert torch.equal(out, want)
+    g = torch.randn_like(out)
+    (gk,) = torch.autograd.grad(out, table, g)
+    (gr,) = torch.autograd.grad(want, table, g)
+    assert _rel(gk, gr) < 1e-2
+
+
+def test_rope_kernel_on_slices():
+    from cppmega_b200.ops import reference as ref
+    from cppmega_b200.ops.cuda import kernels4
+    torch.manual_seed(0)
+    B, S, H, D = 2, 70, 4, 64
+    wide = torch.randn(B, S, H, 2 * D, device="cuda").bfloat16().requires_grad_()
+    cos, sin = ref.rope_tables(S, D, 5e5, device="cuda")
+    x = wide[..., D:]                                   # column slice: rotated in place of a copy
+    y = kernels4.apply_rope(x, cos, sin)
+    g = torch.randn_like(y)
+    (gw,) = torch.autograd.grad(y, wide, g)
+    w2 = wide.detach().clone().requires_grad_()
+    y2 = ref.apply_rope(w2[..., D:], cos, sin)
+    (gw2,) = torch.autograd.grad(y2, w2, g)
+    assert _rel(y, y2) < 1e-2 and _rel(gw, gw2) < 1e-2
+    k = torch.randn(B, S, D, device="cuda").bfloat16()
+    assert _rel(kernels4.apply_rope(k, cos, sin), ref.apply_rope(k, cos, sin)) < 1e-2
