@@ -40,7 +40,7 @@ class M2RNNFn(torch.autograd.Function):
         need = any(ctx.needs_input_grad)
         y = torch.empty(B, S, H, VD, dtype=torch.bfloat16, device=v.device)
         hist = torch.empty(B, H, S, KD, VD, dtype=torch.float32, device=v.device) if need else None
-        ypart = torch.empty(2, B, S, H, VD, dtype=torch.float32, device=v.device) if KD == 64 else None
+        ypart = torch.empty(KD // 16, B, S, H, VD, dtype=torch.float32, device=v.device) if KD > 16 else None
         _check(lib().cm_m2rnn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), W.data_ptr(), f.data_ptr(), y.data_ptr(),
                                   None if ypart is None else ypart.data_ptr(), hist.data_ptr() if need else None, None,
                                   B, S, H, Hq, Hk, KD, VD, stream_ptr()),
@@ -61,8 +61,8 @@ class M2RNNFn(torch.autograd.Function):
         dy = dy.to(torch.bfloat16).contiguous()
         dq_h = torch.empty(B, S, H, KD, dtype=torch.float32, device=dev)
         dk_h = torch.empty(B, S, H, KD, dtype=torch.float32, device=dev)
-        dv = torch.empty(B, S, H, VD, dtype=torch.float32, device=dev)
-        df = torch.empty(B, S, H, dtype=torch.float32, device=dev)
+        dv = torch.zeros(B, S, H, VD, dtype=torch.float32, device=dev)      # accumulated over the CTAs of a head
+        df = torch.zeros(B, S, H, dtype=torch.float32, device=dev)
         dW = torch.zeros(H, VD, VD, dtype=torch.float32, device=dev)
         _check(lib().cm_m2rnn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), W.data_ptr(), f.data_ptr(), hist.data_ptr(),
                                   dy.data_ptr(), dq_h.data_ptr(), dk_h.data_ptr(), dv.data_ptr(), df.data_ptr(),

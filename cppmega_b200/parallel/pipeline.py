@@ -203,3 +203,195 @@ def sync_embedding_copies(model, pc: ParallelContext) -> None:
         g = getattr(p, "main_grad", None)
         if g is not None:
             dist.all_reduce(g, group=grp)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Several model chunks per rank: interleaved 1F1B (virtual pipeline) and the V-shaped DualPipeV placement
+# ---------------------------------------------------------------------------------------------------------
+
+class ChunkedModel(torch.nn.Module):
+    """The model chunks held by one pipeline rank.  ``chunk_ids[i]`` is the position of ``chunks[i]`` in the global
+    chain of ``total_chunks`` chunks; chunk 0 owns the embedding, the last chunk the output layer and the MTP heads.
+    When one rank holds both ends (V placement) they share one embedding module, so no gradient sync is needed."""
+
+    def __init__(self, chunks, chunk_ids, total_chunks: int):
+        super().__init__()
+        self.chunks = torch.nn.ModuleList(chunks)
+        self.chunk_ids = list(chunk_ids)
+        self.total_chunks = total_chunks
+        self.cfg = chunks[0].cfg
+        first = [c for c, i in zip(chunks, chunk_ids) if i == 0]
+        last = [c for c, i in zip(chunks, chunk_ids) if i == total_chunks - 1]
+        self.shared_embedding = False
+        if first and last and first[0] is not last[0] and hasattr(last[0], "embedding"):
+            last[0].embedding = first[0].embedding
+            self.shared_embedding = True
+
+    def chunk(self, chunk_id: int):
+        return self.chunks[self.chunk_ids.index(chunk_id)]
+
+    def moe_layers(self):
+        out = []
+        for c in self.chunks:
+            out += c.moe_layers()
+        return out
+
+    def update_router_biases(self):
+        for c in self.chunks:
+            c.update_router_biases()
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def forward(self, *a, **k):
+        raise RuntimeError("a chunked model runs through run_chunked_schedule")
+
+
+def build_chunked_model(cfg, pc: ParallelContext, schedule: str, **model_kwargs) -> ChunkedModel:
+    """Model chunks of this rank for ``schedule`` = ``interleaved`` (chunk v*pp + stage) or ``dualpipev``
+    (chunks stage and 2*pp-1-stage)."""
+    from ..models.nam56r import NAM56RModel
+    from . import schedules as sch
+    if schedule == "interleaved":
+        total = pc.pp * max(pc.config.vpp, 1)
+        mine = [v * pc.pp + pc.pp_rank for v in range(max(pc.config.vpp, 1))]
+    elif schedule == "dualpipev":
+        if pc.ep > 1:
+            raise ValueError("DualPipeV requires expert parallel size 1")
+        total = 2 * pc.pp
+        mine = [pc.pp_rank, 2 * pc.pp - 1 - pc.pp_rank]
+    else:
+        raise ValueError(f"unknown chunked schedule {schedule!r}")
+    layers = sch.split_layers(cfg.depth, total)
+    chunks = [NAM56RModel(cfg, pc, layer_numbers=layers[c], pre_process=(c == 0), post_process=(c == total - 1),
+                          **model_kwargs) for c in mine]
+    return ChunkedModel(chunks, mine, total)
+
+
+def schedule_actions(schedule: str, pp: int, vpp: int, num_microbatches: int):
+    """Action lists of every pipeline rank and the chunk -> rank map."""
+    from . import schedules as sch
+    if schedule == "interleaved":
+        per_rank = [sch.interleaved_1f1b(pp, vpp, st, num_microbatches) for st in range(pp)]
+        owner = lambda c: sch.chunk_owner_interleaved(c, pp)
+        total = pp * vpp
+    else:
+        per_rank = sch.dualpipev(pp, num_microbatches)
+        owner = lambda c: sch.chunk_owner_v(c, pp)
+        total = 2 * pp
+    sch.validate(per_rank, total, num_microbatches, owner)
+    return per_rank, owner, total
+
+
+def run_chunked_schedule(trainer, microbatches: List[Dict[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
+    """Execute one optimizer step of an interleaved or V-shaped schedule.
+
+    Every rank knows every rank's action list, hence the exact order in which each peer will send to it: all
+    receives are posted up front in that order (point-to-point channels are FIFO per pair), sends are posted as
+    results appear, and a chunk hand-over inside one rank (the turn of the V) is a plain tensor hand-off."""
+    pc: ParallelContext = trainer.pc
+    model: ChunkedModel = trainer.model
+    M = len(microbatches)
+    mbs = [trainer._to_device(mb) for mb in microbatches]
+    B, S = mbs[0]["input_ids"].shape
+    s_local = S // pc.tp if pc.sequence_parallel else S
+    shape = (B, s_local, trainer.model_cfg.hidden_size)
+    dtype, dev = trainer.cfg.torch_dtype(), trainer.device
+    per_rank, owner, total = schedule_actions(trainer.cfg.pipeline_schedule, pc.pp, max(pc.config.vpp, 1), M)
+    me = pc.pp_rank
+
+    def message_of(action):
+        """(key, destination stage) of the tensor an action produces for another chunk, or None."""
+        kind, c, mb = action
+        if kind == "F" and c < total - 1:
+            return ("F", c, mb), owner(c + 1)
+        if kind == "B" and c > 0:
+            return ("B", c, mb), owner(c - 1)
+        return None
+
+    # receives, posted per source in the source's own order
+    recv_buf: Dict[tuple, torch.Tensor] = {}
+    recv_req: Dict[tuple, object] = {}
+    for src in range(pc.pp):
+        if src == me:
+            continue
+        for action in per_rank[src]:
+            msg = message_of(action)
+            if msg is None or msg[1] != me:
+                continue
+            buf = torch.empty(shape, dtype=dtype, device=dev)
+            recv_buf[msg[0]] = buf
+            recv_req[msg[0]] = dist.irecv(buf, src=pc.pp_ranks[src])
+    handoff: Dict[tuple, torch.Tensor] = {}
+    send_reqs = []
+
+    def fetch(key):
+        if key in handoff:
+            return handoff.pop(key)
+        recv_req.pop(key).wait()
+        return recv_buf.pop(key)
+
+    def deliver(action, tensor):
+        msg = message_of(action)
+        if msg is None:
+            return
+        key, dst = msg
+        if dst == me:
+            handoff[key] = tensor
+        else:
+            t = tensor.contiguous()
+            send_reqs.append((dist.isend(t, dst=pc.pp_ranks[dst]), t))
+
+    inputs: Dict[tuple, Optional[torch.Tensor]] = {}
+    outputs: Dict[tuple, torch.Tensor] = {}
+    stats = {"loss": None, "lm_loss": None, "mtp": None}
+    my_actions = per_rank[me]
+    n_bwd_total = sum(1 for a in my_actions if a[0] == "B")
+    n_bwd = 0
+    for action in my_actions:
+        kind, c, mb = action
+        chunk = model.chunk(c)
+        batch = mbs[mb]
+        if kind == "F":
+            x_in = None
+            if c > 0:
+                x_in = fetch(("F", c - 1, mb)).detach().requires_grad_()
+            labels = batch["labels"] if c == total - 1 else None
+            out = chunk(batch["input_ids"], labels, batch.get("loss_mask"), hidden_in=x_in,
+                        structure_inputs=batch.get("structure_inputs"))
+            inputs[(c, mb)] = x_in
+            if c == total - 1:
+                outputs[(c, mb)] = out["loss"] / M
+                l = out["loss"].detach()
+                stats["loss"] = l if stats["loss"] is None else stats["loss"] + l
+                stats["lm_loss"] = out["lm_loss"] if stats["lm_loss"] is None else stats["lm_loss"] + out["lm_loss"]
+                if out["mtp_losses"]:
+                    stats["mtp"] = (out["mtp_losses"] if stats["mtp"] is None
+                                    else [a + b for a, b in zip(stats["mtp"], out["mtp_losses"])])
+            else:
+                outputs[(c, mb)] = out
+                deliver(action, out.detach())
+        else:
+            n_bwd += 1
+            trainer.optimizer.set_microbatch(is_last=(n_bwd == n_bwd_total), grad_scale=1.0)
+            out = outputs.pop((c, mb))
+            if c == total - 1:
+                out.backward()
+            else:
+                torch.autograd.backward(out, grad_tensors=fetch(("B", c + 1, mb)))
+            x_in = inputs.pop((c, mb))
+            if x_in is not None:
+                deliver(action, x_in.grad)
+    for req, _t in send_reqs:
+        req.wait()
+    if not model.shared_embedding:
+        for ch in model.chunks:
+            if hasattr(ch, "embedding"):
+                sync_embedding_copies(ch, pc)
+                break
+    zero = torch.zeros((), device=dev)
+    res = {"loss": (stats["loss"] / M) if stats["loss"] is not None else zero,
+           "lm_loss": (stats["lm_loss"] / M) if stats["lm_loss"] is not None else zero}
+    if stats["mtp"] is not None:
+        res["mtp_losses"] = [m / M for m in stats["mtp"]]
+    return res

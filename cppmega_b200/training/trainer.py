@@ -62,9 +62,16 @@ class Trainer:
             device = (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
                       else torch.device("cpu"))
         self.device = device
-        self.model = model or build_model(model_cfg, self.pc, dtype=train_cfg.torch_dtype(), seed=train_cfg.seed,
-                                          recompute=train_cfg.recompute, device=device,
-                                          recompute_keep_last=train_cfg.recompute_keep_last)
+        self.chunked = (model is None and self.pc.pp > 1 and train_cfg.pipeline_schedule in ("interleaved", "dualpipev")
+                        and (train_cfg.pipeline_schedule == "dualpipev" or self.pc.config.vpp > 1))
+        if self.chunked:
+            from ..parallel.pipeline import build_chunked_model
+            self.model = build_chunked_model(model_cfg, self.pc, train_cfg.pipeline_schedule, dtype=train_cfg.torch_dtype(),
+                                             seed=train_cfg.seed, recompute=train_cfg.recompute, device=device)
+        else:
+            self.model = model or build_model(model_cfg, self.pc, dtype=train_cfg.torch_dtype(), seed=train_cfg.seed,
+                                              recompute=train_cfg.recompute, device=device,
+                                              recompute_keep_last=train_cfg.recompute_keep_last)
         # with pipeline stages the embedding copies are summed before the data-parallel reduction,
         # so the reduction cannot start from inside backward
         from ..ops import functional as F_
@@ -129,6 +136,9 @@ class Trainer:
     def forward_backward(self, microbatches: List[Dict[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
         pc = self.pc
         if pc.pp > 1:
+            if self.chunked:
+                from ..parallel.pipeline import run_chunked_schedule
+                return run_chunked_schedule(self, microbatches)
             from ..parallel.pipeline import run_pipeline_schedule
             return run_pipeline_schedule(self, microbatches)
         n = len(microbatches)

@@ -17,14 +17,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(mode, world, steps=3, timeout=600):
+def _run(mode, world, steps=3, timeout=600, n_mb=None):
     env = dict(os.environ, OMP_NUM_THREADS="2")
+    extra = [] if n_mb is None else [str(n_mb)]
     if world == 1:
-        cmd = [sys.executable, os.path.join(HERE, "dist_worker.py"), mode, str(steps)]
+        cmd = [sys.executable, os.path.join(HERE, "dist_worker.py"), mode, str(steps)] + extra
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-               os.path.join(HERE, "dist_worker.py"), mode, str(steps)]
+               os.path.join(HERE, "dist_worker.py"), mode, str(steps)] + extra
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
@@ -44,3 +45,17 @@ def test_layout_matches_single_process(baseline, mode):
         assert abs(b[1] - g[1]) < 2e-3 * max(1.0, abs(b[1])), (mode, step, baseline, got)
         if mode != "pp":
             assert abs(b[2] - g[2]) < 2e-2 * max(1.0, abs(b[2])), (mode, step, baseline, got)
+
+
+@pytest.fixture(scope="module")
+def baseline4():
+    return _run("dp", 1, n_mb=4)
+
+
+@pytest.mark.parametrize("mode", ["pp_vpp2", "dualpipev"])
+def test_chunked_pipeline_schedules_match_single_process(baseline4, mode):
+    """Interleaved (PP2 x VPP2) and V-shaped (DualPipeV, 4 chunks on 2 ranks) executors reproduce the loss curve."""
+    got = _run(mode, 2, n_mb=4)
+    for step, (b, g) in enumerate(zip(baseline4, got)):
+        assert abs(b[0] - g[0]) < 2e-3 * max(1.0, abs(b[0])), (mode, step, baseline4, got)
+        assert abs(b[1] - g[1]) < 2e-3 * max(1.0, abs(b[1])), (mode, step, baseline4, got)
