@@ -158,7 +158,7 @@ def main() -> int:
     if keep_last < 0:
         # spare memory on a single GPU (180 GB minus parameters, optimizer state and the scan stash) pays for keeping the
         # activations of a few layers; with more ranks "selective" already keeps most of them
-        keep_last = 6 if (world == 1 and recompute == "full" and args.depth is None) else 0
+        keep_last = 6 if (world == 1 and recompute == "full" and not args.depth) else 0
     tcfg = TrainConfig(micro_batch_size=args.micro_batch, seq_length=args.seq, dtype="bf16", recompute=recompute,
                        recompute_keep_last=keep_last,
                        optimizer=OptimizerConfig(lr=1e-5, weight_decay=0.1, grad_dtype="bf16" if world < 4 else "fp32"),

@@ -172,27 +172,26 @@ __global__ void __launch_bounds__(256) m2rnn_sum_parts_kernel(const float* __res
   }
 }
 
-// Backward.  Same decomposition as the forward (16 state rows per CTA, rotated register copies of W).  Per step a
-// thread reloads h_{t-1} (its row) and h_t (its quad) from the history, recomputes tanh(a_t), and updates dh in
-// registers; the pre-activation gradients of the row's other quads arrive by 12 shuffles and feed both the dW
-// accumulators (kept in the same rotated order, un-rotated once at the end) and the W^T product.  dv and df are sums
-// over all state rows of a head, i.e. over the CTAs of a split: they are accumulated with atomics into zeroed
-// outputs, as is dW.
-__device__ __forceinline__ float bf_lo(uint32_t x) { return __uint_as_float(x << 16); }
-__device__ __forceinline__ float bf_hi(uint32_t x) { return __uint_as_float(x & 0xffff0000u); }
-
-template <int KD>
-__global__ void __launch_bounds__(M2Split<KD>::NT) m2rnn_bwd_kernel(
+// Backward.  A CTA owns RS state rows of one (batch, head) (thread = (row, quad), W and W^T in shared memory); with
+// KD = 64 a head is split over two CTAs of 32 rows so that all CTAs are resident at once, and dv / df / dW, which sum
+// over the rows of a head, are accumulated with atomics into zeroed outputs.
+// The state history is walked backwards with rolling registers: the row h_{t-1} needed by a step was requested one
+// step earlier and h_t (own quad) is a slice of the row used by the previous step, so each step issues one row load
+// whose latency hides behind the arithmetic.
+template <int KD, int RS>
+__global__ void __launch_bounds__(RS * 4) m2rnn_bwd_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
     const __nv_bfloat16* __restrict__ W, const float* __restrict__ f, const float* __restrict__ hist,
     const __nv_bfloat16* __restrict__ dy, float* __restrict__ dq_h, float* __restrict__ dk_h,
     float* __restrict__ dv, float* __restrict__ df, float* __restrict__ dW, int S, int H, int Hq, int Hk) {
-  constexpr int RS = M2Split<KD>::RS, SPLITS = M2Split<KD>::SPLITS, NT = M2Split<KD>::NT;
+  constexpr int NT = RS * 4;
+  constexpr int SPLITS = KD / RS;
   constexpr int NW = NT / 32;
   constexpr int QPT = TBB * RS / NT;
-  __shared__ float qs[TBB][RS], ks[TBB][RS], fs[TBB];
-  __shared__ __align__(16) float vs[TBB][VD], gs[TBB][VD];
-  __shared__ float dqs[TBB][RS], dks[TBB][RS], dvpart[TBB][NW][VD], dfpart[TBB][NT];
+  __shared__ float Ws[VD][VD];          // W[u][v]
+  __shared__ float Wt[VD][VD];          // W^T: Wt[v][u]
+  __shared__ float qs[TBB][RS], ks[TBB][RS], vs[TBB][VD], gs[TBB][VD], fs[TBB];
+  __shared__ float dqs[TBB][RS], dks[TBB][RS], dvpart[TBB][NW][VD], dfpart[TBB][NW];
   __shared__ float dWs[VD][VD];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int lrow = tid >> 2, quad = tid & 3;
@@ -201,42 +200,37 @@ __global__ void __launch_bounds__(M2Split<KD>::NT) m2rnn_bwd_kernel(
   const int b = bh / H, h = bh % H;
   const int row = sp * RS + lrow;
   const int hq = Hq == 1 ? 0 : h, hk = Hk == 1 ? 0 : h;
-  const __nv_bfloat16* Wh = W + (size_t)h * VD * VD;
-  // wa[u][c/2]: W[u][4 quad + c] packed in pairs (forward product);  wb[d][u][c/2]: W[4 quad + c][4 ((quad + d) % 4) + u]
-  uint32_t wa[VD][2], wb[4][4][2];
-#pragma unroll
-  for (int u = 0; u < VD; ++u)
-#pragma unroll
-    for (int c2 = 0; c2 < 2; ++c2)
-      wa[u][c2] = *reinterpret_cast<const uint32_t*>(Wh + u * VD + 4 * quad + 2 * c2);
-#pragma unroll
-  for (int d = 0; d < 4; ++d)
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {
-        const int j = 4 * ((quad + d) & 3) + u;
-        const uint32_t lo = __bfloat16_as_ushort(Wh[(4 * quad + 2 * c2) * VD + j]);
-        const uint32_t hi = __bfloat16_as_ushort(Wh[(4 * quad + 2 * c2 + 1) * VD + j]);
-        wb[d][u][c2] = lo | (hi << 16);
-      }
-  for (int i = tid; i < VD * VD; i += NT) dWs[i / VD][i % VD] = 0.f;
+  for (int i = tid; i < VD * VD; i += NT) {
+    const float w = __bfloat162float(W[(size_t)h * VD * VD + i]);
+    Ws[i / VD][i % VD] = w;
+    Wt[i % VD][i / VD] = w;
+    dWs[i / VD][i % VD] = 0.f;
+  }
   float dh[4] = {0.f, 0.f, 0.f, 0.f};
-  float P[4][4][4];            // P[d][u][c] accumulates h_{t-1}[row, 4 quad + c] * da[row, 4 ((quad + d) % 4) + u]
+  float P[4][VD];
 #pragma unroll
-  for (int d = 0; d < 4; ++d)
+  for (int c = 0; c < 4; ++c)
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) P[d][u][c] = 0.f;
+    for (int j = 0; j < VD; ++j) P[c][j] = 0.f;
   const float* hbase = hist + (size_t)(b * H + h) * S * KD * VD;
-  const int src_base = lane & ~3;
   __syncthreads();
 
+  // rolling history registers: row h_{S-2} and own quad of h_{S-1}
+  float4 rowbuf[4], quadbuf;
+  quadbuf = *reinterpret_cast<const float4*>(hbase + ((size_t)(S - 1) * KD + row) * VD + quad * 4);
+  if (S > 1) {
+    const float4* hp = reinterpret_cast<const float4*>(hbase + ((size_t)(S - 2) * KD + row) * VD);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) rowbuf[j] = hp[j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) rowbuf[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   const int nblocks = (S + TBB - 1) / TBB;
   for (int blk = nblocks - 1; blk >= 0; --blk) {
     const int t0 = blk * TBB;
     const int nt = min(TBB, S - t0);
+    // stage this block's inputs
 #pragma unroll
     for (int i = 0; i < QPT; ++i) {
       const int e = tid + i * NT, t = e / RS, c = e % RS;
@@ -254,88 +248,97 @@ __global__ void __launch_bounds__(M2Split<KD>::NT) m2rnn_bwd_kernel(
     __syncthreads();
     for (int t = nt - 1; t >= 0; --t) {
       const int tg = t0 + t;
+      // h_{t-1} (full row) was prefetched one step ago and h_t (own quad) is a slice of the row used then; the row
+      // for the next step (h_{t-2}) is requested now so that its latency hides behind this step's arithmetic
       float hprev[VD];
-      if (tg > 0) {
-        const float4* hp = reinterpret_cast<const float4*>(hbase + ((size_t)(tg - 1) * KD + row) * VD);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float4 x = hp[j];
-          hprev[j * 4 + 0] = x.x; hprev[j * 4 + 1] = x.y; hprev[j * 4 + 2] = x.z; hprev[j * 4 + 3] = x.w;
-        }
+      for (int j = 0; j < 4; ++j) {
+        hprev[j * 4 + 0] = rowbuf[j].x; hprev[j * 4 + 1] = rowbuf[j].y; hprev[j * 4 + 2] = rowbuf[j].z; hprev[j * 4 + 3] = rowbuf[j].w;
+      }
+      const float hcur[4] = {quadbuf.x, quadbuf.y, quadbuf.z, quadbuf.w};
+      if (tg > 1) {
+        const float4* hp = reinterpret_cast<const float4*>(hbase + ((size_t)(tg - 2) * KD + row) * VD);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) rowbuf[j] = hp[j];
       } else {
 #pragma unroll
-        for (int j = 0; j < VD; ++j) hprev[j] = 0.f;
+        for (int j = 0; j < 4; ++j) rowbuf[j] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      const float4 hc = *reinterpret_cast<const float4*>(hbase + ((size_t)tg * KD + row) * VD + quad * 4);
-      const float hcur[4] = {hc.x, hc.y, hc.z, hc.w};
       const float kt = ks[t][lrow], qt = qs[t][lrow], ft = fs[t];
-      const float4 g4 = *reinterpret_cast<const float4*>(&gs[t][quad * 4]);
-      const float4 v4 = *reinterpret_cast<const float4*>(&vs[t][quad * 4]);
-      const float g[4] = {g4.x, g4.y, g4.z, g4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
       // dh_t += q_t (x) dy_t ; dq_t = h_t . dy_t
       float dqp = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        dh[c] += qt * g[c];
-        dqp += hcur[c] * g[c];
+        const float g = gs[t][quad * 4 + c];
+        dh[c] += qt * g;
+        dqp += hcur[c] * g;
       }
+      dqp += __shfl_xor_sync(0xffffffffu, dqp, 1);
+      dqp += __shfl_xor_sync(0xffffffffu, dqp, 2);
+      if (quad == 0) dqs[t][lrow] = dqp;
       // recompute tanh(a_t) for own columns
       float a[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) a[c] = kt * vv[c];
+      for (int c = 0; c < 4; ++c) a[c] = kt * vs[t][quad * 4 + c];
 #pragma unroll
       for (int u = 0; u < VD; ++u) {
-        a[0] = fmaf(hprev[u], bf_lo(wa[u][0]), a[0]);
-        a[1] = fmaf(hprev[u], bf_hi(wa[u][0]), a[1]);
-        a[2] = fmaf(hprev[u], bf_lo(wa[u][1]), a[2]);
-        a[3] = fmaf(hprev[u], bf_hi(wa[u][1]), a[3]);
+        const float4 w = *reinterpret_cast<const float4*>(&Ws[u][quad * 4]);
+        a[0] += hprev[u] * w.x; a[1] += hprev[u] * w.y; a[2] += hprev[u] * w.z; a[3] += hprev[u] * w.w;
       }
-      float hown[4];                     // h_{t-1}[row, own quad], selected without dynamic indexing
+      float hown[4];                     // h_{t-1}[k, own quad], selected without dynamic indexing
 #pragma unroll
       for (int c = 0; c < 4; ++c)
         hown[c] = quad == 0 ? hprev[c] : quad == 1 ? hprev[4 + c] : quad == 2 ? hprev[8 + c] : hprev[12 + c];
-      float da[4], dfp = 0.f, dkp = 0.f;
+      quadbuf = make_float4(hown[0], hown[1], hown[2], hown[3]);      // h_{t-1}[own quad] is next step's h_t
+      float da[4], dfp = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const float hn = fast_tanh(a[c]);
         dfp += dh[c] * (hown[c] - hn);
         da[c] = dh[c] * (1.f - ft) * (1.f - hn * hn);
-        dkp += da[c] * vv[c];
       }
-      dfpart[t][tid] = dfp;
-      // dq_t[row], dk_t[row]: sums over the four quads of the row
-      dqp += __shfl_xor_sync(0xffffffffu, dqp, 1);
-      dkp += __shfl_xor_sync(0xffffffffu, dkp, 1);
-      dqp += __shfl_xor_sync(0xffffffffu, dqp, 2);
-      dkp += __shfl_xor_sync(0xffffffffu, dkp, 2);
-      if (quad == 0) { dqs[t][lrow] = dqp; dks[t][lrow] = dkp; }
-      // dv_t[4 quad + c] = sum over rows of da[c] * k_t[row]: halving reduction over the 8 rows of the warp
-      {
-        const bool u4 = lane & 16, u3 = lane & 8;
-        const float p0 = da[0] * kt, p1 = da[1] * kt, p2 = da[2] * kt, p3 = da[3] * kt;
-        const float k0 = u4 ? p2 : p0, k1 = u4 ? p3 : p1, s0 = u4 ? p0 : p2, s1 = u4 ? p1 : p3;
-        const float a0 = k0 + __shfl_xor_sync(0xffffffffu, s0, 16);
-        const float a1 = k1 + __shfl_xor_sync(0xffffffffu, s1, 16);
-        const float kk = u3 ? a1 : a0, ss = u3 ? a0 : a1;
-        float r = kk + __shfl_xor_sync(0xffffffffu, ss, 8);
-        r += __shfl_xor_sync(0xffffffffu, r, 4);
-        if ((lane & 4) == 0) dvpart[t][warp][quad * 4 + (u4 ? 2 : 0) + (u3 ? 1 : 0)] = r;
+      dfp = warp_sum(dfp);
+      if (lane == 0) dfpart[t][warp] = dfp;
+      // full da row of this k
+      float darow[VD];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) darow[j * 4 + c] = __shfl_sync(0xffffffffu, da[c], (lane & ~3) + j);
+      // dk_t[k] = da[k,:] . v_t
+      if (quad == 0) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < VD; ++j) s += darow[j] * vs[t][j];
+        dks[t][lrow] = s;
       }
-      // dh_{t-1}[own] = f dh_t[own] + sum_j da[row, j] W[own, j];  dW[own, j] += h_{t-1}[own] da[row, j]
+      // dv_t[v] = sum_k da[k,v] k_t[k]  (own columns; reduce over the 8 rows of this warp)
+      float dvp[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        dvp[c] = da[c] * kt;
+        dvp[c] += __shfl_xor_sync(0xffffffffu, dvp[c], 4);
+        dvp[c] += __shfl_xor_sync(0xffffffffu, dvp[c], 8);
+        dvp[c] += __shfl_xor_sync(0xffffffffu, dvp[c], 16);
+      }
+      if (lane < 4) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dvpart[t][warp][quad * 4 + c] = dvp[c];
+      }
+      // dW[u,v] += h_{t-1}[k,u] da[k,v]  for own u = 4*quad + c
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float hu = hown[c];
+#pragma unroll
+        for (int j = 0; j < VD; ++j) P[c][j] += hu * darow[j];
+      }
+      // dh_{t-1}[k,u] = f dh_t[k,u] + sum_v da[k,v] W[u,v]   for own u
 #pragma unroll
       for (int c = 0; c < 4; ++c) dh[c] *= ft;
 #pragma unroll
-      for (int d = 0; d < 4; ++d) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float dv_ = d == 0 ? da[u] : __shfl_sync(0xffffffffu, da[u], src_base | ((quad + d) & 3));
-          dh[0] = fmaf(dv_, bf_lo(wb[d][u][0]), dh[0]);
-          dh[1] = fmaf(dv_, bf_hi(wb[d][u][0]), dh[1]);
-          dh[2] = fmaf(dv_, bf_lo(wb[d][u][1]), dh[2]);
-          dh[3] = fmaf(dv_, bf_hi(wb[d][u][1]), dh[3]);
-#pragma unroll
-          for (int c = 0; c < 4; ++c) P[d][u][c] = fmaf(hown[c], dv_, P[d][u][c]);
-        }
+      for (int j = 0; j < VD; ++j) {
+        const float4 w = *reinterpret_cast<const float4*>(&Wt[j][quad * 4]);   // W[u=4q..4q+3][v=j]
+        dh[0] += darow[j] * w.x; dh[1] += darow[j] * w.y; dh[2] += darow[j] * w.z; dh[3] += darow[j] * w.w;
       }
     }
     __syncthreads();
@@ -355,25 +358,24 @@ __global__ void __launch_bounds__(M2Split<KD>::NT) m2rnn_bwd_kernel(
     }
     if (tid < nt) {
       float s = 0.f;
-      for (int w = 0; w < NT; ++w) s += dfpart[tid][w];
+#pragma unroll
+      for (int w = 0; w < NW; ++w) s += dfpart[tid][w];
       float* dst = df + (size_t)(b * S + t0 + tid) * H + h;
       if (SPLITS == 1) *dst = s; else atomicAdd(dst, s);
     }
     __syncthreads();
   }
-  // reduce dW over the rows of this CTA (un-rotating the accumulators), then over CTAs with atomics
+  // reduce dW over the rows k of this CTA, then over batch with atomics
 #pragma unroll
-  for (int d = 0; d < 4; ++d)
+  for (int c = 0; c < 4; ++c)
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float s = P[d][u][c];
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        s += __shfl_xor_sync(0xffffffffu, s, 8);
-        s += __shfl_xor_sync(0xffffffffu, s, 16);
-        if (lane < 4) atomicAdd(&dWs[quad * 4 + c][4 * ((quad + d) & 3) + u], s);
-      }
+    for (int j = 0; j < VD; ++j) {
+      float s = P[c][j];
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s += __shfl_xor_sync(0xffffffffu, s, 8);
+      s += __shfl_xor_sync(0xffffffffu, s, 16);
+      if (lane < 4) atomicAdd(&dWs[quad * 4 + c][j], s);
+    }
   __syncthreads();
   for (int i = tid; i < VD * VD; i += NT) atomicAdd(dW + (size_t)h * VD * VD + i, dWs[i / VD][i % VD]);
 }
@@ -410,8 +412,7 @@ extern "C" int cm_m2rnn_fwd(const void* q, const void* k, const void* v, const v
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// dq_h, dk_h [B,S,H,KD] fp32 (per head); dv [B,S,H,16] fp32, df [B,S,H] fp32 and dW [H,16,16] fp32 are accumulated
-// with atomics when a head is split over several CTAs (KD > 16): the caller zeroes all three.
+// dq_h, dk_h [B,S,H,KD] fp32 (per head); dv [B,S,H,16], df [B,S,H] and dW [H,16,16] fp32 are accumulated: the caller zeroes them.
 extern "C" int cm_m2rnn_bwd(const void* q, const void* k, const void* v, const void* W, const float* f, const float* hist,
                             const void* dy, float* dq_h, float* dk_h, float* dv, float* df, float* dW, int B, int S, int H,
                             int Hq, int Hk, int KD, int VDim, cudaStream_t s) {
@@ -419,10 +420,10 @@ extern "C" int cm_m2rnn_bwd(const void* q, const void* k, const void* v, const v
   if (VDim != VD) return -10;
   auto qp = (const __nv_bfloat16*)q; auto kp = (const __nv_bfloat16*)k; auto vp = (const __nv_bfloat16*)v;
   auto wp = (const __nv_bfloat16*)W; auto gp = (const __nv_bfloat16*)dy;
-  const int bh = B * H;
-  if (KD == 64) m2rnn_bwd_kernel<64><<<bh * 4, 64, 0, s>>>(qp, kp, vp, wp, f, hist, gp, dq_h, dk_h, dv, df, dW, S, H, Hq, Hk);
-  else if (KD == 32) m2rnn_bwd_kernel<32><<<bh * 2, 64, 0, s>>>(qp, kp, vp, wp, f, hist, gp, dq_h, dk_h, dv, df, dW, S, H, Hq, Hk);
-  else if (KD == 16) m2rnn_bwd_kernel<16><<<bh, 64, 0, s>>>(qp, kp, vp, wp, f, hist, gp, dq_h, dk_h, dv, df, dW, S, H, Hq, Hk);
+  const int grid = B * H;
+  if (KD == 64) m2rnn_bwd_kernel<64, 32><<<grid * 2, 128, 0, s>>>(qp, kp, vp, wp, f, hist, gp, dq_h, dk_h, dv, df, dW, S, H, Hq, Hk);
+  else if (KD == 32) m2rnn_bwd_kernel<32, 32><<<grid, 128, 0, s>>>(qp, kp, vp, wp, f, hist, gp, dq_h, dk_h, dv, df, dW, S, H, Hq, Hk);
+  else if (KD == 16) m2rnn_bwd_kernel<16, 16><<<grid, 64, 0, s>>>(qp, kp, vp, wp, f, hist, gp, dq_h, dk_h, dv, df, dW, S, H, Hq, Hk);
   else return -10;
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -1,0 +1,66 @@
+"""Data preparation, log checking and the lane launcher."""
+import json
+
+import numpy as np
+import pytest
+
+from cppmega_b200.data.indexed import read_index
+from cppmega_b200.tools import data_prep, launch, log_check
+
+
+def test_data_prep_writes_a_readable_indexed_dataset(tmp_path):
+    src = tmp_path / "c.jsonl"
+    docs = ["hello world, this is a document", "short", "another sufficiently long document for the corpus"]
+    src.write_text("\n".join(json.dumps({"text": d}) for d in docs))
+    out = str(tmp_path / "corpus")
+    assert data_prep.main(["--input", str(src), "--tokenizer", "bytes", "--out", out, "--min-tokens", "8"]) == 0
+    idx = read_index(out)
+    assert idx["num_docs"] == 3 and len(idx["sizes"]) == 2                 # "short" was filtered out
+    assert idx["dtype"] == np.uint16
+    raw = np.fromfile(out + ".bin", dtype=np.uint16)
+    first = raw[:idx["sizes"][0]]
+    assert bytes(first[:-1].astype(np.uint8)).decode() == docs[0] and first[-1] == 256
+
+
+def test_fim_transform_keeps_all_tokens():
+    import random
+    ids = list(range(10, 40))
+    out = data_prep.fim_transform(ids, random.Random(1), 1.0, 1000, 1001, 1002)
+    assert sorted(t for t in out if t < 1000) == ids and {1000, 1001, 1002} <= set(out)
+    assert data_prep.fim_transform(ids, random.Random(1), 0.0, 1000, 1001, 1002) == ids
+
+
+def _log(losses, fused="{'optimizer': True, 'moe': True}", fallbacks=None):
+    lines = [f"[cppmega_b200] nam56r: 7.92B params (5.01B active), world 8 (dp8ep8), fused paths {fused}"]
+    for i, l in enumerate(losses):
+        rec = {"iteration": i + 1, "loss": l, "lm_loss": l, "tokens_per_s": 1000.0 + i, "elapsed_ms": 10.0}
+        if fallbacks:
+            rec["fallback_ops"] = fallbacks
+        lines.append(json.dumps(rec))
+    return "\n".join(lines)
+
+
+def test_log_check_accepts_a_healthy_run_and_flags_bad_ones():
+    good = log_check.parse_log(_log([10 - 0.3 * i for i in range(12)]))
+    assert good.fused == {"optimizer": True, "moe": True}
+    assert log_check.check(good, min_steps=10, require_fused=["moe", "optimizer"]) == []
+    rising = log_check.parse_log(_log([5 + 0.3 * i for i in range(12)]))
+    assert any("went up" in p for p in log_check.check(rising))
+    nan = log_check.parse_log(_log([5.0, float("nan"), 4.0]))
+    assert any("non-finite" in p for p in log_check.check(nan))
+    fb = log_check.parse_log(_log([5.0, 4.0], fallbacks={"sparse_mla": 3}))
+    assert any("fallbacks" in p for p in log_check.check(fb))
+    assert any("not active" in p for p in log_check.check(log_check.parse_log(_log([5.0], fused="{'optimizer': False}")),
+                                                          require_fused=["optimizer"]))
+    cmp = log_check.compare(good, rising)
+    assert cmp["tokens_per_s"]["b_over_a"] == pytest.approx(1.0) and cmp["loss_curve"]["steps"] == 12
+
+
+def test_launch_lanes_render(capsys):
+    assert launch.main(["list"]) == 0
+    assert "b200_nam56r_bf16_ep8" in capsys.readouterr().out
+    assert launch.main(["smoke_tiny", "--dry-run", "--set", "training.train_iters=3"]) == 0
+    out = capsys.readouterr().out
+    assert "torch.distributed.run" in out and "--train-iters 3" in out and "NCCL_NVLS_ENABLE=0" in out
+    assert launch.main(["recipe:native_pretrain", "--dry-run", "--data", "/data/c"]) == 0
+    assert "/data/c" in capsys.readouterr().out
