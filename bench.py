@@ -114,6 +114,8 @@ def main() -> int:
     ap.add_argument("--recompute", default="auto", choices=["auto", "none", "selective", "full"])
     ap.add_argument("--keep-last", type=int, default=-1,
                     help="layers at the end of the stack whose activations are kept instead of recomputed (-1: auto)")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"],
+                    help="mxfp8: block-scaled FP8 linears (an extra measurement; the headline number is bf16)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--profile-dir", default=None, help="after timing, capture one step with the torch profiler here")
     args = ap.parse_args()
@@ -160,7 +162,7 @@ def main() -> int:
         # activations of a few layers; with more ranks "selective" already keeps most of them
         keep_last = 6 if (world == 1 and recompute == "full" and not args.depth) else 0
     tcfg = TrainConfig(micro_batch_size=args.micro_batch, seq_length=args.seq, dtype="bf16", recompute=recompute,
-                       recompute_keep_last=keep_last,
+                       recompute_keep_last=keep_last, precision_recipe=args.precision,
                        optimizer=OptimizerConfig(lr=1e-5, weight_decay=0.1, grad_dtype="bf16" if world < 4 else "fp32"),
                        log_interval=0)
     trainer = Trainer(mcfg, tcfg, pc, device=device)
@@ -230,7 +232,7 @@ def main() -> int:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": value / PUBLISHED_TOK_S_BOX, "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights",
+            "vs_baseline": value / PUBLISHED_TOK_S_BOX, "dtype": "bf16" if args.precision == "bf16" else "mxfp8 linears, bf16 elsewhere", "data": "synthetic uniform tokens, random-init weights",
             "impl": "ours",
             "config": {"model": f"{mcfg.name} {n_params / 1e9:.2f}B params on rank 0 ({mcfg.param_count()['total'] / 1e9:.2f}B total), "
                                 f"{mcfg.depth} layers {mcfg.pattern}, hidden {mcfg.hidden_size}, vocab {mcfg.vocab_size}, MTP {mcfg.mtp.num_layers}",
@@ -238,7 +240,7 @@ def main() -> int:
                        "parallelism": f"ep{ep}dp{world}" if world > 1 else "single GPU (16 local experts)",
                        "distributed_optimizer": True, "recompute": recompute, "recompute_keep_last": keep_last,
                        "l2": "weights + activations per step are far larger than the 126 MB L2",
-                       "headline_config": not args.depth and args.seq == 4096 and args.micro_batch == 4},
+                       "headline_config": not args.depth and args.seq == 4096 and args.micro_batch == 4 and args.precision == "bf16"},
             "clocks": sampler.summary() if rank == 0 else None,
             "e2e": e2e, "gpu_launches": launches, "fallback_ops": fallbacks,
             "model_tflops_per_gpu": mcfg.flops_per_token(args.seq) * value / world / 1e12,

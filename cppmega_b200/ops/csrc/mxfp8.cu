@@ -41,9 +41,16 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t b) {
   return __uint_as_float(__float_as_uint(v) | s);
 }
 
+// position of scale (row, k block) in the 128x4 tile order
+__device__ __forceinline__ size_t swizzled_index(long long row, int kb, int kb_tiles) {
+  return ((size_t)(row >> 7) * kb_tiles + (kb >> 2)) * 512 + (size_t)(row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3);
+}
+
 // one thread = 8 consecutive values; 4 threads = one block of 32
 __global__ void __launch_bounds__(256) quantize_rowwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ payload,
-                                                               uint8_t* __restrict__ scales, long long rows, int cols) {
+                                                               uint8_t* __restrict__ scales, uint8_t* __restrict__ sw, long long rows,
+                                                               int cols) {
+  const int kb_row = cols / 32, kb_tiles = (kb_row + 3) / 4;
   const long long nvec = rows * (cols / 8);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
     const uint4 raw = reinterpret_cast<const uint4*>(x)[i];
@@ -65,13 +72,20 @@ __global__ void __launch_bounds__(256) quantize_rowwise_kernel(const __nv_bfloat
     o.x = (uint32_t)to_e4m3x2(f[0] * mult, f[1] * mult) | ((uint32_t)to_e4m3x2(f[2] * mult, f[3] * mult) << 16);
     o.y = (uint32_t)to_e4m3x2(f[4] * mult, f[5] * mult) | ((uint32_t)to_e4m3x2(f[6] * mult, f[7] * mult) << 16);
     reinterpret_cast<uint2*>(payload)[i] = o;
-    if ((threadIdx.x & 3) == 0) scales[i >> 2] = sb;
+    if ((threadIdx.x & 3) == 0) {
+      scales[i >> 2] = sb;
+      if (sw) {
+        const long long blk = i >> 2;
+        sw[swizzled_index(blk / kb_row, (int)(blk % kb_row), kb_tiles)] = sb;
+      }
+    }
   }
 }
 
 // CTA = tile of 32 rows x 128 columns; thread c owns one column: 32 values -> one block
 __global__ void __launch_bounds__(128) quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ payload_t,
-                                                               uint8_t* __restrict__ scales_t, long long rows, int cols) {
+                                                               uint8_t* __restrict__ scales_t, uint8_t* __restrict__ sw, long long rows,
+                                                               int cols) {
   const long long r0 = (long long)blockIdx.y * 32;
   const int c = blockIdx.x * 128 + threadIdx.x;
   if (c >= cols) return;
@@ -92,6 +106,7 @@ __global__ void __launch_bounds__(128) quantize_colwise_kernel(const __nv_bfloat
   dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
   dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
   scales_t[(size_t)c * (rows / 32) + blockIdx.y] = sb;
+  if (sw) sw[swizzled_index(c, (int)blockIdx.y, (int)((rows / 32 + 3) / 4))] = sb;
 }
 
 __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ payload, const uint8_t* __restrict__ scales,
@@ -135,20 +150,24 @@ static int grid1d(long long work) {
   return (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
 }
 
-// x [rows, cols] bf16, cols % 32 == 0 -> payload [rows, cols] u8, scales [rows, cols/32] u8
-extern "C" int cm_mxfp8_quantize_rowwise(const void* x, void* payload, void* scales, long long rows, int cols, cudaStream_t s) {
+// x [rows, cols] bf16, cols % 32 == 0 -> payload [rows, cols] u8, scales [rows, cols/32] u8; `swizzled` (optional) also
+// receives the scales in the 128x4 tile order (its padding entries must already hold the neutral scale)
+extern "C" int cm_mxfp8_quantize_rowwise(const void* x, void* payload, void* scales, void* swizzled, long long rows, int cols,
+                                         cudaStream_t s) {
   if (rows <= 0) return 0;
   if (cols % 32) return -10;
-  quantize_rowwise_kernel<<<grid1d(rows * (cols / 8)), 256, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)payload, (uint8_t*)scales, rows, cols);
+  quantize_rowwise_kernel<<<grid1d(rows * (cols / 8)), 256, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)payload, (uint8_t*)scales,
+                                                                  (uint8_t*)swizzled, rows, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// x [rows, cols] bf16, rows % 32 == 0 -> payload_t [cols, rows] u8, scales_t [cols, rows/32] u8
-extern "C" int cm_mxfp8_quantize_colwise(const void* x, void* payload_t, void* scales_t, long long rows, int cols, cudaStream_t s) {
+// x [rows, cols] bf16, rows % 32 == 0 -> payload_t [cols, rows] u8, scales_t [cols, rows/32] u8 (+ optional swizzled copy)
+extern "C" int cm_mxfp8_quantize_colwise(const void* x, void* payload_t, void* scales_t, void* swizzled, long long rows, int cols,
+                                         cudaStream_t s) {
   if (rows <= 0) return 0;
   if (rows % 32) return -10;
   dim3 grid((cols + 127) / 128, (unsigned)(rows / 32));
-  quantize_colwise_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)payload_t, (uint8_t*)scales_t, rows, cols);
+  quantize_colwise_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)payload_t, (uint8_t*)scales_t, (uint8_t*)swizzled, rows, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -6,8 +6,9 @@ the three products (forward, dgrad, wgrad) is rounded to MXFP8 along the dimensi
 contract of the reference's MXFP8 GEMM wrappers (``tn_gemm`` / ``dgrad_nn_gemm`` / ``wgrad_nt_gemm``,
 cppmega/megatron/cutlass_mxfp8_gemm.py:102,249,506) - and the activation saved for the weight gradient is kept as an
 MXFP8 tensor (1 byte per value + 1/32 scale), which is what the reference's FP8 activation pack saves
-(cppmega/megatron/fp8_activations.py).  The products themselves run on the bf16 tcgen05 GEMM over the dequantised
-operands: same numerics as a block-scaled GEMM up to accumulation order, bf16 tensor-core rate.
+(cppmega/megatron/fp8_activations.py).  The products run on the block-scaled tensor-core GEMM of
+``csrc/mxfp8_gemm.cu`` (:func:`gemm_mxfp8`: ``tcgen05.mma.kind::mxf8f6f4.block_scale`` with the scale bytes in TMEM),
+every one of them as a "TN" product of two operands quantised along the reduction dimension.
 """
 from __future__ import annotations
 
@@ -25,6 +26,12 @@ class Mxfp8Tensor:
     payload: torch.Tensor          # uint8 (E4M3 bit patterns), [rows, cols] of the *stored* orientation
     scales: torch.Tensor           # uint8 (E8M0), [rows, cols / 32]
     shape: Tuple[int, int]         # logical [rows, cols] of the stored orientation
+    _swizzled: torch.Tensor = None  # scales in the 128x4 tile order the tensor cores read (made on first use)
+
+    def swizzled(self) -> torch.Tensor:
+        if self._swizzled is None:
+            self._swizzled = swizzle_scales(self.scales)
+        return self._swizzled
 
     def nbytes(self) -> int:
         return self.payload.numel() + self.scales.numel()
@@ -38,11 +45,13 @@ def _lib():
     L = lib()
     if not getattr(L, "_mx_declared", False):
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-        L.cm_mxfp8_quantize_rowwise.argtypes = [vp, vp, vp, i64, i32, vp]
-        L.cm_mxfp8_quantize_colwise.argtypes = [vp, vp, vp, i64, i32, vp]
+        L.cm_mxfp8_quantize_rowwise.argtypes = [vp, vp, vp, vp, i64, i32, vp]
+        L.cm_mxfp8_quantize_colwise.argtypes = [vp, vp, vp, vp, i64, i32, vp]
         L.cm_mxfp8_dequantize.argtypes = [vp, vp, vp, i64, vp]
         L.cm_mxfp8_swizzle_scales.argtypes = [vp, vp, i64, i32, vp]
-        for n in ("cm_mxfp8_quantize_rowwise", "cm_mxfp8_quantize_colwise", "cm_mxfp8_dequantize", "cm_mxfp8_swizzle_scales"):
+        L.cm_mxfp8_gemm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, vp, vp]
+        for n in ("cm_mxfp8_quantize_rowwise", "cm_mxfp8_quantize_colwise", "cm_mxfp8_dequantize", "cm_mxfp8_swizzle_scales",
+                  "cm_mxfp8_gemm"):
             getattr(L, n).restype = i32
         L._mx_declared = True
     return L
@@ -53,21 +62,30 @@ def _check(rc, what):
         raise RuntimeError(f"{what} failed ({rc})")
 
 
-def quantize_rowwise(x: torch.Tensor) -> Mxfp8Tensor:
-    """Blocks of 32 along the last dimension of a 2-D bf16 tensor."""
+def _swizzled_buffer(rows: int, kb: int, device) -> torch.Tensor:
+    n = ((rows + 127) // 128) * ((kb + 3) // 4) * 512
+    if rows % 128 or kb % 4:                       # padding entries keep the neutral scale
+        return torch.full((n,), 127, dtype=torch.uint8, device=device)
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+def quantize_rowwise(x: torch.Tensor, for_gemm: bool = False) -> Mxfp8Tensor:
+    """Blocks of 32 along the last dimension of a 2-D bf16 tensor.  ``for_gemm`` also writes the scales in the tile
+    order the block-scaled GEMM reads, from the same kernel."""
     from . import stream_ptr
     assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.shape[1] % 32 == 0
     x = x.contiguous()
     rows, cols = x.shape
     pay = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
     sc = torch.empty(rows, cols // 32, dtype=torch.uint8, device=x.device)
-    _check(_lib().cm_mxfp8_quantize_rowwise(x.data_ptr(), pay.data_ptr(), sc.data_ptr(), rows, cols, stream_ptr()),
-           "cm_mxfp8_quantize_rowwise")
+    sw = _swizzled_buffer(rows, cols // 32, x.device) if for_gemm else None
+    _check(_lib().cm_mxfp8_quantize_rowwise(x.data_ptr(), pay.data_ptr(), sc.data_ptr(), sw.data_ptr() if for_gemm else None,
+                                            rows, cols, stream_ptr()), "cm_mxfp8_quantize_rowwise")
     F_.count_launch("mxfp8_quantize")
-    return Mxfp8Tensor(pay, sc, (rows, cols))
+    return Mxfp8Tensor(pay, sc, (rows, cols), sw)
 
 
-def quantize_colwise(x: torch.Tensor) -> Mxfp8Tensor:
+def quantize_colwise(x: torch.Tensor, for_gemm: bool = False) -> Mxfp8Tensor:
     """Blocks of 32 along the rows; the result is stored transposed: payload [cols, rows], scales [cols, rows/32]."""
     from . import stream_ptr
     assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.shape[0] % 32 == 0
@@ -75,10 +93,11 @@ def quantize_colwise(x: torch.Tensor) -> Mxfp8Tensor:
     rows, cols = x.shape
     pay = torch.empty(cols, rows, dtype=torch.uint8, device=x.device)
     sc = torch.empty(cols, rows // 32, dtype=torch.uint8, device=x.device)
-    _check(_lib().cm_mxfp8_quantize_colwise(x.data_ptr(), pay.data_ptr(), sc.data_ptr(), rows, cols, stream_ptr()),
-           "cm_mxfp8_quantize_colwise")
+    sw = _swizzled_buffer(cols, rows // 32, x.device) if for_gemm else None
+    _check(_lib().cm_mxfp8_quantize_colwise(x.data_ptr(), pay.data_ptr(), sc.data_ptr(), sw.data_ptr() if for_gemm else None,
+                                            rows, cols, stream_ptr()), "cm_mxfp8_quantize_colwise")
     F_.count_launch("mxfp8_quantize")
-    return Mxfp8Tensor(pay, sc, (cols, rows))
+    return Mxfp8Tensor(pay, sc, (cols, rows), sw)
 
 
 def dequantize(t: Mxfp8Tensor) -> torch.Tensor:
@@ -100,10 +119,44 @@ def swizzle_scales(scales: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gemm_mxfp8(a: Mxfp8Tensor, b: Mxfp8Tensor, out: torch.Tensor = None, accumulate: bool = False,
+               out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``a [M,K] . b [N,K]^T`` with both operands quantised along K; bf16 result, or fp32 (optionally added to ``out``)."""
+    from . import err_word, stream_ptr
+    (M, K), (N, K2) = a.shape, b.shape
+    assert K == K2 and K % 32 == 0
+    if out is None:
+        assert not accumulate
+        out = torch.empty(M, N, dtype=out_dtype, device=a.payload.device)
+    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    assert out.dtype == torch.float32 or not accumulate
+    sfa, sfb = a.swizzled(), b.swizzled()
+    _check(_lib().cm_mxfp8_gemm(a.payload.data_ptr(), sfa.data_ptr(), b.payload.data_ptr(), sfb.data_ptr(), out.data_ptr(), M, N, K,
+                                a.payload.stride(0), b.payload.stride(0), out.stride(0), int(out.dtype == torch.float32),
+                                int(accumulate), err_word(out.device).data_ptr(), stream_ptr()), "cm_mxfp8_gemm")
+    F_.count_launch("mxfp8_gemm")
+    return out
+
+
 def eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
     rows = x.numel() // x.shape[-1]
     return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2
             and x.shape[-1] % 32 == 0 and w.shape[0] % 32 == 0 and rows % 32 == 0 and rows > 0)
+
+
+def quantize_weight(w: torch.Tensor, colwise: bool) -> Mxfp8Tensor:
+    """MXFP8 copy of a parameter, kept on the parameter until the optimizer next writes it (``_version`` changes), so
+    the replayed forward of a recomputed layer and every micro-batch of a step reuse one quantisation."""
+    key = "_mx_col" if colwise else "_mx_row"
+    hit = getattr(w, key, None)
+    if hit is not None and hit[0] == w._version:
+        return hit[1]
+    q = quantize_colwise(w.detach(), True) if colwise else quantize_rowwise(w.detach(), True)
+    try:
+        setattr(w, key, (w._version, q))
+    except AttributeError:
+        pass
+    return q
 
 
 class Mxfp8LinearFn(torch.autograd.Function):
@@ -111,32 +164,41 @@ class Mxfp8LinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w):
-        from . import gemm
         x2 = x.reshape(-1, x.shape[-1])
-        xq = quantize_rowwise(x2)                       # along K
-        wq = quantize_rowwise(w)                        # along K
-        y = gemm(dequantize(xq), dequantize(wq))
-        x_t = quantize_colwise(x2)                      # [K, T] along tokens: the wgrad operand, kept in 1 byte/value
-        ctx.save_for_backward(x_t.payload, x_t.scales, w)
+        xq = quantize_rowwise(x2, True)                 # along K
+        wq = quantize_weight(w, colwise=False)          # along K
+        y = gemm_mxfp8(xq, wq)
+        x_t = quantize_colwise(x2, True)                # [K, T] along tokens: the wgrad operand, kept in 1 byte/value
+        ctx.save_for_backward(x_t.payload, x_t.scales, x_t._swizzled, w)
         ctx.xshape = x.shape
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
-        from . import gemm, wgrad_into_main_grad
-        xt_pay, xt_sc, w = ctx.saved_tensors
+        from . import wgrad_into_main_grad
+        xt_pay, xt_sc, xt_sw, w = ctx.saved_tensors
         K, T = xt_pay.shape
         dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dyq = dequantize(quantize_rowwise(dy2))                      # along N
-            w_t = dequantize(quantize_colwise(w))                        # [K, N] along N
-            dx = gemm(dyq, w_t).view(ctx.xshape)                          # [T,N] x [K,N]^T
+            dyq = quantize_rowwise(dy2, True)                            # along N
+            w_t = quantize_weight(w, colwise=True)                       # [K, N] along N
+            dx = gemm_mxfp8(dyq, w_t).view(ctx.xshape)                   # [T,N] x [K,N]^T
         if ctx.needs_input_grad[1]:
-            dy_t = dequantize(quantize_colwise(dy2))                     # [N, T] along tokens
-            x_t = dequantize(Mxfp8Tensor(xt_pay, xt_sc, (K, T)))         # [K, T]
-            dw = wgrad_into_main_grad(w, lambda out, acc: gemm(dy_t, x_t, out=out, accumulate=acc))
+            dy_t = quantize_colwise(dy2, True)                           # [N, T] along tokens
+            x_t = Mxfp8Tensor(xt_pay, xt_sc, (K, T), xt_sw)              # [K, T]
+            dw = wgrad_into_main_grad(w, lambda out, acc: _wgrad(dy_t, x_t, out, acc))
         return dx, dw
+
+
+def _wgrad(dy_t: Mxfp8Tensor, x_t: Mxfp8Tensor, out, accumulate: bool):
+    """dW [N,K] = dy^T x over tokens, written or accumulated into ``out`` (fp32 main grad) or returned as bf16."""
+    if out is None:
+        return gemm_mxfp8(dy_t, x_t)
+    if out.dtype == torch.float32:
+        return gemm_mxfp8(dy_t, x_t, out=out, accumulate=accumulate)
+    tmp = gemm_mxfp8(dy_t, x_t)
+    return out.add_(tmp) if accumulate else out.copy_(tmp)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor):

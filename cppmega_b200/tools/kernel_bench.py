@@ -191,5 +191,35 @@ def bench_scan() -> List[dict]:
 CASES["scan"] = bench_scan
 
 
+def bench_mxfp8_gemm() -> List[dict]:
+    """Block-scaled MXFP8 GEMM (operands already quantised; the swizzle of the scales is outside the timed region)."""
+    import ctypes
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import mxfp8
+    pk = peaks()
+    out = []
+    for M, N, K, label in [(16384, 24960, 4096, "mamba in_proj fwd"), (16384, 4096, 8192, "mamba out_proj fwd"),
+                           (8192, 8192, 8192, "square 8192"), (24960, 4096, 16384, "mamba in_proj wgrad (TN of transposes)")]:
+        a = mxfp8.quantize_rowwise(torch.randn(M, K, device="cuda").bfloat16())
+        b = mxfp8.quantize_rowwise(torch.randn(N, K, device="cuda").bfloat16())
+        sfa, sfb = mxfp8.swizzle_scales(a.scales), mxfp8.swizzle_scales(b.scales)
+        C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        L, err = mxfp8._lib(), cu.err_word(C.device)
+
+        def run():
+            rc = L.cm_mxfp8_gemm(a.payload.data_ptr(), sfa.data_ptr(), b.payload.data_ptr(), sfb.data_ptr(), C.data_ptr(), M, N, K,
+                                 K, K, N, 0, 0, err.data_ptr(), cu.stream_ptr())
+            assert rc == 0, rc
+        ms = time_ms(run)
+        cu.check_errors()
+        tf = 2.0 * M * N * K / ms / 1e9
+        out.append({"kernel": "mxfp8_gemm_kernel", "case": label, "M": M, "N": N, "K": K, "ms": ms, "tflops": tf,
+                    "x_of_" + pk["kind"] + "_bf16": tf / pk["bf16_tflops"], "frac_of_nominal_fp8_4500": tf / 4500.0})
+    return out
+
+
+CASES["mxfp8_gemm"] = bench_mxfp8_gemm
+
+
 if __name__ == "__main__":
     sys.exit(main(sys.argv[1:]))

@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for Nsight Compute captures of single kernels.
 
-    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,ce,rmsnorm}
+    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,ce,rmsnorm,mxfp8_gemm}
 
 Each case launches its kernel three times on inputs that exceed the 126 MB L2 but hold at most a few GB, so a
 ``--set full`` capture of one launch finishes in a minute or two:
@@ -22,6 +22,18 @@ def case_gemm(a_mn=False, b_mn=False):
     C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     for _ in range(3):
         cu.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=C)
+    torch.cuda.synchronize()
+    cu.check_errors()
+
+
+def case_mxfp8_gemm():
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import mxfp8
+    M = N = K = 8192
+    a = mxfp8.quantize_rowwise(torch.randn(M, K, device="cuda").bfloat16())
+    b = mxfp8.quantize_rowwise(torch.randn(N, K, device="cuda").bfloat16())
+    for _ in range(3):
+        mxfp8.gemm_mxfp8(a, b)
     torch.cuda.synchronize()
     cu.check_errors()
 
@@ -103,7 +115,7 @@ def case_rmsnorm():
 
 
 CASES = {"gemm": case_gemm, "gemm_wgrad": lambda: case_gemm(True, True), "scan_fwd": case_scan_fwd,
-         "scan_bwd": case_scan_bwd, "m2rnn": case_m2rnn, "ce": case_ce, "rmsnorm": case_rmsnorm}
+         "scan_bwd": case_scan_bwd, "m2rnn": case_m2rnn, "ce": case_ce, "rmsnorm": case_rmsnorm, "mxfp8_gemm": case_mxfp8_gemm}
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else ""

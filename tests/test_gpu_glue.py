@@ -162,6 +162,29 @@ def test_mxfp8_quantize_kernels_match_reference():
     assert ((deq.float() - x.float()).abs() <= 0.07 * x.float().abs() + 1e-6).all()       # 3 mantissa bits
     sw = mxfp8.swizzle_scales(r.scales)
     assert torch.equal(sw, ref.swizzle_scales_128x4(r.scales))
+    # the quantise kernels can write the tile order themselves
+    assert torch.equal(mxfp8.quantize_rowwise(x, True).swizzled(), sw)
+    assert torch.equal(mxfp8.quantize_colwise(x, True).swizzled(), ref.swizzle_scales_128x4(c.scales))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (300, 200, 160), (128, 256, 4096), (1024, 768, 1024)])
+def test_mxfp8_block_scaled_gemm(M, N, K):
+    """tcgen05 block-scaled product against the fp32 product of the dequantised operands."""
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.ops.cuda import mxfp8
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda") * torch.logspace(-2, 1, K, device="cuda")).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * torch.logspace(1, -2, N, device="cuda")[:, None]).bfloat16()
+    aq, bq = mxfp8.quantize_rowwise(a), mxfp8.quantize_rowwise(b)
+    want = mxfp8.dequantize(aq).float() @ mxfp8.dequantize(bq).float().t()
+    before = F_.launch_counts().get("mxfp8_gemm", 0)
+    got = mxfp8.gemm_mxfp8(aq, bq)
+    assert F_.launch_counts().get("mxfp8_gemm", 0) == before + 1
+    assert got.dtype == torch.bfloat16 and _rel(got, want) < 5e-3
+    acc = torch.randn(M, N, device="cuda")
+    got32 = mxfp8.gemm_mxfp8(aq, bq, out=acc.clone(), accumulate=True)
+    assert _rel(got32, want + acc) < 1e-5
+    torch.testing.assert_close(mxfp8.gemm_mxfp8(aq, bq, out_dtype=torch.float32), want, rtol=1e-4, atol=1e-3 * want.abs().max().item())
 
 
 def test_mxfp8_linear_matches_quantised_reference():
