@@ -29,7 +29,7 @@ from ..ops import functional as F_
 from ..ops import reference as ref
 from ..parallel.state import ParallelContext
 from ..parallel.tensor_parallel import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear, copy_to_tp, gather_seq
-from .common import RMSNorm, seed_for
+from .common import RMSNorm, cat_last_dim, seed_for, split_last_dim
 
 
 @dataclass
@@ -65,8 +65,13 @@ class DSAIndexer(nn.Module):
         q = self.linear_wq_b(q_latent).reshape(B, S, self.h, self.d)
         k = self.k_norm(self.linear_wk(x))
         cos, sin = ref.rope_tables(S, self.rope_dim, self.rope_base, device=x.device)
-        q = torch.cat([F_.apply_rope(q[..., :self.rope_dim], cos, sin), q[..., self.rope_dim:]], dim=-1)
-        k = torch.cat([F_.apply_rope(k[..., :self.rope_dim], cos, sin), k[..., self.rope_dim:]], dim=-1)
+        if self.rope_dim < self.d:
+            q_r, q_n = split_last_dim(q, (self.rope_dim, self.d - self.rope_dim))
+            k_r, k_n = split_last_dim(k, (self.rope_dim, self.d - self.rope_dim))
+            q = cat_last_dim([F_.apply_rope(q_r, cos, sin), q_n])
+            k = cat_last_dim([F_.apply_rope(k_r, cos, sin), k_n])
+        else:
+            q, k = F_.apply_rope(q, cos, sin), F_.apply_rope(k, cos, sin)
         w = self.linear_weights_proj(x).float() * self.scale
         return q, k, w
 
@@ -138,25 +143,26 @@ class MLAttention(nn.Module):
         q_lat = self.q_layernorm(self.linear_q_down_proj(x))
         q = self.linear_q_up_proj(q_lat).reshape(B, S, Hl, dq + dr)
         kv_c = self.linear_kv_down_proj(x)
-        kv_lat, k_pe = kv_c[..., :dc], kv_c[..., dc:]
+        kv_lat, k_pe = split_last_dim(kv_c, (dc, dr))
         kv_lat = self.kv_layernorm(kv_lat)
         cos, sin = ref.rope_tables(S, dr, mla.rope_base, device=x.device)
-        q_nope, q_pe = q[..., :dq], F_.apply_rope(q[..., dq:], cos, sin)
+        q_nope, q_pe = split_last_dim(q, (dq, dr))
+        q_pe = F_.apply_rope(q_pe, cos, sin)
         k_pe = copy_to_tp(F_.apply_rope(k_pe, cos, sin), pc)                    # [B,S,dr] shared by heads
         self.last_indexer_loss = None
         if not self.sparse:
             kv = self.linear_kv_up_proj(kv_lat).reshape(B, S, Hl, dq + dv)
-            k = torch.cat([kv[..., :dq], k_pe.unsqueeze(2).expand(B, S, Hl, dr)], dim=-1)
-            o = F_.causal_attention(torch.cat([q_nope, q_pe], dim=-1), k, kv[..., dq:].contiguous(),
-                                    self.softmax_scale)
+            k_nope, v = split_last_dim(kv, (dq, dv))
+            k = cat_last_dim([k_nope, k_pe.unsqueeze(2).expand(B, S, Hl, dr)])
+            o = F_.causal_attention(cat_last_dim([q_nope, q_pe]), k, v.contiguous(), self.softmax_scale)
         else:
             idx = indices if indices is not None else self._indices(x, q_lat, index_cache, (q_nope, q_pe, kv_lat, k_pe))
             w_up = self.linear_kv_up_proj.weight.reshape(Hl, dq + dv, dc)
             w_uk, w_uv = w_up[:, :dq], w_up[:, dq:]
             lat_tp = copy_to_tp(kv_lat, pc)
             q_abs = torch.einsum("bshd,hdc->bshc", q_nope, w_uk.to(q_nope.dtype))
-            q_full = torch.cat([q_abs, q_pe], dim=-1)                           # [B,S,Hl,dc+dr]
-            kv_full = torch.cat([lat_tp, k_pe], dim=-1)                          # [B,S,dc+dr]
+            q_full = cat_last_dim([q_abs, q_pe])                                # [B,S,Hl,dc+dr]
+            kv_full = cat_last_dim([lat_tp, k_pe])                               # [B,S,dc+dr]
             o_lat = F_.sparse_mla(q_full, kv_full, idx, self.softmax_scale, dc)  # [B,S,Hl,dc]
             o = torch.einsum("bshc,hvc->bshv", o_lat, w_uv.to(o_lat.dtype))
         return self.linear_proj(o.reshape(B, S, Hl * dv))

@@ -91,10 +91,45 @@ class _SplitLastDim(torch.autograd.Function):
             dst = out[..., off:off + sz]
             if g is None:
                 dst.zero_()
+            elif g.is_cuda:
+                from ..ops.cuda import fast_copy_
+                fast_copy_(dst, g)
             else:
                 dst.copy_(g)
             off += sz
         return out, None
+
+
+class _CatLastDim(torch.autograd.Function):
+    """``torch.cat`` along the last dim as one vectorised strided copy per piece, both ways (the pieces here are head
+    slices with 128-byte runs, which the library's batched cat and slice-backward kernels move far below memory speed)."""
+
+    @staticmethod
+    def forward(ctx, *xs):
+        from ..ops.cuda import fast_copy_
+        ctx.sizes = tuple(x.shape[-1] for x in xs)
+        out = torch.empty(*xs[0].shape[:-1], sum(ctx.sizes), dtype=xs[0].dtype, device=xs[0].device)
+        off = 0
+        for x, sz in zip(xs, ctx.sizes):
+            fast_copy_(out[..., off:off + sz], x)
+            off += sz
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..ops.cuda import fast_contiguous
+        grads, off = [], 0
+        for need, sz in zip(ctx.needs_input_grad, ctx.sizes):
+            grads.append(fast_contiguous(g[..., off:off + sz]) if need else None)
+            off += sz
+        return tuple(grads)
+
+
+def cat_last_dim(xs):
+    xs = list(xs)
+    if xs[0].is_cuda and all(x.dtype == xs[0].dtype and x.shape[:-1] == xs[0].shape[:-1] for x in xs):
+        return _CatLastDim.apply(*xs)
+    return torch.cat(xs, dim=-1)
 
 
 def split_last_dim(x: torch.Tensor, sizes):

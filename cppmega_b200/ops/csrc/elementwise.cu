@@ -377,9 +377,45 @@ __global__ void __launch_bounds__(256) sum_slots_kernel(const __nv_bfloat16* __r
   }
 }
 
+// Strided copy in 16-byte vectors: a tensor of up to four outer dimensions whose innermost run is contiguous in both
+// source and destination.  Sizes d1..d3 (d0 is implied by n_vec), byte strides per outer dimension.
+struct StridedCopy {
+  long long n_vec;
+  int inner_vecs, d1, d2, d3;
+  long long ss[4], ds[4];
+};
+__global__ void __launch_bounds__(256) strided_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, const StridedCopy c) {
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < c.n_vec; idx += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % c.inner_vecs);
+    long long rest = idx / c.inner_vecs;
+    const int i3 = (int)(rest % c.d3); rest /= c.d3;
+    const int i2 = (int)(rest % c.d2); rest /= c.d2;
+    const int i1 = (int)(rest % c.d1);
+    const long long i0 = rest / c.d1;
+    const uint4 val = *reinterpret_cast<const uint4*>(src + i0 * c.ss[0] + i1 * c.ss[1] + i2 * c.ss[2] + i3 * c.ss[3] + (long long)v * 16);
+    *reinterpret_cast<uint4*>(dst + i0 * c.ds[0] + i1 * c.ds[1] + i2 * c.ds[2] + i3 * c.ds[3] + (long long)v * 16) = val;
+  }
+}
+
 }  // namespace cm
 
 using namespace cm;
+
+// sizes [d0,d1,d2,d3] of the outer dimensions, inner run `inner_bytes` (multiple of 16), byte strides; all addresses 16-byte aligned
+extern "C" int cm_strided_copy(const void* src, void* dst, const long long* sizes, const long long* sstr, const long long* dstr,
+                               long long inner_bytes, cudaStream_t s) {
+  if (inner_bytes <= 0 || (inner_bytes % 16)) return -10;
+  cm::StridedCopy c;
+  c.inner_vecs = (int)(inner_bytes / 16);
+  c.d1 = (int)sizes[1]; c.d2 = (int)sizes[2]; c.d3 = (int)sizes[3];
+  c.n_vec = sizes[0] * sizes[1] * sizes[2] * sizes[3] * c.inner_vecs;
+  if (c.n_vec <= 0) return 0;
+  for (int i = 0; i < 4; ++i) { c.ss[i] = sstr[i]; c.ds[i] = dstr[i]; }
+  long long blocks = (c.n_vec + 255) / 256;
+  const long long cap = (long long)cm::sm_count() * 16;
+  cm::strided_copy_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, c);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
 
 extern "C" int cm_sum_slots(const void* stage, void* out, int n_slots, long long n, cudaStream_t s) {
   if (n <= 0) return 0;

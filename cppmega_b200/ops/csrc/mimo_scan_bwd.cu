@@ -58,16 +58,19 @@ struct BwdArgs {
   int B, S, H, G, C;
   long long ldV, ldZ;           // token strides of V and Z in elements
   int* err;
+  int total_blocks;             // B * H * C
 };
 
-__device__ __forceinline__ void decode_block_b(const BwdArgs& a, int& b, int& g, int& c, int& h) {
+__device__ __forceinline__ void decode_block_b(const BwdArgs& a, int x, int& b, int& g, int& c, int& h) {
   const int hpg = a.H / a.G;
-  int x = blockIdx.x;
   const int hl = x % hpg; x /= hpg;
   c = x % a.C; x /= a.C;
   g = x % a.G; x /= a.G;
   b = x;
   h = g * hpg + hl;
+}
+__device__ __forceinline__ void decode_block_b(const BwdArgs& a, int& b, int& g, int& c, int& h) {
+  decode_block_b(a, (int)blockIdx.x, b, g, c, h);
 }
 
 // gating of this thread's row: gate[p] = Phi[r,p] * silu(Z[t,p] * Zeta[r,p]); also returns silu' pieces on demand
@@ -250,17 +253,8 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
 
   if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
   CM_STAMP(0);
-  int b, g, c, h;
-  decode_block_b(a, b, g, c, h);
-  const int t0 = c * LT;
   const int tid = threadIdx.x;
   const int i = tid & 127, wg = tid >> 7, t = i >> 2, r = i & 3, warp = tid >> 5, lane = tid & 31;
-  // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
-  const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
-  const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
-  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.ldV);
-  const HalfRowRaw yraw = load_half_raw(a.dY, b, t0, h, a.S, (long long)a.H * P);
-  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.ldZ);
   if (tid == 0) {
     for (int q = 0; q < 4; ++q) mbar_init(&bars[q], 1);
     *abort_flag = 0;
@@ -270,8 +264,22 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  CM_STAMP(1);
   const uint32_t tmem = *tmem_slot;
+  // Persistent: one CTA per SM walks the chunks with a grid stride; barriers, TMEM and the kernel prologue are paid
+  // once, and every barrier completes exactly one phase per chunk, so its parity is the iteration's low bit.
+  uint32_t par = 0;
+#pragma unroll 1
+  for (int xblk = blockIdx.x; xblk < a.total_blocks; xblk += gridDim.x, par ^= 1) {
+  int b, g, c, h;
+  decode_block_b(a, xblk, b, g, c, h);
+  const int t0 = c * LT;
+  // every global load of the prologue is issued here, ahead of the set-up, and consumed further down
+  const ScalarLoads sl = load_chunk_scalars(a.ADT, a.DT, a.Trap, ((size_t)b * a.H + h) * a.S + t0, t0, a.S);
+  const float4 ang4 = load_angles4<NROT>(a.angles, b, t0, h, a.S, a.H);
+  const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.ldV);
+  const HalfRowRaw yraw = load_half_raw(a.dY, b, t0, h, a.S, (long long)a.H * P);
+  const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.ldZ);
+  CM_STAMP(1);
   const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
   // phase 1 accumulators                      phase 2 / 3 accumulators
   const uint32_t tS1 = tmem, tdPm = tmem + 128, tO2 = tmem + 256, tX = tmem + 320, tdQb = tmem + 384;
@@ -301,7 +309,7 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   const float dsk = a.Dskip[h];
 
   CM_STAMP(2);
-  bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
+  bool ok = mbar_wait(&bars[0], par, abort_flag, a.err, ERR_WAIT_FULL);
   CM_STAMP(3);
   if (ok) {
     transform_rows<N, NROT, 2, HeadBias<N>::LD>(sQ, hb->qb, cos_tab, sin_tab);
@@ -358,7 +366,7 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
     }
     dtot_part *= __expf(tot);
   }
-  ok = __syncthreads_and(mbar_wait(&bars[1], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
+  ok = __syncthreads_and(mbar_wait(&bars[1], par, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
   tc_fence_after();
   CM_STAMP(5);
 
@@ -432,7 +440,7 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
       if (lane == tl) { colsum[(warp * 2 + 0) * (LT / 2) + tl] = c_; colsum[(warp * 2 + 1) * (LT / 2) + tl] = t_; }
     }
   }
-  ok = __syncthreads_and(mbar_wait(&bars[2], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
+  ok = __syncthreads_and(mbar_wait(&bars[2], par, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
   tc_fence_after();
   CM_STAMP(7);
   // Pm has been consumed by phase 2: its space becomes the reduction scratch
@@ -597,7 +605,7 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
     }
     if (tid == 0) atomicAdd(a.dD + h, gs->dD);
   }
-  ok = __syncthreads_and(mbar_wait(&bars[3], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
+  ok = __syncthreads_and(mbar_wait(&bars[3], par, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
   tc_fence_after();
   CM_STAMP(9);
   // ---------------- epilogue C: dQr = dQ + e dQb (warpgroup 0), dKr (warpgroup 1); inverse rotation; d(angles) ----
@@ -702,6 +710,13 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
       }
     }
   }
+  // the next chunk's TMA loads and MMAs overwrite the tiles and accumulators every thread has just finished with
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*abort_flag) break;
+  }
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, 512); }
   CM_STAMP(11);
 }
@@ -746,7 +761,7 @@ extern "C" int cm_mimo_scan_bwd(const void* Qn, const void* Kn, const void* V, c
   if (rc) return rc;
   BwdArgs a{(const __nv_bfloat16*)V, (const __nv_bfloat16*)Z, (const __nv_bfloat16*)dY, ADT, DT, Trap, Qb, Kb, Psi, Zeta,
             Phi, angles, Dskip, gbuf, (__nv_bfloat16*)dQh, (__nv_bfloat16*)dKh, (__nv_bfloat16*)dV, (__nv_bfloat16*)dZ,
-            dAngles, dADT, dTs, dGam, dPsi, dZeta, dPhi, dD_, B, S, H, G, C, ldV, ldZ, err};
+            dAngles, dADT, dTs, dGam, dPsi, dZeta, dPhi, dD_, B, S, H, G, C, ldV, ldZ, err, B * H * C};
   auto k0 = mimo_grad_state_kernel<128, 32>;
   auto k2 = mimo_chunk_grad_kernel<128, 32>;
   static bool cfg = false;
@@ -759,7 +774,7 @@ extern "C" int cm_mimo_scan_bwd(const void* Qn, const void* Kn, const void* V, c
   k0<<<grid, THREADS2, grad_state_smem(), stream>>>(tmQ, a);
   dim3 g2(B * H, (128 * P + 1023) / 1024);
   mimo_state_scan_rev_kernel<<<g2, 256, 0, stream>>>(gbuf, tot, (__nv_bfloat16*)dend, C, 128 * P);
-  k2<<<grid, THREADS2, chunk_grad_smem(), stream>>>(tmQ, tmK, tmS, tmE, a);
+  k2<<<grid < sm_count() ? grid : sm_count(), THREADS2, chunk_grad_smem(), stream>>>(tmQ, tmK, tmS, tmE, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -51,6 +51,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "cm_swiglu_bwd": [vp, vp, vp, i64, i32, vp],
         "cm_adamw": [vp, vp, vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, f32, i32, i32, vp],
         "cm_sumsq": [vp, i64, vp, i32, vp],
+        "cm_strided_copy": [vp, vp, vp, vp, vp, i64, vp],
     }
     for name, args in sig.items():
         fn = getattr(L, name, None)
@@ -145,6 +146,51 @@ class LinearFn(torch.autograd.Function):
         return dx, dw
 
 
+def _collapse(sizes, sstr, dstr):
+    """Drop unit dimensions and merge neighbours that are contiguous in both tensors."""
+    dims = [(n, a, b) for n, a, b in zip(sizes, sstr, dstr) if n != 1]
+    out = []
+    for n, a, b in dims:
+        if out and out[-1][1] == a * n and out[-1][2] == b * n:
+            pn, _, _ = out[-1]
+            out[-1] = (pn * n, a, b)
+        else:
+            out.append((n, a, b))
+    return out
+
+
+def fast_copy_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """``dst.copy_(src)`` for same-dtype CUDA tensors whose innermost run is contiguous on both sides, as one launch
+    of 16-byte vector moves.  The library's generic strided copy moves such views (slices of a packed projection,
+    head splits) element by element at a fraction of the memory bandwidth.  Anything else falls through to ``copy_``."""
+    if (not (dst.is_cuda and src.is_cuda) or dst.dtype != src.dtype or dst.shape != src.shape or dst.numel() == 0
+            or dst.device != src.device):
+        return dst.copy_(src)
+    es = dst.element_size()
+    dims = _collapse(dst.shape, src.stride(), dst.stride())
+    if not dims:
+        return dst.copy_(src)
+    n_in, s_in, d_in = dims[-1]
+    outer = dims[:-1]
+    if (s_in != 1 or d_in != 1 or (n_in * es) % 16 or len(outer) > 4 or src.data_ptr() % 16 or dst.data_ptr() % 16
+            or any((a * es) % 16 or (b * es) % 16 for _, a, b in outer)):
+        return dst.copy_(src)
+    outer = [(1, 0, 0)] * (4 - len(outer)) + outer
+    arr = ctypes.c_longlong * 4
+    sizes = arr(*[n for n, _, _ in outer])
+    sstr = arr(*[a * es for _, a, _ in outer])
+    dstr = arr(*[b * es for _, _, b in outer])
+    _check(lib().cm_strided_copy(src.data_ptr(), dst.data_ptr(), sizes, sstr, dstr, n_in * es, stream_ptr()), "cm_strided_copy")
+    F_.count_launch("strided_copy")
+    return dst
+
+
+def fast_contiguous(x: torch.Tensor) -> torch.Tensor:
+    if x.is_contiguous() or not x.is_cuda:
+        return x.contiguous()
+    return fast_copy_(torch.empty(x.shape, dtype=x.dtype, device=x.device), x)
+
+
 def wgrad_into_main_grad(w: torch.Tensor, run):
     """Weight gradient either as a fresh tensor or, when the optimizer asked for it (``w.fuse_wgrad_accumulation``),
     accumulated by the GEMM epilogue straight into the parameter's slice of the flat gradient buffer.  In the fused
@@ -210,9 +256,7 @@ class RMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, eps):
         H = x.shape[-1]
-        x2 = x.reshape(-1, H)
-        if not x2.is_contiguous():
-            x2 = x2.contiguous()
+        x2 = fast_contiguous(x).view(-1, H)
         y = torch.empty_like(x2)
         rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
         _check(lib().cm_rmsnorm_fwd(x2.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), x2.shape[0], H,
@@ -226,9 +270,7 @@ class RMSNormFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w, rstd = ctx.saved_tensors
         H = x2.shape[-1]
-        dy2 = dy.reshape(-1, H)
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
+        dy2 = fast_contiguous(dy).view(-1, H)
         dx = torch.empty_like(x2)
         dw = torch.zeros(H, dtype=torch.float32, device=x2.device)
         _check(lib().cm_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr(), dx.data_ptr(),

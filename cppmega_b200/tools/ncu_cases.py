@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for Nsight Compute captures of single kernels.
 
-    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,ce,rmsnorm,mxfp8_gemm}
+    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,m2rnn_bwd,sparse_mla,indexer,ce,rmsnorm,mxfp8_gemm}
 
 Each case launches its kernel three times on inputs that exceed the 126 MB L2 but hold at most a few GB, so a
 ``--set full`` capture of one launch finishes in a minute or two:
@@ -92,6 +92,55 @@ def case_m2rnn():
     torch.cuda.synchronize()
 
 
+def case_m2rnn_bwd():
+    from cppmega_b200.ops.cuda import kernels2
+    B, S, H = 2, 4096, 51
+    q = torch.randn(B, S, 1, 64, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, S, 1, 64, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, S, H, 16, device="cuda").bfloat16().requires_grad_()
+    W = torch.eye(16, device="cuda").repeat(H, 1, 1).bfloat16().requires_grad_()
+    f = torch.rand(B, S, H, device="cuda").requires_grad_()
+    for _ in range(3):
+        y = kernels2.m2rnn_scan(q, k, v, W, f)
+        y = y[0] if isinstance(y, tuple) else y
+        y.backward(torch.ones_like(y))
+    torch.cuda.synchronize()
+
+
+def _sparse_inputs(B=2, S=4096):
+    q = (torch.randn(B, S, 32, 128, device="cuda") * 0.3).bfloat16()
+    kv = (torch.randn(B, S, 128, device="cuda") * 0.3).bfloat16()
+    t = torch.arange(S, device="cuda")
+    idx = (torch.rand(B, S, 256, device="cuda") * (t[None, :, None] + 1)).long().clamp_max(S - 1).int()
+    return q, kv, idx
+
+
+def case_sparse_mla():
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import kernels4
+    q, kv, idx = _sparse_inputs()
+    q.requires_grad_()
+    kv.requires_grad_()
+    for _ in range(3):
+        out = kernels4.SparseMLAFn.apply(q, kv, idx, 128 ** -0.5, 64)
+        out.backward(torch.ones_like(out))
+    torch.cuda.synchronize()
+    cu.check_errors()
+
+
+def case_indexer():
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import kernels4
+    B, S = 2, 4096
+    q = torch.randn(B, S, 32, 64, device="cuda").bfloat16()
+    k = torch.randn(B, S, 64, device="cuda").bfloat16()
+    w = torch.rand(B, S, 32, device="cuda")
+    for _ in range(3):
+        kernels4.indexer_topk(q, k, w, 256)
+    torch.cuda.synchronize()
+    cu.check_errors()
+
+
 def case_ce():
     from cppmega_b200.ops.cuda import extra
     T, H, V = 4096, 4096, 131072
@@ -115,7 +164,8 @@ def case_rmsnorm():
 
 
 CASES = {"gemm": case_gemm, "gemm_wgrad": lambda: case_gemm(True, True), "scan_fwd": case_scan_fwd,
-         "scan_bwd": case_scan_bwd, "m2rnn": case_m2rnn, "ce": case_ce, "rmsnorm": case_rmsnorm, "mxfp8_gemm": case_mxfp8_gemm}
+         "scan_bwd": case_scan_bwd, "m2rnn": case_m2rnn, "ce": case_ce, "rmsnorm": case_rmsnorm, "mxfp8_gemm": case_mxfp8_gemm,
+         "m2rnn_bwd": case_m2rnn_bwd, "sparse_mla": case_sparse_mla, "indexer": case_indexer}
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else ""

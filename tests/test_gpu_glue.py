@@ -269,3 +269,37 @@ def test_rope_kernel_on_slices():
     assert _rel(y, y2) < 1e-2 and _rel(gw, gw2) < 1e-2
     k = torch.randn(B, S, D, device="cuda").bfloat16()
     assert _rel(kernels4.apply_rope(k, cos, sin), ref.apply_rope(k, cos, sin)) < 1e-2
+
+
+def test_fast_strided_copy_and_cat_split_helpers():
+    from cppmega_b200.models.common import cat_last_dim, split_last_dim
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.ops.cuda import fast_contiguous, fast_copy_
+    torch.manual_seed(0)
+    packed = torch.randn(3, 130, 24960, device="cuda").bfloat16()
+    view = packed[..., 8192:8192 + 4096].reshape(3, 130, 8, 4, 128).permute(0, 1, 3, 2, 4)        # 5-D, 256-byte runs
+    n0 = F_.launch_counts().get("strided_copy", 0)
+    assert torch.equal(fast_contiguous(view), view.contiguous())
+    dst = torch.zeros(3, 130, 24960, device="cuda", dtype=torch.bfloat16)
+    src = torch.randn(3, 130, 64, device="cuda").bfloat16()
+    fast_copy_(dst[..., 128:192], src)
+    assert torch.equal(dst[..., 128:192], src) and dst[..., :128].abs().sum() == 0 and dst[..., 192:].abs().sum() == 0
+    exp = torch.randn(3, 130, 1, 64, device="cuda").bfloat16().expand(3, 130, 32, 64)             # stride-0 source
+    assert torch.equal(fast_contiguous(exp), exp.contiguous())
+    assert F_.launch_counts().get("strided_copy", 0) == n0 + 3
+    odd = torch.randn(5, 7, 9, device="cuda").bfloat16()[..., 1:6]                                # 10-byte runs: library path
+    assert torch.equal(fast_contiguous(odd), odd.contiguous())
+    # autograd of the helpers against torch.cat / slicing
+    a = torch.randn(2, 50, 32, 64, device="cuda").bfloat16().requires_grad_()
+    b = torch.randn(2, 50, 1, 64, device="cuda").bfloat16().requires_grad_()
+    x = torch.randn(2, 50, 32, 192, device="cuda").bfloat16().requires_grad_()
+    x1, x2 = split_last_dim(x, (128, 64))
+    y = cat_last_dim([a, b.expand(2, 50, 32, 64), x2])
+    g = torch.randn_like(y)
+    (y * g).sum().add((x1 * x1).sum()).backward()
+    a2, b2, xx = (t.detach().clone().requires_grad_() for t in (a, b, x))
+    y2 = torch.cat([a2, b2.expand(2, 50, 32, 64), xx[..., 128:]], dim=-1)
+    (y2 * g).sum().add((xx[..., :128] * xx[..., :128]).sum()).backward()
+    assert torch.equal(y, y2)
+    for p, q in ((a, a2), (b, b2), (x, xx)):
+        torch.testing.assert_close(p.grad.float(), q.grad.float(), rtol=2e-2, atol=2e-2)
