@@ -27,6 +27,10 @@ constexpr int ROWS = LT * R;      // 128 fused rows
 constexpr int P = 64;             // head dim
 constexpr int THREADS = 128;
 constexpr int SLAB = ROWS * 128;  // bytes of one [128 rows x 64 bf16] swizzled slab
+// Row stride of the per-rank [R, P] vectors in shared memory.  The four lanes of a token read four different ranks at
+// the same column; with a stride of P (a multiple of 32 banks) those reads collide four ways, with P + 4 they do not.
+constexpr int VLD = P + 4;
+__device__ __forceinline__ int vec_idx(int x) { return (x / P) * VLD + (x % P); }   // flat [R*P] index -> padded
 
 // Optional phase timestamps (compile with -DCM_MIMO_TIMING): thread 0 of the first 1024 CTAs records the SM clock at
 // numbered points of a kernel; cm_mimo_read_stamps copies them out.  Compiled out by default.
@@ -280,7 +284,7 @@ __device__ __forceinline__ void pv_from_raw(float (&pv)[P / 2], const HalfRowRaw
   const int i = threadIdx.x & 127, wg = threadIdx.x >> 7, r = i & 3;
   half_raw_to_float(pv, raw);
 #pragma unroll
-  for (int e = 0; e < P / 2; ++e) pv[e] *= psi[r * P + wg * 32 + e];
+  for (int e = 0; e < P / 2; ++e) pv[e] *= psi[r * VLD + wg * 32 + e];
 }
 // Sum 32 per-thread values over the four lanes of a token (lanes that differ in their two low bits); lane r ends up
 // with the totals of columns [8r, 8r + 8).  24 shuffles instead of 64.
@@ -389,9 +393,9 @@ struct HeadBias {
   float kb[R * LD];
 };
 struct HeadVecs {
-  float psi[R * P];
-  float zeta[R * P];
-  float phi[R * P];
+  float psi[R * VLD];
+  float zeta[R * VLD];
+  float phi[R * VLD];
 };
 template <int N>
 __device__ __forceinline__ void load_head_consts(HeadBias<N>* hb, HeadVecs* hv, const float* __restrict__ Qb,
@@ -403,9 +407,9 @@ __device__ __forceinline__ void load_head_consts(HeadBias<N>* hb, HeadVecs* hv, 
     hb->kb[dst] = Kb[(size_t)h * R * N + x];
   }
   for (int x = threadIdx.x; x < R * P; x += blockDim.x) {
-    hv->psi[x] = Psi[(size_t)h * R * P + x];
-    if (Zeta) hv->zeta[x] = Zeta[(size_t)h * R * P + x];
-    if (Phi) hv->phi[x] = Phi[(size_t)h * R * P + x];
+    hv->psi[vec_idx(x)] = Psi[(size_t)h * R * P + x];
+    if (Zeta) hv->zeta[vec_idx(x)] = Zeta[(size_t)h * R * P + x];
+    if (Phi) hv->phi[vec_idx(x)] = Phi[(size_t)h * R * P + x];
   }
 }
 

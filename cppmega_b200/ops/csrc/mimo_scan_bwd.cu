@@ -154,8 +154,8 @@ __global__ void __launch_bounds__(THREADS2) mimo_grad_state_kernel(const __grid_
     float dy[P / 2], z[P / 2];
     half_raw_to_float(dy, yraw);
     half_raw_to_float(z, zraw);
-    const float* zeta = hv->zeta + r * P + wg * 32;
-    const float* phi = hv->phi + r * P + wg * 32;
+    const float* zeta = hv->zeta + r * VLD + wg * 32;
+    const float* phi = hv->phi + r * VLD + wg * 32;
     const float e = __expf(sc->cs[t]);
 #pragma unroll
     for (int p = 0; p < P / 2; ++p) dy[p] = dy[p] * phi[p] * fast_silu(z[p] * zeta[p]);
@@ -217,8 +217,8 @@ struct GradScratch {
   float dgam[LT];
   float dtot;
   float dD;
-  float par[3][4][R][P];     // per-lane-quarter partials of dPsi, dZeta, dPhi (each warpgroup fills its own columns)
-  float dang[LT][NROT_MAX];  // K-side d(angle) partials handed from warpgroup 1 to warpgroup 0
+  float par[3][4][R][VLD];   // per-lane-quarter partials of dPsi, dZeta, dPhi (each warpgroup fills its own columns)
+  float dang[LT][NROT_MAX + 4];  // K-side d(angle) partials (padded rows: eight tokens of a warp write one column) handed from warpgroup 1 to warpgroup 0
 };
 
 template <int N, int NROT>
@@ -246,9 +246,8 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 1);             // tma, ph1, ph2, ph3
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* colsum = reinterpret_cast<float*>(tmem_slot + 4);          // [8 warps][2][16]
-  HeadBias<N>* hb = reinterpret_cast<HeadBias<N>*>(sPm);            // aliases Pm: biases die before phase A writes Pm
-  GradScratch* gs = reinterpret_cast<GradScratch*>(sPm);            // aliases Pm: used only after phase 2 has read it
+  // colsum [8 warps][2][16] floats follow the abort flag; the head biases and later the reduction scratch alias Pm
+  // (biases die before phase A writes Pm; the scratch is used only after phase 2 has read it)
   static_assert(sizeof(GradScratch) <= 2 * SLAB && sizeof(HeadBias<N>) <= 2 * SLAB, "scratch must fit the Pm tile");
 
   if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
@@ -270,6 +269,27 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   uint32_t par = 0;
 #pragma unroll 1
   for (int xblk = blockIdx.x; xblk < a.total_blocks; xblk += gridDim.x, par ^= 1) {
+  // Re-derive every shared-memory address from a value the compiler cannot see through: otherwise the addresses and
+  // the ~80 MMA descriptors built from them are hoisted out of this loop and spill the 255-register budget.
+  uint8_t* smem_l;
+  asm volatile("mov.u64 %0, %1;" : "=l"(smem_l) : "l"(smem));
+  uint8_t* sQ = smem_l;
+  uint8_t* sK = sQ + 2 * SLAB;
+  uint8_t* sPV = sK + 2 * SLAB;
+  uint8_t* sdO = sPV + SLAB;
+  uint8_t* sSt = sdO + SLAB;
+  uint8_t* sdE = sSt + SLAB;
+  uint8_t* sPm = sdE + SLAB;
+  uint8_t* sdS = sPm + 2 * SLAB;
+  uint8_t* sPVw = sdS + 2 * SLAB;
+  float* cos_tab = reinterpret_cast<float*>(sPVw + SLAB);
+  float* sin_tab = cos_tab + tab_floats<NROT>();
+  HeadVecs* hv = reinterpret_cast<HeadVecs*>(sin_tab + tab_floats<NROT>());
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(hv + 1);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 1);
+  float* colsum = reinterpret_cast<float*>(reinterpret_cast<uint32_t*>(bars + 4) + 4);
+  HeadBias<N>* hb = reinterpret_cast<HeadBias<N>*>(sPm);
+  GradScratch* gs = reinterpret_cast<GradScratch*>(sPm);
   int b, g, c, h;
   decode_block_b(a, xblk, b, g, c, h);
   const int t0 = c * LT;
@@ -300,9 +320,9 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   fill_sincos4<NROT>(cos_tab, sin_tab, ang4);
   __syncthreads();
   const size_t rowoff = (((size_t)b * a.S + t0 + t) * a.H + h) * P + wg * 32;     // this thread's half row
-  const float* zeta = hv->zeta + r * P + wg * 32;
-  const float* phi = hv->phi + r * P + wg * 32;
-  const float* psi = hv->psi + r * P + wg * 32;
+  const float* zeta = hv->zeta + r * VLD + wg * 32;
+  const float* phi = hv->phi + r * VLD + wg * 32;
+  const float* psi = hv->psi + r * VLD + wg * 32;
   const float csi = sc->cs[t], gi = sc->gam[t], tsi = sc->ts[t], tot = sc->tot;
   const float ei = __expf(csi);
   const float wi = tsi * __expf(tot - csi);

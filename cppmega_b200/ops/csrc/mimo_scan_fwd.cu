@@ -211,9 +211,9 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   static_assert(sizeof(HeadBias<N>) <= SLAB, "bias block must fit the PV slab it borrows");
   float* psi_s = sin_tab + tab_floats<NROT>();                 // [R, P]
   float* zeta_s = cos_tab;                                      // zeta / phi move into the sin/cos tables once the
-  float* phi_s = cos_tab + R * P;                               // rotations are done (registers hold them until then)
-  static_assert(2 * R * P <= 2 * tab_floats<NROT>(), "zeta and phi must fit the retired tables");
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(psi_s + R * P);
+  float* phi_s = cos_tab + R * VLD;                              // rotations are done (registers hold them until then)
+  static_assert(2 * R * VLD <= 2 * tab_floats<NROT>(), "zeta and phi must fit the retired tables");
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(psi_s + R * VLD);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sc + 1);            // [0] tma, [1] S1+O2, [2] O1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
     hb->qb[dst] = a.Qb[(size_t)h * R * N + x];
     hb->kb[dst] = a.Kb[(size_t)h * R * N + x];
   }
-  psi_s[threadIdx.x] = psi_v;
+  psi_s[vec_idx(threadIdx.x)] = psi_v;
   finish_chunk_scalars(sc, sl, t0, a.S);
   fill_sincos4<NROT>(cos_tab, sin_tab, ang4);
   __syncthreads();
@@ -277,8 +277,8 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   }
   CM_STAMP(4);
   __syncthreads();                               // every thread is done with the biases stored in the PV slab and the tables
-  zeta_s[threadIdx.x] = zeta_v;
-  phi_s[threadIdx.x] = phi_v;
+  zeta_s[vec_idx(threadIdx.x)] = zeta_v;
+  phi_s[vec_idx(threadIdx.x)] = phi_v;
   if (ok) {
     store_half64(sPV, pv, 1.f);
     fence_proxy_async_smem();
@@ -342,8 +342,8 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   CM_STAMP(8);
   if (ok) {
     const float ecs = __expf(sc->cs[t]);
-    const float* zeta = zeta_s + r * P + wg * 32;
-    const float* phi = phi_s + r * P + wg * 32;
+    const float* zeta = zeta_s + r * VLD + wg * 32;
+    const float* phi = phi_s + r * VLD + wg * 32;
     __nv_bfloat16* yrow = a.y + (((size_t)b * a.S + t0 + t) * a.H + h) * P + wg * 32;
     uint32_t o1[32], o2[32];
     tmem_ld_32x32(tO1 + lane_addr + wg * 32, o1);
@@ -380,7 +380,7 @@ constexpr int local_state_smem() {
 template <int N>
 constexpr int chunk_out_smem() {
   return ((N / 64) * SLAB > 2 * SLAB ? (N / 64) * SLAB : 2 * SLAB) + (N / 64) * SLAB + SLAB + (N > 128 ? N : 128) * 128 +
-         2 * tab_floats<N / 4>() * 4 + R * P * 4 + sizeof(ChunkScalars) + 64 + 1024;
+         2 * tab_floats<N / 4>() * 4 + R * VLD * 4 + sizeof(ChunkScalars) + 64 + 1024;
 }
 
 }  // namespace mimo
