@@ -183,8 +183,8 @@ class NAM56RModel(nn.Module):
         for pos, (key, layer) in enumerate(self.decoder.layers.items()):
             ck = self.training and (self.recompute == "full" or
                                     (self.recompute == "selective" and layer.kind in ("mamba3", "m2rnn")))
-            if pos >= n_layers - self.recompute_keep_last:
-                ck = False
+            if pos >= n_layers - self.recompute_keep_last or getattr(layer, "_graphed", None) is not None:
+                ck = False      # kept layers and CUDA-graph-captured layers hold their activations
             if ck and layer.kind == "dsa" and self.cfg.dsa.indexer_loss_coeff > 0:
                 ck = False      # the indexer loss needs the layer's own graph
             if ck and layer.kind == "dsa":

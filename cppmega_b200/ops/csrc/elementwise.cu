@@ -183,6 +183,103 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const __nv_bfloat16* _
   }
 }
 
+// narrow rows (H = 8 * LPR <= 256): LPR lanes per row, 32 / LPR rows per warp and two such groups in flight, so a warp
+// keeps 2 * 512 bytes of each operand outstanding instead of one half-used row; dw goes through one shared-memory
+// reduction per CTA before the atomics.
+template <int LPR>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_small(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                         const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in,
+                                                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int rows) {
+  constexpr int H = LPR * 8, RPW = 32 / LPR, U = 2;
+  __shared__ float red[8][H];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int l = lane % LPR, sub = lane / LPR;
+  float wf[8], dwacc[8];
+  {
+    const uint4 wv = reinterpret_cast<const uint4*>(w)[l];
+    const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 t = __bfloat1622float2(wb[j]);
+      wf[2 * j] = t.x; wf[2 * j + 1] = t.y;
+      dwacc[2 * j] = 0.f; dwacc[2 * j + 1] = 0.f;
+    }
+  }
+  const long long step = (long long)gridDim.x * 8 * RPW * U;
+  for (long long row0 = ((long long)blockIdx.x * 8 + warp) * RPW * U; row0 < rows; row0 += step) {
+    uint4 xv[U], gv[U];
+    float rs[U];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = row0 + u * RPW + sub;
+      ok[u] = row < rows;
+      if (ok[u]) {
+        xv[u] = reinterpret_cast<const uint4*>(x + row * H)[l];
+        gv[u] = reinterpret_cast<const uint4*>(dy + row * H)[l];
+        rs[u] = rstd_in[row];
+      } else {
+        xv[u] = make_uint4(0, 0, 0, 0); gv[u] = xv[u]; rs[u] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv[u]);
+      const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv[u]);
+      float xh[8], gw[8], dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 xf = __bfloat1622float2(xb[j]), gf = __bfloat1622float2(gb[j]);
+        xh[2 * j] = xf.x * rs[u];            xh[2 * j + 1] = xf.y * rs[u];
+        gw[2 * j] = gf.x * wf[2 * j];        gw[2 * j + 1] = gf.y * wf[2 * j + 1];
+        dwacc[2 * j] += gf.x * xh[2 * j];    dwacc[2 * j + 1] += gf.y * xh[2 * j + 1];
+        dot += gw[2 * j] * xh[2 * j] + gw[2 * j + 1] * xh[2 * j + 1];
+      }
+#pragma unroll
+      for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      dot *= (1.f / H);
+      if (ok[u]) {
+        uint4 o4;
+        uint32_t* op = reinterpret_cast<uint32_t*>(&o4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          op[j] = pack_bf16(rs[u] * (gw[2 * j] - xh[2 * j] * dot), rs[u] * (gw[2 * j + 1] - xh[2 * j + 1] * dot));
+        reinterpret_cast<uint4*>(dx + (row0 + u * RPW + sub) * H)[l] = o4;
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int o = LPR; o < 32; o <<= 1) dwacc[j] += __shfl_xor_sync(0xffffffffu, dwacc[j], o);
+      if (sub == 0) red[warp][l * 8 + j] = dwacc[j];
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      float t = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t += red[k][c];
+      atomicAdd(dw + c, t);
+    }
+  }
+}
+
+template <int TPB, int VPT>
+__device__ __forceinline__ void rms_fetch_row(uint4 (&xn)[VPT], uint4 (&gn)[VPT], float& rn, const __nv_bfloat16* __restrict__ x,
+                                              const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in, int row, int rows,
+                                              int H) {
+  if (row >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+  const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * H);
+  rn = rstd_in[row];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * TPB;
+    if (idx < H / 8) { xn[i] = xr[idx]; gn[i] = gr[idx]; }
+  }
+}
+
 // wide rows: one CTA per row (grid-stride), dw partials for this thread's columns stay in registers
 template <int TPB, int VPT>
 __global__ void __launch_bounds__(TPB) rmsnorm_bwd_wide(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
@@ -197,20 +294,38 @@ __global__ void __launch_bounds__(TPB) rmsnorm_bwd_wide(const __nv_bfloat16* __r
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
+  // the next row's vectors are requested before this row's reduction, so the block-wide sum and the two barriers
+  // of a row overlap the loads of the following one
+  uint4 xn[VPT], gn[VPT];
+  float rn = 0.f;
+  constexpr bool PREFETCH = VPT <= 4;          // wider rows would not fit two rows of operands in registers
+  if constexpr (PREFETCH) rms_fetch_row<TPB, VPT>(xn, gn, rn, x, dy, rstd_in, blockIdx.x, rows, H);
+  uint4 wv[PREFETCH ? VPT : 1];
+  if constexpr (PREFETCH) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * TPB;
+      wv[i] = idx < nvec ? wr[idx] : make_uint4(0, 0, 0, 0);
+    }
+  }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
-    const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * H);
-    const float rstd = rstd_in[row];
+    if constexpr (!PREFETCH) rms_fetch_row<TPB, VPT>(xn, gn, rn, x, dy, rstd_in, row, rows, H);
+    const float rstd = rn;
+    uint4 xc[VPT], gc[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { xc[i] = xn[i]; gc[i] = gn[i]; }
+    if constexpr (PREFETCH) rms_fetch_row<TPB, VPT>(xn, gn, rn, x, dy, rstd_in, row + gridDim.x, rows, H);
     float xh[VPT][8], gw[VPT][8];
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * TPB;
       if (idx < nvec) {
-        const uint4 xv = xr[idx], gv = gr[idx], wv = wr[idx];
-        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
-        const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv);
-        const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xc[i]);
+        const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gc[i]);
+        uint4 wcur;
+        if constexpr (PREFETCH) wcur = wv[i]; else wcur = wr[idx];
+        const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wcur);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float2 xf = __bfloat1622float2(xb[j]), gf = __bfloat1622float2(gb[j]), wf = __bfloat1622float2(wb[j]);
@@ -460,9 +575,14 @@ extern "C" int cm_rmsnorm_bwd(const void* x, const void* w, const void* dy, cons
   grid = grid < cap ? grid : cap;
   auto xp = (const __nv_bfloat16*)x; auto wp = (const __nv_bfloat16*)w; auto gp = (const __nv_bfloat16*)dy;
   auto dxp = (__nv_bfloat16*)dx;
-  if (H <= 32 * 1 * 8) rmsnorm_bwd_kernel<1><<<grid, 256, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
+  const int cap8 = sm_count() * 8;
+  auto small_grid = [&](int rpw) { long long g = ((long long)rows + 8 * rpw * 2 - 1) / (8 * rpw * 2); return (int)(g < cap8 ? g : cap8); };
+  if (H == 64) rmsnorm_bwd_small<8><<<small_grid(4), 256, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows);
+  else if (H == 128) rmsnorm_bwd_small<16><<<small_grid(2), 256, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows);
+  else if (H == 256) rmsnorm_bwd_small<32><<<small_grid(1), 256, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows);
+  else if (H <= 32 * 1 * 8) rmsnorm_bwd_kernel<1><<<grid, 256, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
   else if (H <= 128 * 1 * 8) rmsnorm_bwd_wide<128, 1><<<(rows < cap ? rows : cap), 128, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
-  else if (H <= 128 * 4 * 8) rmsnorm_bwd_wide<128, 4><<<(rows < cap ? rows : cap), 128, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
+  else if (H <= 256 * 2 * 8) rmsnorm_bwd_wide<256, 2><<<(rows < cap ? rows : cap), 256, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
   else if (H <= 256 * 8 * 8) rmsnorm_bwd_wide<256, 8><<<(rows < cap ? rows : cap), 256, 0, s>>>(xp, wp, gp, rstd, dxp, dw, rows, H);
   else return -12;
   return cudaGetLastError() == cudaSuccess ? 0 : -3;

@@ -34,7 +34,10 @@ constexpr int GEMM_THREADS = 192;
 //         operand loads: row block m0 belongs to segment m0 / rows_per_seg = (batch, peer));
 // PEER_C: every output tile is stored into the staging slot `my_slot` of the GPU that owns its rows (the scatter half
 //         of a reduce-scatter fused into the epilogue; the owner sums the slots afterwards).
-enum GemmMode : int { DENSE = 0, GROUPED_ROWS = 1, GROUPED_K = 2, PEER_A = 3, PEER_C = 4 };
+// PEER_KA / PEER_KB: weight gradient of a sequence-parallel linear, C[M,N] (+)= A^T B over the tokens of all ranks; the
+//         MN-major operand A (or B) is the gathered one: its reduction rows [k0, k0 + 64) live in the symmetric buffer
+//         of the peer that owns token segment k0 / rows_per_seg, the other operand is local.
+enum GemmMode : int { DENSE = 0, GROUPED_ROWS = 1, GROUPED_K = 2, PEER_A = 3, PEER_C = 4, PEER_KA = 5, PEER_KB = 6 };
 constexpr int MAX_TP_PEERS = 8;
 struct PeerMaps {
   CUtensorMap m[MAX_TP_PEERS];
@@ -48,6 +51,14 @@ struct PeerParam {
 };
 template <>
 struct PeerParam<PEER_A> {
+  using type = PeerMaps;
+};
+template <>
+struct PeerParam<PEER_KA> {
+  using type = PeerMaps;
+};
+template <>
+struct PeerParam<PEER_KB> {
   using type = PeerMaps;
 };
 
@@ -171,7 +182,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sb = sa + L::A_BYTES;
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           const int k0 = (kb0 + kb) * BK;
-          if constexpr (MODE == PEER_A) {
+          [[maybe_unused]] int peer_k = 0, peer_id = 0;
+          if constexpr (MODE == PEER_KA || MODE == PEER_KB) {
+            const int seg = k0 / args.rows_per_seg;              // a 64-row k block never straddles segments
+            peer_id = seg % args.n_peers;
+            peer_k = (seg / args.n_peers) * args.rows_per_seg + (k0 - seg * args.rows_per_seg);
+          }
+          if constexpr (MODE == PEER_KA) {
+            static_assert(MODE != PEER_KA || A_MN, "the gathered operand of a weight gradient is MN-major");
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sa + c * (BK * 128), &peer_maps.m[peer_id], &full_bar[stage], m0 + c * 64, peer_k);
+          } else if constexpr (MODE == PEER_A) {
             // plain (single-CTA) tiled load from the peer that holds this row segment
             const int seg = m0 / args.rows_per_seg;
             const int src_row = (seg / args.n_peers) * args.rows_per_seg + (m0 - seg * args.rows_per_seg);
@@ -183,7 +205,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int c = 0; c < BM / 64; ++c)                                        // boxes [64 k, 64 m]
               tma_load_2d(sa + c * (BK * 128), &tmA, &full_bar[stage], m0 + c * 64, k0);
           }
-          if (!B_MN) {
+          if constexpr (MODE == PEER_KB) {
+            static_assert(MODE != PEER_KB || B_MN, "the gathered operand of a weight gradient is MN-major");
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (BK * 128), &peer_maps.m[peer_id], &full_bar[stage], n0 + c * 64, peer_k);
+          } else if (!B_MN) {
             if (MODE == GROUPED_ROWS) tma_load_3d(sb, &tmB, &full_bar[stage], k0, n0, e);
             else tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);                    // box [BN rows, 64 k]
           } else {
@@ -542,6 +569,54 @@ extern "C" int cm_gemm_bf16_peer_a(void* const* a_ptrs, int n_peers, int rows_pe
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   if (b_mn) return launch_peer_a<BN, true>(pm, tmB, (__nv_bfloat16*)C, args, tiles, stream);
   return launch_peer_a<BN, false>(pm, tmB, (__nv_bfloat16*)C, args, tiles, stream);
+}
+
+template <typename OutT, bool ACC, int MODE>
+static int launch_peer_k(const PeerMaps& pm, const CUtensorMap& tmA, const CUtensorMap& tmB, OutT* C, const GemmArgs& args,
+                         int total_tiles, cudaStream_t stream) {
+  constexpr int BN = 256;
+  auto kern = gemm_bf16_kernel<BN, true, true, OutT, ACC, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL) != cudaSuccess) return -2;
+    configured = true;
+  }
+  int grid = total_tiles < sm_count() ? total_tiles : sm_count();
+  if (grid <= 0) return 0;
+  kern<<<grid, GEMM_THREADS, SmemLayout<BN>::TOTAL, stream>>>(tmA, tmB, C, args, pm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// all-gather -> weight gradient:  C[M,N] (+)= A^T B with A [T, M] and B [T, N] (T = batch * n_peers * rows_per_seg tokens).
+// peer_is_a: A is the gathered operand, peer_ptrs[p] = peer p's [batch * rows_per_seg, M] shard and `local` is B [T, N];
+// otherwise B is gathered (shards [batch * rows_per_seg, N]) and `local` is A [T, M].
+extern "C" int cm_gemm_bf16_peer_k(void* const* peer_ptrs, int n_peers, int rows_per_seg, int batch, int peer_is_a, const void* local,
+                                   void* C, int M, int N, long long ld_local, long long ldc, int out_fp32, int accumulate, int* err,
+                                   cudaStream_t stream) {
+  if (n_peers <= 0 || n_peers > MAX_TP_PEERS || batch <= 0 || rows_per_seg <= 0) return -10;
+  if (rows_per_seg % BK || (M % 8) || (N % 8) || (ld_local % 8) || (reinterpret_cast<uintptr_t>(local) & 15)) return -10;
+  const int T = batch * n_peers * rows_per_seg;
+  const int peer_w = peer_is_a ? M : N;
+  PeerMaps pm;
+  for (int p = 0; p < n_peers; ++p) {
+    if (reinterpret_cast<uintptr_t>(peer_ptrs[p]) & 15) return -10;
+    int rc = make_tmap_2d_bf16(&pm.m[p], peer_ptrs[p], (uint64_t)batch * rows_per_seg, peer_w, peer_w, 64);
+    if (rc) return rc;
+  }
+  for (int p = n_peers; p < MAX_TP_PEERS; ++p) pm.m[p] = pm.m[0];
+  CUtensorMap tmL;
+  int rc = make_tmap_2d_bf16(&tmL, local, T, peer_is_a ? N : M, ld_local, 64);
+  if (rc) return rc;
+  GemmArgs args{M, N, T, ldc, 1, nullptr, nullptr, err, rows_per_seg, n_peers, 0, 0, {}};
+  const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+  const CUtensorMap& tmA = peer_is_a ? pm.m[0] : tmL;
+  const CUtensorMap& tmB = peer_is_a ? tmL : pm.m[0];
+#define CM_PEER_K(OUT, ACC_)                                                                                         \
+  (peer_is_a ? launch_peer_k<OUT, ACC_, PEER_KA>(pm, tmA, tmB, (OUT*)C, args, tiles, stream)                          \
+             : launch_peer_k<OUT, ACC_, PEER_KB>(pm, tmA, tmB, (OUT*)C, args, tiles, stream))
+  if (out_fp32) return accumulate ? CM_PEER_K(float, true) : CM_PEER_K(float, false);
+  return accumulate ? CM_PEER_K(__nv_bfloat16, true) : CM_PEER_K(__nv_bfloat16, false);
+#undef CM_PEER_K
 }
 
 // GEMM -> scatter:  partial[M, N] = A[M, K] . op(B), every tile stored into slot `my_slot` of the staging buffer of the

@@ -8,9 +8,12 @@
   epilogue stores every output tile into a staging slot on the rank that owns those rows; after a flag barrier the
   owner sums its ``tp`` slots (one pass, fp32 accumulation).
 
-Both need ``(S / tp) % 128 == 0`` (row blocks must not straddle ranks), bf16, and peer access; otherwise the NCCL
-mappings in :mod:`cppmega_b200.parallel.tensor_parallel` are used.  The weight gradient still needs the gathered
-operand as a whole and takes it through one library all-gather.  This is the replacement for the reference's
+* ``ag_wgrad`` (weight gradient of either linear):  ``dW (+)= gather_seq(a)^T b`` or ``a^T gather_seq(b)``.  The reduction
+  runs over the tokens of all ranks; the producer takes every 64-token block of the gathered operand from the peer
+  that owns it (the same staging buffer as ``ag_gemm``; a row-parallel backward stages ``dy`` once for dgrad and wgrad).
+
+All need ``(S / tp) % 128 == 0`` (row blocks must not straddle ranks), bf16, and peer access; otherwise the NCCL
+mappings in :mod:`cppmega_b200.parallel.tensor_parallel` are used.  This is the replacement for the reference's
 Megatron column/row linears with ``--sequence-parallel`` (cppmega/megatron/cppmega_mamba3_tp_mixer.py:217-229,363-375)
 and its TP communication overlap flags (cppmega/recipes/nam56r_nemo_recipe.py:429-443).
 """
@@ -20,7 +23,6 @@ import ctypes
 from typing import Optional
 
 import torch
-import torch.distributed as dist
 
 from ..ops import functional as F_
 from .symm_mem import SymmetricHeap
@@ -36,7 +38,8 @@ def _lib():
         L.cm_gemm_bf16_peer_a.argtypes = [vp, i32, i32, i32, vp, vp, i32, i32, i64, i64, i32, vp, vp]
         L.cm_gemm_bf16_peer_c.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i32, i64, i64, i32, vp, vp]
         L.cm_sum_slots.argtypes = [vp, vp, i32, i64, vp]
-        for n in ("cm_gemm_bf16_peer_a", "cm_gemm_bf16_peer_c", "cm_sum_slots"):
+        L.cm_gemm_bf16_peer_k.argtypes = [vp, i32, i32, i32, i32, vp, vp, i32, i32, i64, i64, i32, i32, vp, vp]
+        for n in ("cm_gemm_bf16_peer_a", "cm_gemm_bf16_peer_c", "cm_sum_slots", "cm_gemm_bf16_peer_k"):
             getattr(L, n).restype = i32
         L._tp_declared = True
     return L
@@ -61,23 +64,53 @@ class FusedTP:
                 and width_in % 8 == 0 and width_out % 8 == 0)
 
     # ---- all-gather -> GEMM ------------------------------------------------------------------
-    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
+    def stage_shard(self, x_local: torch.Tensor) -> torch.Tensor:
+        """Copy this rank's [B, S/tp, W] shard into the symmetric buffer and meet the group; returns the staged view
+        [B * S/tp, W].  Every ``stage_shard`` is closed by one ``release`` after the last kernel that reads the peers."""
+        B, Sl, W = x_local.shape
+        self.ag_epoch += 1
+        src = self.xbuf[:B * Sl * W].view(B * Sl, W)
+        self.heap.wait(FLAG_AG_DONE, self.ag_epoch - 1)          # every rank has finished reading the previous contents
+        src.copy_(x_local.reshape(B * Sl, W))
+        self.heap.barrier(FLAG_AG, self.ag_epoch)                # all shards are in place
+        return src
+
+    def release(self) -> None:
+        self.heap.signal(FLAG_AG_DONE, self.ag_epoch)
+
+    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool, keep_staged: bool = False) -> torch.Tensor:
         """x_local [B, S/tp, K] bf16 -> [B, S, N];  w is [N, K] (b_mn False) or [K, N] (b_mn True)."""
         from ..ops.cuda import err_word, stream_ptr
         B, Sl, K = x_local.shape
         N = w.shape[1] if b_mn else w.shape[0]
-        self.ag_epoch += 1
-        src = self.xbuf[:B * Sl * K].view(B * Sl, K)
-        self.heap.wait(FLAG_AG_DONE, self.ag_epoch - 1)          # every rank has finished reading the previous contents
-        src.copy_(x_local.reshape(B * Sl, K))
-        self.heap.barrier(FLAG_AG, self.ag_epoch)                # all shards are in place
+        src = self.stage_shard(x_local)
         out = torch.empty(B, self.tp * Sl, N, dtype=torch.bfloat16, device=x_local.device)
         rc = _lib().cm_gemm_bf16_peer_a(self.heap.peer_ptr_array(src), self.tp, Sl, B, w.data_ptr(), out.data_ptr(), N, K,
                                         w.stride(0), N, int(b_mn), err_word(self.device).data_ptr(), stream_ptr())
         if rc:
             raise RuntimeError(f"cm_gemm_bf16_peer_a failed ({rc})")
-        self.heap.signal(FLAG_AG_DONE, self.ag_epoch)
+        if not keep_staged:
+            self.release()
         F_.count_launch("tp_ag_gemm")
+        return out
+
+    def ag_wgrad(self, staged: torch.Tensor, batch: int, local: torch.Tensor, peer_is_a: bool, out: Optional[torch.Tensor],
+                 accumulate: bool, out_shape) -> torch.Tensor:
+        """``out [M, N] (+)= A^T B`` over all tokens, where the staged operand ([B * S/tp, W] per rank) is A when
+        ``peer_is_a`` (then ``local`` is B [B * S, N]) and B otherwise (``local`` is A [B * S, M])."""
+        from ..ops.cuda import err_word, stream_ptr
+        M, N = out_shape
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=local.device)
+            accumulate = False
+        assert local.stride(1) == 1 and out.is_contiguous() and out.dtype in (torch.bfloat16, torch.float32)
+        rc = _lib().cm_gemm_bf16_peer_k(self.heap.peer_ptr_array(staged), self.tp, staged.shape[0] // batch, batch, int(peer_is_a),
+                                        local.data_ptr(), out.data_ptr(), M, N, local.stride(0), N,
+                                        int(out.dtype == torch.float32), int(accumulate), err_word(self.device).data_ptr(),
+                                        stream_ptr())
+        if rc:
+            raise RuntimeError(f"cm_gemm_bf16_peer_k failed ({rc})")
+        F_.count_launch("tp_ag_wgrad")
         return out
 
     # ---- GEMM -> reduce-scatter --------------------------------------------------------------
@@ -132,12 +165,6 @@ def current() -> Optional[FusedTP]:
     return _STATE
 
 
-def _gather_seq_nccl(x: torch.Tensor, group) -> torch.Tensor:
-    parts = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
-    dist.all_gather(parts, x.contiguous(), group=group)
-    return torch.cat(parts, dim=1)
-
-
 class ColumnLinearSPFn(torch.autograd.Function):
     """y = gather_seq(x) W^T with W [N_local, K]."""
 
@@ -149,7 +176,7 @@ class ColumnLinearSPFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        from ..ops.cuda import gemm, wgrad_into_main_grad
+        from ..ops.cuda import wgrad_into_main_grad
         x_local, w = ctx.saved_tensors
         tp = ctx.tp
         dy = dy.contiguous()
@@ -157,9 +184,10 @@ class ColumnLinearSPFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = tp.gemm_rs(dy, w, b_mn=True)                                   # [B,S,N_l] . W[N_l,K] -> scatter
         if ctx.needs_input_grad[1]:
-            xg = _gather_seq_nccl(x_local, tp.pc.tp_group)
-            dy2, x2 = dy.reshape(-1, dy.shape[-1]), xg.reshape(-1, xg.shape[-1])
-            dw = wgrad_into_main_grad(w, lambda out, acc: gemm(dy2, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
+            dy2 = dy.reshape(-1, dy.shape[-1])                                   # [T, N_l]: the local operand A
+            staged = tp.stage_shard(x_local)                                           # gather(x) is operand B, read from the peers
+            dw = wgrad_into_main_grad(w, lambda out, acc: tp.ag_wgrad(staged, x_local.shape[0], dy2, False, out, acc, tuple(w.shape)))
+            tp.release()
         return dx, dw, None
 
 
@@ -174,17 +202,25 @@ class RowLinearSPFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy_local):
-        from ..ops.cuda import gemm, wgrad_into_main_grad
+        from ..ops.cuda import wgrad_into_main_grad
         x, w = ctx.saved_tensors
         tp = ctx.tp
         dy_local = dy_local.contiguous()
         dx = dw = None
+        need_dw = ctx.needs_input_grad[1]
+        staged = None
         if ctx.needs_input_grad[0]:
-            dx = tp.ag_gemm(dy_local, w, b_mn=True)                             # gather(dy)[B,S,N] . W[N,K_l]
-        if ctx.needs_input_grad[1]:
-            dyg = _gather_seq_nccl(dy_local, tp.pc.tp_group)
-            dy2, x2 = dyg.reshape(-1, dyg.shape[-1]), x.reshape(-1, x.shape[-1])
-            dw = wgrad_into_main_grad(w, lambda out, acc: gemm(dy2, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
+            dx = tp.ag_gemm(dy_local, w, b_mn=True, keep_staged=need_dw)        # gather(dy)[B,S,N] . W[N,K_l]
+            if need_dw:
+                staged = tp.xbuf[:dy_local.numel()].view(-1, dy_local.shape[-1])
+        if need_dw:
+            if staged is None:
+                staged = tp.stage_shard(dy_local)
+            x2 = x.reshape(-1, x.shape[-1])                                      # [T, K_l]: the local operand B
+            if not x2.is_contiguous():
+                x2 = x2.contiguous()
+            dw = wgrad_into_main_grad(w, lambda out, acc: tp.ag_wgrad(staged, dy_local.shape[0], x2, True, out, acc, tuple(w.shape)))
+            tp.release()                                                         # one staging of dy served dgrad and wgrad
         return dx, dw, None
 
 

@@ -126,6 +126,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--fp32", action="store_true")
     g.add_argument("--fp8-recipe", default=None, choices=["mxfp8", "tensorwise"])
     g.add_argument("--recompute-granularity", default=None, choices=["selective", "full"])
+    g.add_argument("--cuda-graph-scope", nargs="*", default=[],
+                   help="layer kinds captured as CUDA graphs: mamba attn mlp (moe_router / moe_preprocess are accepted and ignored)")
     g.add_argument("--seed", type=int, default=1234)
     g.add_argument("--optimizer", default="adamw", choices=["adam", "adamw", "muon"])
     g.add_argument("--lr", type=float, default=1e-5)
@@ -280,7 +282,7 @@ def configs_from_namespace(ns: argparse.Namespace) -> Tuple[ModelConfig, Paralle
                        recompute=ns.recompute_granularity or "none", seed=ns.seed, log_interval=ns.log_interval,
                        check_finite=not ns.no_check_for_nan_in_loss_and_grad,
                        precision_recipe=ns.fp8_recipe or "bf16", optimizer=ocfg, lr_schedule=sched,
-                       pipeline_schedule=ns.pipeline_schedule)
+                       pipeline_schedule=ns.pipeline_schedule, cuda_graph_scope=tuple(ns.cuda_graph_scope))
     extras = {k: getattr(ns, k) for k in ("train_iters", "data_path", "mock_data", "save", "load", "save_interval",
                                           "log_throughput", "monitor_port", "profile", "profile_step_start",
                                           "profile_step_end", "step_timeout_s")}
@@ -402,6 +404,9 @@ def render_args(mcfg: ModelConfig, pcfg: ParallelConfig, tcfg: TrainConfig, *, t
         kv("--fp8-recipe", tcfg.precision_recipe)
     if tcfg.recompute != "none":
         kv("--recompute-granularity", tcfg.recompute)
+    if tcfg.cuda_graph_scope:
+        a.append("--cuda-graph-scope")
+        a.extend(tcfg.cuda_graph_scope)
     kv("--seed", tcfg.seed)
     o = tcfg.optimizer
     kv("--optimizer", o.optimizer)

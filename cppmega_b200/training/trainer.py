@@ -39,6 +39,7 @@ class TrainConfig:
     log_interval: int = 1
     check_finite: bool = True
     precision_recipe: str = "bf16"               # bf16 | mxfp8 (block-scaled linears)
+    cuda_graph_scope: tuple = ()                 # subset of ("mamba", "attn", "mlp"): layers captured as CUDA graphs
     optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
     lr_schedule: Optional[LRSchedule] = None
     update_router_bias: bool = True
@@ -92,6 +93,11 @@ class Trainer:
             from ..parallel import fused_moe          # permute-fused MoE kernels on local buffers
             self._moe_bufs = fused_moe.attach(self.model, self.pc, device, tokens_per_rank=0)
             self.fused["moe"] = self._moe_bufs is not None
+        self.graphed_layers = 0
+        if train_cfg.cuda_graph_scope and device.type == "cuda" and not self.chunked and self.pc.tp == 1:
+            from ..utils.cuda_graphs import capture_model_layers
+            shape = (train_cfg.micro_batch_size, train_cfg.seq_length, model_cfg.hidden_size)
+            self.graphed_layers = capture_model_layers(self.model, train_cfg.cuda_graph_scope, shape, train_cfg.torch_dtype(), device)
         self.lr_schedule = train_cfg.lr_schedule or LRSchedule(lr=train_cfg.optimizer.lr, style="constant")
         self.step = 0
         dp = self.pc.dp

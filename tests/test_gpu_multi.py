@@ -55,4 +55,5 @@ def test_fused_tensor_parallel_linears_match_nccl():
     for o in outs:
         assert all(v < 2e-2 for v in o["rel"]), outs
         assert o["launches"].get("tp_ag_gemm", 0) == 2 and o["launches"].get("tp_gemm_rs", 0) == 2, outs
+        assert o["launches"].get("tp_ag_wgrad", 0) == 2, outs          # both weight gradients read their gathered operand from peers
         assert "tp_ag_gemm" not in o["base_launches"]

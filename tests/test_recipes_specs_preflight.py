@@ -150,3 +150,19 @@ def test_heartbeat_threads_share_a_store():
     stop.set()
     for t in ts:
         t.join()
+
+
+def test_cuda_graph_scope_parsing_and_argument_round_trip():
+    from cppmega_b200.training.arguments import build_parser, configs_from_namespace
+    from cppmega_b200.utils import cuda_graphs
+    assert cuda_graphs.parse_scope(["mamba", "attn", "moe_router"]) == ("mamba3", "m2rnn", "mla")
+    assert cuda_graphs.parse_scope([]) == ()
+    with pytest.raises(ValueError):
+        cuda_graphs.parse_scope(["everything"])
+    with cuda_graphs.forbid_host_sync():          # no CUDA here: must be a no-op
+        pass
+    ns = build_parser().parse_args(["--cuda-graph-scope", "mamba", "mlp"])
+    tcfg = configs_from_namespace(ns)[2]
+    assert tcfg.cuda_graph_scope == ("mamba", "mlp")
+    import torch.nn as nn
+    assert cuda_graphs.capture_model_layers(nn.Linear(2, 2), ["mamba"], (1, 2, 2), None, "cpu") == 0
