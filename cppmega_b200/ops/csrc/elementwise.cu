@@ -451,6 +451,54 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, 
   }
 }
 
+// four elements per thread: 16-byte accesses to master / m / v, 8- or 16-byte gradient loads, one mask word
+template <typename GradT, typename OutT>
+__global__ void __launch_bounds__(256) adamw_vec4_kernel(float4* __restrict__ master, float4* __restrict__ m, float4* __restrict__ v,
+                                                         const GradT* __restrict__ g, OutT* __restrict__ out,
+                                                         const uchar4* __restrict__ wd_mask, const float* __restrict__ clip,
+                                                         long long n4, float lr, float b1, float b2, float eps, float wd,
+                                                         float inv_bc1, float inv_bc2) {
+  const float cs = clip ? *clip : 1.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float gi[4];
+    if constexpr (sizeof(GradT) == 2) {
+      const uint2 raw = reinterpret_cast<const uint2*>(g)[i];
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      gi[0] = a.x; gi[1] = a.y; gi[2] = b.x; gi[3] = b.y;
+    } else {
+      const float4 raw = reinterpret_cast<const float4*>(g)[i];
+      gi[0] = raw.x; gi[1] = raw.y; gi[2] = raw.z; gi[3] = raw.w;
+    }
+    float4 mm = m[i], vv = v[i], pp = master[i];
+    const uchar4 wm = wd_mask[i];
+    float* mp = reinterpret_cast<float*>(&mm);
+    float* vp = reinterpret_cast<float*>(&vv);
+    float* p = reinterpret_cast<float*>(&pp);
+    const unsigned char wmask[4] = {wm.x, wm.y, wm.z, wm.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gj = gi[j] * cs;
+      mp[j] = b1 * mp[j] + (1.f - b1) * gj;
+      vp[j] = b2 * vp[j] + (1.f - b2) * gj * gj;
+      float upd = (mp[j] * inv_bc1) / (sqrtf(vp[j] * inv_bc2) + eps);
+      if (wmask[j]) upd += wd * p[j];
+      p[j] -= lr * upd;
+    }
+    m[i] = mm;
+    v[i] = vv;
+    master[i] = pp;
+    if constexpr (sizeof(OutT) == 2) {
+      uint2 o;
+      o.x = pack_bf16(p[0], p[1]);
+      o.y = pack_bf16(p[2], p[3]);
+      reinterpret_cast<uint2*>(out)[i] = o;
+    } else {
+      reinterpret_cast<float4*>(out)[i] = pp;
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) sumsq_kernel(const T* __restrict__ g, long long n, float* __restrict__ out) {
   float s = 0.f;
@@ -611,9 +659,35 @@ extern "C" int cm_adamw(float* master, float* m, float* v, const void* g, void* 
                         const float* clip, long long n, float lr, float b1, float b2, float eps, float wd, float bc1,
                         float bc2, int grad_kind, int out_kind, cudaStream_t s) {
   if (n <= 0) return 0;
+  const float i1 = 1.f / bc1, i2 = 1.f / bc2;
+  {
+    // vector body when every array starts on a 16-byte (mask: 4-byte) boundary; the scalar kernel takes the tail
+    const uintptr_t al = reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                         reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out);
+    const long long n4 = n / 4;
+    if (!(al & 15) && !(reinterpret_cast<uintptr_t>(wd_mask) & 3) && n4 > 0) {
+      long long vb = (n4 + 255) / 256;
+      const int vgrid = (int)(vb < (long long)sm_count() * 16 ? vb : (long long)sm_count() * 16);
+#define CM_ADAMW_V4(GT, OT)                                                                                               \
+  adamw_vec4_kernel<GT, OT><<<vgrid, 256, 0, s>>>((float4*)master, (float4*)m, (float4*)v, (const GT*)g, (OT*)out,         \
+                                                  (const uchar4*)wd_mask, clip, n4, lr, b1, b2, eps, wd, i1, i2)
+      if (grad_kind == 0 && out_kind == 1) CM_ADAMW_V4(float, __nv_bfloat16);
+      else if (grad_kind == 1 && out_kind == 1) CM_ADAMW_V4(__nv_bfloat16, __nv_bfloat16);
+      else if (grad_kind == 0 && out_kind == 0) CM_ADAMW_V4(float, float);
+      else CM_ADAMW_V4(__nv_bfloat16, float);
+#undef CM_ADAMW_V4
+      if (cudaGetLastError() != cudaSuccess) return -3;
+      const long long done = n4 * 4;
+      if (done == n) return 0;
+      const size_t gsz = grad_kind == 0 ? 4 : 2, osz = out_kind == 0 ? 4 : 2;
+      master += done; m += done; v += done; wd_mask += done;
+      g = (const char*)g + done * gsz;
+      out = (char*)out + done * osz;
+      n -= done;
+    }
+  }
   long long blocks = (n + 255) / 256;
   int grid = (int)(blocks < (long long)sm_count() * 16 ? blocks : (long long)sm_count() * 16);
-  const float i1 = 1.f / bc1, i2 = 1.f / bc2;
   if (grad_kind == 0 && out_kind == 1)
     adamw_kernel<float, __nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, (const float*)g, (__nv_bfloat16*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2);
   else if (grad_kind == 1 && out_kind == 1)

@@ -109,6 +109,82 @@ __global__ void __launch_bounds__(128) quantize_colwise_kernel(const __nv_bfloat
   if (sw) sw[swizzled_index(c, (int)blockIdx.y, (int)((rows / 32 + 3) / 4))] = sb;
 }
 
+// Both orientations from one read of x: CTA = tile of 32 rows x 256 columns.  Phase 1 is the row-wise kernel (8 values
+// per thread, 4 threads per block) and parks the values as fp32 in shared memory; phase 2 walks the columns of the tile.
+// The tile is stored column-permuted (logical column 8 v + j at physical column 32 j + v) with a row stride of 257 floats,
+// which makes both the phase-1 stores and the phase-2 column reads bank-conflict free.
+__global__ void __launch_bounds__(256) quantize_both_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ pay_r,
+                                                            uint8_t* __restrict__ sc_r, uint8_t* __restrict__ sw_r,
+                                                            uint8_t* __restrict__ pay_t, uint8_t* __restrict__ sc_t,
+                                                            uint8_t* __restrict__ sw_t, long long rows, int cols) {
+  __shared__ float tile[32][257];
+  const long long r0 = (long long)blockIdx.y * 32;
+  const int c0 = blockIdx.x * 256;
+  const int kb_row = cols / 32, kbt_row = (kb_row + 3) / 4;
+  const int kb_col = (int)(rows / 32), kbt_col = (kb_col + 3) / 4;
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int row = it * 8 + (threadIdx.x >> 5);
+    const int col = c0 + lane * 8;
+    const bool valid = col < cols;
+    float f[8];
+    float am = 0.f;
+    if (valid) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(r0 + row) * cols + col);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = __bfloat1622float2(b[j]);
+        f[2 * j] = t.x; f[2 * j + 1] = t.y;
+        am = fmaxf(am, fmaxf(fabsf(t.x), fabsf(t.y)));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) tile[row][j * 32 + lane] = f[j];
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+    if (valid) {
+      const uint8_t sb = e8m0_from_amax(am);
+      const float mult = exp2f(127.f - (float)sb);
+      uint2 o;
+      o.x = (uint32_t)to_e4m3x2(f[0] * mult, f[1] * mult) | ((uint32_t)to_e4m3x2(f[2] * mult, f[3] * mult) << 16);
+      o.y = (uint32_t)to_e4m3x2(f[4] * mult, f[5] * mult) | ((uint32_t)to_e4m3x2(f[6] * mult, f[7] * mult) << 16);
+      *reinterpret_cast<uint2*>(pay_r + (size_t)(r0 + row) * cols + col) = o;
+      if ((lane & 3) == 0) {
+        const int kb = col >> 5;
+        sc_r[(size_t)(r0 + row) * kb_row + kb] = sb;
+        if (sw_r) sw_r[swizzled_index(r0 + row, kb, kbt_row)] = sb;
+      }
+    }
+  }
+  __syncthreads();
+  const int p = threadIdx.x;                                // physical column of the tile
+  const int col = c0 + (p & 31) * 8 + (p >> 5);             // its logical column
+  if (col >= cols) return;
+  float f[32];
+  float am = 0.f;
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    f[r] = tile[r][p];
+    am = fmaxf(am, fabsf(f[r]));
+  }
+  const uint8_t sb = e8m0_from_amax(am);
+  const float mult = exp2f(127.f - (float)sb);
+  uint32_t w[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    w[q] = (uint32_t)to_e4m3x2(f[4 * q] * mult, f[4 * q + 1] * mult) | ((uint32_t)to_e4m3x2(f[4 * q + 2] * mult, f[4 * q + 3] * mult) << 16);
+  uint4* dst = reinterpret_cast<uint4*>(pay_t + (size_t)col * rows + r0);
+  dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  sc_t[(size_t)col * kb_col + blockIdx.y] = sb;
+  if (sw_t) sw_t[swizzled_index(col, (int)blockIdx.y, kbt_col)] = sb;
+}
+
 __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ payload, const uint8_t* __restrict__ scales,
                                                          __nv_bfloat16* __restrict__ out, long long n) {
   const long long nvec = n / 8;
@@ -168,6 +244,18 @@ extern "C" int cm_mxfp8_quantize_colwise(const void* x, void* payload_t, void* s
   if (rows % 32) return -10;
   dim3 grid((cols + 127) / 128, (unsigned)(rows / 32));
   quantize_colwise_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)payload_t, (uint8_t*)scales_t, (uint8_t*)swizzled, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// x [rows, cols] bf16 (rows % 32 == 0, cols % 32 == 0) -> row-wise payload / scales and the transposed column-wise pair in
+// one pass; the swizzled scale outputs are optional
+extern "C" int cm_mxfp8_quantize_both(const void* x, void* pay_r, void* sc_r, void* sw_r, void* pay_t, void* sc_t, void* sw_t,
+                                      long long rows, int cols, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if ((rows % 32) || (cols % 32)) return -10;
+  dim3 grid((cols + 255) / 256, (unsigned)(rows / 32));
+  quantize_both_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)pay_r, (uint8_t*)sc_r, (uint8_t*)sw_r, (uint8_t*)pay_t,
+                                           (uint8_t*)sc_t, (uint8_t*)sw_t, rows, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

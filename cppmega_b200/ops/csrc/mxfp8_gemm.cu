@@ -222,11 +222,23 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             uint4* dst = reinterpret_cast<uint4*>(crow + c * 32);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[c][v * 8 + j]);
+              if (ACC) {
+                const uint4 old = dst[v];
+                const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 t = __bfloat1622float2(ob[j]);
+                  f[2 * j] += t.x; f[2 * j + 1] += t.y;
+                }
+              }
               uint4 o;
-              o.x = pack_bf16(__uint_as_float(r[c][v * 8 + 0]), __uint_as_float(r[c][v * 8 + 1]));
-              o.y = pack_bf16(__uint_as_float(r[c][v * 8 + 2]), __uint_as_float(r[c][v * 8 + 3]));
-              o.z = pack_bf16(__uint_as_float(r[c][v * 8 + 4]), __uint_as_float(r[c][v * 8 + 5]));
-              o.w = pack_bf16(__uint_as_float(r[c][v * 8 + 6]), __uint_as_float(r[c][v * 8 + 7]));
+              o.x = pack_bf16(f[0], f[1]);
+              o.y = pack_bf16(f[2], f[3]);
+              o.z = pack_bf16(f[4], f[5]);
+              o.w = pack_bf16(f[6], f[7]);
               dst[v] = o;
             }
           } else {
@@ -301,19 +313,19 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, const
 }  // namespace cm
 
 // A [M,K] / B [N,K] E4M3 bytes (row strides lda / ldb bytes, multiples of 16); sfa / sfb swizzled scale tiles of
-// ceil(rows/128) x ceil(K/128) x 512 bytes; C [M,N] bf16 (out_fp32 = 0) or fp32, `accumulate` adds to an fp32 C.
+// ceil(rows/128) x ceil(K/128) x 512 bytes; C [M,N] bf16 (out_fp32 = 0) or fp32, `accumulate` adds to C.
 extern "C" int cm_mxfp8_gemm(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, long long lda,
                              long long ldb, long long ldc, int out_fp32, int accumulate, int* err, cudaStream_t s) {
   using namespace cm;
   using namespace cm::mxg;
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K % 32) || (lda % 16) || (ldb % 16) || (accumulate && !out_fp32)) return -10;
+  if (K <= 0 || (K % 32) || (lda % 16) || (ldb % 16)) return -10;
   if ((reinterpret_cast<uintptr_t>(sfa) | reinterpret_cast<uintptr_t>(sfb) | reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15)
     return -11;
   CUtensorMap tmA, tmB;
   if (int rc = make_tmap_u8(&tmA, A, M, K, lda, BM)) return 100 + rc;
   if (int rc = make_tmap_u8(&tmB, B, N, K, ldb, BN)) return 100 + rc;
   Args args{M, N, K, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, err};
-  if (!out_fp32) return launch<__nv_bfloat16, false>(tmA, tmB, C, args, s);
+  if (!out_fp32) return accumulate ? launch<__nv_bfloat16, true>(tmA, tmB, C, args, s) : launch<__nv_bfloat16, false>(tmA, tmB, C, args, s);
   return accumulate ? launch<float, true>(tmA, tmB, C, args, s) : launch<float, false>(tmA, tmB, C, args, s);
 }

@@ -49,9 +49,10 @@ def _lib():
         L.cm_mxfp8_quantize_colwise.argtypes = [vp, vp, vp, vp, i64, i32, vp]
         L.cm_mxfp8_dequantize.argtypes = [vp, vp, vp, i64, vp]
         L.cm_mxfp8_swizzle_scales.argtypes = [vp, vp, i64, i32, vp]
+        L.cm_mxfp8_quantize_both.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i32, vp]
         L.cm_mxfp8_gemm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, vp, vp]
         for n in ("cm_mxfp8_quantize_rowwise", "cm_mxfp8_quantize_colwise", "cm_mxfp8_dequantize", "cm_mxfp8_swizzle_scales",
-                  "cm_mxfp8_gemm"):
+                  "cm_mxfp8_gemm", "cm_mxfp8_quantize_both"):
             getattr(L, n).restype = i32
         L._mx_declared = True
     return L
@@ -100,6 +101,26 @@ def quantize_colwise(x: torch.Tensor, for_gemm: bool = False) -> Mxfp8Tensor:
     return Mxfp8Tensor(pay, sc, (cols, rows), sw)
 
 
+def quantize_both(x: torch.Tensor, for_gemm: bool = True):
+    """Row-wise and transposed column-wise MXFP8 copies of a 2-D bf16 tensor from one read of it."""
+    from . import stream_ptr
+    assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.shape[0] % 32 == 0 and x.shape[1] % 32 == 0
+    x = x.contiguous()
+    rows, cols = x.shape
+    dev = x.device
+    pay_r = torch.empty(rows, cols, dtype=torch.uint8, device=dev)
+    sc_r = torch.empty(rows, cols // 32, dtype=torch.uint8, device=dev)
+    pay_t = torch.empty(cols, rows, dtype=torch.uint8, device=dev)
+    sc_t = torch.empty(cols, rows // 32, dtype=torch.uint8, device=dev)
+    sw_r = _swizzled_buffer(rows, cols // 32, dev) if for_gemm else None
+    sw_t = _swizzled_buffer(cols, rows // 32, dev) if for_gemm else None
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    _check(_lib().cm_mxfp8_quantize_both(x.data_ptr(), pay_r.data_ptr(), sc_r.data_ptr(), ptr(sw_r), pay_t.data_ptr(),
+                                         sc_t.data_ptr(), ptr(sw_t), rows, cols, stream_ptr()), "cm_mxfp8_quantize_both")
+    F_.count_launch("mxfp8_quantize")
+    return Mxfp8Tensor(pay_r, sc_r, (rows, cols), sw_r), Mxfp8Tensor(pay_t, sc_t, (cols, rows), sw_t)
+
+
 def dequantize(t: Mxfp8Tensor) -> torch.Tensor:
     from . import stream_ptr
     out = torch.empty(t.shape, dtype=torch.bfloat16, device=t.payload.device)
@@ -129,7 +150,6 @@ def gemm_mxfp8(a: Mxfp8Tensor, b: Mxfp8Tensor, out: torch.Tensor = None, accumul
         assert not accumulate
         out = torch.empty(M, N, dtype=out_dtype, device=a.payload.device)
     assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
-    assert out.dtype == torch.float32 or not accumulate
     sfa, sfb = a.swizzled(), b.swizzled()
     _check(_lib().cm_mxfp8_gemm(a.payload.data_ptr(), sfa.data_ptr(), b.payload.data_ptr(), sfb.data_ptr(), out.data_ptr(), M, N, K,
                                 a.payload.stride(0), b.payload.stride(0), out.stride(0), int(out.dtype == torch.float32),
@@ -165,10 +185,11 @@ class Mxfp8LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
         x2 = x.reshape(-1, x.shape[-1])
-        xq = quantize_rowwise(x2, True)                 # along K
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        xq, x_t = quantize_both(x2)                     # along K, and [K, T] along tokens: the wgrad operand (1 byte/value)
         wq = quantize_weight(w, colwise=False)          # along K
         y = gemm_mxfp8(xq, wq)
-        x_t = quantize_colwise(x2, True)                # [K, T] along tokens: the wgrad operand, kept in 1 byte/value
         ctx.save_for_backward(x_t.payload, x_t.scales, x_t._swizzled, w)
         ctx.xshape = x.shape
         return y.view(*x.shape[:-1], w.shape[0])
@@ -180,25 +201,25 @@ class Mxfp8LinearFn(torch.autograd.Function):
         K, T = xt_pay.shape
         dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
         dx = dw = None
+        dyq = dy_t = None
+        if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
+            dyq, dy_t = quantize_both(dy2)                               # one read of dy for both products
         if ctx.needs_input_grad[0]:
-            dyq = quantize_rowwise(dy2, True)                            # along N
+            dyq = dyq if dyq is not None else quantize_rowwise(dy2, True)   # along N
             w_t = quantize_weight(w, colwise=True)                       # [K, N] along N
             dx = gemm_mxfp8(dyq, w_t).view(ctx.xshape)                   # [T,N] x [K,N]^T
         if ctx.needs_input_grad[1]:
-            dy_t = quantize_colwise(dy2, True)                           # [N, T] along tokens
+            dy_t = dy_t if dy_t is not None else quantize_colwise(dy2, True)   # [N, T] along tokens
             x_t = Mxfp8Tensor(xt_pay, xt_sc, (K, T), xt_sw)              # [K, T]
             dw = wgrad_into_main_grad(w, lambda out, acc: _wgrad(dy_t, x_t, out, acc))
         return dx, dw
 
 
 def _wgrad(dy_t: Mxfp8Tensor, x_t: Mxfp8Tensor, out, accumulate: bool):
-    """dW [N,K] = dy^T x over tokens, written or accumulated into ``out`` (fp32 main grad) or returned as bf16."""
+    """dW [N,K] = dy^T x over tokens, written or accumulated into ``out`` (fp32 or bf16 main grad) or returned as bf16."""
     if out is None:
         return gemm_mxfp8(dy_t, x_t)
-    if out.dtype == torch.float32:
-        return gemm_mxfp8(dy_t, x_t, out=out, accumulate=accumulate)
-    tmp = gemm_mxfp8(dy_t, x_t)
-    return out.add_(tmp) if accumulate else out.copy_(tmp)
+    return gemm_mxfp8(dy_t, x_t, out=out, accumulate=accumulate)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor):

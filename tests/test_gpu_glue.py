@@ -162,6 +162,14 @@ def test_mxfp8_quantize_kernels_match_reference():
     assert ((deq.float() - x.float()).abs() <= 0.07 * x.float().abs() + 1e-6).all()       # 3 mantissa bits
     sw = mxfp8.swizzle_scales(r.scales)
     assert torch.equal(sw, ref.swizzle_scales_128x4(r.scales))
+    both_r, both_c = mxfp8.quantize_both(x)
+    assert torch.equal(both_r.payload, r.payload) and torch.equal(both_r.scales, r.scales)
+    assert torch.equal(both_c.payload, c.payload) and torch.equal(both_c.scales, c.scales)
+    assert torch.equal(both_r.swizzled(), sw) and torch.equal(both_c.swizzled(), ref.swizzle_scales_128x4(c.scales))
+    wide = (torch.randn(64, 544, device="cuda") * 3).bfloat16()          # 2 full column tiles + a 32-wide tail
+    wr, wc = mxfp8.quantize_both(wide)
+    assert torch.equal(wr.payload, mxfp8.quantize_rowwise(wide).payload) and torch.equal(wc.payload, mxfp8.quantize_colwise(wide).payload)
+    assert torch.equal(wc.scales, mxfp8.quantize_colwise(wide).scales)
     # the quantise kernels can write the tile order themselves
     assert torch.equal(mxfp8.quantize_rowwise(x, True).swizzled(), sw)
     assert torch.equal(mxfp8.quantize_colwise(x, True).swizzled(), ref.swizzle_scales_128x4(c.scales))
@@ -184,6 +192,9 @@ def test_mxfp8_block_scaled_gemm(M, N, K):
     acc = torch.randn(M, N, device="cuda")
     got32 = mxfp8.gemm_mxfp8(aq, bq, out=acc.clone(), accumulate=True)
     assert _rel(got32, want + acc) < 1e-5
+    acc16 = torch.randn(M, N, device="cuda").bfloat16()
+    got16 = mxfp8.gemm_mxfp8(aq, bq, out=acc16.clone(), accumulate=True)
+    assert _rel(got16, want + acc16.float()) < 5e-3
     torch.testing.assert_close(mxfp8.gemm_mxfp8(aq, bq, out_dtype=torch.float32), want, rtol=1e-4, atol=1e-3 * want.abs().max().item())
 
 
