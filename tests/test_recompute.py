@@ -77,3 +77,30 @@ def test_model_gradients_identical_with_and_without_recompute():
     for n in grads[0]:         # same mathematics, different fp32 accumulation order
         a, b = grads[0][n], grads[1][n]
         assert ((a - b).norm() / (a.norm() + 1e-12)).item() < 2e-3, n
+
+
+def test_m2rnn_chunked_reference_matches_stepwise_definition():
+    import torch
+    from cppmega_b200.ops import reference as ref
+    from cppmega_b200.ops.m2rnn_chunk_ref import m2rnn_scan_chunked
+    torch.manual_seed(0)
+    B, S, H, K, V = 2, 37, 3, 8, 4
+    mk = lambda *s: torch.randn(*s, dtype=torch.float64).mul(0.5).requires_grad_()
+    q, k, v = mk(B, S, 1, K), mk(B, S, 1, K), mk(B, S, H, V)
+    W = (torch.eye(V, dtype=torch.float64).repeat(H, 1, 1) + 0.1 * torch.randn(H, V, V, dtype=torch.float64)).requires_grad_()
+    f = torch.rand(B, S, H, dtype=torch.float64).requires_grad_()
+    h0 = mk(B, H, K, V)
+    gy, gh = torch.randn(B, S, H, V, dtype=torch.float64), torch.randn(B, H, K, V, dtype=torch.float64)
+
+    def run(fn, with_h0):
+        ins = [t.detach().clone().requires_grad_() for t in (q, k, v, W, f)] + ([h0.detach().clone().requires_grad_()] if with_h0 else [])
+        y, h = fn(*ins)
+        ((y.double() * gy).sum() + (h.double() * gh).sum()).backward()
+        return y, h, [t.grad for t in ins]
+
+    for with_h0 in (False, True):
+        y1, h1, g1 = run(ref.m2rnn_scan, with_h0)
+        y2, h2, g2 = run(lambda *a: m2rnn_scan_chunked(*a, chunk=8), with_h0)
+        assert torch.allclose(y1.double(), y2.double(), atol=1e-5) and torch.allclose(h1.double(), h2.double(), atol=1e-5)
+        for a, b in zip(g1, g2):
+            assert torch.allclose(a.double(), b.double(), atol=1e-4), (a - b).abs().max()
