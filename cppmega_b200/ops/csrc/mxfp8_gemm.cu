@@ -15,6 +15,11 @@
 //   warps 2..9  epilogue: warp w drains lane quarter w%4, column half (w-2)/4 of the accumulator into 128 registers,
 //               hands the accumulator back at once and only then converts and stores, so the next tile's main loop
 //               runs under the stores although only one 256-column accumulator fits beside the scale columns.
+// Grouped modes (experts): GROUPED_ROWS takes the expert of every 128-row tile of A / C from tile_expert[] (-1 = unused
+// tile) and addresses B as one [rows, K] matrix in which expert e starts b_row_e rows further down (forward: the
+// stacked [E*N, K] weights) or b_k_e columns further right (dgrad: the stacked transposed weights [N, E*K]);
+// GROUPED_K reduces over per-expert ranges of the shared K axis (token rows, multiples of 128) into a stack [E, M, N]
+// (expert weight gradients from the token-transposed operands).
 // The other products of a linear layer use the same kernel on operands quantised along their own reduction
 // dimension and stored transposed (dgrad: dy along N with W^T; wgrad: dy^T and x^T along tokens), so no
 // MN-major FP8 path is needed.  This is the sm_100 counterpart of the reference's CUTLASS / FlashInfer MXFP8 GEMM
@@ -35,12 +40,26 @@ constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;                   // 256 accumulator + 4 SFA + 8 SFB, rounded up to a power of two
 constexpr int SFA_COL = 256, SFB_COL = 260;
 
+enum Mode : int { DENSE = 0, GROUPED_ROWS = 1, GROUPED_K = 2 };
+
 struct Args {
-  int M, N, K;
+  int M, N, K;               // GROUPED_ROWS: M = allocated rows; GROUPED_K: M, N per expert, K = total reduction length
   long long ldc;
   const uint8_t* sfa;
   const uint8_t* sfb;
   int* err;
+  int sfa_nkt, sfb_nkt;      // k tiles per row tile in the two scale buffers
+  const int* tile_expert;    // GROUPED_ROWS: [M / 128]
+  const int* seg_offsets;    // GROUPED_K: [E + 1], multiples of 128
+  int num_experts;
+  int b_row_e, b_k_e;        // GROUPED_ROWS: row / column offset of expert e in B is e * b_row_e / e * b_k_e (multiples of 128)
+};
+
+struct Tile {
+  int mt, nt, e;
+  int kt0, nkt;              // k tiles [kt0, kt0 + nkt) of A (and of B, shifted by b_kt0)
+  int b_row0, b_kt0;         // first row of the B tile, first k tile of B
+  bool two;                  // the second 128-row scale tile of B exists
 };
 
 // no-swizzle descriptor of a 32 x 16-byte scale tile: 8-row core matrices 128 bytes apart
@@ -75,7 +94,7 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
                : "memory");
 }
 
-template <typename OutT, bool ACC>
+template <typename OutT, bool ACC, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ C, const Args args) {
   extern __shared__ uint8_t smem_raw[];
@@ -95,8 +114,9 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int lane = threadIdx.x & 31;
   const int tiles_n = (args.N + BN - 1) / BN;
   const int tiles_m = (args.M + BM - 1) / BM;
-  const int total_tiles = tiles_m * tiles_n;
-  const int nkt = (args.K + BK - 1) / BK;
+  const int tiles_per_problem = tiles_m * tiles_n;
+  const int total_tiles = MODE == GROUPED_K ? tiles_per_problem * args.num_experts : tiles_per_problem;
+  const int dense_nkt = (args.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -117,14 +137,41 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto decode = [&](int tile, int& mt, int& nt) {
+  auto decode = [&](int tile) {
+    Tile t;
+    int local = tile;
+    t.e = 0;
+    if (MODE == GROUPED_K) {
+      t.e = tile / tiles_per_problem;
+      local = tile - t.e * tiles_per_problem;
+    }
     const int band = 8;                       // bands of 8 row tiles share B tiles in L2
     const int band_tiles = band * tiles_n;
-    const int b = tile / band_tiles;
-    const int r = tile - b * band_tiles;
+    const int b = local / band_tiles;
+    const int r = local - b * band_tiles;
     const int rows_in_band = min(band, tiles_m - b * band);
-    mt = b * band + r % rows_in_band;
-    nt = r / rows_in_band;
+    t.mt = b * band + r % rows_in_band;
+    t.nt = r / rows_in_band;
+    t.kt0 = 0;
+    t.nkt = dense_nkt;
+    t.b_row0 = t.nt * BN;
+    t.b_kt0 = 0;
+    if (MODE == GROUPED_ROWS) {
+      t.e = args.tile_expert[t.mt];
+      if (t.e < 0) t.nkt = 0;
+      else {
+        t.b_row0 += t.e * args.b_row_e;
+        t.b_kt0 = t.e * (args.b_k_e / BK);
+      }
+    }
+    if (MODE == GROUPED_K) {
+      const int s0 = args.seg_offsets[t.e], s1 = args.seg_offsets[t.e + 1];
+      t.kt0 = s0 / BK;
+      t.nkt = (s1 - s0) / BK;
+      t.b_kt0 = t.kt0;
+    }
+    t.two = t.nt * BN + 128 < args.N;
+    return t;
   };
 
   if (warp == 0) {
@@ -134,22 +181,20 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int mt, nt;
-        decode(tile, mt, nt);
-        const bool two = nt * BN + 128 < args.N;                 // does the second 128-row scale tile of B exist?
-        const uint8_t* sfa = args.sfa + (size_t)mt * nkt * 512;
-        const uint8_t* sfb0 = args.sfb + (size_t)(2 * nt) * nkt * 512;
-        const uint8_t* sfb1 = sfb0 + (size_t)nkt * 512;
-        for (int kt = 0; kt < nkt; ++kt) {
+        const Tile t = decode(tile);
+        const uint8_t* sfa = args.sfa + ((size_t)t.mt * args.sfa_nkt + t.kt0) * 512;
+        const uint8_t* sfb0 = args.sfb + ((size_t)(t.b_row0 / 128) * args.sfb_nkt + t.b_kt0) * 512;
+        const uint8_t* sfb1 = sfb0 + (size_t)args.sfb_nkt * 512;
+        for (int kt = 0; kt < t.nkt; ++kt) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.err, ERR_WAIT_EMPTY);
           if (!ok) break;
-          mbar_expect_tx(&full_bar[stage], A_BYTES + B_BYTES + SFA_BYTES + (two ? 1024 : 512));
-          tma_load_2d(sA + stage * A_BYTES, &tmA, &full_bar[stage], kt * BK, mt * BM);
-          tma_load_2d(sB + stage * B_BYTES, &tmB, &full_bar[stage], kt * BK, nt * BN);
+          mbar_expect_tx(&full_bar[stage], A_BYTES + B_BYTES + SFA_BYTES + (t.two ? 1024 : 512));
+          tma_load_2d(sA + stage * A_BYTES, &tmA, &full_bar[stage], (t.kt0 + kt) * BK, t.mt * BM);
+          tma_load_2d(sB + stage * B_BYTES, &tmB, &full_bar[stage], (t.b_kt0 + kt) * BK, t.b_row0);
           uint8_t* sf = sSF + stage * (SFA_BYTES + SFB_BYTES);
           bulk_load(sf, sfa + (size_t)kt * 512, 512, &full_bar[stage]);
           bulk_load(sf + 512, sfb0 + (size_t)kt * 512, 512, &full_bar[stage]);
-          if (two) bulk_load(sf + 1024, sfb1 + (size_t)kt * 512, 512, &full_bar[stage]);
+          if (t.two) bulk_load(sf + 1024, sfb1 + (size_t)kt * 512, 512, &full_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -160,13 +205,13 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t stage = 0, phase = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int mt, nt;
-        decode(tile, mt, nt);
-        const bool two = nt * BN + 128 < args.N;
+        const Tile t = decode(tile);
+        if (t.nkt == 0) continue;
+        const bool two = t.two;
         ok = mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, args.err, ERR_WAIT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
-        for (int kt = 0; kt < nkt; ++kt) {
+        for (int kt = 0; kt < t.nkt; ++kt) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, args.err, ERR_WAIT_FULL);
           if (!ok) break;
           tc_fence_after();
@@ -196,8 +241,19 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      int mt, nt;
-      decode(tile, mt, nt);
+      const Tile t = decode(tile);
+      const int mt = t.mt, nt = t.nt;
+      if (t.nkt == 0) {
+        if (MODE == GROUPED_K && !ACC) {           // an expert without tokens: its gradient block is zero
+          const int row = mt * BM + q * 32 + lane;
+          const int col0 = nt * BN + half * 128;
+          if (row < args.M) {
+            OutT* crow = C + (long long)t.e * args.M * args.ldc + (long long)row * args.ldc;
+            for (int c = col0; c < min(col0 + 128, args.N); ++c) crow[c] = OutT(0.f);
+          }
+        }
+        continue;
+      }
       ok = mbar_wait(tmem_full, acc_phase, abort_flag, args.err, ERR_WAIT_TMEM_FULL);
       if (!ok) break;
       acc_phase ^= 1;
@@ -214,7 +270,7 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int row = mt * BM + q * 32 + lane;
       const int col0 = nt * BN + half * 128;
       if (row >= args.M || col0 >= args.N) continue;
-      OutT* crow = C + (long long)row * args.ldc + col0;
+      OutT* crow = C + (MODE == GROUPED_K ? (long long)t.e * args.M * args.ldc : 0ll) + (long long)row * args.ldc + col0;
       if (col0 + 128 <= args.N && (args.ldc % 8) == 0) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -295,16 +351,17 @@ static int make_tmap_u8(CUtensorMap* out, const void* base, uint64_t rows, uint6
   return r == CUDA_SUCCESS ? 0 : int(r);
 }
 
-template <typename OutT, bool ACC>
+template <typename OutT, bool ACC, int MODE = DENSE>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, const Args& args, cudaStream_t s) {
-  auto kern = mxfp8_gemm_kernel<OutT, ACC>;
+  auto kern = mxfp8_gemm_kernel<OutT, ACC, MODE>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess) return -2;
     attr_set = true;
   }
-  const int tiles = ((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN);
+  const int tiles = ((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN) * (MODE == GROUPED_K ? args.num_experts : 1);
   const int grid = tiles < sm_count() ? tiles : sm_count();
+  if (grid <= 0) return 0;
   kern<<<grid, THREADS, SMEM_TOTAL, s>>>(tmA, tmB, reinterpret_cast<OutT*>(C), args);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -325,7 +382,45 @@ extern "C" int cm_mxfp8_gemm(const void* A, const void* sfa, const void* B, cons
   CUtensorMap tmA, tmB;
   if (int rc = make_tmap_u8(&tmA, A, M, K, lda, BM)) return 100 + rc;
   if (int rc = make_tmap_u8(&tmB, B, N, K, ldb, BN)) return 100 + rc;
-  Args args{M, N, K, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, err};
+  const int nkt = (K + BK - 1) / BK;
+  Args args{M, N, K, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, err, nkt, nkt, nullptr, nullptr, 1, 0, 0};
   if (!out_fp32) return accumulate ? launch<__nv_bfloat16, true>(tmA, tmB, C, args, s) : launch<__nv_bfloat16, false>(tmA, tmB, C, args, s);
   return accumulate ? launch<float, true>(tmA, tmB, C, args, s) : launch<float, false>(tmA, tmB, C, args, s);
+}
+
+// Expert products on the 128-row-aligned, expert-sorted token layout.  A [rows, K] E4M3 with scales sfa; tile_expert[rows/128].
+//   b_kmode = 0 (forward):  B is the stacked weight [E * N, K]            -> C[r, :N] = A[r] . W[e(r)]^T
+//   b_kmode = 1 (dgrad):    B is the stacked transposed weight [N, E * K] -> C[r, :N] = A[r] . Wt[:, e(r) K : (e(r)+1) K]^T
+// N % 128 == 0 (forward) / K % 128 == 0 (dgrad) keep the scale tiles of different experts apart.
+extern "C" int cm_mxfp8_grouped_rows(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int rows, int N, int K,
+                                     int num_experts, int b_kmode, const int* tile_expert, int* err, cudaStream_t s) {
+  using namespace cm;
+  using namespace cm::mxg;
+  if (rows <= 0 || N <= 0) return 0;
+  if ((rows % 128) || (K % 32) || (K % 16) || (b_kmode ? (K % 128) : (N % 128))) return -10;
+  CUtensorMap tmA, tmB;
+  if (int rc = make_tmap_u8(&tmA, A, rows, K, K, BM)) return 100 + rc;
+  const long long b_rows = b_kmode ? N : (long long)num_experts * N;
+  const long long b_cols = b_kmode ? (long long)num_experts * K : K;
+  if (int rc = make_tmap_u8(&tmB, B, b_rows, b_cols, b_cols, BN)) return 100 + rc;
+  Args args{rows, N, K, N, (const uint8_t*)sfa, (const uint8_t*)sfb, err, (K + BK - 1) / BK, (int)((b_cols + BK - 1) / BK),
+            tile_expert, nullptr, num_experts, b_kmode ? 0 : N, b_kmode ? K : 0};
+  return launch<__nv_bfloat16, false, GROUPED_ROWS>(tmA, tmB, C, args, s);
+}
+
+// Expert weight gradients: C[e] [M, N] (+)= At[:, seg_e] . Bt[:, seg_e]^T with At [M, R], Bt [N, R] the token-transposed
+// E4M3 operands (R = allocated rows, a multiple of 128) and seg_offsets[E + 1] the experts' row ranges.
+extern "C" int cm_mxfp8_grouped_k(const void* At, const void* sfa, const void* Bt, const void* sfb, void* C, int R, int M, int N,
+                                  int num_experts, const int* seg_offsets, int out_fp32, int accumulate, int* err, cudaStream_t s) {
+  using namespace cm;
+  using namespace cm::mxg;
+  if (M <= 0 || N <= 0 || num_experts <= 0) return 0;
+  if (R <= 0 || (R % 128)) return -10;
+  CUtensorMap tmA, tmB;
+  if (int rc = make_tmap_u8(&tmA, At, M, R, R, BM)) return 100 + rc;
+  if (int rc = make_tmap_u8(&tmB, Bt, N, R, R, BN)) return 100 + rc;
+  Args args{M, N, R, N, (const uint8_t*)sfa, (const uint8_t*)sfb, err, R / BK, R / BK, nullptr, seg_offsets, num_experts, 0, 0};
+  if (!out_fp32)
+    return accumulate ? launch<__nv_bfloat16, true, GROUPED_K>(tmA, tmB, C, args, s) : launch<__nv_bfloat16, false, GROUPED_K>(tmA, tmB, C, args, s);
+  return accumulate ? launch<float, true, GROUPED_K>(tmA, tmB, C, args, s) : launch<float, false, GROUPED_K>(tmA, tmB, C, args, s);
 }

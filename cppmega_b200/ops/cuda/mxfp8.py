@@ -50,9 +50,11 @@ def _lib():
         L.cm_mxfp8_dequantize.argtypes = [vp, vp, vp, i64, vp]
         L.cm_mxfp8_swizzle_scales.argtypes = [vp, vp, i64, i32, vp]
         L.cm_mxfp8_quantize_both.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i32, vp]
+        L.cm_mxfp8_grouped_rows.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]
+        L.cm_mxfp8_grouped_k.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp]
         L.cm_mxfp8_gemm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, vp, vp]
         for n in ("cm_mxfp8_quantize_rowwise", "cm_mxfp8_quantize_colwise", "cm_mxfp8_dequantize", "cm_mxfp8_swizzle_scales",
-                  "cm_mxfp8_gemm", "cm_mxfp8_quantize_both"):
+                  "cm_mxfp8_gemm", "cm_mxfp8_quantize_both", "cm_mxfp8_grouped_rows", "cm_mxfp8_grouped_k"):
             getattr(L, n).restype = i32
         L._mx_declared = True
     return L
@@ -177,6 +179,56 @@ def quantize_weight(w: torch.Tensor, colwise: bool) -> Mxfp8Tensor:
     except AttributeError:
         pass
     return q
+
+
+def quantize_expert_weights(w: torch.Tensor, transposed: bool) -> Mxfp8Tensor:
+    """MXFP8 copy of a stacked expert weight [E, N, K], cached until the optimizer writes it.  ``transposed`` False:
+    [E * N, K] quantised along K (forward operand).  True: the stack read as [E * N, K] and quantised along its rows,
+    stored transposed [K, E * N] - the dgrad operand, whose reduction axis is N and whose expert e occupies the
+    columns [e N, (e + 1) N)."""
+    key = "_mx_ecol" if transposed else "_mx_erow"
+    hit = getattr(w, key, None)
+    if hit is not None and hit[0] == w._version:
+        return hit[1]
+    w2 = w.detach().reshape(-1, w.shape[-1])
+    q = quantize_colwise(w2, True) if transposed else quantize_rowwise(w2, True)
+    try:
+        setattr(w, key, (w._version, q))
+    except AttributeError:
+        pass
+    return q
+
+
+def grouped_rows_mxfp8(xq: Mxfp8Tensor, wq: Mxfp8Tensor, tile_expert: torch.Tensor, num_experts: int, n_out: int, dgrad: bool,
+                       out: torch.Tensor = None) -> torch.Tensor:
+    """Expert forward (``wq`` = stacked [E * n_out, K]) or dgrad (``wq`` = transposed stack [n_out, E * K]) on the padded
+    expert-sorted rows of ``xq`` [rows, K]."""
+    from . import err_word, stream_ptr
+    rows, K = xq.shape
+    if out is None:
+        out = torch.empty(rows, n_out, dtype=torch.bfloat16, device=xq.payload.device)
+    _check(_lib().cm_mxfp8_grouped_rows(xq.payload.data_ptr(), xq.swizzled().data_ptr(), wq.payload.data_ptr(), wq.swizzled().data_ptr(),
+                                        out.data_ptr(), rows, n_out, K, num_experts, int(dgrad), tile_expert.data_ptr(),
+                                        err_word(out.device).data_ptr(), stream_ptr()), "cm_mxfp8_grouped_rows")
+    F_.count_launch("mxfp8_grouped_gemm")
+    return out
+
+
+def grouped_wgrad_mxfp8(dy_t: Mxfp8Tensor, x_t: Mxfp8Tensor, seg_offsets: torch.Tensor, num_experts: int, out: torch.Tensor = None,
+                        accumulate: bool = False) -> torch.Tensor:
+    """dW[e] [N, K] (+)= dy_e^T x_e from the token-transposed operands dy_t [N, R], x_t [K, R]."""
+    from . import err_word, stream_ptr
+    (N, R), (K, R2) = dy_t.shape, x_t.shape
+    assert R == R2
+    if out is None:
+        out = torch.empty(num_experts, N, K, dtype=torch.bfloat16, device=dy_t.payload.device)
+        accumulate = False
+    assert out.is_contiguous() and out.dtype in (torch.bfloat16, torch.float32)
+    _check(_lib().cm_mxfp8_grouped_k(dy_t.payload.data_ptr(), dy_t.swizzled().data_ptr(), x_t.payload.data_ptr(), x_t.swizzled().data_ptr(),
+                                     out.data_ptr(), R, N, K, num_experts, seg_offsets.data_ptr(), int(out.dtype == torch.float32),
+                                     int(accumulate), err_word(out.device).data_ptr(), stream_ptr()), "cm_mxfp8_grouped_k")
+    F_.count_launch("mxfp8_grouped_gemm")
+    return out
 
 
 class Mxfp8LinearFn(torch.autograd.Function):

@@ -254,6 +254,42 @@ def _grouped_wgrad(dy, x, seg_offsets, E, w=None):
     return run(None, False) if w is None else wgrad_into_main_grad(w, run)
 
 
+def _mx_experts_ok(w1, w2) -> bool:
+    """Block-scaled expert GEMMs want every expert's rows / columns to start on a 128 boundary of the stacked weights."""
+    return (F_.precision_recipe() == "mxfp8" and w1.dtype == torch.bfloat16 and w1.shape[1] % 128 == 0 and w1.shape[2] % 128 == 0
+            and w2.shape[1] % 128 == 0 and w2.shape[2] % 128 == 0)
+
+
+def _experts_fwd_mx(xin, w1, w2, tile_expert, yout):
+    """h = xin W1^T, yout = swiglu(h) W2^T on the block-scaled grouped GEMM; returns h."""
+    from ..ops.cuda import mxfp8 as mx, swiglu
+    E = w1.shape[0]
+    h = mx.grouped_rows_mxfp8(mx.quantize_rowwise(xin, True), mx.quantize_expert_weights(w1, False), tile_expert, E, w1.shape[1], False)
+    a = swiglu(h)
+    mx.grouped_rows_mxfp8(mx.quantize_rowwise(a, True), mx.quantize_expert_weights(w2, False), tile_expert, E, w2.shape[1], False, out=yout)
+    return h
+
+
+def _experts_bwd_mx(grad_in, h, xin, w1, w2, plan, grad_out):
+    """Expert backward in MXFP8: every operand is quantised along the axis its product reduces over; a tensor that
+    feeds both a dgrad (along features) and a wgrad (along tokens) is read once for both copies."""
+    from ..ops.cuda import lib, mxfp8 as mx, stream_ptr, swiglu, wgrad_into_main_grad, _check
+    E, cap = w1.shape[0], grad_in.shape[0]
+    a = swiglu(h)
+    g_row, g_col = mx.quantize_both(grad_in)                                            # [cap, H] and [H, cap]
+    da = mx.grouped_rows_mxfp8(g_row, mx.quantize_expert_weights(w2, True), plan.tile_expert, E, w2.shape[2], True)     # [cap, F]
+    a_col = mx.quantize_colwise(a, True)                                                # [F, cap]
+    dw2 = wgrad_into_main_grad(w2, lambda out, acc: mx.grouped_wgrad_mxfp8(g_col, a_col, plan.seg_offsets, E, out, acc))
+    dh = torch.empty_like(h)
+    _check(lib().cm_swiglu_bwd(h.data_ptr(), da.data_ptr(), dh.data_ptr(), cap, w2.shape[2], stream_ptr()), "cm_swiglu_bwd")
+    F_.count_launch("swiglu_bwd")
+    dh_row, dh_col = mx.quantize_both(dh)                                               # [cap, 2F] and [2F, cap]
+    mx.grouped_rows_mxfp8(dh_row, mx.quantize_expert_weights(w1, True), plan.tile_expert, E, w1.shape[2], True, out=grad_out)
+    x_col = mx.quantize_colwise(xin, True)                                              # [H, cap]
+    dw1 = wgrad_into_main_grad(w1, lambda out, acc: mx.grouped_wgrad_mxfp8(dh_col, x_col, plan.seg_offsets, E, out, acc))
+    return dw1, dw2
+
+
 class _FusedMoEFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, probs, w1, w2, ids, bufs: FusedMoEBuffers, layer_slot: int):
@@ -270,9 +306,12 @@ class _FusedMoEFn(torch.autograd.Function):
         heap.barrier(f0 + 0, ep0)
         _zero_pad(xin, plan, cap)
         with torch.no_grad():
-            h = _grouped(xin, w1, plan.tile_expert, cap, False)
-            a = swiglu(h)
-            _grouped(a, w2, plan.tile_expert, cap, False, out=yout)
+            if _mx_experts_ok(w1, w2):
+                h = _experts_fwd_mx(xin, w1, w2, plan.tile_expert, yout)
+            else:
+                h = _grouped(xin, w1, plan.tile_expert, cap, False)
+                a = swiglu(h)
+                _grouped(a, w2, plan.tile_expert, cap, False, out=yout)
         heap.barrier(f0 + 1, ep0)
         p32 = probs.float().contiguous()
         y = _pull_combine(heap, yout, plan, p32.reshape(-1), H, x.dtype)
@@ -301,6 +340,12 @@ class _FusedMoEFn(torch.autograd.Function):
         Fh = w2.shape[2]
         # recompute a = swiglu(h); expert backward on the padded layout
         from ..ops.cuda import swiglu as _sw
+        if _mx_experts_ok(w1, w2):
+            with torch.no_grad():
+                dw1, dw2 = _experts_bwd_mx(grad_in, h, xin, w1, w2, plan, grad_out)
+            heap.barrier(f0 + 3, epb)
+            dx = _pull_combine(heap, grad_out, plan, None, H, ctx.x_dtype)
+            return dx, dprobs.to(ctx.p_dtype), dw1, dw2, None, None, None
         with torch.no_grad():
             a = _sw(h)
             da = _grouped(grad_in, w2, plan.tile_expert, cap, True)                  # [cap, F]

@@ -314,3 +314,48 @@ def test_fast_strided_copy_and_cat_split_helpers():
     assert torch.equal(y, y2)
     for p, q in ((a, a2), (b, b2), (x, xx)):
         torch.testing.assert_close(p.grad.float(), q.grad.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_mxfp8_grouped_expert_gemms():
+    """Block-scaled grouped GEMMs (forward / dgrad / per-expert wgrad) against fp32 products of the dequantised operands."""
+    from cppmega_b200.ops.cuda import mxfp8
+    torch.manual_seed(3)
+    E, N, K = 3, 384, 256
+    tile_expert = torch.tensor([0, 0, 2, -1, 1, 2], dtype=torch.int32, device="cuda")      # 6 tiles of 128 rows, one unused
+    rows = tile_expert.numel() * 128
+    x = (torch.randn(rows, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(E, N, K, device="cuda") * 0.1).bfloat16()
+    xq = mxfp8.quantize_rowwise(x, True)
+    xd = mxfp8.dequantize(xq).float()
+    te = tile_expert.repeat_interleave(128).long()
+    live = te >= 0
+    # forward: y[r] = x[r] . W[e(r)]^T
+    wq = mxfp8.quantize_expert_weights(w, False)
+    wd = mxfp8.dequantize(wq).float().view(E, N, K)
+    y = mxfp8.grouped_rows_mxfp8(xq, wq, tile_expert, E, N, False)
+    want = torch.einsum("rk,rnk->rn", xd[live], wd[te[live]])
+    assert _rel(y[live], want) < 5e-3
+    # dgrad: dx[r] = g[r] . W[e(r)]  (reduction over N)
+    g = (torch.randn(rows, N, device="cuda") * 0.5).bfloat16()
+    gq = mxfp8.quantize_rowwise(g, True)
+    wtq = mxfp8.quantize_expert_weights(w, True)                                          # [K, E*N]
+    wtd = mxfp8.dequantize(wtq).float().view(K, E, N).permute(1, 2, 0)                    # [E, N, K]
+    dx = mxfp8.grouped_rows_mxfp8(gq, wtq, tile_expert, E, K, True)
+    want = torch.einsum("rn,rnk->rk", mxfp8.dequantize(gq).float()[live], wtd[te[live]])
+    assert _rel(dx[live], want) < 5e-3
+    # wgrad: dW[e] = g_e^T x_e over expert e's rows; expert segments are contiguous in the sorted layout
+    order = torch.tensor([0, 1, 4, 2, 5], device="cuda")                                   # tiles sorted by expert: 0,0,1,2,2
+    xs = x.view(-1, 128, K)[order].reshape(-1, K).contiguous()
+    gs = g.view(-1, 128, N)[order].reshape(-1, N).contiguous()
+    seg = torch.tensor([0, 256, 384, 640], dtype=torch.int32, device="cuda")
+    g_t, x_t = mxfp8.quantize_colwise(gs, True), mxfp8.quantize_colwise(xs, True)
+    dw = mxfp8.grouped_wgrad_mxfp8(g_t, x_t, seg, E)
+    gd, xdt = mxfp8.dequantize(g_t).float(), mxfp8.dequantize(x_t).float()                # [N, R], [K, R]
+    for e in range(E):
+        s0, s1 = int(seg[e]), int(seg[e + 1])
+        assert _rel(dw[e], gd[:, s0:s1] @ xdt[:, s0:s1].t()) < 5e-3, e
+    acc = torch.randn(E, N, K, device="cuda")
+    dw32 = mxfp8.grouped_wgrad_mxfp8(g_t, x_t, seg, E, out=acc.clone(), accumulate=True)
+    assert _rel(dw32 - acc, dw.float()) < 1e-2
+    empty = torch.tensor([0, 256, 256, 640], dtype=torch.int32, device="cuda")             # expert 1 without tokens
+    assert mxfp8.grouped_wgrad_mxfp8(g_t, x_t, empty, E)[1].abs().sum() == 0
