@@ -3,7 +3,7 @@
 Pipeline transfers stay on the library's p2p primitives (NCCL on GPUs, gloo on CPU), batched per
 step so that matching sends and receives are posted together; activations are
 ``[micro_batch, seq(/tp under SP), hidden]`` in the model dtype, the message the reference's
-schedules exchange (SURVEY collective C13; split rule of cppmega/recipes/run_profiles.py:308-321).
+schedules exchange (split rule of cppmega/recipes/run_profiles.py:308-321).
 The last stage owns the MTP heads and therefore a second copy of the input embedding; the two
 copies are kept identical by summing their gradients over the (first, last) stage pair.
 """

@@ -5,7 +5,7 @@ Each tensor-parallel rank holds ``W_local [V/tp, H]``.  Per token chunk: local l
 pass recomputes the chunk's logits, forms ``softmax - onehot`` for the local vocabulary slice and
 accumulates ``dW_local`` and a partial ``dh`` that is all-reduced over the group.  The full
 ``[tokens, V]`` logits never exist (the scalars the reference's Megatron stack all-reduces for its
-vocab-parallel loss, SURVEY collective C16).
+vocab-parallel loss).
 """
 from __future__ import annotations
 
