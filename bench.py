@@ -247,10 +247,13 @@ def main() -> int:
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
         }
         print(json.dumps(out))
-    if args.profile_dir and rank == 0:
+    if args.profile_dir:
+        # every rank runs the profiled step (it contains collectives); rank 0 keeps the tables
         from cppmega_b200.utils.profiling import profile_steps
-        table = profile_steps(step_device, 1, args.profile_dir)
-        print(table[:200], file=sys.stderr)
+        pdir = args.profile_dir if rank == 0 else os.path.join(args.profile_dir, f"rank{rank}")
+        table = profile_steps(step_device, 1, pdir)
+        if rank == 0:
+            print(table[:200], file=sys.stderr)
     if world > 1:
         dist.barrier()
         pstate.destroy()

@@ -36,7 +36,7 @@ def install_layer_nvtx(model) -> None:
         layer.forward = wrapped
 
 
-def profile_steps(step_fn: Callable[[int], None], steps: int, out_dir: Optional[str] = None, row_limit: int = 60) -> str:
+def profile_steps(step_fn: Callable[[int], None], steps: int, out_dir: Optional[str] = None, row_limit: int = 200) -> str:
     """Run ``step_fn(i)`` for ``steps`` iterations under the torch profiler; returns the kernel table
     sorted by device time and writes ``kernel_table.txt`` / ``by_shape.txt`` into ``out_dir``."""
     from torch.profiler import ProfilerActivity, profile

@@ -64,3 +64,27 @@ def test_launch_lanes_render(capsys):
     assert "torch.distributed.run" in out and "--train-iters 3" in out and "NCCL_NVLS_ENABLE=0" in out
     assert launch.main(["recipe:native_pretrain", "--dry-run", "--data", "/data/c"]) == 0
     assert "/data/c" in capsys.readouterr().out
+
+
+def test_profile_report_groups_kernel_rows():
+    from cppmega_b200.tools import profile_report as pr
+    hdr = ("-" * 90 + "  " + "  ".join(["-" * 12] * 10) + "\n" +
+           f"{'Name':>90}  " + "  ".join(f"{c:>12}" for c in ["Self CPU %", "Self CPU", "CPU total %", "CPU total", "CPU time avg",
+                                                                "Self CUDA", "Self CUDA %", "CUDA total", "CUDA time avg", "# of Calls"]) + "\n")
+
+    def row(name, self_cuda, calls):
+        vals = ["0.00%", "0.000us", "0.00%", "0.000us", "0.000us", self_cuda, "1.00%", self_cuda, "1.000us", str(calls)]
+        return f"{name[:90]:>90}  " + "  ".join(f"{v:>12}" for v in vals) + "\n"
+
+    text = hdr + row("void cm::gemm_bf16_kernel<256, false, false, bf16, false, 0>(C", "100.000ms", 10) + \
+        row("void cm::gemm_bf16_kernel<256, false, false, bf16, false, 1>(C", "20.000ms", 4) + \
+        row("void cm::mimo::mimo_chunk_grad_kernel<128, 32>(CUtensorMap_st", "50.000ms", 13) + \
+        row("LinearFnBackward", "100.000ms", 10) + \
+        row("void at::native::vectorized_elementwise_kernel<8, at::native", "500.000us", 100) + \
+        "Self CUDA time total: 170.5ms\n"
+    rep = pr.report(text)
+    groups = {g["group"]: g for g in rep["groups"]}
+    assert abs(rep["total_ms"] - 170.5) < 1e-6                                     # the autograd row is not double counted
+    assert groups["dense GEMM (tcgen05 bf16)"]["ms"] == 100.0 and groups["grouped GEMM (experts)"]["launches"] == 4
+    assert groups["Mamba3 MIMO scan"]["ms"] == 50.0 and groups["PyTorch elementwise / copy / cat"]["ms"] == 0.5
+    assert rep["top"][0]["ms"] == 100.0
