@@ -137,8 +137,9 @@ __device__ __forceinline__ uint32_t orderable(float f) {
   return u ^ ((u >> 31) ? 0xffffffffu : 0x80000000u);
 }
 
-template <int PER>
-__global__ void __launch_bounds__(256) indexer_topk_kernel(const float* __restrict__ scores, int* __restrict__ out, int S, int K) {
+// NT threads hold PER keys each in registers (S <= NT * PER); the 256-bin histogram is scanned by the first 256 threads.
+template <int PER, int NT = 256>
+__global__ void __launch_bounds__(NT) indexer_topk_kernel(const float* __restrict__ scores, int* __restrict__ out, int S, int K) {
   __shared__ int hist[256];
   __shared__ int warp_tot[8];
   __shared__ int sel_bin, sel_need, cnt_gt, cnt_eq;
@@ -148,42 +149,44 @@ __global__ void __launch_bounds__(256) indexer_topk_kernel(const float* __restri
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int* orow = out + row * K;
   if (n <= K) {
-    for (int t = tid; t < K; t += 256) orow[t] = t < n ? t : -1;
+    for (int t = tid; t < K; t += NT) orow[t] = t < n ? t : -1;
     return;
   }
   const float* srow = scores + row * S;
   uint32_t key[PER];
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const int j = e * 256 + tid;
+    const int j = e * NT + tid;
     key[e] = j < n ? orderable(srow[j]) : 0u;
   }
   uint32_t prefix = 0, mask = 0;
   int need = K;
 #pragma unroll 1
   for (int shift = 24; shift >= 0; shift -= 8) {
-    hist[tid] = 0;
+    if (tid < 256) hist[tid] = 0;
     __syncthreads();
 #pragma unroll
     for (int e = 0; e < PER; ++e)
       if (key[e] != 0u && (key[e] & mask) == prefix) atomicAdd(&hist[(key[e] >> shift) & 255], 1);
     __syncthreads();
-    // inclusive scan over bins in descending order: thread t looks at bin 255 - t
-    const int h = hist[255 - tid];
+    // inclusive scan over bins in descending order: thread t < 256 looks at bin 255 - t
+    const int h = tid < 256 ? hist[255 - tid] : 0;
     int sc = h;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int v = __shfl_up_sync(0xffffffffu, sc, o);
       if (lane >= o) sc += v;
     }
-    if (lane == 31) warp_tot[warp] = sc;
+    if (lane == 31 && warp < 8) warp_tot[warp] = sc;
     __syncthreads();
-    int base = 0;
-    for (int w2 = 0; w2 < warp; ++w2) base += warp_tot[w2];
-    sc += base;                                  // elements in bins >= 255 - tid
-    if (sc >= need && sc - h < need) {
-      sel_bin = 255 - tid;
-      sel_need = need - (sc - h);
+    if (tid < 256) {
+      int base = 0;
+      for (int w2 = 0; w2 < warp; ++w2) base += warp_tot[w2];
+      sc += base;                                  // elements in bins >= 255 - tid
+      if (sc >= need && sc - h < need) {
+        sel_bin = 255 - tid;
+        sel_need = need - (sc - h);
+      }
     }
     __syncthreads();
     prefix |= (uint32_t)sel_bin << shift;
@@ -196,7 +199,7 @@ __global__ void __launch_bounds__(256) indexer_topk_kernel(const float* __restri
   const int n_gt = K - need;
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const int j = e * 256 + tid;
+    const int j = e * NT + tid;
     if (key[e] > prefix) {
       const int p = atomicAdd(&cnt_gt, 1);
       if (p < n_gt) orow[p] = j;
@@ -243,6 +246,8 @@ extern "C" int cm_indexer_topk(const float* scores, int* out, int B, int S, int 
   if (S <= 256 * 4) indexer_topk_kernel<4><<<rows, 256, 0, stream>>>(scores, out, S, K);
   else if (S <= 256 * 16) indexer_topk_kernel<16><<<rows, 256, 0, stream>>>(scores, out, S, K);
   else if (S <= 256 * 32) indexer_topk_kernel<32><<<rows, 256, 0, stream>>>(scores, out, S, K);
+  else if (S <= 512 * 32) indexer_topk_kernel<32, 512><<<rows, 512, 0, stream>>>(scores, out, S, K);
+  else if (S <= 1024 * 32) indexer_topk_kernel<32, 1024><<<rows, 1024, 0, stream>>>(scores, out, S, K);
   else return -12;
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -146,7 +146,7 @@ def head_reduce(dh: torch.Tensor, G: int):
 def indexer_topk(q_idx, k_idx, w, topk: int):
     """Causal top-k key positions per query (int32 [B,S,topk], unordered, -1 padded) on the indexer kernels."""
     if (q_idx.dtype != torch.bfloat16 or k_idx.dtype != torch.bfloat16 or q_idx.dim() != 4 or q_idx.shape[2] != 32
-            or q_idx.shape[3] != 64 or q_idx.shape[1] % 4 or q_idx.shape[1] > 8192 or k_idx.shape[1] != q_idx.shape[1]
+            or q_idx.shape[3] != 64 or q_idx.shape[1] % 4 or q_idx.shape[1] > 32768 or k_idx.shape[1] != q_idx.shape[1]
             or topk > 2048):
         return None
     from . import lib, err_word, stream_ptr, _check

@@ -221,5 +221,64 @@ def bench_mxfp8_gemm() -> List[dict]:
 CASES["mxfp8_gemm"] = bench_mxfp8_gemm
 
 
+def bench_longctx() -> List[dict]:
+    """Single-layer long-context sweep at hidden 4096, batch 1: MIMO scan fwd / bwd (128 heads) and the DSA path
+    (indexer top-256 + sparse MLA fwd / bwd, 32 heads) at seq 4096 .. 32768."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops.cuda import kernels3, kernels4
+    from cppmega_b200.ops.cuda.mimo_bwd import mimo_bwd
+    pk = peaks()
+    out = []
+    dev = "cuda"
+    for S in (4096, 8192, 16384, 32768):
+        B, H, G, N, P, R = 1, 128, 8, 128, 64, 4
+        Qn = (torch.randn(B, S, G, R, N, device=dev) * 0.5).bfloat16()
+        Kn = (torch.randn(B, S, G, R, N, device=dev) * 0.5).bfloat16()
+        V = torch.randn(B, S, H, P, device=dev).bfloat16()
+        Z = torch.randn(B, S, H, P, device=dev).bfloat16()
+        DT = torch.rand(B, H, S, device=dev) * 0.1
+        ADT = -DT * torch.rand(B, H, S, device=dev)
+        Trap = torch.randn(B, H, S, device=dev)
+        Qb, Kb = torch.randn(H, R, N, device=dev), torch.randn(H, R, N, device=dev)
+        Psi, Zeta, Phi = (torch.randn(H, R, P, device=dev) for _ in range(3))
+        ang = torch.randn(B, S, H, N // 4, device=dev)
+        D = torch.randn(H, device=dev)
+        args = (Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D)
+        ms_f = time_ms(lambda: kernels3.mimo_fwd_raw(*args), iters=5)
+        y, states, tot = kernels3.mimo_fwd_raw(*args)
+        saved = [Qn.permute(0, 1, 3, 2, 4), Kn.permute(0, 1, 3, 2, 4), V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D, Z]
+        dy = torch.randn_like(y)
+        ms_b = time_ms(lambda: mimo_bwd(saved, dy, states, tot), iters=5)
+        cu.check_errors()
+        chunks = B * H * (S // 32)
+        flops = chunks * (2.0 * 128 * 128 * 128 + 3 * 2.0 * 128 * 64 * 128)
+        out.append({"kernel": "mimo_scan", "S": S, "fwd_ms": ms_f, "bwd_ms": ms_b, "fwd_tflops": flops / ms_f / 1e9,
+                    "fwd_frac_of_" + pk["kind"]: flops / ms_f / 1e9 / pk["bf16_tflops"], "tokens_per_s_fwd_bwd": S / (ms_f + ms_b) * 1e3})
+        del y, states, tot, saved, dy, args
+        qi = torch.randn(B, S, 32, 64, device=dev).bfloat16()
+        ki = torch.randn(B, S, 64, device=dev).bfloat16()
+        wi = torch.rand(B, S, 32, device=dev)
+        ms_i = time_ms(lambda: kernels4.indexer_topk(qi, ki, wi, 256), iters=5)
+        idx = kernels4.indexer_topk(qi, ki, wi, 256)
+        q = (torch.randn(B, S, 32, 128, device=dev) * 0.3).bfloat16().requires_grad_()
+        kv = (torch.randn(B, S, 128, device=dev) * 0.3).bfloat16().requires_grad_()
+        ms_sf = time_ms(lambda: kernels4.sparse_mla_fwd_raw(q.detach(), kv.detach(), idx, 128 ** -0.5, 64), iters=5)
+        o = kernels4.SparseMLAFn.apply(q, kv, idx, 128 ** -0.5, 64)
+        g = torch.randn_like(o)
+        ms_sb = time_ms(lambda: torch.autograd.grad(o, (q, kv), g, retain_graph=True), iters=5)
+        cu.check_errors()
+        idx_flops = 2.0 * B * S * (S / 2) * 32 * 64
+        smla_flops = 2.0 * B * S * 32 * 256 * (128 + 64)
+        out.append({"kernel": "dsa", "S": S, "indexer_topk_ms": ms_i, "indexer_tflops": idx_flops / ms_i / 1e9,
+                    "sparse_mla_fwd_ms": ms_sf, "sparse_mla_fwd_tflops": smla_flops / ms_sf / 1e9, "sparse_mla_bwd_ms": ms_sb,
+                    "indexer_frac_of_" + pk["kind"]: idx_flops / ms_i / 1e9 / pk["bf16_tflops"]})
+        del qi, ki, wi, idx, q, kv, o, g
+        torch.cuda.empty_cache()
+    return out
+
+
+CASES["longctx"] = bench_longctx
+
+
 if __name__ == "__main__":
     sys.exit(main(sys.argv[1:]))

@@ -22,7 +22,7 @@ GROUPS: List[Tuple[str, str]] = [
     ("dense GEMM (tcgen05 bf16)", r"gemm_bf16_kernel<.*, [034]>\(|gemm_bf16_kernel<.*, [56]>\("),
     ("grouped GEMM (experts)", r"gemm_bf16_kernel<.*, [12]>\("),
     ("MXFP8 GEMM + quantise", r"mxfp8_gemm_kernel|quantize_(rowwise|colwise|both)_kernel|dequantize_kernel|swizzle_scales"),
-    ("Mamba3 MIMO scan", r"mimo_|angle_cumsum|head_reduce_kernel|state_scan"),
+    ("Mamba3 MIMO scan", r"mimo_|angle_|head_reduce_kernel|state_scan"),
     ("M2RNN", r"m2rnn_"),
     ("cross-entropy (non-GEMM part)", r"ce_fwd_bwd|cross_entropy|ce_"),
     ("MoE transport / permute", r"moe_|router_topk|zero_pad"),
@@ -31,8 +31,9 @@ GROUPS: List[Tuple[str, str]] = [
     ("sparse attention + indexer", r"sparse_mla|indexer_"),
     ("library attention (cuDNN)", r"cudnn|sdpa|flash_(fprop|bprop)|fmha"),
     ("NCCL", r"nccl"),
+    ("peer flag waits / signals", r"wait_flags_kernel|signal_peers_kernel"),
     ("strided copies (own kernel)", r"strided_copy_kernel|sum_slots"),
-    ("PyTorch elementwise / copy / cat", r"at::native|elementwise_kernel|CatArray|Memcpy|Memset|fill"),
+    ("PyTorch elementwise / copy / cat", r"at::native|at_cuda_detail|at::cuda|elementwise_kernel|CatArray|Memcpy|Memset|fill"),
 ]
 _TIME = re.compile(r"^([0-9.]+)(us|ms|s)$")
 

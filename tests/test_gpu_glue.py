@@ -114,7 +114,7 @@ def test_mimo_scan_reads_column_slices_in_place():
     assert torch.equal(y0, y1)
 
 
-@pytest.mark.parametrize("B,S,topk", [(2, 512, 256), (1, 1100, 256)])
+@pytest.mark.parametrize("B,S,topk", [(2, 512, 256), (1, 1100, 256), (1, 8448, 256)])   # the last one: 512-thread select
 def test_indexer_topk_kernels(B, S, topk):
     from cppmega_b200.ops import reference as ref
     from cppmega_b200.ops import cuda as cu
