@@ -24,12 +24,17 @@ def main():
     world = int(os.environ["WORLD_SIZE"])
     local_rank = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local_rank)
-    pc = pstate.initialize(ParallelConfig(ep=world, fused_collectives=(mode == "fused")))
-    mcfg = nam56r_tiny(seq_length=128)
-    tcfg = TrainConfig(micro_batch_size=2, seq_length=128, dtype="bf16", recompute=recompute,
+    tp_mode = mode.startswith("tp_")
+    seq = 256 if tp_mode else 128                      # fused TP wants (seq / tp) % 128 == 0
+    if tp_mode:
+        pc = pstate.initialize(ParallelConfig(tp=world, sequence_parallel=True, fused_collectives=(mode == "tp_fused")))
+    else:
+        pc = pstate.initialize(ParallelConfig(ep=world, fused_collectives=(mode == "fused")))
+    mcfg = nam56r_tiny(seq_length=seq)
+    tcfg = TrainConfig(micro_batch_size=2, seq_length=seq, dtype="bf16", recompute=recompute,
                        optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0), log_interval=0)
     trainer = Trainer(mcfg, tcfg, pc, device=torch.device("cuda", local_rank))
-    stream = synthetic_batches(mcfg.vocab_size, 2, 128, num_microbatches=world, seed=0, pin=False, rank=0)
+    stream = synthetic_batches(mcfg.vocab_size, 2, seq, num_microbatches=world, seed=0, pin=False, rank=0)
     F_.reset_counters()
     losses = []
     for _ in range(steps):

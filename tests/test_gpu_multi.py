@@ -57,3 +57,14 @@ def test_fused_tensor_parallel_linears_match_nccl():
         assert o["launches"].get("tp_ag_gemm", 0) == 2 and o["launches"].get("tp_gemm_rs", 0) == 2, outs
         assert o["launches"].get("tp_ag_wgrad", 0) == 2, outs          # both weight gradients read their gathered operand from peers
         assert "tp_ag_gemm" not in o["base_launches"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_training_fused_matches_nccl():
+    """Whole tiny model, TP 2 + sequence parallel: the peer-memory TP GEMMs follow the NCCL loss curve."""
+    base = _run("tp_nccl", 2)
+    fused = _run("tp_fused", 2)
+    assert fused["fused"].get("tp"), fused
+    assert fused["launches"].get("tp_ag_gemm", 0) > 0 and fused["launches"].get("tp_gemm_rs", 0) > 0 and fused["launches"].get("tp_ag_wgrad", 0) > 0
+    for b, f in zip(base["losses"], fused["losses"]):
+        assert abs(b[0] - f[0]) < 3e-2 * max(1.0, abs(b[0])), (base, fused)
