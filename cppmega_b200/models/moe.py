@@ -62,6 +62,17 @@ class Router(nn.Module):
         self.tokens_per_expert.zero_()
 
 
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = torch.device(device).index
+    st = _SIDE_STREAMS.get(key)
+    if st is None:
+        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return st
+
+
 class GroupedExperts(nn.Module):
     """``E_local`` SwiGLU experts evaluated with grouped GEMMs over expert-sorted rows."""
 
@@ -104,6 +115,7 @@ class MoELayer(nn.Module):
                                if cfg.shared_expert_ffn > 0 else None)
         self.dispatcher = AllToAllDispatcher(pc, cfg.num_experts)
         self.fused_dispatcher = None          # set by parallel.fused_moe.attach() on peer-capable GPUs
+        self.overlap_shared_expert = False    # opt-in, EP > 1: shared expert on a second stream beside the routed path
         self.last_aux_loss: Optional[torch.Tensor] = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -114,6 +126,18 @@ class MoELayer(nn.Module):
         if self.cfg.aux_loss_coeff > 0 and self.training:
             self.last_aux_loss = ref.moe_aux_loss(scores, ids, self.cfg.num_experts, self.cfg.topk,
                                                   self.cfg.aux_loss_coeff)
+        shared = None
+        overlap = (self.shared_experts is not None and self.fused_dispatcher is not None and flat.is_cuda and self.pc.ep > 1
+                   and self.overlap_shared_expert)
+        if overlap:
+            # The routed path spends most of its time in NVLink row transfers and flag waits, which leave the SMs'
+            # tensor cores idle: the shared expert (no communication) runs beside it on a second stream, forward and,
+            # through autograd's stream bookkeeping, backward.
+            main = torch.cuda.current_stream()
+            side = _side_stream(x.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                shared = self.shared_experts(x)
         if self.fused_dispatcher is not None and flat.is_cuda:
             y = self.fused_dispatcher(flat, probs, ids, self.experts)
         else:
@@ -121,6 +145,10 @@ class MoELayer(nn.Module):
             ys = self.experts(xs, plan.counts_local, plan.counts_local_host)
             y = self.dispatcher.combine(ys, probs, plan)
         y = y.reshape(B, S, H)
-        if self.shared_experts is not None:
+        if overlap:
+            main.wait_stream(side)
+            shared.record_stream(main)
+            y = y + shared
+        elif self.shared_experts is not None:
             y = y + self.shared_experts(x)
         return y

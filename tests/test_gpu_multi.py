@@ -23,10 +23,20 @@ def _run(mode, world, steps=3, recompute="none"):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(HERE, "dist_gpu_worker.py"), mode, str(steps), recompute]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    r = _launch(cmd, env)
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
     return json.loads(line[len("RESULT "):])
+
+
+def _launch(cmd, env):
+    """Run a torchrun command; a rendezvous port that got taken between probing and binding is retried on another."""
+    for attempt in range(3):
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+        if r.returncode == 0 or "EADDRINUSE" not in r.stderr:
+            break
+        cmd = [str(_free_port()) if i > 0 and cmd[i - 1] == "--master-port" else c for i, c in enumerate(cmd)]
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return r
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
@@ -48,8 +58,7 @@ def test_fused_tensor_parallel_linears_match_nccl():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(HERE, "dist_gpu_worker_tp.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    r = _launch(cmd, env)
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
     outs = json.loads(line[len("RESULT "):])
     for o in outs:
