@@ -54,6 +54,16 @@ __global__ void signal_peers_kernel(unsigned long long* const* flag_ptrs, int wo
   }
 }
 
+// Copy `n` 8-byte words from `src` to byte offset `dst_off` of every peer's buffer (a tiny all-gather contribution: expert
+// counts, a few hundred bytes); the signal that follows on the same stream publishes it.
+__global__ void put_words_kernel(const unsigned long long* __restrict__ src, unsigned long long* const* dst_ptrs, int world,
+                                 long long dst_off_words, int n) {
+  for (int i = threadIdx.x; i < n * world; i += blockDim.x) {
+    const int p = i / n, j = i - p * n;
+    dst_ptrs[p][dst_off_words + j] = src[j];
+  }
+}
+
 // Wait until words [first, first+count) of the local flag array are all >= value.
 __global__ void wait_flags_kernel(const unsigned long long* flags, int first, int count, unsigned long long value,
                                   unsigned long long timeout_ns, int* err) {
@@ -67,6 +77,14 @@ __global__ void wait_flags_kernel(const unsigned long long* flags, int first, in
 // flag_ptrs: device array of `world` pointers (each peer's flag array, as mapped in this process).
 extern "C" int cm_signal_peers(void* flag_ptrs, int world, int index, unsigned long long value, cudaStream_t s) {
   cm::signal_peers_kernel<<<1, 32, 0, s>>>((unsigned long long* const*)flag_ptrs, world, index, value);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// dst_ptrs: device array of `world` pointers to the same symmetric tensor on every peer; writes src[0..n) at word offset
+// dst_off_words of each
+extern "C" int cm_put_words(const void* src, void* dst_ptrs, int world, long long dst_off_words, int n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  cm::put_words_kernel<<<1, 256, 0, s>>>((const unsigned long long*)src, (unsigned long long* const*)dst_ptrs, world, dst_off_words, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -32,6 +32,7 @@ from .symm_mem import SymmetricHeap
 
 TILE = 128
 FLAG_BASE = 16
+FLAGS_PER_LAYER = 5          # dispatch, expert outputs, grad dispatch, grad outputs, count exchange
 
 
 def _lib():
@@ -52,13 +53,15 @@ def _lib():
 class MoEPlan:
     """Device-side routing plan of one call (no host synchronisation)."""
 
-    def __init__(self, ids: torch.Tensor, num_experts: int, ep: int, ep_rank: int, group, capacity_rows: int):
+    def __init__(self, ids: torch.Tensor, num_experts: int, ep: int, ep_rank: int, group, capacity_rows: int, gather=None):
         T, k = ids.shape
         E, El = num_experts, num_experts // ep
         dev = ids.device
         flat = ids.reshape(-1)
         counts = torch.bincount(flat, minlength=E)
-        if ep > 1:
+        if ep > 1 and gather is not None:
+            allc = gather(counts)                                # [src rank, expert] through peer memory
+        elif ep > 1:
             allc = torch.empty(ep * E, dtype=counts.dtype, device=dev)
             dist.all_gather_into_tensor(allc, counts.contiguous(), group=group)
             allc = allc.view(ep, E)                              # [src rank, expert]
@@ -110,7 +113,7 @@ class FusedMoEBuffers:
         mean_rows = tokens_per_rank * topk
         self.capacity = int((mean_rows * capacity_factor + 16 * TILE + TILE - 1) // TILE * TILE)
         n_bufs = (2 * num_layers if per_layer else 2) + 2
-        nbytes = n_bufs * (self.capacity * hidden * 2 + 4096)
+        nbytes = n_bufs * (self.capacity * hidden * 2 + 4096) + num_layers * 4096 * 2
         self.heap = SymmetricHeap(pc.ep_group, pc.ep_ranks, nbytes, device)
         self.per_layer = per_layer
         self.layer_bufs: List = []
@@ -120,8 +123,19 @@ class FusedMoEBuffers:
                                     self.heap.alloc((self.capacity, hidden), torch.bfloat16)))
         self.grad_in_ = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
         self.grad_out_ = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
+        self.num_layers = num_layers
+        self.count_bufs = {}                  # (layer slot, expert count) -> [ep, E] int64 exchange buffer
         self.epoch = 0
         _ = El
+
+    def gather_counts(self, layer_slot: int, epoch: int, counts: torch.Tensor) -> torch.Tensor:
+        """[E] per-expert copy counts of this rank -> [ep, E] of all ranks, through peer stores and one flag barrier
+        (flag 4 of the layer's group of five) instead of a library all-gather."""
+        key = (layer_slot, counts.numel())
+        buf = self.count_bufs.get(key)
+        if buf is None:
+            buf = self.count_bufs[key] = self.heap.alloc((self.heap.world, counts.numel()), torch.int64)
+        return self.heap.all_gather_words(counts.to(torch.int64).contiguous(), buf, FLAG_BASE + FLAGS_PER_LAYER * layer_slot + 4, epoch)
 
     def capacity_for(self, ncopies: int) -> int:
         return self.capacity
@@ -297,10 +311,11 @@ class _FusedMoEFn(torch.autograd.Function):
         pc, heap = bufs.pc, bufs.heap
         cap = bufs.capacity_for(ids.numel())
         H = x.shape[1]
-        plan = MoEPlan(ids, w1.shape[0] * pc.ep, pc.ep, pc.ep_rank, pc.ep_group, cap)
-        xin, yout = bufs.bufs(layer_slot, cap)
         ep0 = bufs.next_epoch()
-        f0 = FLAG_BASE + 4 * layer_slot
+        gather = (lambda c: bufs.gather_counts(layer_slot, ep0, c)) if hasattr(bufs, "gather_counts") else None
+        plan = MoEPlan(ids, w1.shape[0] * pc.ep, pc.ep, pc.ep_rank, pc.ep_group, cap, gather)
+        xin, yout = bufs.bufs(layer_slot, cap)
+        f0 = FLAG_BASE + FLAGS_PER_LAYER * layer_slot
         x = x.contiguous()
         _push(heap, x, plan, xin)
         heap.barrier(f0 + 0, ep0)
@@ -331,7 +346,7 @@ class _FusedMoEFn(torch.autograd.Function):
         H = dy.shape[1]
         dy = dy.contiguous()
         epb = bufs.next_epoch()
-        f0 = FLAG_BASE + 4 * ctx.slot
+        f0 = FLAG_BASE + FLAGS_PER_LAYER * ctx.slot
         dprobs = _pull_rowdot(heap, yout, plan, dy)
         _push(heap, dy, plan, grad_in, scale=p32.reshape(-1))
         heap.barrier(f0 + 2, epb)

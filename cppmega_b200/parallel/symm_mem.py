@@ -43,8 +43,9 @@ def _declare(L: ctypes.CDLL) -> None:
     L.cm_can_access_peer.argtypes = [i32, i32]
     L.cm_signal_peers.argtypes = [vp, i32, i32, u64, vp]
     L.cm_wait_flags.argtypes = [vp, i32, i32, u64, u64, vp, vp]
+    L.cm_put_words.argtypes = [vp, vp, i32, ctypes.c_longlong, i32, vp]
     for n in ("cm_symm_alloc", "cm_symm_free", "cm_ipc_get_handle", "cm_ipc_open_handle", "cm_ipc_close_handle",
-              "cm_can_access_peer", "cm_signal_peers", "cm_wait_flags"):
+              "cm_can_access_peer", "cm_signal_peers", "cm_wait_flags", "cm_put_words"):
         getattr(L, n).restype = i32
 
 
@@ -144,6 +145,24 @@ class SymmetricHeap:
     def barrier(self, index: int, value: int) -> None:
         self.signal(index, value)
         self.wait(index, value)
+
+    def all_gather_words(self, src: torch.Tensor, buf: torch.Tensor, index: int, value: int) -> torch.Tensor:
+        """All-gather of a small int64 vector without a library collective: every rank stores ``src`` [n] into row ``me``
+        of the symmetric tensor ``buf`` [world, n] on every peer, then the group meets on flag ``index``.  Returns the
+        local ``buf``.  The caller must not reuse ``buf`` before every rank has consumed the previous contents (one
+        later barrier of the same group is enough)."""
+        from ..ops.cuda import stream_ptr
+        n = src.numel()
+        assert src.dtype == torch.int64 and src.is_contiguous() and buf.dtype == torch.int64 and tuple(buf.shape) == (self.world, n)
+        ptrs = getattr(buf, "_peer_ptr_tensor", None)
+        if ptrs is None:
+            ptrs = torch.tensor(self.peer_ptrs(buf), dtype=torch.int64, device=self.device)
+            buf._peer_ptr_tensor = ptrs
+        rc = self.L.cm_put_words(src.data_ptr(), ptrs.data_ptr(), self.world, self.me * n, n, stream_ptr())
+        if rc:
+            raise RuntimeError(f"cm_put_words failed ({rc})")
+        self.barrier(index, value)
+        return buf
 
     def close(self) -> None:
         for i, p in enumerate(self.peer_base):
