@@ -128,6 +128,132 @@ __global__ void __launch_bounds__(256) moe_zero_pad_rows_kernel(__nv_bfloat16* _
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = z;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Routing plan.  Two launches replace a few dozen small library kernels per MoE call:
+//   moe_count:  counts[e] = number of (token, j) copies routed to expert e on this rank;
+//   moe_plan:   from the counts of all source ranks, the destination of every copy and this rank's receive layout.
+// Row layout on the owner of expert e: experts in order, each segment padded to a multiple of `tile` rows; inside a
+// segment the copies of source rank 0 come first, then rank 1, ...; a rank's copies keep their (token, j) order, so the
+// plan is deterministic.  One CTA of 1024 threads: thread t ranks the copies [t * per, (t + 1) * per).
+// ---------------------------------------------------------------------------------------------
+constexpr int PLAN_THREADS = 1024;
+constexpr int PLAN_MAX_E = 32;          // 2 * E * 1024 16-bit counters must fit shared memory
+
+__global__ void __launch_bounds__(256) moe_count_kernel(const long long* __restrict__ ids, long long n, int E, long long* __restrict__ counts) {
+  __shared__ unsigned int h[PLAN_MAX_E];
+  if (threadIdx.x < PLAN_MAX_E) h[threadIdx.x] = 0;
+  __syncthreads();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&h[e], 1u);
+  }
+  __syncthreads();
+  if (threadIdx.x < E && h[threadIdx.x]) atomicAdd(reinterpret_cast<unsigned long long*>(counts) + threadIdx.x, (unsigned long long)h[threadIdx.x]);
+}
+
+struct PlanOut {
+  long long* dest_row;        // [n]
+  int* dest_rank;             // [n]
+  int* token_of_copy;         // [n]
+  int* seg_start_local;       // [El]
+  int* tot_local;             // [El]
+  int* seg_offsets;           // [El + 1]
+  int* tile_expert;           // [n_tiles]
+  long long* counts_global;   // [E]
+};
+
+__global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long* __restrict__ ids, long long n, int k, int E, int ep, int ep_rank,
+                                                                const long long* __restrict__ allc, int tile, int n_tiles, PlanOut o) {
+  __shared__ long long base[PLAN_MAX_E];          // first row of this rank's copies of expert e on its owner
+  __shared__ long long my_end[PLAN_MAX_E];
+  __shared__ unsigned int warp_tot[32];
+  extern __shared__ unsigned short cnt[];         // [E][PLAN_THREADS] per-thread counts, then exclusive prefixes
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int El = E / ep;
+  if (tid < E) {
+    long long tot = 0, before = 0;
+    for (int r = 0; r < ep; ++r) {
+      const long long c = allc[(long long)r * E + tid];
+      tot += c;
+      if (r < ep_rank) before += c;
+    }
+    o.counts_global[tid] = tot;
+    const int owner = tid / El;
+    long long start = 0;                           // padded sizes of the owner's earlier experts
+    for (int e2 = owner * El; e2 < tid; ++e2) {
+      long long t2 = 0;
+      for (int r = 0; r < ep; ++r) t2 += allc[(long long)r * E + e2];
+      start += (t2 + tile - 1) / tile * tile;
+    }
+    base[tid] = start + before;
+    if (owner == ep_rank) {
+      const int le = tid - owner * El;
+      const long long padded = (tot + tile - 1) / tile * tile;
+      o.seg_start_local[le] = (int)start;
+      o.tot_local[le] = (int)tot;
+      my_end[le] = start + padded;
+      o.seg_offsets[le + 1] = (int)(start + padded);
+      if (le == 0) o.seg_offsets[0] = 0;
+    }
+  }
+  const long long per = (n + PLAN_THREADS - 1) / PLAN_THREADS;
+  const long long c0 = (long long)tid * per, c1 = min(n, c0 + per);
+  for (int e = 0; e < E; ++e) cnt[e * PLAN_THREADS + tid] = 0;
+  for (long long c = c0; c < c1; ++c) {
+    const int e = (int)ids[c];
+    cnt[e * PLAN_THREADS + tid] += 1;
+  }
+  __syncthreads();
+  // exclusive scan over the threads, one expert at a time
+  for (int e = 0; e < E; ++e) {
+    const unsigned int v = cnt[e * PLAN_THREADS + tid];
+    unsigned int sc = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned int u = __shfl_up_sync(0xffffffffu, sc, off);
+      if (lane >= off) sc += u;
+    }
+    if (lane == 31) warp_tot[warp] = sc;
+    __syncthreads();
+    if (warp == 0) {
+      unsigned int w = warp_tot[lane], ws = w;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const unsigned int u = __shfl_up_sync(0xffffffffu, ws, off);
+        if (lane >= off) ws += u;
+      }
+      warp_tot[lane] = ws - w;
+    }
+    __syncthreads();
+    cnt[e * PLAN_THREADS + tid] = (unsigned short)0;       // the prefix may exceed 16 bits: keep it in a register below
+    const unsigned int excl = warp_tot[warp] + sc - v;
+    // stash the 32-bit prefix in two 16-bit halves of the (now free) counter slots of experts e and e + E
+    cnt[e * PLAN_THREADS + tid] = (unsigned short)(excl & 0xffffu);
+    cnt[(E + e) * PLAN_THREADS + tid] = (unsigned short)(excl >> 16);
+    __syncthreads();
+  }
+  unsigned int run[PLAN_MAX_E / 4];                 // running counts of this thread, 8 bits each (per <= 255 copies)
+#pragma unroll
+  for (int i = 0; i < PLAN_MAX_E / 4; ++i) run[i] = 0;
+  for (long long c = c0; c < c1; ++c) {
+    const int e = (int)ids[c];
+    const unsigned int excl = (unsigned int)cnt[e * PLAN_THREADS + tid] | ((unsigned int)cnt[(E + e) * PLAN_THREADS + tid] << 16);
+    const unsigned int r = (run[e >> 2] >> ((e & 3) * 8)) & 0xffu;
+    run[e >> 2] += 1u << ((e & 3) * 8);
+    o.dest_row[c] = base[e] + excl + r;
+    o.dest_rank[c] = e / El;
+    o.token_of_copy[c] = (int)(c / k);
+  }
+  __syncthreads();
+  for (int t = tid; t < n_tiles; t += PLAN_THREADS) {
+    const long long row = (long long)t * tile;
+    int te = 0;
+    while (te < El && my_end[te] <= row) ++te;
+    o.tile_expert[t] = te < El ? te : -1;
+  }
+}
+
 }  // namespace cm
 
 using namespace cm;
@@ -175,5 +301,32 @@ extern "C" int cm_moe_zero_pad_rows(void* buf, const int* seg_start, const int* 
   if (H % 8) return -10;
   dim3 grid(num_local_experts, 128);
   moe_zero_pad_rows_kernel<<<grid, 256, 0, s>>>((__nv_bfloat16*)buf, seg_start, tot, H, capacity_rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// counts [E] int64 (zeroed by the caller) += histogram of ids [n] int64
+extern "C" int cm_moe_count(const long long* ids, long long n, int E, long long* counts, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (E > cm::PLAN_MAX_E) return -10;
+  long long blocks = (n + 255) / 256;
+  cm::moe_count_kernel<<<(int)(blocks < 64 ? blocks : 64), 256, 0, s>>>(ids, n, E, counts);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// ids [n = T * k] int64, allc [ep, E] int64 (copies per source rank and expert) -> routing plan (see moe_plan_kernel)
+extern "C" int cm_moe_plan(const long long* ids, long long n, int k, int E, int ep, int ep_rank, const long long* allc, int tile, int n_tiles,
+                           long long* dest_row, int* dest_rank, int* token_of_copy, int* seg_start_local, int* tot_local, int* seg_offsets,
+                           int* tile_expert, long long* counts_global, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (E > cm::PLAN_MAX_E || E % ep || (n + cm::PLAN_THREADS - 1) / cm::PLAN_THREADS > 255) return -10;
+  const int smem = 2 * E * cm::PLAN_THREADS * (int)sizeof(unsigned short);
+  static bool cfg = false;
+  if (!cfg) {
+    if (cudaFuncSetAttribute(cm::moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * cm::PLAN_MAX_E * cm::PLAN_THREADS * 2) != cudaSuccess)
+      return -2;
+    cfg = true;
+  }
+  cm::PlanOut o{dest_row, dest_rank, token_of_copy, seg_start_local, tot_local, seg_offsets, tile_expert, counts_global};
+  cm::moe_plan_kernel<<<1, cm::PLAN_THREADS, smem, s>>>(ids, n, k, E, ep, ep_rank, allc, tile, n_tiles, o);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

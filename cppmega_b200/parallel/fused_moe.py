@@ -44,7 +44,9 @@ def _lib():
         L.cm_moe_pull_combine.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, vp]
         L.cm_moe_pull_rowdot.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, vp]
         L.cm_moe_zero_pad_rows.argtypes = [vp, vp, vp, i32, i32, i64, vp]
-        for n in ("cm_moe_push_rows", "cm_moe_pull_combine", "cm_moe_pull_rowdot", "cm_moe_zero_pad_rows"):
+        L.cm_moe_count.argtypes = [vp, i64, i32, vp, vp]
+        L.cm_moe_plan.argtypes = [vp, i64, i32, i32, i32, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        for n in ("cm_moe_push_rows", "cm_moe_pull_combine", "cm_moe_pull_rowdot", "cm_moe_zero_pad_rows", "cm_moe_count", "cm_moe_plan"):
             getattr(L, n).restype = i32
         L._moe_declared = True
     return L
@@ -53,11 +55,16 @@ def _lib():
 class MoEPlan:
     """Device-side routing plan of one call (no host synchronisation)."""
 
+    use_kernels = True        # False: build the plan from library ops (the definition the kernels are tested against)
+
     def __init__(self, ids: torch.Tensor, num_experts: int, ep: int, ep_rank: int, group, capacity_rows: int, gather=None):
         T, k = ids.shape
         E, El = num_experts, num_experts // ep
         dev = ids.device
         flat = ids.reshape(-1)
+        if self.use_kernels and ids.is_cuda and ids.dtype == torch.int64 and E <= 32 and (T * k + 1023) // 1024 <= 255 and T * k > 0:
+            self._build_on_device(flat.contiguous(), T, k, E, El, ep, ep_rank, group, capacity_rows, gather)
+            return
         counts = torch.bincount(flat, minlength=E)
         if ep > 1 and gather is not None:
             allc = gather(counts)                                # [src rank, expert] through peer memory
@@ -100,6 +107,41 @@ class MoEPlan:
         self.tile_expert = torch.where(te < El, te, torch.full_like(te, -1)).to(torch.int32)
         self.rows_used = my_end[-1]
         self.counts_global = tot
+
+
+def _build_on_device(self, flat, T, k, E, El, ep, ep_rank, group, capacity_rows, gather):
+    """The plan from two kernels (`moe_count`, `moe_plan`) instead of the chain of library ops below."""
+    from ..ops.cuda import stream_ptr
+    L, dev, n = _lib(), flat.device, T * k
+    counts = torch.zeros(E, dtype=torch.int64, device=dev)
+    rc = L.cm_moe_count(flat.data_ptr(), n, E, counts.data_ptr(), stream_ptr())
+    if rc:
+        raise RuntimeError(f"cm_moe_count failed ({rc})")
+    if ep > 1 and gather is not None:
+        allc = gather(counts)
+    elif ep > 1:
+        allc = torch.empty(ep * E, dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(allc, counts, group=group)
+    else:
+        allc = counts
+    n_tiles = capacity_rows // TILE
+    i32 = lambda m: torch.empty(m, dtype=torch.int32, device=dev)
+    self.dest_row = torch.empty(n, dtype=torch.int64, device=dev)
+    self.dest_rank, self.token_of_copy = i32(n), i32(n)
+    self.seg_start_local, self.tot_local, self.seg_offsets, self.tile_expert = i32(El), i32(El), i32(El + 1), i32(n_tiles)
+    self.counts_global = torch.empty(E, dtype=torch.int64, device=dev)
+    rc = L.cm_moe_plan(flat.data_ptr(), n, k, E, ep, ep_rank, allc.data_ptr(), TILE, n_tiles, self.dest_row.data_ptr(),
+                       self.dest_rank.data_ptr(), self.token_of_copy.data_ptr(), self.seg_start_local.data_ptr(),
+                       self.tot_local.data_ptr(), self.seg_offsets.data_ptr(), self.tile_expert.data_ptr(),
+                       self.counts_global.data_ptr(), stream_ptr())
+    if rc:
+        raise RuntimeError(f"cm_moe_plan failed ({rc})")
+    F_.count_launch("moe_plan", 2)
+    self.T, self.k = T, k
+    self.rows_used = self.seg_offsets[-1]
+
+
+MoEPlan._build_on_device = _build_on_device
 
 
 class FusedMoEBuffers:

@@ -359,3 +359,31 @@ def test_mxfp8_grouped_expert_gemms():
     assert _rel(dw32 - acc, dw.float()) < 1e-2
     empty = torch.tensor([0, 256, 256, 640], dtype=torch.int32, device="cuda")             # expert 1 without tokens
     assert mxfp8.grouped_wgrad_mxfp8(g_t, x_t, empty, E)[1].abs().sum() == 0
+
+
+@pytest.mark.parametrize("ep,ep_rank", [(1, 0), (4, 2)])
+def test_moe_plan_kernels_match_library_ops(ep, ep_rank):
+    from cppmega_b200.parallel.fused_moe import MoEPlan, TILE
+    torch.manual_seed(ep)
+    T, k, E = 3000, 4, 16
+    ids = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)])          # distinct experts per token
+    ids[:200, 0] = 5                                                                       # some skew
+    others = torch.randint(0, 900, (ep, E), device="cuda")
+
+    def gather(counts):
+        allc = others.clone()
+        allc[ep_rank] = counts
+        return allc
+
+    cap = ((T * k * 4 + 16 * TILE) // TILE) * TILE
+    plans = []
+    for flag in (False, True):
+        MoEPlan.use_kernels = flag
+        try:
+            plans.append(MoEPlan(ids, E, ep, ep_rank, None, cap, gather if ep > 1 else None))
+        finally:
+            MoEPlan.use_kernels = True
+    a, b = plans
+    for name in ("dest_row", "dest_rank", "token_of_copy", "seg_start_local", "tot_local", "seg_offsets", "tile_expert", "counts_global"):
+        assert torch.equal(getattr(a, name).long(), getattr(b, name).long()), name
+    assert int(a.rows_used) == int(b.rows_used) and (a.T, a.k) == (b.T, b.k)
