@@ -135,21 +135,26 @@ __global__ void __launch_bounds__(256) moe_zero_pad_rows_kernel(__nv_bfloat16* _
 //   moe_plan:   from the counts of all source ranks, the destination of every copy and this rank's receive layout.
 // Row layout on the owner of expert e: experts in order, each segment padded to a multiple of `tile` rows; inside a
 // segment the copies of source rank 0 come first, then rank 1, ...; a rank's copies keep their (token, j) order, so the
-// plan is deterministic.  One CTA of 1024 threads: thread t ranks the copies [t * per, (t + 1) * per).
+// plan is deterministic.  One CTA of 1024 threads per chunk of about 4096 copies: thread t ranks `per` consecutive copies.
 // ---------------------------------------------------------------------------------------------
 constexpr int PLAN_THREADS = 1024;
 constexpr int PLAN_MAX_E = 32;          // 2 * E * 1024 16-bit counters must fit shared memory
 
-__global__ void __launch_bounds__(256) moe_count_kernel(const long long* __restrict__ ids, long long n, int E, long long* __restrict__ counts) {
+__global__ void __launch_bounds__(256) moe_count_kernel(const long long* __restrict__ ids, long long n, long long chunk, int E,
+                                                        long long* __restrict__ counts, int* __restrict__ block_counts) {
   __shared__ unsigned int h[PLAN_MAX_E];
   if (threadIdx.x < PLAN_MAX_E) h[threadIdx.x] = 0;
   __syncthreads();
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+  const long long c0 = blockIdx.x * chunk, c1 = min(n, c0 + chunk);       // the same partition moe_plan_kernel walks
+  for (long long i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
     const long long e = ids[i];
     if (e >= 0 && e < E) atomicAdd(&h[e], 1u);
   }
   __syncthreads();
-  if (threadIdx.x < E && h[threadIdx.x]) atomicAdd(reinterpret_cast<unsigned long long*>(counts) + threadIdx.x, (unsigned long long)h[threadIdx.x]);
+  if (threadIdx.x < E) {
+    block_counts[blockIdx.x * E + threadIdx.x] = (int)h[threadIdx.x];
+    if (h[threadIdx.x]) atomicAdd(reinterpret_cast<unsigned long long*>(counts) + threadIdx.x, (unsigned long long)h[threadIdx.x]);
+  }
 }
 
 struct PlanOut {
@@ -163,8 +168,9 @@ struct PlanOut {
   long long* counts_global;   // [E]
 };
 
-__global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long* __restrict__ ids, long long n, int k, int E, int ep, int ep_rank,
-                                                                const long long* __restrict__ allc, int tile, int n_tiles, PlanOut o) {
+__global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long* __restrict__ ids, long long n, long long chunk, int k, int E, int ep,
+                                                                int ep_rank, const long long* __restrict__ allc,
+                                                                const int* __restrict__ block_counts, int tile, int n_tiles, PlanOut o) {
   __shared__ long long base[PLAN_MAX_E];          // first row of this rank's copies of expert e on its owner
   __shared__ long long my_end[PLAN_MAX_E];
   __shared__ unsigned int warp_tot[32];
@@ -178,7 +184,8 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
       tot += c;
       if (r < ep_rank) before += c;
     }
-    o.counts_global[tid] = tot;
+    if (blockIdx.x == 0) o.counts_global[tid] = tot;
+    for (int g = 0; g < (int)blockIdx.x; ++g) before += block_counts[g * E + tid];     // this rank's copies in earlier CTAs
     const int owner = tid / El;
     long long start = 0;                           // padded sizes of the owner's earlier experts
     for (int e2 = owner * El; e2 < tid; ++e2) {
@@ -190,15 +197,18 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
     if (owner == ep_rank) {
       const int le = tid - owner * El;
       const long long padded = (tot + tile - 1) / tile * tile;
-      o.seg_start_local[le] = (int)start;
-      o.tot_local[le] = (int)tot;
       my_end[le] = start + padded;
-      o.seg_offsets[le + 1] = (int)(start + padded);
-      if (le == 0) o.seg_offsets[0] = 0;
+      if (blockIdx.x == 0) {
+        o.seg_start_local[le] = (int)start;
+        o.tot_local[le] = (int)tot;
+        o.seg_offsets[le + 1] = (int)(start + padded);
+        if (le == 0) o.seg_offsets[0] = 0;
+      }
     }
   }
-  const long long per = (n + PLAN_THREADS - 1) / PLAN_THREADS;
-  const long long c0 = (long long)tid * per, c1 = min(n, c0 + per);
+  const long long b0 = blockIdx.x * chunk, b1 = min(n, b0 + chunk);            // this CTA's copies
+  const long long per = (chunk + PLAN_THREADS - 1) / PLAN_THREADS;
+  const long long c0 = min(b1, b0 + (long long)tid * per), c1 = min(b1, c0 + per);
   for (int e = 0; e < E; ++e) cnt[e * PLAN_THREADS + tid] = 0;
   for (long long c = c0; c < c1; ++c) {
     const int e = (int)ids[c];
@@ -246,6 +256,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
     o.token_of_copy[c] = (int)(c / k);
   }
   __syncthreads();
+  if (blockIdx.x != 0) return;
   for (int t = tid; t < n_tiles; t += PLAN_THREADS) {
     const long long row = (long long)t * tile;
     int te = 0;
@@ -304,21 +315,28 @@ extern "C" int cm_moe_zero_pad_rows(void* buf, const int* seg_start, const int* 
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// counts [E] int64 (zeroed by the caller) += histogram of ids [n] int64
-extern "C" int cm_moe_count(const long long* ids, long long n, int E, long long* counts, cudaStream_t s) {
+// Both kernels walk the copies in the same contiguous chunks, one CTA per chunk.
+static int plan_blocks(long long n) {
+  long long g = (n + 4095) / 4096;
+  return (int)(g < 1 ? 1 : (g > 64 ? 64 : g));
+}
+static long long plan_chunk(long long n) { return (n + plan_blocks(n) - 1) / plan_blocks(n); }
+
+// counts [E] int64 (zeroed by the caller) += histogram of ids [n] int64; block_counts [64, E] int32 receives the per-chunk parts
+extern "C" int cm_moe_count(const long long* ids, long long n, int E, long long* counts, int* block_counts, cudaStream_t s) {
   if (n <= 0) return 0;
   if (E > cm::PLAN_MAX_E) return -10;
-  long long blocks = (n + 255) / 256;
-  cm::moe_count_kernel<<<(int)(blocks < 64 ? blocks : 64), 256, 0, s>>>(ids, n, E, counts);
+  cm::moe_count_kernel<<<plan_blocks(n), 256, 0, s>>>(ids, n, plan_chunk(n), E, counts, block_counts);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// ids [n = T * k] int64, allc [ep, E] int64 (copies per source rank and expert) -> routing plan (see moe_plan_kernel)
-extern "C" int cm_moe_plan(const long long* ids, long long n, int k, int E, int ep, int ep_rank, const long long* allc, int tile, int n_tiles,
-                           long long* dest_row, int* dest_rank, int* token_of_copy, int* seg_start_local, int* tot_local, int* seg_offsets,
-                           int* tile_expert, long long* counts_global, cudaStream_t s) {
+// ids [n = T * k] int64, allc [ep, E] int64 (copies per source rank and expert), block_counts from cm_moe_count -> routing plan
+extern "C" int cm_moe_plan(const long long* ids, long long n, int k, int E, int ep, int ep_rank, const long long* allc, const int* block_counts,
+                           int tile, int n_tiles, long long* dest_row, int* dest_rank, int* token_of_copy, int* seg_start_local,
+                           int* tot_local, int* seg_offsets, int* tile_expert, long long* counts_global, cudaStream_t s) {
   if (n <= 0) return 0;
-  if (E > cm::PLAN_MAX_E || E % ep || (n + cm::PLAN_THREADS - 1) / cm::PLAN_THREADS > 255) return -10;
+  const long long chunk = plan_chunk(n);
+  if (E > cm::PLAN_MAX_E || E % ep || (chunk + cm::PLAN_THREADS - 1) / cm::PLAN_THREADS > 255) return -10;
   const int smem = 2 * E * cm::PLAN_THREADS * (int)sizeof(unsigned short);
   static bool cfg = false;
   if (!cfg) {
@@ -327,6 +345,6 @@ extern "C" int cm_moe_plan(const long long* ids, long long n, int k, int E, int 
     cfg = true;
   }
   cm::PlanOut o{dest_row, dest_rank, token_of_copy, seg_start_local, tot_local, seg_offsets, tile_expert, counts_global};
-  cm::moe_plan_kernel<<<1, cm::PLAN_THREADS, smem, s>>>(ids, n, k, E, ep, ep_rank, allc, tile, n_tiles, o);
+  cm::moe_plan_kernel<<<plan_blocks(n), cm::PLAN_THREADS, smem, s>>>(ids, n, chunk, k, E, ep, ep_rank, allc, block_counts, tile, n_tiles, o);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

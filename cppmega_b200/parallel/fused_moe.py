@@ -44,8 +44,8 @@ def _lib():
         L.cm_moe_pull_combine.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, vp]
         L.cm_moe_pull_rowdot.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, vp]
         L.cm_moe_zero_pad_rows.argtypes = [vp, vp, vp, i32, i32, i64, vp]
-        L.cm_moe_count.argtypes = [vp, i64, i32, vp, vp]
-        L.cm_moe_plan.argtypes = [vp, i64, i32, i32, i32, i32, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.cm_moe_count.argtypes = [vp, i64, i32, vp, vp, vp]
+        L.cm_moe_plan.argtypes = [vp, i64, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]
         for n in ("cm_moe_push_rows", "cm_moe_pull_combine", "cm_moe_pull_rowdot", "cm_moe_zero_pad_rows", "cm_moe_count", "cm_moe_plan"):
             getattr(L, n).restype = i32
         L._moe_declared = True
@@ -62,7 +62,7 @@ class MoEPlan:
         E, El = num_experts, num_experts // ep
         dev = ids.device
         flat = ids.reshape(-1)
-        if self.use_kernels and ids.is_cuda and ids.dtype == torch.int64 and E <= 32 and (T * k + 1023) // 1024 <= 255 and T * k > 0:
+        if self.use_kernels and ids.is_cuda and ids.dtype == torch.int64 and E <= 32 and 0 < T * k <= 64 * 255 * 1024:
             self._build_on_device(flat.contiguous(), T, k, E, El, ep, ep_rank, group, capacity_rows, gather)
             return
         counts = torch.bincount(flat, minlength=E)
@@ -114,7 +114,8 @@ def _build_on_device(self, flat, T, k, E, El, ep, ep_rank, group, capacity_rows,
     from ..ops.cuda import stream_ptr
     L, dev, n = _lib(), flat.device, T * k
     counts = torch.zeros(E, dtype=torch.int64, device=dev)
-    rc = L.cm_moe_count(flat.data_ptr(), n, E, counts.data_ptr(), stream_ptr())
+    block_counts = torch.empty(64 * E, dtype=torch.int32, device=dev)          # per-chunk parts, same chunks in both kernels
+    rc = L.cm_moe_count(flat.data_ptr(), n, E, counts.data_ptr(), block_counts.data_ptr(), stream_ptr())
     if rc:
         raise RuntimeError(f"cm_moe_count failed ({rc})")
     if ep > 1 and gather is not None:
@@ -130,7 +131,7 @@ def _build_on_device(self, flat, T, k, E, El, ep, ep_rank, group, capacity_rows,
     self.dest_rank, self.token_of_copy = i32(n), i32(n)
     self.seg_start_local, self.tot_local, self.seg_offsets, self.tile_expert = i32(El), i32(El), i32(El + 1), i32(n_tiles)
     self.counts_global = torch.empty(E, dtype=torch.int64, device=dev)
-    rc = L.cm_moe_plan(flat.data_ptr(), n, k, E, ep, ep_rank, allc.data_ptr(), TILE, n_tiles, self.dest_row.data_ptr(),
+    rc = L.cm_moe_plan(flat.data_ptr(), n, k, E, ep, ep_rank, allc.data_ptr(), block_counts.data_ptr(), TILE, n_tiles, self.dest_row.data_ptr(),
                        self.dest_rank.data_ptr(), self.token_of_copy.data_ptr(), self.seg_start_local.data_ptr(),
                        self.tot_local.data_ptr(), self.seg_offsets.data_ptr(), self.tile_expert.data_ptr(),
                        self.counts_global.data_ptr(), stream_ptr())
