@@ -65,8 +65,9 @@ def parse_table(text: str) -> List[Tuple[str, float, int]]:
         ms = _ms(rest[i_self])
         if ms is None or ms <= 0 or not rest[i_calls].isdigit():
             continue
-        if not (name.startswith("void ") or "::" in name and "(" in name or "kernel" in name.lower() or "Memcpy" in name
-                or "Memset" in name or name.startswith("nccl")):
+        is_kernel = (name.startswith("void ") or "::" in name and "(" in name or "kernel" in name.lower() or "Memcpy" in name
+                     or "Memset" in name or name.startswith("nccl") or re.search(r"cudnn_generated|_sdpa_|flash_[fb]prop|cutlass", name))
+        if not is_kernel or name.startswith("aten::") or name.startswith("autograd::"):
             continue          # autograd / operator rows repeat their kernels' time
         rows.append((name, ms, int(rest[i_calls])))
     return rows
