@@ -15,15 +15,28 @@ __global__ void __launch_bounds__(TPB) rmsnorm_fwd_wide(const __nv_bfloat16* __r
                                                         int rows, int H, float eps) {
   __shared__ float red[TPB / 32];
   const int nvec = H / 8;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  // the next row is requested before this row's block-wide sum, so the two barriers of a row overlap its loads
+  uint4 nxt[VPT];
+  auto fetch = [&](int row) {
+    if (row < rows) {
+      const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * TPB;
+        if (idx < nvec) nxt[i] = xr[idx];
+      }
+    }
+  };
+  fetch(blockIdx.x);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
     uint4 v[VPT];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * TPB;
+      v[i] = nxt[i];
       if (idx < nvec) {
-        v[i] = xr[idx];
         const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -32,6 +45,7 @@ __global__ void __launch_bounds__(TPB) rmsnorm_fwd_wide(const __nv_bfloat16* __r
         }
       }
     }
+    fetch(row + gridDim.x);
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
@@ -42,7 +56,6 @@ __global__ void __launch_bounds__(TPB) rmsnorm_fwd_wide(const __nv_bfloat16* __r
     const float rstd = rsqrtf(tot / H + eps);
     if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
     uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
-    const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * TPB;
@@ -547,16 +560,31 @@ struct StridedCopy {
   int inner_vecs, d1, d2, d3;
   long long ss[4], ds[4];
 };
+// One work item = U consecutive 16-byte vectors of one inner run (they share the outer indices, so the index arithmetic -
+// 32-bit here, the 64-bit divisions of a flat index made this kernel ALU-bound - is paid once per 16 U bytes).
+// WS (warp-strided, runs of at least 32 U vectors): a warp moves 32 U consecutive vectors, lane l taking l, l + 32, ...,
+// so every load and store instruction covers 512 contiguous bytes; otherwise a thread moves U consecutive vectors.
+template <int U, bool WS>
 __global__ void __launch_bounds__(256) strided_copy_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, const StridedCopy c) {
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < c.n_vec; idx += (long long)gridDim.x * blockDim.x) {
-    const int v = (int)(idx % c.inner_vecs);
-    long long rest = idx / c.inner_vecs;
-    const int i3 = (int)(rest % c.d3); rest /= c.d3;
-    const int i2 = (int)(rest % c.d2); rest /= c.d2;
-    const int i1 = (int)(rest % c.d1);
-    const long long i0 = rest / c.d1;
-    const uint4 val = *reinterpret_cast<const uint4*>(src + i0 * c.ss[0] + i1 * c.ss[1] + i2 * c.ss[2] + i3 * c.ss[3] + (long long)v * 16);
-    *reinterpret_cast<uint4*>(dst + i0 * c.ds[0] + i1 * c.ds[1] + i2 * c.ds[2] + i3 * c.ds[3] + (long long)v * 16) = val;
+  const unsigned groups_per_run = (unsigned)c.inner_vecs / U;          // WS: in units of lanes, i.e. 32 groups per warp item
+  const unsigned n_items = (unsigned)(c.n_vec / U);
+  for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n_items; idx += gridDim.x * blockDim.x) {
+    const unsigned vg = idx % groups_per_run;
+    unsigned rest = idx / groups_per_run;
+    const unsigned i3 = rest % (unsigned)c.d3; rest /= (unsigned)c.d3;
+    const unsigned i2 = rest % (unsigned)c.d2; rest /= (unsigned)c.d2;
+    const unsigned i1 = rest % (unsigned)c.d1;
+    const unsigned i0 = rest / (unsigned)c.d1;
+    // WS: vg = 32 * block + lane within the run; the block's vectors start at 32 U block
+    const unsigned first = WS ? (vg >> 5) * (32u * U) + (vg & 31u) : vg * U;
+    constexpr unsigned step = WS ? 32u : 1u;
+    const uint4* sp = reinterpret_cast<const uint4*>(src + i0 * c.ss[0] + i1 * c.ss[1] + i2 * c.ss[2] + i3 * c.ss[3]) + first;
+    uint4* dp = reinterpret_cast<uint4*>(dst + i0 * c.ds[0] + i1 * c.ds[1] + i2 * c.ds[2] + i3 * c.ds[3]) + first;
+    uint4 val[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) val[u] = sp[u * step];
+#pragma unroll
+    for (int u = 0; u < U; ++u) dp[u * step] = val[u];
   }
 }
 
@@ -574,9 +602,15 @@ extern "C" int cm_strided_copy(const void* src, void* dst, const long long* size
   c.n_vec = sizes[0] * sizes[1] * sizes[2] * sizes[3] * c.inner_vecs;
   if (c.n_vec <= 0) return 0;
   for (int i = 0; i < 4; ++i) { c.ss[i] = sstr[i]; c.ds[i] = dstr[i]; }
-  long long blocks = (c.n_vec + 255) / 256;
+  if (c.n_vec >= (1ll << 31)) return -11;                         // 32 GiB in one copy: split it
+  const int U = (c.inner_vecs % 4 == 0) ? 4 : (c.inner_vecs % 2 == 0 ? 2 : 1);
+  long long blocks = (c.n_vec / U + 255) / 256;
   const long long cap = (long long)cm::sm_count() * 16;
-  cm::strided_copy_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, c);
+  const int grid = (int)(blocks < cap ? blocks : cap);
+  if (c.inner_vecs % 128 == 0) cm::strided_copy_kernel<4, true><<<grid, 256, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, c);
+  else if (U == 4) cm::strided_copy_kernel<4, false><<<grid, 256, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, c);
+  else if (U == 2) cm::strided_copy_kernel<2, false><<<grid, 256, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, c);
+  else cm::strided_copy_kernel<1, false><<<grid, 256, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, c);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

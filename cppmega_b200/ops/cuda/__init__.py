@@ -173,6 +173,7 @@ def fast_copy_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
     n_in, s_in, d_in = dims[-1]
     outer = dims[:-1]
     if (s_in != 1 or d_in != 1 or (n_in * es) % 16 or len(outer) > 4 or src.data_ptr() % 16 or dst.data_ptr() % 16
+            or dst.numel() * es >= 2 ** 35
             or any((a * es) % 16 or (b * es) % 16 for _, a, b in outer)):
         return dst.copy_(src)
     outer = [(1, 0, 0)] * (4 - len(outer)) + outer

@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for Nsight Compute captures of single kernels.
 
-    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,m2rnn_bwd,sparse_mla,indexer,ce,rmsnorm,mxfp8_gemm}
+    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,m2rnn_bwd,sparse_mla,indexer,ce,rmsnorm,rmsnorm_bwd,adamw,quantize,strided_copy,mxfp8_gemm}
 
 Each case launches its kernel three times on inputs that exceed the 126 MB L2 but hold at most a few GB, so a
 ``--set full`` capture of one launch finishes in a minute or two:
@@ -163,9 +163,51 @@ def case_rmsnorm():
     torch.cuda.synchronize()
 
 
+def case_rmsnorm_bwd():
+    from cppmega_b200.ops import cuda as cu
+    x = torch.randn(65536, 4096, device="cuda").bfloat16().requires_grad_()
+    w = torch.ones(4096, device="cuda").bfloat16().requires_grad_()
+    g = torch.randn(65536, 4096, device="cuda").bfloat16()
+    for _ in range(3):
+        cu.rmsnorm(x, w, 1e-5).backward(g)
+    torch.cuda.synchronize()
+
+
+def case_adamw():
+    from cppmega_b200.ops import cuda as cu
+    n = 256 * 1024 * 1024
+    master, m, v = (torch.randn(n, device="cuda") * 0.01 for _ in range(3))
+    v.abs_()
+    g = torch.randn(n, device="cuda").bfloat16()
+    out = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    wd = torch.ones(n, device="cuda", dtype=torch.bool)
+    clip = torch.tensor(1.0, device="cuda")
+    for _ in range(3):
+        cu.adamw_shard(master, m, v, g, out, wd, clip, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05)
+    torch.cuda.synchronize()
+
+
+def case_quantize():
+    from cppmega_b200.ops.cuda import mxfp8
+    x = torch.randn(16384, 24960, device="cuda").bfloat16()
+    for _ in range(3):
+        mxfp8.quantize_both(x)
+    torch.cuda.synchronize()
+
+
+def case_strided_copy():
+    from cppmega_b200.ops.cuda import fast_contiguous
+    packed = torch.randn(4, 4096, 24960, device="cuda").bfloat16()
+    view = packed[..., 8192:16384]
+    for _ in range(3):
+        fast_contiguous(view)
+    torch.cuda.synchronize()
+
+
 CASES = {"gemm": case_gemm, "gemm_wgrad": lambda: case_gemm(True, True), "scan_fwd": case_scan_fwd,
          "scan_bwd": case_scan_bwd, "m2rnn": case_m2rnn, "ce": case_ce, "rmsnorm": case_rmsnorm, "mxfp8_gemm": case_mxfp8_gemm,
-         "m2rnn_bwd": case_m2rnn_bwd, "sparse_mla": case_sparse_mla, "indexer": case_indexer}
+         "m2rnn_bwd": case_m2rnn_bwd, "sparse_mla": case_sparse_mla, "indexer": case_indexer,
+         "rmsnorm_bwd": case_rmsnorm_bwd, "adamw": case_adamw, "quantize": case_quantize, "strided_copy": case_strided_copy}
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else ""

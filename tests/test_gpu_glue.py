@@ -298,6 +298,8 @@ def test_fast_strided_copy_and_cat_split_helpers():
     exp = torch.randn(3, 130, 1, 64, device="cuda").bfloat16().expand(3, 130, 32, 64)             # stride-0 source
     assert torch.equal(fast_contiguous(exp), exp.contiguous())
     assert F_.launch_counts().get("strided_copy", 0) == n0 + 3
+    wide = packed[..., 8192:8192 + 4096]                                                          # 8 KB runs: warp-strided variant
+    assert torch.equal(fast_contiguous(wide), wide.contiguous())
     odd = torch.randn(5, 7, 9, device="cuda").bfloat16()[..., 1:6]                                # 10-byte runs: library path
     assert torch.equal(fast_contiguous(odd), odd.contiguous())
     # autograd of the helpers against torch.cat / slicing
