@@ -9,6 +9,51 @@ namespace cm {
 // ---------------------------------------------------------------------------------------------
 // RMSNorm.  One CTA of TPB threads per row for wide rows; one warp per row for narrow rows.
 // ---------------------------------------------------------------------------------------------
+// H = 256 VPL: one warp per row, VPL 16-byte vectors per lane (lane l takes vectors l, l + 32, ...): no block barrier,
+// eight independent rows in flight per CTA.
+template <int VPL>
+__global__ void __launch_bounds__(256, 2) rmsnorm_fwd_warp(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                        __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int rows, float eps) {
+  constexpr int H = VPL * 256;
+  const int lane = threadIdx.x & 31;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+    uint4 v[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) v[i] = xr[lane + i * 32];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(b[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / H + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * H);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const uint4 wv = wr[lane + i * 32];
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+      const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      uint4 o;
+      uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(b[j]);
+        const float2 g = __bfloat1622float2(wb[j]);
+        op[j] = pack_bf16(f.x * rstd * g.x, f.y * rstd * g.y);
+      }
+      yr[lane + i * 32] = o;
+    }
+  }
+}
+
 template <int TPB, int VPT>   // VPT 16-byte vectors per thread; row width <= TPB*VPT*8
 __global__ void __launch_bounds__(TPB) rmsnorm_fwd_wide(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                         __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
@@ -635,6 +680,10 @@ extern "C" int cm_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
     int grid = (rows + wpb - 1) / wpb;
     grid = grid < sm_count() * 8 ? grid : sm_count() * 8;
     rmsnorm_fwd_narrow<<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, H, eps);
+  } else if (H == 4096) {
+    int grid = (rows + 7) / 8;
+    grid = grid < sm_count() * 4 ? grid : sm_count() * 4;
+    rmsnorm_fwd_warp<16><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, rows, eps);
   } else if (H <= 128 * 4 * 8) {
     int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
     rmsnorm_fwd_wide<128, 4><<<grid, 128, 0, s>>>(xp, wp, yp, rstd, rows, H, eps);
