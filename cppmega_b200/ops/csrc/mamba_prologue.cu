@@ -12,31 +12,57 @@ namespace cm {
 
 constexpr int ANG_SEG = 512;
 
-// grid: ceil(B*H*nseg / 4) blocks of 128 threads.  Warps with the longest read-only prefix come first.
+// Forward prefix sums in two passes over segments of ANG_FSEG tokens, one warp per (batch, head, segment), lane = angle:
+//   pass 1 (WRITE = false)  segment totals -> segsum[b, h, seg, a];
+//   pass 2 (WRITE = true)   start from the totals of the earlier segments and write the running sums.
+// The dt of a segment sits in registers (lane l holds tokens l, l + 32, ...) and reaches the serial chain by shuffle,
+// the raw angles of 32 tokens are requested together, so the chain of 256 dependent FMAs never waits on memory.
+constexpr int ANG_FSEG = 256;
+
+template <bool WRITE>
 __global__ void __launch_bounds__(128) angle_cumsum_fwd_kernel(const float* __restrict__ raw, const float* __restrict__ dt,
                                                                long long dsb, long long dsh, long long dss,
-                                                               float* __restrict__ out, int B, int S, int H, int A, int nseg) {
+                                                               float* __restrict__ out, float* __restrict__ segsum, int B, int S, int H,
+                                                               int A, int nseg) {
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   const long long BH = (long long)B * H;
   if (w >= BH * nseg) return;
-  const int seg = nseg - 1 - (int)(w / BH);
+  const int seg = (int)(w / BH);                 // neighbouring warps: neighbouring heads, the same dt cache lines
   const int bh = (int)(w % BH);
   const int b = bh / H, h = bh % H;
   const bool on = lane < A;
-  const float* rp = raw + (size_t)b * S * A + (on ? lane : 0);
-  const float* dp = dt + b * dsb + h * dsh;
-  float acc = 0.f;
-  const int t0 = seg * ANG_SEG;
-  const int t1 = min(S, t0 + ANG_SEG);
-#pragma unroll 8
-  for (int t = 0; t < t0; ++t) acc = fmaf(rp[(size_t)t * A], dp[t * dss], acc);
-  float* op = out + ((size_t)b * S * H + h) * A + lane;
-#pragma unroll 8
-  for (int t = t0; t < t1; ++t) {
-    acc = fmaf(rp[(size_t)t * A], dp[t * dss], acc);
-    if (on) op[(size_t)t * H * A] = acc;
+  const int t0 = seg * ANG_FSEG;
+  const float* rp = raw + ((size_t)b * S + t0) * A + (on ? lane : 0);
+  const float* dp = dt + b * dsb + h * dsh + (long long)t0 * dss;
+  float dreg[ANG_FSEG / 32];
+#pragma unroll
+  for (int k = 0; k < ANG_FSEG / 32; ++k) {
+    const int t = t0 + k * 32 + lane;
+    dreg[k] = t < S ? dp[(long long)(k * 32 + lane) * dss] : 0.f;
   }
+  float acc = 0.f;
+  if (WRITE && on) {
+    const float* sp = segsum + ((size_t)bh * nseg) * A + lane;
+    for (int s2 = 0; s2 < seg; ++s2) acc += sp[(size_t)s2 * A];
+  }
+  float* op = out + (((size_t)b * S + t0) * H + h) * A + lane;
+#pragma unroll 1
+  for (int k = 0; k < ANG_FSEG / 32; ++k) {
+    if (t0 + k * 32 >= S) break;
+    float r[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = (t0 + k * 32 + j < S) ? rp[(size_t)(k * 32 + j) * A] : 0.f;
+    float dk = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < ANG_FSEG / 32; ++kk) dk = (kk == k) ? dreg[kk] : dk;      // keeps dreg in registers
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      acc = fmaf(r[j], __shfl_sync(0xffffffffu, dk, j), acc);
+      if (WRITE && on && t0 + k * 32 + j < S) op[(size_t)(k * 32 + j) * H * A] = acc;
+    }
+  }
+  if (!WRITE && on) segsum[((size_t)bh * nseg + seg) * A + lane] = acc;
 }
 
 // segsum[b,h,seg,a] = sum over the segment of g[b,t,h,a]
@@ -162,13 +188,16 @@ extern "C" int cm_head_reduce(const void* dh, void* dgrp, float* dbias, long lon
 }
 
 // raw [B,S,A] fp32 contiguous; dt addressed as dt[b*dsb + h*dsh + t*dss] (element strides); out [B,S,H,A] fp32.
+// segsum: [B * H * ceil(S / 256) * A] fp32 scratch
 extern "C" int cm_angle_cumsum_fwd(const float* raw, const float* dt, long long dsb, long long dsh, long long dss, float* out,
-                                   int B, int S, int H, int A, cudaStream_t s) {
+                                   float* segsum, int B, int S, int H, int A, cudaStream_t s) {
   if (B <= 0 || S <= 0 || H <= 0) return 0;
   if (A <= 0 || A > 32) return -10;
-  const int nseg = (S + ANG_SEG - 1) / ANG_SEG;
+  const int nseg = (S + ANG_FSEG - 1) / ANG_FSEG;
   const long long warps = (long long)B * H * nseg;
-  angle_cumsum_fwd_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, s>>>(raw, dt, dsb, dsh, dss, out, B, S, H, A, nseg);
+  const unsigned grid = (unsigned)((warps + 3) / 4);
+  if (nseg > 1) angle_cumsum_fwd_kernel<false><<<grid, 128, 0, s>>>(raw, dt, dsb, dsh, dss, out, segsum, B, S, H, A, nseg);
+  angle_cumsum_fwd_kernel<true><<<grid, 128, 0, s>>>(raw, dt, dsb, dsh, dss, out, segsum, B, S, H, A, nseg);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -13,7 +13,7 @@ ANG_SEG = 512
 def declare(L: ctypes.CDLL) -> None:
     vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     sig = {
-        "cm_angle_cumsum_fwd": [vp, vp, i64, i64, i64, vp, i32, i32, i32, i32, vp],
+        "cm_angle_cumsum_fwd": [vp, vp, i64, i64, i64, vp, vp, i32, i32, i32, i32, vp],
         "cm_angle_cumsum_bwd": [vp, vp, vp, i64, i64, i64, vp, vp, vp, i32, i32, i32, i32, vp],
     }
     f32 = ctypes.c_float
@@ -46,7 +46,8 @@ class AngleCumsumFn(torch.autograd.Function):
         dt32 = dt if dt.dtype == torch.float32 else dt.float()
         out = torch.empty(B, S, H, A, dtype=torch.float32, device=raw.device)
         sb, sh, ss = dt32.stride()
-        _check(lib().cm_angle_cumsum_fwd(raw32.data_ptr(), dt32.data_ptr(), sb, sh, ss, out.data_ptr(), B, S, H, A,
+        seg_tot = torch.empty(B * H * ((S + 255) // 256) * A, dtype=torch.float32, device=raw.device)
+        _check(lib().cm_angle_cumsum_fwd(raw32.data_ptr(), dt32.data_ptr(), sb, sh, ss, out.data_ptr(), seg_tot.data_ptr(), B, S, H, A,
                                          stream_ptr()), "cm_angle_cumsum_fwd")
         F_.count_launch("angle_cumsum")
         ctx.save_for_backward(raw32, dt32)
