@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for Nsight Compute captures of single kernels.
 
-    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,m2rnn_bwd,sparse_mla,indexer,ce,rmsnorm,rmsnorm_bwd,adamw,quantize,strided_copy,mxfp8_gemm}
+    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,m2rnn_bwd,sparse_mla,indexer,ce,rmsnorm,rmsnorm_bwd,adamw,quantize,strided_copy,moe_local,mxfp8_gemm}
 
 Each case launches its kernel three times on inputs that exceed the 126 MB L2 but hold at most a few GB, so a
 ``--set full`` capture of one launch finishes in a minute or two:
@@ -204,10 +204,42 @@ def case_strided_copy():
     torch.cuda.synchronize()
 
 
+def case_moe_local():
+    """One MoE layer of the NAM56R recipe on one GPU (16 local experts): the permute-fused push / pull kernels and the
+    grouped GEMMs, forward + backward."""
+    import dataclasses
+    from cppmega_b200.config.model import nam56r_full
+    from cppmega_b200.models.moe import MoELayer
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.parallel import fused_moe
+    from cppmega_b200.parallel import state as pstate
+    from cppmega_b200.parallel.state import ParallelConfig
+    pc = pstate.initialize(ParallelConfig())
+    mcfg = nam56r_full()
+    mcfg = dataclasses.replace(mcfg, moe=dataclasses.replace(mcfg.moe, aux_loss_coeff=0.0))
+    dev = torch.device("cuda", 0)
+    layer = MoELayer(mcfg.hidden_size, mcfg.moe, pc, "case.layer", dtype=torch.bfloat16, seed=1).to(dev)
+
+    class _M(torch.nn.Module):
+        cfg = mcfg
+
+        def moe_layers(self):
+            return [layer]
+
+    fused_moe.attach(_M(), pc, dev, tokens_per_rank=0)
+    x = (torch.randn(4, 4096, mcfg.hidden_size, device=dev) * 0.5).bfloat16().requires_grad_()
+    g = torch.randn_like(x)
+    for _ in range(3):
+        layer(x).backward(g)
+    torch.cuda.synchronize()
+    cu.check_errors()
+    pstate.destroy()
+
+
 CASES = {"gemm": case_gemm, "gemm_wgrad": lambda: case_gemm(True, True), "scan_fwd": case_scan_fwd,
          "scan_bwd": case_scan_bwd, "m2rnn": case_m2rnn, "ce": case_ce, "rmsnorm": case_rmsnorm, "mxfp8_gemm": case_mxfp8_gemm,
          "m2rnn_bwd": case_m2rnn_bwd, "sparse_mla": case_sparse_mla, "indexer": case_indexer,
-         "rmsnorm_bwd": case_rmsnorm_bwd, "adamw": case_adamw, "quantize": case_quantize, "strided_copy": case_strided_copy}
+         "rmsnorm_bwd": case_rmsnorm_bwd, "adamw": case_adamw, "quantize": case_quantize, "strided_copy": case_strided_copy, "moe_local": case_moe_local}
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else ""
