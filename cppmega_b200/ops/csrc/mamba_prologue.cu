@@ -71,16 +71,17 @@ __global__ void __launch_bounds__(128) angle_segsum_kernel(const float* __restri
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (w >= (long long)B * H * nseg) return;
-  const int seg = (int)(w % nseg);
-  const int bh = (int)(w / nseg);
+  const long long BH = (long long)B * H;
+  const int seg = (int)(w / BH);                 // the warps of a CTA take neighbouring heads: neighbouring 128-byte lines
+  const int bh = (int)(w % BH);
   const int b = bh / H, h = bh % H;
   if (lane >= A) return;
   const float* gp = g + ((size_t)b * S * H + h) * A + lane;
   const int t0 = seg * ANG_SEG, t1 = min(S, t0 + ANG_SEG);
   float acc = 0.f;
-#pragma unroll 8
+#pragma unroll 16
   for (int t = t0; t < t1; ++t) acc += gp[(size_t)t * H * A];
-  segsum[w * A + lane] = acc;
+  segsum[((size_t)bh * nseg + seg) * A + lane] = acc;
 }
 
 // suffix sums in place: g[b,t,h,a] <- sum_{s>=t} g[b,s,h,a]
@@ -89,18 +90,32 @@ __global__ void __launch_bounds__(128) angle_suffix_kernel(float* __restrict__ g
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (w >= (long long)B * H * nseg) return;
-  const int seg = (int)(w % nseg);
-  const int bh = (int)(w / nseg);
+  const long long BH = (long long)B * H;
+  const int seg = (int)(w / BH);
+  const int bh = (int)(w % BH);
   const int b = bh / H, h = bh % H;
   if (lane >= A) return;
   float acc = 0.f;
   for (int s2 = nseg - 1; s2 > seg; --s2) acc += segsum[((size_t)bh * nseg + s2) * A + lane];
   float* gp = g + ((size_t)b * S * H + h) * A + lane;
   const int t0 = seg * ANG_SEG, t1 = min(S, t0 + ANG_SEG);
-#pragma unroll 8
-  for (int t = t1 - 1; t >= t0; --t) {
-    acc += gp[(size_t)t * H * A];
-    gp[(size_t)t * H * A] = acc;
+  // 16 independent loads first, then the running sum and the stores: in a plain read-modify-write loop every load waits
+  // behind the previous store to the same array
+  const size_t st = (size_t)H * A;
+  int t = t1 - 1;
+  for (; t - 15 >= t0; t -= 16) {
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = gp[(size_t)(t - j) * st];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      acc += v[j];
+      gp[(size_t)(t - j) * st] = acc;
+    }
+  }
+  for (; t >= t0; --t) {
+    acc += gp[(size_t)t * st];
+    gp[(size_t)t * st] = acc;
   }
 }
 
