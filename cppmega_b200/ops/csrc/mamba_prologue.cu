@@ -119,6 +119,57 @@ __global__ void __launch_bounds__(128) angle_suffix_kernel(float* __restrict__ g
   }
 }
 
+// Same reduction for A == 32 and S % 32 == 0, one block per 32 consecutive tokens, lane = token: a thread reads the 32
+// angles of its (token, head) as one 128-byte run, so ddt needs no shuffle and is written 32 tokens at a time; draw is
+// accumulated over a warp's heads in registers and summed over the 8 warps through shared memory.
+__global__ void __launch_bounds__(256) angle_reduce32_kernel(const float* __restrict__ g, const float* __restrict__ raw,
+                                                             const float* __restrict__ dt, long long dsb, long long dsh, long long dss,
+                                                             float* __restrict__ draw, float* __restrict__ ddt, int B, int S, int H) {
+  constexpr int A = 32;
+  __shared__ float red[8][32][A + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long tile = blockIdx.x;                       // 32 tokens
+  const int tiles_per_b = S / 32;
+  const int b = (int)(tile / tiles_per_b);
+  const int t = (int)(tile % tiles_per_b) * 32 + lane;
+  const size_t tok = (size_t)b * S + t;
+  float rv[A], acc[A];
+  {
+    const float4* rp = reinterpret_cast<const float4*>(raw + tok * A);
+#pragma unroll
+    for (int q = 0; q < A / 4; ++q) {
+      const float4 v = rp[q];
+      rv[4 * q] = v.x; rv[4 * q + 1] = v.y; rv[4 * q + 2] = v.z; rv[4 * q + 3] = v.w;
+      acc[4 * q] = 0.f; acc[4 * q + 1] = 0.f; acc[4 * q + 2] = 0.f; acc[4 * q + 3] = 0.f;
+    }
+  }
+  for (int h = warp; h < H; h += 8) {
+    const float4* gp = reinterpret_cast<const float4*>(g + (tok * H + h) * A);
+    const float d = dt[b * dsb + h * dsh + (long long)t * dss];
+    float s = 0.f;
+#pragma unroll
+    for (int q = 0; q < A / 4; ++q) {
+      const float4 v = gp[q];
+      s += v.x * rv[4 * q] + v.y * rv[4 * q + 1] + v.z * rv[4 * q + 2] + v.w * rv[4 * q + 3];
+      acc[4 * q] = fmaf(v.x, d, acc[4 * q]);
+      acc[4 * q + 1] = fmaf(v.y, d, acc[4 * q + 1]);
+      acc[4 * q + 2] = fmaf(v.z, d, acc[4 * q + 2]);
+      acc[4 * q + 3] = fmaf(v.w, d, acc[4 * q + 3]);
+    }
+    ddt[((size_t)b * H + h) * S + t] = s;
+  }
+#pragma unroll
+  for (int a = 0; a < A; ++a) red[warp][lane][a] = acc[a];
+  __syncthreads();
+  for (int e = threadIdx.x; e < 32 * A; e += 256) {
+    const int tt = e / A, a = e % A;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += red[w][tt][a];
+    draw[((size_t)b * S + (tile % tiles_per_b) * 32 + tt) * A + a] = s;
+  }
+}
+
 // one block per token: draw[b,t,a] = sum_h g*dt ; ddt[b,h,t] = sum_a g*raw     (g holds the suffix sums)
 __global__ void __launch_bounds__(256) angle_reduce_kernel(const float* __restrict__ g, const float* __restrict__ raw,
                                                            const float* __restrict__ dt, long long dsb, long long dsh, long long dss,
@@ -227,6 +278,9 @@ extern "C" int cm_angle_cumsum_bwd(float* g, const float* raw, const float* dt, 
   const unsigned grid = (unsigned)((warps + 3) / 4);
   angle_segsum_kernel<<<grid, 128, 0, s>>>(g, segsum, B, S, H, A, nseg);
   angle_suffix_kernel<<<grid, 128, 0, s>>>(g, segsum, B, S, H, A, nseg);
-  angle_reduce_kernel<<<(unsigned)((long long)B * S), 256, 0, s>>>(g, raw, dt, dsb, dsh, dss, draw, ddt, B, S, H, A);
+  if (A == 32 && S % 32 == 0)
+    angle_reduce32_kernel<<<(unsigned)((long long)B * S / 32), 256, 0, s>>>(g, raw, dt, dsb, dsh, dss, draw, ddt, B, S, H);
+  else
+    angle_reduce_kernel<<<(unsigned)((long long)B * S), 256, 0, s>>>(g, raw, dt, dsb, dsh, dss, draw, ddt, B, S, H, A);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
