@@ -88,3 +88,16 @@ def test_profile_report_groups_kernel_rows():
     assert groups["dense GEMM (tcgen05 bf16)"]["ms"] == 100.0 and groups["grouped GEMM (experts)"]["launches"] == 4
     assert groups["Mamba3 MIMO scan"]["ms"] == 50.0 and groups["PyTorch elementwise / copy / cat"]["ms"] == 0.5
     assert rep["top"][0]["ms"] == 100.0
+
+
+def test_gpu_tool_modules_import_and_list_their_cases():
+    """The GPU-side tools must at least import on a CPU box and expose the cases the profile notes cite."""
+    from cppmega_b200.tools import kernel_bench, moe_bench, ncu_cases
+    for name in ("gemm", "scan_fwd", "scan_bwd", "m2rnn_bwd", "sparse_mla", "indexer", "mxfp8_gemm", "adamw", "rmsnorm",
+                 "rmsnorm_bwd", "quantize", "strided_copy", "moe_local", "ce"):
+        assert name in ncu_cases.CASES, name
+    for name in ("gemm", "grouped", "rmsnorm", "ce", "scan", "mxfp8_gemm", "longctx"):
+        assert name in kernel_bench.CASES, name
+    assert callable(moe_bench.main)
+    pk = kernel_bench.peaks()
+    assert pk["bf16_tflops"] > 0 and pk["kind"] in ("measured", "fallback")
