@@ -101,3 +101,40 @@ def test_gpu_tool_modules_import_and_list_their_cases():
     assert callable(moe_bench.main)
     pk = kernel_bench.peaks()
     assert pk["bf16_tflops"] > 0 and pk["kind"] in ("measured", "fallback")
+
+
+def test_verify_dataset_accepts_good_and_flags_bad(tmp_path):
+    import numpy as np
+    from cppmega_b200.data.indexed import write_indexed_dataset
+    from cppmega_b200.tools import verify_dataset
+    docs = [np.array([5, 6, 7, 0], dtype=np.int32), np.array([9, 0], dtype=np.int32)]
+    prefix = str(tmp_path / "d")
+    write_indexed_dataset(prefix, docs, dtype=np.int32)
+    good = verify_dataset.verify(prefix, vocab_size=16, eod=0)
+    assert good["problems"] == [] and good["documents"] == 2 and good["tokens"] == 6
+    assert any("vocabulary" in p for p in verify_dataset.verify(prefix, vocab_size=8)["problems"])
+    assert any("eod" in p for p in verify_dataset.verify(prefix, eod=3)["problems"])
+    with open(prefix + ".bin", "ab") as f:
+        f.write(b"\\x00\\x00\\x00\\x00")
+    assert any(".bin file" in p for p in verify_dataset.verify(prefix)["problems"])
+    assert verify_dataset.main([prefix]) == 1
+
+
+def test_nan_hunter_names_the_first_bad_module():
+    import torch
+    import torch.nn as nn
+    from cppmega_b200.utils.nan_hunt import NonFiniteHunter
+
+    class Bad(nn.Module):
+        def forward(self, x):
+            return x / (x - x)            # 0 / 0
+
+    net = nn.Sequential(nn.Linear(4, 4), nn.Tanh(), Bad(), nn.Linear(4, 2))
+    with NonFiniteHunter(net) as h:
+        net(torch.ones(3, 4)).sum().backward()
+        assert h.first == ("forward", "2") and "forward of '2'" in h.report()
+        h.reset()
+        net[2] = nn.Identity()
+    with NonFiniteHunter(net) as h2:
+        net(torch.ones(3, 4)).sum().backward()
+        assert h2.first is None and "finite" in h2.report()
