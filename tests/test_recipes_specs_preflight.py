@@ -166,3 +166,33 @@ def test_cuda_graph_scope_parsing_and_argument_round_trip():
     assert tcfg.cuda_graph_scope == ("mamba", "mlp")
     import torch.nn as nn
     assert cuda_graphs.capture_model_layers(nn.Linear(2, 2), ["mamba"], (1, 2, 2), None, "cpu") == 0
+
+
+def test_moe_plan_invariants_on_cpu():
+    """The library-op definition of the routing plan (the oracle of the plan kernels): destinations are unique, lie in
+    their expert's padded segment on the owning rank, and the tile map agrees with the segments."""
+    from cppmega_b200.parallel.fused_moe import MoEPlan, TILE
+    torch.manual_seed(0)
+    T, k, E, ep = 500, 4, 16, 4
+    El = E // ep
+    ids_by_rank = [torch.stack([torch.randperm(E)[:k] for _ in range(T)]) for _ in range(ep)]
+    counts = torch.stack([torch.bincount(i.reshape(-1), minlength=E) for i in ids_by_rank])      # [ep, E]
+    cap = ((T * k * ep + 16 * TILE) // TILE) * TILE
+    plans = [MoEPlan(ids_by_rank[r], E, ep, r, None, cap, gather=lambda c, r=r: counts.clone()) for r in range(ep)]
+    for owner in range(ep):
+        rows = torch.cat([p.dest_row[p.dest_rank == owner] for p in plans])
+        assert rows.unique().numel() == rows.numel()                                              # no two copies share a row
+        po = plans[owner]
+        tot = counts.sum(0)[owner * El:(owner + 1) * El]
+        assert torch.equal(po.tot_local.long(), tot)
+        seg = po.seg_offsets.long()
+        assert (seg % TILE == 0).all() and int(po.rows_used) == int(seg[-1]) <= cap
+        for r, p in enumerate(plans):
+            sel = p.dest_rank == owner
+            e_local = p_ids = ids_by_rank[r].reshape(-1)[sel] - owner * El
+            assert ((p.dest_row[sel] >= seg[e_local]) & (p.dest_row[sel] < seg[e_local] + tot[e_local])).all()
+        used_tiles = int(seg[-1]) // TILE
+        te = po.tile_expert.long()
+        assert (te[used_tiles:] == -1).all()
+        for e in range(El):
+            assert (te[int(seg[e]) // TILE:int(seg[e + 1]) // TILE] == e).all()
