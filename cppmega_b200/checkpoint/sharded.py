@@ -23,6 +23,7 @@ import dataclasses
 import json
 import os
 import re
+import warnings
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
@@ -111,7 +112,10 @@ def _iter_dir(root: str, iteration: int) -> str:
     return os.path.join(root, f"iter_{iteration:07d}")
 
 
-def save_checkpoint(root: str, iteration: int, model: nn.Module, pc, optimizer=None, extra: Optional[dict] = None) -> str:
+def save_checkpoint(root: str, iteration: int, model: nn.Module, pc, optimizer=None, extra: Optional[dict] = None,
+                    rank_extra: Optional[dict] = None) -> str:
+    """``extra`` (JSON-serialisable, rank 0's copy is kept) goes into ``metadata.json``; ``rank_extra`` (any picklable
+    per-rank state, e.g. random-generator states) into ``rank_state_rank<r>.pt``."""
     d = _iter_dir(root, iteration)
     rank = pc.rank
     if rank == 0:
@@ -124,6 +128,8 @@ def save_checkpoint(root: str, iteration: int, model: nn.Module, pc, optimizer=N
     metas = [dict(r.meta(), file=f"shards_rank{rank:05d}.pt", index=str(i)) for i, r in enumerate(recs)]
     if optimizer is not None:
         torch.save(optimizer.state_dict(), os.path.join(d, f"optim_rank{rank:05d}.pt"))
+    if rank_extra:
+        torch.save(rank_extra, os.path.join(d, f"rank_state_rank{rank:05d}.pt"))
     gathered: List[Optional[list]] = [None] * pc.world_size
     if dist.is_initialized() and pc.world_size > 1:
         dist.all_gather_object(gathered, metas)
@@ -186,8 +192,16 @@ def _overlap(dst_off, dst_shape, src_off, src_shape):
 
 
 def load_checkpoint(root: str, model: nn.Module, pc, optimizer=None, iteration: Optional[int] = None,
-                    strict: bool = True) -> dict:
-    """Fill every local shard from whatever shards the checkpoint holds (any TP/EP/PP layout)."""
+                    strict: bool = True, allow_optimizer_reset: bool = True) -> dict:
+    """Fill every local shard from whatever shards the checkpoint holds (any TP/EP/PP layout).
+
+    The optimizer shards can only be restored under the layout that wrote them.  Otherwise, with
+    ``allow_optimizer_reset`` the master weights are re-seeded from the loaded parameters and the moments start at
+    zero - reported with a warning and in the returned ``optimizer_reset``; without it the load raises.
+
+    Compatibility with Megatron checkpoints is at the level of keys, global shapes, offsets and replica rules; the
+    files themselves (``.pt`` shards plus ``metadata.json``) are this package's own and Megatron's dist-ckpt tools do
+    not read them."""
     it = iteration if iteration is not None else latest_iteration(root)
     if it is None:
         raise FileNotFoundError(f"no checkpoint under {root}")
@@ -226,14 +240,28 @@ def load_checkpoint(root: str, model: nn.Module, pc, optimizer=None, iteration: 
                 raise ValueError(f"{rec.key}: only {filled} of {rec.data.numel()} local elements found in the checkpoint")
     if missing and strict:
         raise KeyError(f"keys missing from the checkpoint: {missing[:8]}{'...' if len(missing) > 8 else ''}")
+    optimizer_reset = None
     if optimizer is not None:
         f = os.path.join(d, f"optim_rank{pc.rank:05d}.pt")
         same = meta["parallel"] == {"tp": pc.tp, "pp": pc.pp, "ep": pc.ep, "dp": pc.dp}
         if os.path.exists(f) and same:
             optimizer.load_state_dict(torch.load(f, map_location="cpu"))
         else:
+            why = (f"parallel layout changed ({meta['parallel']} -> tp{pc.tp} pp{pc.pp} ep{pc.ep} dp{pc.dp})" if not same
+                   else f"{os.path.basename(f)} is missing")
+            if not allow_optimizer_reset:
+                raise ValueError(f"cannot restore the optimizer state: {why}; pass allow_optimizer_reset=True "
+                                 "(--no-load-optim) to continue from the weights with fresh AdamW moments")
+            optimizer_reset = (f"optimizer state NOT restored ({why}): fp32 master weights re-seeded from the loaded "
+                               "parameters, AdamW moments zeroed")
+            warnings.warn(optimizer_reset)
             optimizer.reset_master_from_params()
-    return {"iteration": it, "extra": meta.get("extra", {}), "missing": missing}
+    rank_extra = {}
+    f = os.path.join(d, f"rank_state_rank{pc.rank:05d}.pt")
+    if os.path.exists(f) and meta.get("world_size") == pc.world_size:
+        rank_extra = torch.load(f, map_location="cpu")
+    return {"iteration": it, "extra": meta.get("extra", {}), "missing": missing, "rank_extra": rank_extra,
+            "optimizer_reset": optimizer_reset}
 
 
 _ = (Iterable, Sequence)

@@ -117,6 +117,24 @@ class TokenStream:
             batch = torch.stack(rows)
         return {"input_ids": batch[:, :-1].contiguous(), "labels": batch[:, 1:].contiguous()}
 
+    def skip(self, n_batches: int) -> None:
+        """Advance the stream by ``n_batches`` micro-batches without returning them (resume from a checkpoint: the
+        number of batches a run has consumed is stored with it).  The pure-Python reader replays only the cursor
+        arithmetic; the native loader has its samples in flight already and consumes them."""
+        if n_batches <= 0:
+            return
+        if self._lib is not None:
+            for _ in range(n_batches):
+                next(self)
+            return
+        for _ in range(n_batches * self.micro_batch):
+            g = self._cursor * self.world + self.rank
+            if g >= self.num_samples:
+                self._epoch += 1
+                self._order = self._perm()
+                self._cursor = 0
+            self._cursor += 1
+
     def close(self) -> None:
         if self._lib is not None and getattr(self, "_h", None):
             self._lib.cm_loader_close(self._h)

@@ -291,4 +291,16 @@ int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t batch, uint64
 
 int sm_count();
 
+// Function attributes (the dynamic shared-memory limit) are per device: a flag per (call site, device) says whether the
+// current device has been configured.  Usage: `static PerDevice cfg; if (cfg.first()) { cudaFuncSetAttribute(...); cfg.done(); }`
+struct PerDevice {
+  bool set[64] = {};
+  int dev = -1;
+  bool first() {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { dev = -1; return true; }
+    return !set[dev];
+  }
+  void done() { if (dev >= 0) set[dev] = true; }
+};
+
 }  // namespace cm

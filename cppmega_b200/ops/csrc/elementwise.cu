@@ -492,7 +492,8 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, 
                                                     const GradT* __restrict__ g, OutT* __restrict__ out,
                                                     const uint8_t* __restrict__ wd_mask, const float* __restrict__ clip,
                                                     long long n, float lr, float b1, float b2, float eps, float wd,
-                                                    float inv_bc1, float inv_bc2) {
+                                                    float inv_bc1, float inv_bc2, const int* __restrict__ gate) {
+  if (gate && *reinterpret_cast<const volatile int*>(gate) != 0) return;     // error word set: leave the state untouched
   const float cs = clip ? *clip : 1.f;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const float gi = float(g[i]) * cs;
@@ -515,7 +516,8 @@ __global__ void __launch_bounds__(256) adamw_vec4_kernel(float4* __restrict__ ma
                                                          const GradT* __restrict__ g, OutT* __restrict__ out,
                                                          const uchar4* __restrict__ wd_mask, const float* __restrict__ clip,
                                                          long long n4, float lr, float b1, float b2, float eps, float wd,
-                                                         float inv_bc1, float inv_bc2) {
+                                                         float inv_bc1, float inv_bc2, const int* __restrict__ gate) {
+  if (gate && *reinterpret_cast<const volatile int*>(gate) != 0) return;
   const float cs = clip ? *clip : 1.f;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     float gi[4];
@@ -737,10 +739,11 @@ extern "C" int cm_swiglu_bwd(const void* in, const void* dout, void* din, long l
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// grad_kind: 0 fp32, 1 bf16; out_kind: 0 fp32, 1 bf16
-extern "C" int cm_adamw(float* master, float* m, float* v, const void* g, void* out, const uint8_t* wd_mask,
-                        const float* clip, long long n, float lr, float b1, float b2, float eps, float wd, float bc1,
-                        float bc2, int grad_kind, int out_kind, cudaStream_t s) {
+// grad_kind: 0 fp32, 1 bf16; out_kind: 0 fp32, 1 bf16.  `gate` (may be null): a device word; when it is non-zero at run
+// time the update is skipped (the kernels' error word: a step whose collectives gave up must not reach the weights).
+extern "C" int cm_adamw_gated(float* master, float* m, float* v, const void* g, void* out, const uint8_t* wd_mask,
+                              const float* clip, long long n, float lr, float b1, float b2, float eps, float wd, float bc1,
+                              float bc2, int grad_kind, int out_kind, const int* gate, cudaStream_t s) {
   if (n <= 0) return 0;
   const float i1 = 1.f / bc1, i2 = 1.f / bc2;
   {
@@ -753,7 +756,7 @@ extern "C" int cm_adamw(float* master, float* m, float* v, const void* g, void* 
       const int vgrid = (int)(vb < (long long)sm_count() * 16 ? vb : (long long)sm_count() * 16);
 #define CM_ADAMW_V4(GT, OT)                                                                                               \
   adamw_vec4_kernel<GT, OT><<<vgrid, 256, 0, s>>>((float4*)master, (float4*)m, (float4*)v, (const GT*)g, (OT*)out,         \
-                                                  (const uchar4*)wd_mask, clip, n4, lr, b1, b2, eps, wd, i1, i2)
+                                                  (const uchar4*)wd_mask, clip, n4, lr, b1, b2, eps, wd, i1, i2, gate)
       if (grad_kind == 0 && out_kind == 1) CM_ADAMW_V4(float, __nv_bfloat16);
       else if (grad_kind == 1 && out_kind == 1) CM_ADAMW_V4(__nv_bfloat16, __nv_bfloat16);
       else if (grad_kind == 0 && out_kind == 0) CM_ADAMW_V4(float, float);
@@ -772,14 +775,20 @@ extern "C" int cm_adamw(float* master, float* m, float* v, const void* g, void* 
   long long blocks = (n + 255) / 256;
   int grid = (int)(blocks < (long long)sm_count() * 16 ? blocks : (long long)sm_count() * 16);
   if (grad_kind == 0 && out_kind == 1)
-    adamw_kernel<float, __nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, (const float*)g, (__nv_bfloat16*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2);
+    adamw_kernel<float, __nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, (const float*)g, (__nv_bfloat16*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2, gate);
   else if (grad_kind == 1 && out_kind == 1)
-    adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, (const __nv_bfloat16*)g, (__nv_bfloat16*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2);
+    adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, (const __nv_bfloat16*)g, (__nv_bfloat16*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2, gate);
   else if (grad_kind == 0 && out_kind == 0)
-    adamw_kernel<float, float><<<grid, 256, 0, s>>>(master, m, v, (const float*)g, (float*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2);
+    adamw_kernel<float, float><<<grid, 256, 0, s>>>(master, m, v, (const float*)g, (float*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2, gate);
   else
-    adamw_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(master, m, v, (const __nv_bfloat16*)g, (float*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2);
+    adamw_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(master, m, v, (const __nv_bfloat16*)g, (float*)out, wd_mask, clip, n, lr, b1, b2, eps, wd, i1, i2, gate);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int cm_adamw(float* master, float* m, float* v, const void* g, void* out, const uint8_t* wd_mask,
+                        const float* clip, long long n, float lr, float b1, float b2, float eps, float wd, float bc1,
+                        float bc2, int grad_kind, int out_kind, cudaStream_t s) {
+  return cm_adamw_gated(master, m, v, g, out, wd_mask, clip, n, lr, b1, b2, eps, wd, bc1, bc2, grad_kind, out_kind, nullptr, s);
 }
 
 // out (device float, caller zeroes it) += sum of squares of g.  kind: 0 fp32, 1 bf16

@@ -7,7 +7,8 @@
 //                 parameter all-gather).
 // One pass over the shard each; no staging copies, no separate cast / scale / update kernels.
 // Ordering across GPUs is carried by flag words (see symm.cu): gradients-ready before the pull,
-// parameters-ready after the push.
+// parameters-ready after the push.  Both kernels read the device error word first and do nothing when it is set:
+// a flag wait that timed out must not let half-reduced gradients reach the master weights or the peers.
 // Baseline being replaced: NCCL reduce-scatter + all-gather around a separate optimizer step
 // (87 ms/iter in the reference profile, docs/nam56r_mimo7_nsys_profile_2026_04_11.md:13,39).
 #include "common.cuh"
@@ -46,7 +47,11 @@ __device__ __forceinline__ void load8<float>(const float* p, float (&f)[8]) {
 // n must be a multiple of 8; all pointers 32-byte aligned at lo.
 template <typename GradT>
 __global__ void __launch_bounds__(256) reduce_shard_kernel(PeerPtrs grads, int world, int self, long long lo, long long n,
-                                                           float scale, float* __restrict__ red, float* __restrict__ sumsq) {
+                                                           float scale, float* __restrict__ red, float* __restrict__ sumsq,
+                                                           const int* __restrict__ err) {
+  // A bounded wait that ran out earlier on this stream (a peer never signalled) leaves the error word set: the peers'
+  // gradients may be incomplete, so this step's reduction and update are skipped on the device, with no host round trip.
+  if (err && *reinterpret_cast<const volatile int*>(err) != 0) return;
   float ss = 0.f;
   const long long nv = n / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
@@ -81,7 +86,8 @@ __global__ void __launch_bounds__(256) adamw_push_kernel(float* __restrict__ mas
                                                          const float* __restrict__ red, const uint8_t* __restrict__ wd_mask,
                                                          const float* __restrict__ clip, PeerPtrsMut params, int world,
                                                          long long lo, long long n, float lr, float b1, float b2, float eps,
-                                                         float wd, float inv_bc1, float inv_bc2) {
+                                                         float wd, float inv_bc1, float inv_bc2, const int* __restrict__ err) {
+  if (err && *reinterpret_cast<const volatile int*>(err) != 0) return;      // see reduce_shard_kernel: master, moments and peers stay untouched
   const float cs = clip ? *clip : 1.f;
   const long long nv = n / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
@@ -134,21 +140,21 @@ using namespace cm;
 
 // grad_ptrs / param_ptrs: host arrays of `world` device pointers (peer-mapped buffer bases).
 extern "C" int cm_reduce_shard(const void* const* grad_ptrs, int world, int self, long long lo, long long n, float scale,
-                               float* red, float* sumsq, int grad_kind, cudaStream_t s) {
+                               float* red, float* sumsq, int grad_kind, const int* err, cudaStream_t s) {
   if (n <= 0) return 0;
   if (world > MAX_PEERS || (n % 8) || (lo % 8)) return -10;
   PeerPtrs pp;
   for (int i = 0; i < world; ++i) pp.p[i] = grad_ptrs[i];
   long long blocks = (n / 8 + 255) / 256;
   int grid = (int)(blocks < (long long)sm_count() * 8 ? blocks : (long long)sm_count() * 8);
-  if (grad_kind == 0) reduce_shard_kernel<float><<<grid, 256, 0, s>>>(pp, world, self, lo, n, scale, red, sumsq);
-  else reduce_shard_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(pp, world, self, lo, n, scale, red, sumsq);
+  if (grad_kind == 0) reduce_shard_kernel<float><<<grid, 256, 0, s>>>(pp, world, self, lo, n, scale, red, sumsq, err);
+  else reduce_shard_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(pp, world, self, lo, n, scale, red, sumsq, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int cm_adamw_push(float* master, float* m, float* v, const float* red, const uint8_t* wd_mask, const float* clip,
                              void* const* param_ptrs, int world, long long lo, long long n, float lr, float b1, float b2,
-                             float eps, float wd, float bc1, float bc2, int out_kind, cudaStream_t s) {
+                             float eps, float wd, float bc1, float bc2, int out_kind, const int* err, cudaStream_t s) {
   if (n <= 0) return 0;
   if (world > MAX_PEERS || (n % 8) || (lo % 8)) return -10;
   PeerPtrsMut pp;
@@ -156,8 +162,8 @@ extern "C" int cm_adamw_push(float* master, float* m, float* v, const float* red
   long long blocks = (n / 8 + 255) / 256;
   int grid = (int)(blocks < (long long)sm_count() * 8 ? blocks : (long long)sm_count() * 8);
   if (out_kind == 1)
-    adamw_push_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, red, wd_mask, clip, pp, world, lo, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2);
+    adamw_push_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, red, wd_mask, clip, pp, world, lo, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2, err);
   else
-    adamw_push_kernel<float><<<grid, 256, 0, s>>>(master, m, v, red, wd_mask, clip, pp, world, lo, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2);
+    adamw_push_kernel<float><<<grid, 256, 0, s>>>(master, m, v, red, wd_mask, clip, pp, world, lo, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

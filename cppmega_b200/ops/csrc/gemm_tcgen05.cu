@@ -428,11 +428,11 @@ template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACC, int MODE>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, OutT* C, const GemmArgs& args, int total_tiles,
                   cudaStream_t stream) {
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT, ACC, MODE>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDevice configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL) != cudaSuccess)
       return -2;
-    configured = true;
+    configured.done();
   }
   int grid = total_tiles < sm_count() ? total_tiles : sm_count();
   if (grid <= 0) return 0;
@@ -444,11 +444,11 @@ template <int BN, bool B_MN>
 static int launch_peer_a(const PeerMaps& pm, const CUtensorMap& tmB, __nv_bfloat16* C, const GemmArgs& args, int total_tiles,
                          cudaStream_t stream) {
   auto kern = gemm_bf16_kernel<BN, false, B_MN, __nv_bfloat16, false, PEER_A>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDevice configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL) != cudaSuccess)
       return -2;
-    configured = true;
+    configured.done();
   }
   int grid = total_tiles < sm_count() ? total_tiles : sm_count();
   if (grid <= 0) return 0;
@@ -576,10 +576,10 @@ static int launch_peer_k(const PeerMaps& pm, const CUtensorMap& tmA, const CUten
                          int total_tiles, cudaStream_t stream) {
   constexpr int BN = 256;
   auto kern = gemm_bf16_kernel<BN, true, true, OutT, ACC, MODE>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDevice configured;
+  if (configured.first()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL) != cudaSuccess) return -2;
-    configured = true;
+    configured.done();
   }
   int grid = total_tiles < sm_count() ? total_tiles : sm_count();
   if (grid <= 0) return 0;

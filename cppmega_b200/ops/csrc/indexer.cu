@@ -227,10 +227,10 @@ extern "C" int cm_indexer_scores(const void* q, const void* k, const float* w, f
   if (rc) return rc;
   rc = make_tmap_3d_bf16(&tmK, k, B, S, DI, DI, KT, 64);
   if (rc) return rc;
-  static bool cfg = false;
-  if (!cfg) {
+  static PerDevice cfg;
+  if (cfg.first()) {
     if (cudaFuncSetAttribute(indexer_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, score_smem()) != cudaSuccess) return -2;
-    cfg = true;
+    cfg.done();
   }
   ScoreArgs a{w, scores, S, err};
   dim3 grid(S / QT, B);

@@ -784,11 +784,11 @@ extern "C" int cm_mimo_scan_bwd(const void* Qn, const void* Kn, const void* V, c
             dAngles, dADT, dTs, dGam, dPsi, dZeta, dPhi, dD_, B, S, H, G, C, ldV, ldZ, err, B * H * C};
   auto k0 = mimo_grad_state_kernel<128, 32>;
   auto k2 = mimo_chunk_grad_kernel<128, 32>;
-  static bool cfg = false;
-  if (!cfg) {
+  static PerDevice cfg;
+  if (cfg.first()) {
     if (cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, grad_state_smem()) != cudaSuccess) return -2;
     if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, chunk_grad_smem()) != cudaSuccess) return -2;
-    cfg = true;
+    cfg.done();
   }
   const int grid = B * H * C;
   k0<<<grid, THREADS2, grad_state_smem(), stream>>>(tmQ, a);

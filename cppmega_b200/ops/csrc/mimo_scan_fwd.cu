@@ -417,11 +417,11 @@ extern "C" int cm_mimo_scan_fwd(const void* Qn, const void* Kn, const void* V, c
   if (N == 128) {
     auto k1 = mimo_local_state_kernel<128, 32>;
     auto k3 = mimo_chunk_out_kernel<128, 32>;
-    static bool cfg = false;
-    if (!cfg) {
+    static PerDevice cfg;
+    if (cfg.first()) {
       if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, local_state_smem<128>()) != cudaSuccess) return -2;
       if (cudaFuncSetAttribute(k3, cudaFuncAttributeMaxDynamicSharedMemorySize, chunk_out_smem<128>()) != cudaSuccess) return -2;
-      cfg = true;
+      cfg.done();
     }
     k1<<<grid, THREADS2, local_state_smem<128>(), stream>>>(tmK, a);
     dim3 g2(B * H, (128 * P + 1023) / 1024);

@@ -25,7 +25,7 @@ struct MoePeers {
 __global__ void __launch_bounds__(256) moe_push_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ token_of_copy,
                                                             const int* __restrict__ dest_rank, const long long* __restrict__ dest_row,
                                                             const float* __restrict__ scale, MoePeers dst, int ncopies, int H,
-                                                            long long capacity_rows, int* __restrict__ err) {
+                                                            int world, long long capacity_rows, int* __restrict__ err) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int nvec = H / 8;
@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(256) moe_push_rows_kernel(const __nv_bfloat16*
     const int t = token_of_copy[c];
     const int r = dest_rank[c];
     const long long row = dest_row[c];
-    if (row < 0 || row >= capacity_rows) {          // receiver buffer too small for this routing: drop + report
+    if (row < 0 || row >= capacity_rows || r < 0 || r >= world) {   // receiver buffer too small for this routing: drop + report
       if (lane == 0 && err) atomicCAS(err, 0, ERR_BAD_ARG);
       continue;
     }
@@ -60,14 +60,26 @@ __global__ void __launch_bounds__(256) moe_push_rows_kernel(const __nv_bfloat16*
 // one warp per token
 __global__ void __launch_bounds__(256) moe_pull_combine_kernel(MoePeers src, const int* __restrict__ dest_rank, const long long* __restrict__ dest_row,
                                                                const float* __restrict__ weights, __nv_bfloat16* __restrict__ out,
-                                                               int T, int k, int H) {
+                                                               int T, int k, int H, int world, long long capacity_rows,
+                                                               int* __restrict__ err) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int nvec = H / 8;
   for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += gridDim.x * wpb) {
+    // a copy whose row lies outside the owner's buffer was never stored (push dropped it): it contributes zero and
+    // is reported; no address outside the peer mapping is ever formed
+    unsigned bad = 0;
+    for (int j = 0; j < k; ++j) {
+      const int c = t * k + j;
+      const long long row = dest_row[c];
+      const int r = dest_rank[c];
+      if (row < 0 || row >= capacity_rows || r < 0 || r >= world) bad |= 1u << j;
+    }
+    if (bad && lane == 0 && err) atomicCAS(err, 0, ERR_BAD_ARG);
     for (int v = lane; v < nvec; v += 32) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int j = 0; j < k; ++j) {
+        if (bad & (1u << j)) continue;
         const int c = t * k + j;
         const uint4 x = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src.p[dest_rank[c]]) + dest_row[c] * H)[v];
         const float w = weights ? weights[c] : 1.f;
@@ -89,13 +101,25 @@ __global__ void __launch_bounds__(256) moe_pull_combine_kernel(MoePeers src, con
 
 // one warp per copy: out[c] = dy[token(c)] . y_rows[row(c)]
 __global__ void __launch_bounds__(256) moe_pull_rowdot_kernel(MoePeers src, const int* __restrict__ dest_rank, const long long* __restrict__ dest_row,
-                                                              const __nv_bfloat16* __restrict__ dy, float* __restrict__ out, int T, int k, int H) {
+                                                              const __nv_bfloat16* __restrict__ dy, float* __restrict__ out, int T, int k, int H,
+                                                              int world, long long capacity_rows, int* __restrict__ err) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int nvec = H / 8;
   const int n = T * k;
   for (int c = blockIdx.x * wpb + (threadIdx.x >> 5); c < n; c += gridDim.x * wpb) {
     const int t = c / k;
+    {
+      const long long row = dest_row[c];
+      const int r = dest_rank[c];
+      if (row < 0 || row >= capacity_rows || r < 0 || r >= world) {      // dropped copy: zero, reported, never dereferenced
+        if (lane == 0) {
+          out[c] = 0.f;
+          if (err) atomicCAS(err, 0, ERR_BAD_ARG);
+        }
+        continue;
+      }
+    }
     const uint4* a = reinterpret_cast<const uint4*>(dy + (size_t)t * H);
     const uint4* b = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src.p[dest_rank[c]]) + dest_row[c] * H);
     float s = 0.f;
@@ -199,9 +223,13 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
       const long long padded = (tot + tile - 1) / tile * tile;
       my_end[le] = start + padded;
       if (blockIdx.x == 0) {
-        o.seg_start_local[le] = (int)start;
-        o.tot_local[le] = (int)tot;
-        o.seg_offsets[le + 1] = (int)(start + padded);
+        // a routing that needs more rows than the buffer holds is reported by the push kernel; the receive layout is
+        // clipped to the buffer here so that no GEMM tile or reduction range reaches past it
+        const long long cap = (long long)n_tiles * tile;
+        const long long s0 = start < cap ? start : cap, s1 = start + padded < cap ? start + padded : cap;
+        o.seg_start_local[le] = (int)s0;
+        o.tot_local[le] = (int)(tot < s1 - s0 ? tot : s1 - s0);
+        o.seg_offsets[le + 1] = (int)s1;
         if (le == 0) o.seg_offsets[0] = 0;
       }
     }
@@ -211,8 +239,8 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
   const long long c0 = min(b1, b0 + (long long)tid * per), c1 = min(b1, c0 + per);
   for (int e = 0; e < E; ++e) cnt[e * PLAN_THREADS + tid] = 0;
   for (long long c = c0; c < c1; ++c) {
-    const int e = (int)ids[c];
-    cnt[e * PLAN_THREADS + tid] += 1;
+    const long long e = ids[c];
+    if (e >= 0 && e < E) cnt[(int)e * PLAN_THREADS + tid] += 1;       // same filter as moe_count_kernel
   }
   __syncthreads();
   // exclusive scan over the threads, one expert at a time
@@ -247,7 +275,14 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
 #pragma unroll
   for (int i = 0; i < PLAN_MAX_E / 4; ++i) run[i] = 0;
   for (long long c = c0; c < c1; ++c) {
-    const int e = (int)ids[c];
+    const long long e64 = ids[c];
+    if (e64 < 0 || e64 >= E) {                  // not an expert id: the copy gets no row (push and pull skip and report it)
+      o.dest_row[c] = -1;
+      o.dest_rank[c] = 0;
+      o.token_of_copy[c] = (int)(c / k);
+      continue;
+    }
+    const int e = (int)e64;
     const unsigned int excl = (unsigned int)cnt[e * PLAN_THREADS + tid] | ((unsigned int)cnt[(E + e) * PLAN_THREADS + tid] << 16);
     const unsigned int r = (run[e >> 2] >> ((e & 3) * 8)) & 0xffu;
     run[e >> 2] += 1u << ((e & 3) * 8);
@@ -282,27 +317,28 @@ extern "C" int cm_moe_push_rows(const void* src, const int* token_of_copy, const
   if (H % 8 || world > MOE_MAX_PEERS) return -10;
   MoePeers p;
   for (int i = 0; i < world; ++i) p.p[i] = dst_ptrs[i];
-  moe_push_rows_kernel<<<grid_for(ncopies), 256, 0, s>>>((const __nv_bfloat16*)src, token_of_copy, dest_rank, dest_row, scale, p, ncopies, H, capacity_rows, err);
+  moe_push_rows_kernel<<<grid_for(ncopies), 256, 0, s>>>((const __nv_bfloat16*)src, token_of_copy, dest_rank, dest_row, scale, p, ncopies, H, world, capacity_rows, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int cm_moe_pull_combine(void* const* src_ptrs, int world, const int* dest_rank, const long long* dest_row,
-                                   const float* weights, void* out, int T, int k, int H, cudaStream_t s) {
+                                   const float* weights, void* out, int T, int k, int H, long long capacity_rows, int* err,
+                                   cudaStream_t s) {
   if (T <= 0) return 0;
   if (H % 8 || world > MOE_MAX_PEERS) return -10;
   MoePeers p;
   for (int i = 0; i < world; ++i) p.p[i] = src_ptrs[i];
-  moe_pull_combine_kernel<<<grid_for(T), 256, 0, s>>>(p, dest_rank, dest_row, weights, (__nv_bfloat16*)out, T, k, H);
+  moe_pull_combine_kernel<<<grid_for(T), 256, 0, s>>>(p, dest_rank, dest_row, weights, (__nv_bfloat16*)out, T, k, H, world, capacity_rows, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int cm_moe_pull_rowdot(void* const* src_ptrs, int world, const int* dest_rank, const long long* dest_row,
-                                  const void* dy, float* out, int T, int k, int H, cudaStream_t s) {
+                                  const void* dy, float* out, int T, int k, int H, long long capacity_rows, int* err, cudaStream_t s) {
   if (T <= 0) return 0;
   if (H % 8 || world > MOE_MAX_PEERS) return -10;
   MoePeers p;
   for (int i = 0; i < world; ++i) p.p[i] = src_ptrs[i];
-  moe_pull_rowdot_kernel<<<grid_for((long long)T * k), 256, 0, s>>>(p, dest_rank, dest_row, (const __nv_bfloat16*)dy, out, T, k, H);
+  moe_pull_rowdot_kernel<<<grid_for((long long)T * k), 256, 0, s>>>(p, dest_rank, dest_row, (const __nv_bfloat16*)dy, out, T, k, H, world, capacity_rows, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -338,11 +374,11 @@ extern "C" int cm_moe_plan(const long long* ids, long long n, int k, int E, int 
   const long long chunk = plan_chunk(n);
   if (E > cm::PLAN_MAX_E || E % ep || (chunk + cm::PLAN_THREADS - 1) / cm::PLAN_THREADS > 255) return -10;
   const int smem = 2 * E * cm::PLAN_THREADS * (int)sizeof(unsigned short);
-  static bool cfg = false;
-  if (!cfg) {
+  static cm::PerDevice cfg;
+  if (cfg.first()) {
     if (cudaFuncSetAttribute(cm::moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * cm::PLAN_MAX_E * cm::PLAN_THREADS * 2) != cudaSuccess)
       return -2;
-    cfg = true;
+    cfg.done();
   }
   cm::PlanOut o{dest_row, dest_rank, token_of_copy, seg_start_local, tot_local, seg_offsets, tile_expert, counts_global};
   cm::moe_plan_kernel<<<plan_blocks(n), cm::PLAN_THREADS, smem, s>>>(ids, n, chunk, k, E, ep, ep_rank, allc, block_counts, tile, n_tiles, o);

@@ -354,10 +354,10 @@ static int make_tmap_u8(CUtensorMap* out, const void* base, uint64_t rows, uint6
 template <typename OutT, bool ACC, int MODE = DENSE>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, const Args& args, cudaStream_t s) {
   auto kern = mxfp8_gemm_kernel<OutT, ACC, MODE>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDevice attr_set;
+  if (attr_set.first()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess) return -2;
-    attr_set = true;
+    attr_set.done();
   }
   const int tiles = ((args.M + BM - 1) / BM) * ((args.N + BN - 1) / BN) * (MODE == GROUPED_K ? args.num_experts : 1);
   const int grid = tiles < sm_count() ? tiles : sm_count();

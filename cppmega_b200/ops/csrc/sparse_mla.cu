@@ -435,10 +435,10 @@ extern "C" int cm_sparse_mla_fwd(const void* q, const void* kv, const int* idx, 
   CUtensorMap tmQ;
   int rc = make_tmap_2d_bf16(&tmQ, q, (uint64_t)tokens * HQ, D, D, HQ, 64);
   if (rc) return rc;
-  static bool cfg = false;
-  if (!cfg) {
+  static PerDevice cfg;
+  if (cfg.first()) {
     if (cudaFuncSetAttribute(sparse_mla_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem()) != cudaSuccess) return -2;
-    cfg = true;
+    cfg.done();
   }
   FwdArgs a{(const __nv_bfloat16*)kv, idx, (__nv_bfloat16*)out, lse, S, Skv, tokens, scale * 1.4426950408889634f, err};
   sparse_mla_fwd_kernel<<<(unsigned)tokens, THREADS, fwd_smem(), stream>>>(tmQ, a);
@@ -458,10 +458,10 @@ extern "C" int cm_sparse_mla_bwd(const void* q, const void* kv, const int* idx, 
   if (rc) return rc;
   rc = make_tmap_2d_bf16(&tmdO, dout, (uint64_t)tokens * HQ, DV, DV, HQ, 64);
   if (rc) return rc;
-  static bool cfg = false;
-  if (!cfg) {
+  static PerDevice cfg;
+  if (cfg.first()) {
     if (cudaFuncSetAttribute(sparse_mla_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem()) != cudaSuccess) return -2;
-    cfg = true;
+    cfg.done();
   }
   BwdArgs a{(const __nv_bfloat16*)kv, idx, (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, lse, (__nv_bfloat16*)dq, dkv,
             S, Skv, scale, scale * 1.4426950408889634f, err};

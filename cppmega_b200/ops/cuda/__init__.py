@@ -50,6 +50,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "cm_swiglu_fwd": [vp, vp, i64, i32, vp],
         "cm_swiglu_bwd": [vp, vp, vp, i64, i32, vp],
         "cm_adamw": [vp, vp, vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, f32, i32, i32, vp],
+        "cm_adamw_gated": [vp, vp, vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, f32, i32, i32, vp, vp],
         "cm_sumsq": [vp, i64, vp, i32, vp],
         "cm_strided_copy": [vp, vp, vp, vp, vp, i64, vp],
     }
@@ -327,7 +328,8 @@ def swiglu(gu):
 # optimizer
 # ---------------------------------------------------------------------------
 
-def adamw_shard(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd, bc1, bc2):
+def adamw_shard(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd, bc1, bc2, gate=None):
+    """``gate``: optional device int32 word; the update is skipped on the device when it is non-zero."""
     gk = {torch.float32: 0, torch.bfloat16: 1}.get(g.dtype)
     ok = {torch.float32: 0, torch.bfloat16: 1}.get(out.dtype)
     if gk is None or ok is None:
@@ -335,9 +337,10 @@ def adamw_shard(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd, bc1, b
         return adamw_reference(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd, bc1, bc2)
     clip_t = clip if torch.is_tensor(clip) else torch.tensor(float(clip), device=master.device)
     clip_t = clip_t.reshape(1).float()
-    _check(lib().cm_adamw(master.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), out.data_ptr(),
-                          wd_mask.data_ptr(), clip_t.data_ptr(), master.numel(), float(lr), float(b1), float(b2),
-                          float(eps), float(wd), float(bc1), float(bc2), gk, ok, stream_ptr()), "cm_adamw")
+    _check(lib().cm_adamw_gated(master.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), out.data_ptr(),
+                                wd_mask.data_ptr(), clip_t.data_ptr(), master.numel(), float(lr), float(b1), float(b2),
+                                float(eps), float(wd), float(bc1), float(bc2), gk, ok,
+                                None if gate is None else gate.data_ptr(), stream_ptr()), "cm_adamw")
     F_.count_launch("adamw")
 
 

@@ -22,10 +22,11 @@ def adamw_reference(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd, bc
 
 
 def adamw_shard_update(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd, bc1, bc2,
-                       skip_segments: Sequence[Tuple[int, int, tuple]] = ()):
+                       skip_segments: Sequence[Tuple[int, int, tuple]] = (), gate=None):
     """Update ``master/m/v`` from gradient shard ``g`` (any float dtype) and store the cast
     result in ``out``.  ``clip`` is a 0-dim tensor multiplied into the gradient (stays on
-    device: no host sync).  Ranges in ``skip_segments`` were already updated by Muon."""
+    device: no host sync).  Ranges in ``skip_segments`` were already updated by Muon.  ``gate`` (CUDA only): a device
+    int32 word; when it is non-zero the kernel leaves everything untouched."""
     if skip_segments:
         keep = torch.ones_like(wd_mask)
         for s, e, _ in skip_segments:
@@ -42,7 +43,7 @@ def adamw_shard_update(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd,
         from ..ops import functional as F_
         fn = F_._cuda("adamw_shard", master)
         if fn is not None:
-            fn(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd, bc1, bc2)
+            fn(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd, bc1, bc2, gate=gate)
             return
     adamw_reference(master, m, v, g, out, wd_mask, clip, lr, b1, b2, eps, wd, bc1, bc2)
 

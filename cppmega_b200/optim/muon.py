@@ -6,9 +6,11 @@ Per matrix ``W [rows, cols]`` with gradient ``G``:
     U   <- NewtonSchulz5(m / ||m||_F)                   (bf16 GEMMs; per normalisation group for fused projections)
     W   <- W * (1 - lr * wd) - lr * scale * U,          scale = 0.2 * sqrt(max(rows, cols))
 
-Scalars, embeddings and the output layer stay on AdamW (``muon_scalar_optimizer``).  Under ZeRO-1 a matrix is updated
-by Muon on the rank whose shard holds all of it; a matrix cut by a shard boundary falls back to AdamW for that step
-layout (the bucket planner aligns large matrices to shard boundaries, so this only hits small ones).
+Scalars, embeddings and the output layer stay on AdamW (``muon_scalar_optimizer``).  Stacked expert weights
+``[E, rows, cols]`` are E separate matrices.  Under ZeRO-1 a matrix whose elements all lie in one rank's shard is
+updated there; for a matrix cut by a shard boundary every owner updates its piece of the momentum, the bucket's
+momentum is all-gathered, and each owner applies its rows of the orthogonalised full matrix
+(:func:`muon_update_cut_matrices`), so the update is the same for every data-parallel size and bucket size.
 
 The q8 state and its kernels follow the reference's contract (cppmega/megatron/quantized_muon_momentum.py:29-46 state,
 :97-185 norm plan for fused-QKV segments, :287-676 update entry points; kernel arithmetic at
@@ -225,6 +227,43 @@ def muon_update_segments(st: dict, g: torch.Tensor, clip: torch.Tensor, lr: floa
             w.mul_(1.0 - lr * cfg.weight_decay)
         w.add_(U, alpha=-lr * muon_scale(shape))
         out[s:e].copy_(w.reshape(-1).to(out.dtype))
+
+
+def _all_gather_flat(x: torch.Tensor, group, n: int) -> torch.Tensor:
+    import torch.distributed as dist
+    if x.device.type == "cpu":
+        parts = [torch.empty_like(x) for _ in range(n)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.cat(parts)
+    out = torch.empty(n * x.numel(), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+    return out
+
+
+def muon_update_cut_matrices(st: dict, g: torch.Tensor, clip: torch.Tensor, lr: float, cfg) -> None:
+    """Muon for the matrices of one bucket that a shard boundary cuts.  The momentum update is elementwise, so every
+    rank updates the piece it owns; Newton-Schulz needs the whole matrix, so the bucket's momentum shards are
+    all-gathered (one collective per such bucket, issued by every rank of the group whether or not it owns a piece),
+    each owner orthogonalises the full matrix and applies its own rows.  The result does not depend on where the
+    shard boundaries fall.  Momentum of these matrices stays fp32 (the q8 blocks do not line up with the cuts)."""
+    buf = st["buf"]
+    out = buf.param_buffer[st["lo"]:st["hi"]]
+    for c in st["muon_cross"]:
+        s, e = c["local"]
+        grad = g[s:e].float() * clip
+        st["m"][s:e].mul_(cfg.muon_momentum).add_(grad, alpha=1.0 - cfg.muon_momentum)
+    full = _all_gather_flat(st["m"], buf.group, buf.n)          # [bucket numel], rank-major = bucket order
+    for c in st["muon_cross"]:
+        s, e = c["local"]
+        a, b_ = c["bucket"]
+        i0, i1 = c["inner"]
+        shape = c["shape"]
+        U = newton_schulz(full[a:b_].view(shape), cfg.muon_ns_steps).float().reshape(-1)[i0:i1]
+        w = st["master"][s:e]
+        if cfg.weight_decay > 0:
+            w.mul_(1.0 - lr * cfg.weight_decay)
+        w.add_(U, alpha=-lr * muon_scale(shape))
+        out[s:e].copy_(w.to(out.dtype))
 
 
 def momentum_bytes(shapes: Sequence[Sequence[int]], quantized: bool) -> int:

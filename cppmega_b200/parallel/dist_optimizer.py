@@ -164,6 +164,30 @@ class ParamGroupBuffer:
                 dist.all_gather_into_tensor(full, self.param_buffer[lo:hi], group=self.group)
 
 
+def _muon_eligible(p) -> bool:
+    """Matrices (and stacks of expert matrices) other than the embedding / output layer."""
+    return p.dim() in (2, 3) and not getattr(p, "is_embedding_or_output_parameter", False)
+
+
+def _bucket_has_cut_matrix(buf: "ParamGroupBuffer", b: Bucket) -> bool:
+    """True when some Muon matrix of bucket ``b`` is split between two ranks' shards.  Depends only on the bucket
+    layout, so every rank of the reduction group gets the same answer."""
+    if not buf.distributed or buf.n == 1:
+        return False
+    per = (b.end - b.start) // buf.n
+    for p in b.params:
+        if not _muon_eligible(p):
+            continue
+        off = buf.offsets[p]
+        mats = p.shape[0] if p.dim() == 3 else 1
+        sz = p.numel() // mats
+        for i in range(mats):
+            a, e = off + i * sz - b.start, off + (i + 1) * sz - 1 - b.start
+            if a // per != e // per:
+                return True
+    return False
+
+
 class DistributedOptimizer:
     """AdamW (and Muon for matrices) over sharded fp32 master weights."""
 
@@ -214,7 +238,7 @@ class DistributedOptimizer:
                 lo, hi = buf.shard_range(b)
                 master = buf.param_buffer[lo:hi].float().clone()
                 wd_mask = torch.zeros(hi - lo, dtype=torch.bool, device=master.device)
-                muon_segments = []
+                muon_segments, muon_cross = [], []
                 for p in b.params:
                     off = buf.offsets[p]
                     s, e = max(off, lo), min(off + p.numel(), hi)
@@ -223,13 +247,26 @@ class DistributedOptimizer:
                     decay = p.dim() >= 2 and not getattr(p, "no_weight_decay", False)
                     if decay:
                         wd_mask[s - lo:e - lo] = True
-                    if (self.cfg.optimizer == "muon" and p.dim() == 2 and s == off and e == off + p.numel()
-                            and not getattr(p, "is_embedding_or_output_parameter", False)):
-                        muon_segments.append((s - lo, e - lo, tuple(p.shape)))
+                    if self.cfg.optimizer == "muon" and _muon_eligible(p):
+                        # a 3-D expert stack is E separate matrices; each matrix is one Muon unit
+                        mats = p.shape[0] if p.dim() == 3 else 1
+                        shape = tuple(p.shape[-2:])
+                        per = p.numel() // mats
+                        for i in range(mats):
+                            ms, me = off + i * per, off + (i + 1) * per
+                            if me <= lo or ms >= hi:
+                                continue
+                            if ms >= lo and me <= hi:
+                                muon_segments.append((ms - lo, me - lo, shape))
+                            else:     # cut by a shard boundary: this rank holds [cs, ce) of the matrix
+                                cs, ce = max(ms, lo), min(me, hi)
+                                muon_cross.append({"local": (cs - lo, ce - lo), "bucket": (ms - b.start, me - b.start),
+                                                   "inner": (cs - ms, ce - ms), "shape": shape})
                 self.state.append({
                     "buf": buf, "bucket": b, "lo": lo, "hi": hi, "master": master,
                     "m": torch.zeros_like(master), "v": torch.zeros_like(master),
-                    "wd_mask": wd_mask, "muon": muon_segments,
+                    "wd_mask": wd_mask, "muon": muon_segments, "muon_cross": muon_cross,
+                    "muon_gather": self.cfg.optimizer == "muon" and _bucket_has_cut_matrix(buf, b),
                 })
 
     def _install_hooks(self):
@@ -352,12 +389,16 @@ class DistributedOptimizer:
         for st, g in self._shard_grads():
             buf = st["buf"]
             out = buf.param_buffer[st["lo"]:st["hi"]]
-            if st["muon"]:
+            skip = st["muon"]
+            if st["muon"] or st["muon_gather"]:
                 from ..optim import muon as muon_ops
                 muon_ops.muon_update_segments(st, g, clip, lr, cfg)
+                if st["muon_gather"]:          # same decision on every rank of the group: the gather is a collective
+                    muon_ops.muon_update_cut_matrices(st, g, clip, lr, cfg)
+                    skip = list(st["muon"]) + [(c["local"][0], c["local"][1], c["shape"]) for c in st["muon_cross"]]
             adamw_ops.adamw_shard_update(st["master"], st["m"], st["v"], g, out, st["wd_mask"], clip,
                                          lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2,
-                                         skip_segments=st["muon"])
+                                         skip_segments=skip)
         for buf in self.buffers:
             buf.gather_params()
         return {"grad_norm": gnorm, "clip_coef": clip}

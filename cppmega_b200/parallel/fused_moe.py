@@ -17,7 +17,9 @@ is a row-dot against the owners' saved outputs.
 
 Symmetric buffers: per layer an input and an output row buffer (they must survive until that
 layer's backward), plus two buffers shared by all layers for the backward traffic.  Capacity is
-``capacity_factor`` times the mean load; an overflow sets the kernel error word.
+``capacity_factor`` times the mean load (the worst case, ``ep`` times, when the buffers are shared by all
+layers); an overflow drops the copies that do not fit, never forms an address outside a buffer, and sets the
+kernel error word.
 """
 from __future__ import annotations
 
@@ -41,8 +43,8 @@ def _lib():
     if not getattr(L, "_moe_declared", False):
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         L.cm_moe_push_rows.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, vp, vp]
-        L.cm_moe_pull_combine.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, vp]
-        L.cm_moe_pull_rowdot.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, vp]
+        L.cm_moe_pull_combine.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, i64, vp, vp]
+        L.cm_moe_pull_rowdot.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32, i64, vp, vp]
         L.cm_moe_zero_pad_rows.argtypes = [vp, vp, vp, i32, i32, i64, vp]
         L.cm_moe_count.argtypes = [vp, i64, i32, vp, vp, vp]
         L.cm_moe_plan.argtypes = [vp, i64, i32, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]
@@ -99,8 +101,10 @@ class MoEPlan:
         my_tot = tot[lo:lo + El]
         my_pad = padded[lo:lo + El]
         my_end = torch.cumsum(my_pad, 0)
-        self.seg_start_local = (my_end - my_pad).to(torch.int32)
-        self.tot_local = my_tot.to(torch.int32)
+        my_start = (my_end - my_pad).clamp(max=capacity_rows)
+        my_end = my_end.clamp(max=capacity_rows)                 # an overflowing routing is clipped to the buffer (and reported by push)
+        self.seg_start_local = my_start.to(torch.int32)
+        self.tot_local = torch.minimum(my_tot, my_end - my_start).to(torch.int32)
         self.seg_offsets = torch.cat([torch.zeros(1, dtype=my_end.dtype, device=dev), my_end]).to(torch.int32)
         tiles = torch.arange(capacity_rows // TILE, device=dev) * TILE
         te = torch.searchsorted(my_end, tiles, right=True)
@@ -149,12 +153,21 @@ class FusedMoEBuffers:
     """Symmetric buffers of one EP group; one instance shared by all MoE layers of the model."""
 
     def __init__(self, pc, hidden: int, tokens_per_rank: int, topk: int, num_layers: int, device,
-                 capacity_factor: float = 2.0, per_layer: bool = True):
+                 capacity_factor: Optional[float] = None, per_layer: bool = True, num_local_experts: int = 16):
+        """``capacity_factor``: receive rows per buffer as a multiple of the mean load ``tokens_per_rank * topk``.
+        ``None`` picks the worst case (every copy of every rank lands here: ``ep`` times the mean, no routing can
+        overflow) when the buffers are shared by all layers, and 2.0 when every layer keeps its own pair, where the
+        worst case would not fit; an overflow there drops the copies, zeroes their contribution and sets the error word."""
         self.pc = pc
         self.hidden = hidden
         El = 1
         mean_rows = tokens_per_rank * topk
-        self.capacity = int((mean_rows * capacity_factor + 16 * TILE + TILE - 1) // TILE * TILE)
+        if capacity_factor is None:
+            capacity_factor = 2.0 if per_layer else float(pc.ep)
+        capacity_factor = min(float(capacity_factor), float(pc.ep))
+        self.capacity_factor = capacity_factor
+        pad_rows = max(16, num_local_experts) * TILE          # every local expert segment may end in a partial tile
+        self.capacity = int((mean_rows * capacity_factor + pad_rows + TILE - 1) // TILE * TILE)
         n_bufs = (2 * num_layers if per_layer else 2) + 2
         nbytes = n_bufs * (self.capacity * hidden * 2 + 4096) + num_layers * 4096 * 2
         self.heap = SymmetricHeap(pc.ep_group, pc.ep_ranks, nbytes, device)
@@ -247,11 +260,12 @@ def _push(heap: SymmetricHeap, src, plan: MoEPlan, dst_buf, scale=None):
 
 
 def _pull_combine(heap: SymmetricHeap, src_buf, plan: MoEPlan, weights, H, dtype):
-    from ..ops.cuda import stream_ptr
+    from ..ops.cuda import err_word, stream_ptr
     out = torch.empty(plan.T, H, dtype=dtype, device=src_buf.device)
     rc = _lib().cm_moe_pull_combine(heap.peer_ptr_array(src_buf), heap.world, plan.dest_rank.data_ptr(),
                                     plan.dest_row.data_ptr(), None if weights is None else weights.data_ptr(),
-                                    out.data_ptr(), plan.T, plan.k, H, stream_ptr())
+                                    out.data_ptr(), plan.T, plan.k, H, src_buf.shape[0],
+                                    err_word(src_buf.device).data_ptr(), stream_ptr())
     if rc:
         raise RuntimeError(f"cm_moe_pull_combine failed ({rc})")
     F_.count_launch("moe_pull_combine")
@@ -259,11 +273,11 @@ def _pull_combine(heap: SymmetricHeap, src_buf, plan: MoEPlan, weights, H, dtype
 
 
 def _pull_rowdot(heap: SymmetricHeap, src_buf, plan: MoEPlan, dy):
-    from ..ops.cuda import stream_ptr
+    from ..ops.cuda import err_word, stream_ptr
     out = torch.empty(plan.T, plan.k, dtype=torch.float32, device=dy.device)
     rc = _lib().cm_moe_pull_rowdot(heap.peer_ptr_array(src_buf), heap.world, plan.dest_rank.data_ptr(),
                                    plan.dest_row.data_ptr(), dy.data_ptr(), out.data_ptr(), plan.T, plan.k, dy.shape[1],
-                                   stream_ptr())
+                                   src_buf.shape[0], err_word(dy.device).data_ptr(), stream_ptr())
     if rc:
         raise RuntimeError(f"cm_moe_pull_rowdot failed ({rc})")
     F_.count_launch("moe_pull_rowdot")
@@ -428,7 +442,7 @@ class FusedMoEDispatcher:
         return _FusedMoEFn.apply(flat, probs, experts.weight1, experts.weight2, ids, self.bufs, self.slot)
 
 
-def attach(model, pc, device, tokens_per_rank: int, per_layer: bool = True, capacity_factor: float = 2.0) -> Optional[FusedMoEBuffers]:
+def attach(model, pc, device, tokens_per_rank: int, per_layer: bool = True, capacity_factor: Optional[float] = None) -> Optional[FusedMoEBuffers]:
     """Install the fused dispatcher on every MoE layer of ``model`` (EP > 1, bf16, peer access)."""
     layers = model.moe_layers()
     if not layers:
@@ -439,8 +453,11 @@ def attach(model, pc, device, tokens_per_rank: int, per_layer: bool = True, capa
         for slot, m in enumerate(layers):
             m.fused_dispatcher = FusedMoEDispatcher(local, slot)
         return local
+    if capacity_factor is None:
+        capacity_factor = model.cfg.moe.capacity_factor
     bufs = FusedMoEBuffers(pc, hidden, tokens_per_rank, model.cfg.moe.topk, len(layers), device,
-                           capacity_factor=capacity_factor, per_layer=per_layer)
+                           capacity_factor=capacity_factor, per_layer=per_layer,
+                           num_local_experts=model.cfg.moe.num_experts // pc.ep)
     for slot, m in enumerate(layers):
         m.fused_dispatcher = FusedMoEDispatcher(bufs, slot)
     return bufs

@@ -40,16 +40,16 @@ class FusedDistributedOptimizer(DistributedOptimizer):
         from ..ops import cuda as cu
         self.L = cu.lib()
         vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-        self.L.cm_reduce_shard.argtypes = [vp, i32, i32, i64, i64, f32, vp, vp, i32, vp]
+        self.L.cm_reduce_shard.argtypes = [vp, i32, i32, i64, i64, f32, vp, vp, i32, vp, vp]
         self.L.cm_reduce_shard.restype = i32
-        self.L.cm_adamw_push.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i64, i64, f32, f32, f32, f32, f32, f32, f32, i32, vp]
+        self.L.cm_adamw_push.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i64, i64, f32, f32, f32, f32, f32, f32, f32, i32, vp, vp]
         self.L.cm_adamw_push.restype = i32
         for st in self.state:
             buf: ParamGroupBuffer = st["buf"]
             if buf.n > 1:
                 st["red"] = torch.empty(st["hi"] - st["lo"], dtype=torch.float32, device=st["master"].device)
         self._param_wait_pending = False
-        if any(st.get("muon") for st in self.state):
+        if cfg.optimizer == "muon" or any(st.get("muon") or st.get("muon_cross") for st in self.state):
             raise NotImplementedError("the fused optimizer path implements AdamW; use the NCCL path for Muon")
 
     def _buffer_allocator(self, is_expert: bool, params, grad_dtype):
@@ -122,7 +122,8 @@ class FusedDistributedOptimizer(DistributedOptimizer):
                 gk = 0 if buf.grad_buffer.dtype == torch.float32 else 1
                 arr = buf.heap.peer_ptr_array(buf.grad_buffer)
                 rc = self.L.cm_reduce_shard(arr, buf.n, buf.rank, st["lo"], st["hi"] - st["lo"],
-                                            float(self._grad_scale / buf.grad_div), st["red"].data_ptr(), sq.data_ptr(), gk, s)
+                                            float(self._grad_scale / buf.grad_div), st["red"].data_ptr(), sq.data_ptr(), gk,
+                                            cu.err_word(dev).data_ptr(), s)
                 if rc:
                     raise RuntimeError(f"cm_reduce_shard failed ({rc})")
                 from ..ops import functional as F_
@@ -146,7 +147,7 @@ class FusedDistributedOptimizer(DistributedOptimizer):
                 rc = self.L.cm_adamw_push(st["master"].data_ptr(), st["m"].data_ptr(), st["v"].data_ptr(),
                                           st["red"].data_ptr(), st["wd_mask"].data_ptr(), clip_t.data_ptr(), arr, buf.n,
                                           st["lo"], st["hi"] - st["lo"], float(lr), cfg.beta1, cfg.beta2, cfg.eps,
-                                          cfg.weight_decay, bc1, bc2, ok, s)
+                                          cfg.weight_decay, bc1, bc2, ok, cu.err_word(dev).data_ptr(), s)
                 if rc:
                     raise RuntimeError(f"cm_adamw_push failed ({rc})")
                 from ..ops import functional as F_
@@ -155,7 +156,8 @@ class FusedDistributedOptimizer(DistributedOptimizer):
                 g = buf.grad_buffer[st["lo"]:st["hi"]]
                 out = buf.param_buffer[st["lo"]:st["hi"]]
                 adamw_ops.adamw_shard_update(st["master"], st["m"], st["v"], g, out, st["wd_mask"], clip, lr,
-                                             cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2)
+                                             cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2,
+                                             gate=cu.err_word(dev))
         for h in heaps:
             h.signal(FLAG_PARAM, step)
         self._param_wait_pending = bool(heaps)

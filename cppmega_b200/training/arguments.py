@@ -149,6 +149,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--mock-data", action="store_true", help="synthetic uniform tokens")
     g.add_argument("--save", default=None)
     g.add_argument("--load", default=None)
+    g.add_argument("--no-load-optim", action="store_true",
+                   help="when the optimizer shards cannot be restored (other parallel layout, missing file), continue from "
+                        "the weights with fresh AdamW moments instead of failing")
     g.add_argument("--save-interval", type=int, default=0)
     g.add_argument("--log-interval", type=int, default=1)
     g.add_argument("--log-throughput", action="store_true")
@@ -285,7 +288,7 @@ def configs_from_namespace(ns: argparse.Namespace) -> Tuple[ModelConfig, Paralle
                        pipeline_schedule=ns.pipeline_schedule, cuda_graph_scope=tuple(ns.cuda_graph_scope))
     extras = {k: getattr(ns, k) for k in ("train_iters", "data_path", "mock_data", "save", "load", "save_interval",
                                           "log_throughput", "monitor_port", "profile", "profile_step_start",
-                                          "profile_step_end", "step_timeout_s")}
+                                          "profile_step_end", "step_timeout_s", "no_load_optim")}
     return mcfg, pcfg, tcfg, extras
 
 

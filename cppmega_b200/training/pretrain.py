@@ -28,11 +28,16 @@ from .arguments import parse_args
 from .trainer import Trainer, synthetic_batches
 
 
-def _data_iterator(extras: Dict, mcfg, tcfg, pc, num_microbatches: int) -> Iterator[List[Dict[str, torch.Tensor]]]:
+def _data_iterator(extras: Dict, mcfg, tcfg, pc, num_microbatches: int,
+                   consumed_steps: int = 0) -> Iterator[List[Dict[str, torch.Tensor]]]:
+    """Batches for this data-parallel rank.  ``consumed_steps`` optimizer steps of data were used by the run being
+    resumed: the stream starts after them, so a resumed run sees the samples the uninterrupted run would have seen
+    (Megatron keeps ``consumed_train_samples`` for the same purpose)."""
     if extras["data_path"] and not extras["mock_data"]:
         from ..data.indexed import TokenStream
         stream = TokenStream(extras["data_path"], tcfg.seq_length, tcfg.micro_batch_size, rank=pc.dp_rank, world=pc.dp,
                              seed=tcfg.seed)
+        stream.skip(consumed_steps * num_microbatches)
 
         def gen():
             while True:
@@ -42,7 +47,23 @@ def _data_iterator(extras: Dict, mcfg, tcfg, pc, num_microbatches: int) -> Itera
         raise SystemExit("no --data-path given: pass --mock-data to train on synthetic uniform tokens "
                          "(throughput measured that way is not a real-data number)")
     return synthetic_batches(mcfg.vocab_size, tcfg.micro_batch_size, tcfg.seq_length, num_microbatches,
-                             seed=tcfg.seed, rank=pc.dp_rank)
+                             seed=tcfg.seed, rank=pc.dp_rank, skip=consumed_steps)
+
+
+def _rng_state() -> Dict:
+    st = {"torch_cpu": torch.get_rng_state()}
+    if torch.cuda.is_available():
+        st["torch_cuda"] = torch.cuda.get_rng_state()
+    return st
+
+
+def _restore_rng(st: Optional[Dict]) -> None:
+    if not st:
+        return
+    if "torch_cpu" in st:
+        torch.set_rng_state(st["torch_cpu"].cpu().to(torch.uint8))
+    if "torch_cuda" in st and torch.cuda.is_available():
+        torch.cuda.set_rng_state(st["torch_cuda"].cpu().to(torch.uint8))
 
 
 def main(argv: Optional[Sequence[str]] = None) -> int:
@@ -57,19 +78,25 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
               f"pattern {mcfg.plan().full_pattern[:64]}..., world {pc.world_size} ({pcfg.describe(pc.world_size)}), "
               f"fused paths {trainer.fused}", flush=True)
     start_iter = 0
+    consumed_steps = 0
     if extras["load"]:
         it = sharded.latest_iteration(extras["load"])
         if it is not None:
-            info = sharded.load_checkpoint(extras["load"], trainer.model, pc, trainer.optimizer)
+            info = sharded.load_checkpoint(extras["load"], trainer.model, pc, trainer.optimizer,
+                                           allow_optimizer_reset=extras.get("no_load_optim", False))
             start_iter = info["iteration"]
             trainer.step = start_iter
             trainer.tokens_seen = info["extra"].get("tokens_seen", 0)
+            consumed_steps = info["extra"].get("consumed_steps", start_iter)
+            _restore_rng(info.get("rank_extra", {}).get("rng"))
+            if info.get("optimizer_reset") and pc.rank == 0:
+                print("[cppmega_b200] WARNING: " + info["optimizer_reset"], flush=True)
     if extras["profile"]:
         install_layer_nvtx(trainer.model)
     server = MetricsServer(extras["monitor_port"]).start() if (extras["monitor_port"] and pc.rank == 0) else None
     if extras["step_timeout_s"] > 0:
         trainer.watchdog = StepWatchdog(extras["step_timeout_s"], rank=pc.rank).start()
-    batches = _data_iterator(extras, mcfg, tcfg, pc, trainer.num_microbatches)
+    batches = _data_iterator(extras, mcfg, tcfg, pc, trainer.num_microbatches, consumed_steps)
     flops_tok = mcfg.flops_per_token(tcfg.seq_length)
     t_last = time.perf_counter()
     try:
@@ -93,8 +120,12 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                 if server is not None:
                     server.publish(rec)
             if extras["save"] and extras["save_interval"] and (it + 1) % extras["save_interval"] == 0:
+                if device.type == "cuda":
+                    from ..ops import cuda as cu
+                    cu.check_errors(device)       # a step whose kernels gave up must not be written out as a good state
                 sharded.save_checkpoint(extras["save"], it + 1, trainer.model, pc, trainer.optimizer,
-                                        extra={"tokens_seen": trainer.tokens_seen})
+                                        extra={"tokens_seen": trainer.tokens_seen, "consumed_steps": it + 1},
+                                        rank_extra={"rng": _rng_state()})
     finally:
         if trainer.watchdog is not None:
             trainer.watchdog.stop()

@@ -231,6 +231,9 @@ class Trainer:
             res = self.train_step(next(batches))
             if cfg.log_interval and self.step % cfg.log_interval == 0:
                 rec = self.reduce_loss_for_logging(res)
+                if self.device.type == "cuda":
+                    from ..ops import cuda as cu
+                    cu.check_errors(self.device)      # raises if a kernel's bounded wait ran out since the last check
                 now = time.perf_counter()
                 dt = (now - t_last) / cfg.log_interval
                 t_last = now
@@ -254,12 +257,14 @@ def allreduce_sequence_parallel_grads_main(params, pc: ParallelContext) -> None:
 
 
 def synthetic_batches(vocab: int, micro_batch: int, seq: int, num_microbatches: int = 1, seed: int = 0,
-                      pin: bool = True, rank: int = 0) -> Iterator[List[Dict[str, torch.Tensor]]]:
+                      pin: bool = True, rank: int = 0, skip: int = 0) -> Iterator[List[Dict[str, torch.Tensor]]]:
     """Endless stream of uniform-random token batches in (pinned) host memory; labels are
-    the next token."""
+    the next token.  ``skip`` steps are generated and dropped first (resume)."""
     gen = torch.Generator(device="cpu")
     gen.manual_seed(seed + 7919 * rank)
     pin = pin and torch.cuda.is_available()
+    for _ in range(skip * num_microbatches):
+        torch.randint(0, vocab, (micro_batch, seq + 1), generator=gen, dtype=torch.long)
     while True:
         mbs = []
         for _ in range(num_microbatches):

@@ -26,6 +26,7 @@ def main():
         "tp_sp": ParallelConfig(tp=world, sequence_parallel=True),
         "pp": ParallelConfig(pp=world), "ep_nodistopt": ParallelConfig(ep=world, distributed_optimizer=False),
         "pp_vpp2": ParallelConfig(pp=world, vpp=2), "dualpipev": ParallelConfig(pp=world),
+        "dp_muon": ParallelConfig(), "ep_muon": ParallelConfig(ep=world),
     }
     schedule = {"pp_vpp2": "interleaved", "dualpipev": "dualpipev"}.get(mode, "1f1b")
     n_mb = 4 if schedule != "1f1b" else 2
@@ -36,7 +37,9 @@ def main():
     if len(sys.argv) > 3:
         n_mb = int(sys.argv[3])
     tcfg = TrainConfig(micro_batch_size=mb, global_batch_size=n_mb * mb, seq_length=seq, dtype="fp32",
-                       optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0), log_interval=0, pipeline_schedule=schedule)
+                       optimizer=(OptimizerConfig(optimizer="muon", lr=1e-3, weight_decay=0.01, bucket_mb=1)
+                                  if mode.endswith("_muon") else OptimizerConfig(lr=1e-3, weight_decay=0.0)),
+                       log_interval=0, pipeline_schedule=schedule)
     trainer = Trainer(mcfg, tcfg, pc, device=torch.device("cpu"))
     # the global batch is always the same 2 micro-batches; each DP rank takes its slice
     stream = synthetic_batches(mcfg.vocab_size, mb, seq, num_microbatches=n_mb, seed=0, pin=False, rank=0)
@@ -50,6 +53,10 @@ def main():
         rec = trainer.reduce_loss_for_logging(res) if has_loss else {"loss": 0.0, "lm_loss": 0.0, "grad_norm": float(res["grad_norm"])}
         losses.append([rec["loss"], rec["lm_loss"], rec["grad_norm"]])
     out = {"mode": mode, "world": world, "losses": losses}
+    if mode.endswith("_muon"):
+        st = trainer.optimizer.state
+        out["muon_whole"] = sum(len(x["muon"]) for x in st)
+        out["muon_cut"] = sum(len(x["muon_cross"]) for x in st)
     report_rank = (world - 1 if mode in ("pp", "pp_vpp2") else 0)
     if mode == "dualpipev":
         report_rank = 0                      # the V turns back: the last chunk lives on the first rank
