@@ -460,11 +460,27 @@ def nam56r_quarter(**overrides) -> ModelConfig:
     return ModelConfig(**base)
 
 
+def nam56r_slice(**overrides) -> ModelConfig:
+    """One layer of every kind at the production kernel shapes (``M A(DSA) E R``: Mamba3 MIMO d_state 128 / headdim 64 /
+    rank 4, 32-head MLA with 64+64 query dims, indexer 32 x 64 with top-k 256, 16 experts top-4, M2RNN 64 x 16) behind a
+    small hidden size and vocabulary: the smallest model on which every hand-written kernel accepts its shapes."""
+    base = dict(
+        name="nam56r_slice", pattern="MAER", depth=4, hidden_size=1024, ffn_hidden_size=2048, vocab_size=8192,
+        seq_length=512,
+        dsa=DSAConfig(attention_ranks=(0,), full_layer_ranks=(0,)),
+        mtp=MTPConfig(num_layers=1),
+        ngram_hash=NgramHashConfig(orders=(2, 3), heads=4, table_size=4096, embed_dim=16),
+    )
+    base.update(overrides)
+    return ModelConfig(**base)
+
+
 PRESETS = {
     "nam56r": nam56r_full,
     "nam56r_full": nam56r_full,
     "nam56r_tiny": nam56r_tiny,
     "nam56r_quarter": nam56r_quarter,
+    "nam56r_slice": nam56r_slice,
 }
 
 
@@ -484,6 +500,6 @@ def human_count(n: float) -> str:
 __all__ = [
     "Mamba3Config", "M2RNNConfig", "MLAConfig", "DSAConfig", "MoEConfig", "MTPConfig",
     "NgramHashConfig", "StructureConfig", "EngramConfig", "MHCConfig", "MoDConfig", "ModelConfig",
-    "nam56r_full", "nam56r_tiny", "nam56r_quarter", "get_preset", "PRESETS", "human_count",
+    "nam56r_full", "nam56r_tiny", "nam56r_quarter", "nam56r_slice", "get_preset", "PRESETS", "human_count",
 ]
 _ = math  # keep import for downstream formulas

@@ -38,6 +38,8 @@ class ProfilingProfile:
     step_end: int = 4
     trace: str = "cuda,nvtx,osrt"
     output_dir: str = "profiles_out"
+    ncu_case: str = ""                   # tool == "ncu": single-kernel workload of tools/ncu_cases.py to capture
+    ncu_kernel: str = ""                 # kernel-name regex (default: the case name)
 
     def __post_init__(self):
         if self.tool not in ("torch", "nsys", "ncu"):
@@ -133,8 +135,16 @@ class RunProfile:
         if prof.enabled and prof.tool == "nsys":
             head = ["nsys", "profile", "-t", prof.trace, "-c", prof.capture_mode, "-o", f"{prof.output_dir}/{self.name}"] + head
         elif prof.enabled and prof.tool == "ncu":
-            head = ["ncu", "--clock-control", "none", "--profile-from-start", "off", "-o",
-                    f"{prof.output_dir}/{self.name}"] + head
+            # Nsight Compute replays every captured launch dozens of times and serialises the process: it is only ever
+            # wrapped around ONE process running ONE small single-kernel workload (tools/ncu_cases.py), never around a
+            # training run and never around several ranks.
+            case = prof.ncu_case
+            if not case:
+                raise ValueError("profiling.tool='ncu' needs profiling.ncu_case (a workload name of "
+                                 "cppmega_b200.tools.ncu_cases); a whole training run is not captured under ncu")
+            cmd = ["ncu", "--set", "full", "--clock-control", "none", "-k", f"regex:{prof.ncu_kernel or case}", "-c", "3",
+                   "-o", f"{prof.output_dir}/{case}", "python", "-m", "cppmega_b200.tools.ncu_cases", case]
+            return " ".join(shlex.quote(x) for x in cmd)
         return " ".join(shlex.quote(x) for x in head + self.argv())
 
     def describe(self) -> Dict:

@@ -160,11 +160,11 @@ class MLAttention(nn.Module):
             w_up = self.linear_kv_up_proj.weight.reshape(Hl, dq + dv, dc)
             w_uk, w_uv = w_up[:, :dq], w_up[:, dq:]
             lat_tp = copy_to_tp(kv_lat, pc)
-            q_abs = torch.einsum("bshd,hdc->bshc", q_nope, w_uk.to(q_nope.dtype))
+            q_abs = F_.head_linear(q_nope, w_uk.transpose(1, 2))                 # [B,S,Hl,dc] = q_nope . W_uk
             q_full = cat_last_dim([q_abs, q_pe])                                # [B,S,Hl,dc+dr]
             kv_full = cat_last_dim([lat_tp, k_pe])                               # [B,S,dc+dr]
             o_lat = F_.sparse_mla(q_full, kv_full, idx, self.softmax_scale, dc)  # [B,S,Hl,dc]
-            o = torch.einsum("bshc,hvc->bshv", o_lat, w_uv.to(o_lat.dtype))
+            o = F_.head_linear(o_lat, w_uv)                                      # [B,S,Hl,dv] = o_lat . W_uv^T
         return self.linear_proj(o.reshape(B, S, Hl * dv))
 
     def _indices(self, x, q_lat, cache: Optional[IndexCacheState], attn_parts) -> torch.Tensor:

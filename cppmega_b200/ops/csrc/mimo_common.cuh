@@ -32,20 +32,6 @@ constexpr int SLAB = ROWS * 128;  // bytes of one [128 rows x 64 bf16] swizzled 
 constexpr int VLD = P + 4;
 __device__ __forceinline__ int vec_idx(int x) { return (x / P) * VLD + (x % P); }   // flat [R*P] index -> padded
 
-// Optional phase timestamps (compile with -DCM_MIMO_TIMING): thread 0 of the first 1024 CTAs records the SM clock at
-// numbered points of a kernel; cm_mimo_read_stamps copies them out.  Compiled out by default.
-#ifdef CM_MIMO_TIMING
-static __device__ unsigned long long cm_mimo_stamps[1024 * 16];
-#define CM_STAMP(k)                                                                                      \
-  do {                                                                                                   \
-    if (threadIdx.x == 0 && blockIdx.x < 1024) cm_mimo_stamps[blockIdx.x * 16 + (k)] = (unsigned long long)clock64(); \
-  } while (0)
-#else
-#define CM_STAMP(k) \
-  do {              \
-  } while (0)
-#endif
-
 // byte offset of logical 16-byte chunk `c` (0..7) of row `row` inside a 128B-swizzled slab
 __device__ __forceinline__ int sw_off(int row, int c) { return row * 128 + ((c ^ (row & 7)) << 4); }
 

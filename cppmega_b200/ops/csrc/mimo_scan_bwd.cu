@@ -251,7 +251,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   static_assert(sizeof(GradScratch) <= 2 * SLAB && sizeof(HeadBias<N>) <= 2 * SLAB, "scratch must fit the Pm tile");
 
   if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
-  CM_STAMP(0);
   const int tid = threadIdx.x;
   const int i = tid & 127, wg = tid >> 7, t = i >> 2, r = i & 3, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
@@ -299,7 +298,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   const HalfRowRaw vraw = load_half_raw(a.V, b, t0, h, a.S, a.ldV);
   const HalfRowRaw yraw = load_half_raw(a.dY, b, t0, h, a.S, (long long)a.H * P);
   const HalfRowRaw zraw = load_half_raw(a.Z, b, t0, h, a.S, a.ldZ);
-  CM_STAMP(1);
   const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
   // phase 1 accumulators                      phase 2 / 3 accumulators
   const uint32_t tS1 = tmem, tdPm = tmem + 128, tO2 = tmem + 256, tX = tmem + 320, tdQb = tmem + 384;
@@ -328,9 +326,7 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   const float wi = tsi * __expf(tot - csi);
   const float dsk = a.Dskip[h];
 
-  CM_STAMP(2);
   bool ok = mbar_wait(&bars[0], par, abort_flag, a.err, ERR_WAIT_FULL);
-  CM_STAMP(3);
   if (ok) {
     transform_rows<N, NROT, 2, HeadBias<N>::LD>(sQ, hb->qb, cos_tab, sin_tab);
     transform_rows<N, NROT, 2, HeadBias<N>::LD>(sK, hb->kb, cos_tab, sin_tab);
@@ -350,7 +346,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
     }
     fence_proxy_async_smem();
   }
-  CM_STAMP(4);
   __syncthreads();
   const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aPV = smem_u32(sPV), adO = smem_u32(sdO), aSt = smem_u32(sSt),
                  adE = smem_u32(sdE), aPm = smem_u32(sPm), adS = smem_u32(sdS), aPVw = smem_u32(sPVw);
@@ -388,7 +383,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   }
   ok = __syncthreads_and(mbar_wait(&bars[1], par, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
   tc_fence_after();
-  CM_STAMP(5);
 
   // ---------------- phase A: masks, Pm, dS1, scalar gradients from dM = dPm o S1 ----------------
   // this warpgroup's key tokens: [16 wg, 16 wg + 16)
@@ -438,7 +432,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
     }
     fence_proxy_async_smem();
   }
-  CM_STAMP(6);
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && !*abort_flag) {
@@ -462,7 +455,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   }
   ok = __syncthreads_and(mbar_wait(&bars[2], par, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
   tc_fence_after();
-  CM_STAMP(7);
   // Pm has been consumed by phase 2: its space becomes the reduction scratch
   if (tid < LT) { gs->dcs[tid] = 0.f; gs->dts[tid] = 0.f; gs->dgam[tid] = 0.f; }
   if (tid == 0) { gs->dtot = 0.f; gs->dD = 0.f; }
@@ -586,7 +578,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
       atomicAdd(&gs->dts[wg * 16 + lane], colsum[(warp * 2 + 1) * (LT / 2) + lane]);
     }
   }
-  CM_STAMP(8);
   tc_fence_before();
   __syncthreads();
   // ---------------- phase 3: dK ----------------
@@ -627,7 +618,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   }
   ok = __syncthreads_and(mbar_wait(&bars[3], par, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
   tc_fence_after();
-  CM_STAMP(9);
   // ---------------- epilogue C: dQr = dQ + e dQb (warpgroup 0), dKr (warpgroup 1); inverse rotation; d(angles) ----
   float dang[NROT / 8][8];
   if (ok) {
@@ -714,7 +704,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
       }
     }
   }
-  CM_STAMP(10);
   tc_fence_before();
   __syncthreads();
   if (ok && wg == 0) {
@@ -738,7 +727,6 @@ __global__ void __launch_bounds__(THREADS2, 1) mimo_chunk_grad_kernel(const __gr
   if (*abort_flag) break;
   }
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, 512); }
-  CM_STAMP(11);
 }
 
 constexpr int grad_state_smem() {
@@ -798,8 +786,3 @@ extern "C" int cm_mimo_scan_bwd(const void* Qn, const void* Kn, const void* V, c
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-#ifdef CM_MIMO_TIMING
-extern "C" int cm_mimo_read_stamps_bwd(unsigned long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, cm::mimo::cm_mimo_stamps, sizeof(cm::mimo::cm_mimo_stamps)) == cudaSuccess ? 0 : -1;
-}
-#endif

@@ -219,7 +219,6 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (a.err && *reinterpret_cast<volatile int*>(a.err) != 0) return;   // an earlier CTA / kernel gave up: drain
-  CM_STAMP(0);
   int b, g, c, h;
   decode_block(a, b, g, c, h);
   const int t0 = c * LT;
@@ -245,7 +244,6 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  CM_STAMP(1);
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS1 = tmem, tO2 = tmem + 128, tO1 = tmem + 192;
   if (threadIdx.x == 0) {
@@ -266,16 +264,13 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
   finish_chunk_scalars(sc, sl, t0, a.S);
   fill_sincos4<NROT>(cos_tab, sin_tab, ang4);
   __syncthreads();
-  CM_STAMP(2);
   bool ok = mbar_wait(&bars[0], 0, abort_flag, a.err, ERR_WAIT_FULL);
-  CM_STAMP(3);
   float pv[P / 2];
   if (ok) {
     transform_rows<N, NROT, 2, HeadBias<N>::LD>(sQ, hb->qb, cos_tab, sin_tab);
     transform_rows<N, NROT, 2, HeadBias<N>::LD>(sK, hb->kb, cos_tab, sin_tab);
     pv_from_raw(pv, vraw, psi_s);
   }
-  CM_STAMP(4);
   __syncthreads();                               // every thread is done with the biases stored in the PV slab and the tables
   zeta_s[vec_idx(threadIdx.x)] = zeta_v;
   phi_s[vec_idx(threadIdx.x)] = phi_v;
@@ -294,10 +289,8 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
     for (int k = 0; k < N / 16; ++k) umma_f16(tO2, desc_kmajor(aQ, k), desc_mnmajor_rows(aSt, k), id_o, k != 0);
     umma_commit(&bars[1]);
   }
-  CM_STAMP(5);
   ok = mbar_wait(&bars[1], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL);
   tc_fence_after();
-  CM_STAMP(6);
   const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
   if (ok) {
     // mask the scores of this row and store them as the A operand of the second product
@@ -336,10 +329,8 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
     for (int k = 0; k < ROWS / 16; ++k) umma_f16(tO1, desc_kmajor(aPm, k), desc_mnmajor_rows(aPV, k), id_o, k != 0);
     umma_commit(&bars[2]);
   }
-  CM_STAMP(7);
   ok = mbar_wait(&bars[2], 0, abort_flag, a.err, ERR_WAIT_TMEM_FULL);
   tc_fence_after();
-  CM_STAMP(8);
   if (ok) {
     const float ecs = __expf(sc->cs[t]);
     const float* zeta = zeta_s + r * VLD + wg * 32;
@@ -366,11 +357,9 @@ __global__ void __launch_bounds__(THREADS2, 2) mimo_chunk_out_kernel(const __gri
     // lane r holds the sums over the four ranks for columns [8r, 8r + 8) of this warpgroup's half
     *reinterpret_cast<uint4*>(yrow + r * 8) = pack8(mine);
   }
-  CM_STAMP(9);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, 256); }
-  CM_STAMP(10);
 }
 
 template <int N>
@@ -430,12 +419,6 @@ extern "C" int cm_mimo_scan_fwd(const void* Qn, const void* Kn, const void* V, c
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
-
-#ifdef CM_MIMO_TIMING
-extern "C" int cm_mimo_read_stamps(unsigned long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, cm_mimo_stamps, sizeof(cm_mimo_stamps)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 // ------------------------------------------------------------------------------------------
 // Variant with the work buffers in a fixed device array (see mimo_scan_static.h for the contract).

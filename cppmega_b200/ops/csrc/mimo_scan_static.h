@@ -14,7 +14,10 @@
 //           CM_MIMO_STATIC_E_TOO_LARGE and a message on stderr; nothing is launched.
 // Set-up:   the first call on each device looks the array's address up (that device must be current, as it must be
 //           for the launch anyway).  Make that first call during initialisation, ahead of any stream capture the
-//           program does later; later calls on the same device only launch kernels.
+//           program does later; later calls on the same device only launch kernels.  The address is cached per device
+//           ordinal for the life of the process: a program that destroys a device's primary context (cudaDeviceReset)
+//           and creates a new one must not call this entry point again on that device, because the cached address
+//           belongs to the module image of the destroyed context.
 // Contents: every word the kernels read from the array is written earlier in the same call, so nothing has to be
 //           cleared beforehand; the array simply keeps what the last call left in it.
 // Sharing:  there is ONE array per device.  Two calls whose kernels may overlap in time (different streams, different

@@ -285,6 +285,7 @@ def rmsnorm(x, w, eps):
     H = x.shape[-1]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or H % 8 or H > 16384 or x.numel() == 0:
         from .. import reference as ref
+        F_._miss("rmsnorm(shape/dtype)", x)
         return ref.rmsnorm(x, w, eps)
     return RMSNormFn.apply(x, w, eps)
 
@@ -320,6 +321,7 @@ class SwiGLUFn(torch.autograd.Function):
 def swiglu(gu):
     if gu.dtype != torch.bfloat16 or (gu.shape[-1] // 2) % 8 or gu.numel() == 0:
         from .. import reference as ref
+        F_._miss("swiglu(shape/dtype)", gu)
         return ref.swiglu(gu)
     return SwiGLUFn.apply(gu)
 

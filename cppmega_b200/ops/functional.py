@@ -67,6 +67,12 @@ def _ensure_ext() -> None:
     from . import cuda  # noqa: F401  (registers kernels; raises if the .so is missing on a GPU box)
 
 
+def _miss(name: str, t: torch.Tensor) -> None:
+    """A CUDA call that ends in a PyTorch / library kernel instead of one of this package's kernels."""
+    if t.is_cuda:
+        _FALLBACKS[name] += 1
+
+
 def _cuda(name: str, *tensors) -> Optional[Callable]:
     t = tensors[0]
     if not t.is_cuda:
@@ -111,6 +117,7 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         y = fn(x, w)
         if y is not None:
             return y
+        _miss("linear(shape/dtype)", x)
     return F.linear(x, w.to(x.dtype) if w.dtype != x.dtype else w)
 
 
@@ -122,6 +129,7 @@ def linear_fp32out(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         y = fn(x, weight)
         if y is not None:
             return y
+    _miss("linear_fp32out(shape/dtype)", x)
     return F.linear(x.float(), weight.float())
 
 
@@ -132,6 +140,7 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, count
         y = fn(x, w, counts, counts_host)
         if y is not None:
             return y
+        _miss("grouped_linear(shape)", x)
     ch = counts_host if counts_host is not None else counts.tolist()
     return ref.grouped_gemm(x, w.transpose(1, 2).to(x.dtype), ch)
 
@@ -158,7 +167,15 @@ def rmsnorm(x, weight, eps: float = 1e-5):
 
 
 def rmsnorm_gated(x, weight, z=None, eps: float = 1e-5, group_size=None, norm_before_gate=True):
+    _miss("rmsnorm_gated", x)          # PyTorch definition on every device
     return ref.rmsnorm_gated(x, weight, z, eps, group_size, norm_before_gate)
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Per-head product ``y[..., h, :] = x[..., h, :] @ w[h]^T`` with ``x`` [..., H, in] and ``w`` [H, out, in] (the
+    absorbed MLA up-projections of the sparse-attention path).  A batched library GEMM on every device: counted."""
+    _miss("head_linear(library bmm)", x)
+    return torch.einsum("...hi,hoi->...ho", x, w.to(x.dtype))
 
 
 def swiglu(gate_up):
@@ -174,6 +191,7 @@ def apply_rope(x, cos, sin):
         y = fn(x, cos, sin)
         if y is not None:
             return y
+        _miss("apply_rope(shape)", x)
     return ref.apply_rope(x, cos, sin)
 
 
@@ -185,6 +203,7 @@ def ngram_hash_embed(token_ids, table, mults, bias, table_sizes, table_offsets, 
         out = fn(token_ids, table, mults, bias, table_sizes, table_offsets, order_of_table)
         if out is not None:
             return out
+        _miss("ngram_hash_embed(shape)", table)
     return ref.ngram_hash_embed(token_ids, table, mults, bias, table_sizes, table_offsets, order_of_table)
 
 
@@ -210,6 +229,7 @@ def angle_cumsum(angles_raw, dt):
         out = fn(angles_raw, dt)
         if out is not None:
             return out
+        _miss("angle_cumsum(shape)", angles_raw)
     return mimo_scan_ref.angle_cumsum(angles_raw, dt)
 
 
@@ -275,6 +295,7 @@ def linear_cross_entropy_weighted(hidden, weight, labels, row_weights, ignore_in
         out = fn(hidden, weight, labels, row_weights, ignore_index)
         if out is not None:
             return out
+        _miss("linear_cross_entropy(shape)", hidden)
     per_tok = ref.linear_cross_entropy(hidden, weight, labels, ignore_index, "none")
     return (per_tok * row_weights.to(per_tok.dtype)).sum(), per_tok.detach()
 
@@ -287,4 +308,5 @@ def router_topk(logits, topk, score_function="sigmoid", expert_bias=None, norm_t
         out = fn(logits, topk, score_function, expert_bias, norm_topk_prob)
         if out is not None:
             return out
+        _miss("router_topk(shape)", logits)
     return ref.router_topk(logits, topk, score_function, expert_bias, norm_topk_prob)

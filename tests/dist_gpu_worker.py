@@ -29,7 +29,8 @@ def main():
     if tp_mode:
         pc = pstate.initialize(ParallelConfig(tp=world, sequence_parallel=True, fused_collectives=(mode == "tp_fused")))
     else:
-        pc = pstate.initialize(ParallelConfig(ep=world, fused_collectives=(mode == "fused")))
+        ep = min(world, nam56r_tiny().moe.num_experts)
+        pc = pstate.initialize(ParallelConfig(ep=ep, fused_collectives=(mode == "fused")))
     mcfg = nam56r_tiny(seq_length=seq)
     tcfg = TrainConfig(micro_batch_size=2, seq_length=seq, dtype="bf16", recompute=recompute,
                        optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0), log_interval=0)

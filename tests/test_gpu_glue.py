@@ -389,3 +389,36 @@ def test_moe_plan_kernels_match_library_ops(ep, ep_rank):
     for name in ("dest_row", "dest_rank", "token_of_copy", "seg_start_local", "tot_local", "seg_offsets", "tile_expert", "counts_global"):
         assert torch.equal(getattr(a, name).long(), getattr(b, name).long()), name
     assert int(a.rows_used) == int(b.rows_used) and (a.T, a.k) == (b.T, b.k)
+
+
+def test_moe_transport_skips_and_reports_rows_beyond_capacity():
+    """Receive buffer smaller than the routing needs (EP 1, so the "peer" is this GPU): push drops the copies that do
+    not fit, the pulls treat them as zero, no address beyond the buffer is formed, and the error word says so."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.parallel import fused_moe as fm
+    cu.check_errors()
+    torch.manual_seed(0)
+    T, k, E, H = 512, 2, 4, 256
+    ids = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)])
+    cap = 4 * fm.TILE                                          # T*k = 1024 copies need >= 1024 rows
+    plan = fm.MoEPlan(ids, E, 1, 0, None, cap, None)
+    heap = fm._LocalHeap()
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    guard = 64
+    buf = torch.full((cap + guard, H), 7.0, device="cuda", dtype=torch.bfloat16)    # rows past `cap` must stay untouched
+    dst = buf[:cap]
+    fm._push(heap, x, plan, dst)
+    torch.cuda.synchronize()
+    assert (buf[cap:] == 7.0).all()
+    with pytest.raises(cu.KernelError, match="bad argument"):
+        cu.check_errors()
+    w = torch.ones(T * k, device="cuda")
+    y = fm._pull_combine(heap, dst, plan, w, H, torch.bfloat16)
+    d = fm._pull_rowdot(heap, dst, plan, x)
+    torch.cuda.synchronize()
+    with pytest.raises(cu.KernelError, match="bad argument"):
+        cu.check_errors()
+    keep = (plan.dest_row < cap).view(T, k)
+    expect = (x.float() * keep.sum(1, keepdim=True)).bfloat16()     # every kept copy returns the token itself
+    assert _rel(y, expect) < 1e-2
+    assert (d.view(T, k)[~keep] == 0).all()

@@ -196,3 +196,32 @@ def test_moe_plan_invariants_on_cpu():
         assert (te[used_tiles:] == -1).all()
         for e in range(El):
             assert (te[int(seg[e]) // TILE:int(seg[e + 1]) // TILE] == e).all()
+
+
+def test_moe_plan_overflow_is_clipped_to_the_buffer():
+    """A skewed routing that needs more rows than the receive buffer holds: the receive layout (segments, tile map,
+    reduction ranges) never reaches past the buffer, and the copies that do not fit are exactly those the transport
+    kernels skip and report (row >= capacity)."""
+    from cppmega_b200.parallel.fused_moe import MoEPlan, TILE
+    torch.manual_seed(1)
+    T, k, E, ep = 600, 2, 8, 2
+    El = E // ep
+    ids_by_rank = []
+    for _ in range(ep):
+        ids = torch.stack([torch.randperm(E)[:k] for _ in range(T)])
+        ids[: T * 3 // 4, 0] = 1                               # expert 1 (rank 0) takes three quarters of the tokens
+        ids[: T * 3 // 4, 1] = 2
+        ids_by_rank.append(ids)
+    counts = torch.stack([torch.bincount(i.reshape(-1), minlength=E) for i in ids_by_rank])
+    cap = 6 * TILE                                             # far below rank 0's load
+    need0 = int(((counts.sum(0)[:El] + TILE - 1) // TILE * TILE).sum())
+    assert need0 > cap
+    plans = [MoEPlan(ids_by_rank[r], E, ep, r, None, cap, gather=lambda c: counts.clone()) for r in range(ep)]
+    p0 = plans[0]
+    assert int(p0.seg_offsets.max()) <= cap and int(p0.rows_used) <= cap
+    assert ((p0.seg_start_local.long() + p0.tot_local.long()) <= cap).all()
+    assert p0.tile_expert.numel() == cap // TILE
+    dropped = sum(int(((p.dest_row >= cap) & (p.dest_rank == 0)).sum()) for p in plans)
+    assert dropped > 0                                          # these are skipped + reported by push / pull
+    kept = torch.cat([p.dest_row[(p.dest_rank == 0) & (p.dest_row < cap)] for p in plans])
+    assert kept.unique().numel() == kept.numel() and int(kept.max()) < cap

@@ -61,8 +61,10 @@ def test_static_scratch_matches_regular_entry_point_twice():
         torch.cuda.synchronize()
         cu.check_errors()
         assert torch.isfinite(y.float()).all()
-        torch.testing.assert_close(y.float(), y_ref.float(), rtol=2e-2, atol=2e-2)
-        torch.testing.assert_close(final, f_ref, rtol=2e-2, atol=2e-2)
+        # both entry points run the same kernels on the same inputs: bit-for-bit, so a stale word of the shared array
+        # leaking into a result of any size shows up
+        assert torch.equal(y, y_ref)
+        assert torch.equal(final, f_ref)
 
 
 @pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
@@ -79,4 +81,4 @@ def test_static_scratch_rejects_oversize_and_full_size_fits():
     assert rc == 0
     torch.cuda.synchronize()
     cu.check_errors()
-    torch.testing.assert_close(y.float(), y_ref.float(), rtol=2e-2, atol=2e-2)
+    assert torch.equal(y, y_ref)
