@@ -14,6 +14,11 @@ over ranks:
   * ``value``: K optimizer steps on batches already resident on the device;
   * ``e2e``: K steps through ``Trainer.train_step`` fed from pinned host memory, with the
     loss read back to the host every step.
+Extra keys that explain the headline (short runs, a few steps each):
+  * ``like_for_like``: the same step with the SAME per-GPU memory policy at every N (every layer recomputed, nothing
+    kept), so that values at different N can be divided by each other;
+  * ``nccl_path`` (N >= 2): the same step with the library collectives (NCCL reduce-scatter / all-gather / all-to-all)
+    instead of the peer-memory kernels (``--no-fused-collectives`` runs only that arm as the main measurement).
 ``--impl reference`` reports why the reference stack cannot run on this machine.
 """
 from __future__ import annotations
@@ -113,7 +118,12 @@ def main() -> int:
     ap.add_argument("--depth", type=int, default=0, help="debug: truncate the stack (result is then not the headline config)")
     ap.add_argument("--recompute", default="auto", choices=["auto", "none", "selective", "full"])
     ap.add_argument("--keep-last", type=int, default=-1,
-                    help="layers at the end of the stack whose activations are kept instead of recomputed (-1: auto)")
+                    help="layers at the end of the stack whose activations are kept instead of recomputed "
+                         "(-1: 6 on one GPU in the headline config, else 0)")
+    ap.add_argument("--no-fused-collectives", action="store_true",
+                    help="main measurement on the NCCL collectives instead of the peer-memory kernels")
+    ap.add_argument("--no-extras", action="store_true", help="skip the like_for_like and nccl_path side measurements")
+    ap.add_argument("--extra-steps", type=int, default=3, help="timed steps of each side measurement")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"],
                     help="mxfp8: block-scaled FP8 linears (an extra measurement; the headline number is bf16)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -148,7 +158,7 @@ def main() -> int:
         overrides["seq_length"] = args.seq
     mcfg = get_preset(args.model, **overrides)
     ep = world if mcfg.moe.num_experts % world == 0 else 1
-    pcfg = ParallelConfig(tp=1, pp=1, ep=ep, distributed_optimizer=True)
+    pcfg = ParallelConfig(tp=1, pp=1, ep=ep, distributed_optimizer=True, fused_collectives=not args.no_fused_collectives)
     pc = pstate.initialize(pcfg)
     recompute = args.recompute
     if recompute == "auto":
@@ -159,19 +169,19 @@ def main() -> int:
     keep_last = args.keep_last
     if keep_last < 0:
         # spare memory on a single GPU (180 GB minus parameters, optimizer state and the scan stash) pays for keeping the
-        # activations of a few layers; with more ranks "selective" already keeps most of them
-        keep_last = 0
-        if (world == 1 and recompute == "full" and not args.depth and args.seq == 4096 and args.micro_batch == 4
-                and args.precision == "bf16"):
-            # measured on this config: 161.7 GB peak with every layer recomputed, +1.8 GB per kept layer; size the number
-            # of kept layers from what the device has free right now (6 on an empty 180 GB B200), keeping 3 GB in hand
-            free_gb = torch.cuda.mem_get_info(device)[0] / 2**30
-            keep_last = max(0, min(6, int((free_gb - 162.5 - 3.0) / 1.8)))
-    tcfg = TrainConfig(micro_batch_size=args.micro_batch, seq_length=args.seq, dtype="bf16", recompute=recompute,
-                       recompute_keep_last=keep_last, precision_recipe=args.precision,
-                       optimizer=OptimizerConfig(lr=1e-5, weight_decay=0.1, grad_dtype="bf16" if world < 4 else "fp32"),
-                       log_interval=0)
-    trainer = Trainer(mcfg, tcfg, pc, device=device)
+        # activations of the last 6 layers (161.7 GB peak with every layer recomputed, +1.8 GB per kept layer); a fixed
+        # number: if the device does not have that much free the run fails instead of measuring another configuration
+        keep_last = 6 if (world == 1 and recompute == "full" and not args.depth and args.seq == 4096
+                          and args.micro_batch == 4 and args.precision == "bf16") else 0
+    grad_dtype = "bf16" if world < 4 else "fp32"
+
+    def make_trainer(pctx, rc, kl):
+        tcfg = TrainConfig(micro_batch_size=args.micro_batch, seq_length=args.seq, dtype="bf16", recompute=rc,
+                           recompute_keep_last=kl, precision_recipe=args.precision,
+                           optimizer=OptimizerConfig(lr=1e-5, weight_decay=0.1, grad_dtype=grad_dtype), log_interval=0)
+        return Trainer(mcfg, tcfg, pctx, device=device)
+
+    trainer = make_trainer(pc, recompute, keep_last)
     n_params = sum(p.numel() for p in trainer.model.parameters())
     holder = {"trainer": trainer}
 
@@ -230,6 +240,60 @@ def main() -> int:
 
     tokens_per_step = args.micro_batch * args.seq * world
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    fused_paths = dict(trainer.fused)
+
+    # ---- side measurements ------------------------------------------------------------------------------------------
+    def short_run(tag):
+        for i in range(2):
+            step_device(i)
+        torch.cuda.synchronize()
+        cu.check_errors()
+        ms = timed(step_device, args.extra_steps) / args.extra_steps
+        return {"ms_per_step": ms, "tokens_per_s": tokens_per_step / (ms / 1e3), "steps": args.extra_steps, "warmup": 2}
+
+    like, nccl = None, None
+    if args.profile_dir:
+        args.no_extras = True                       # the profiled step must be the main configuration
+    if not args.no_extras:
+        # (1) every layer recomputed and nothing kept, at every N: the only memory policy that fits one GPU, so the one
+        # under which values at different N are comparable.  Same trainer: the policy is a property of the layer loop.
+        try:
+            m = trainer.model
+            old_policy = (m.recompute, m.recompute_keep_last)
+            m.recompute, m.recompute_keep_last = "full", 0
+            if old_policy == ("full", 0):           # the headline already is that configuration
+                like = {"ms_per_step": ms_dev / args.steps, "tokens_per_s": value, "steps": args.steps, "warmup": args.warmup}
+            else:
+                like = short_run("like_for_like")
+            like.update(recompute="full", recompute_keep_last=0, grad_dtype=grad_dtype,
+                        note="same memory policy at every N; the gradient buffers are bf16 below 4 GPUs (fp32 does not fit one GPU) and fp32 from 4 GPUs")
+            m.recompute, m.recompute_keep_last = old_policy
+        except Exception as e:                                   # never lose the headline over a side measurement
+            like = {"failed": f"{type(e).__name__}: {str(e)[:200]}"}
+        # (2) the same step on the library collectives.  Needs its own trainer (other buffers), so the first one goes.
+        if world > 1 and pcfg.fused_collectives:
+            try:
+                import dataclasses
+                import gc
+                holder["trainer"] = None
+                trainer.close()
+                trainer = m = None
+                gc.collect()
+                torch.cuda.empty_cache()
+                barrier()
+                pc_nccl = dataclasses.replace(pc, config=dataclasses.replace(pc.config, fused_collectives=False))
+                holder["trainer"] = make_trainer(pc_nccl, recompute, keep_last)
+                nccl = short_run("nccl_path")
+                nccl["fused_paths"] = dict(holder["trainer"].fused)
+                nccl["fused_over_nccl"] = nccl["ms_per_step"] / (ms_dev / args.steps)
+            except Exception as e:
+                nccl = {"failed": f"{type(e).__name__}: {str(e)[:200]}"}
+    # FLOPs the GPU actually executes: a recomputed layer runs its forward twice (the scan and sparse-attention kernels
+    # reuse their stashed outputs; their share is left in, so this is an upper bound by a few per cent)
+    kinds = mcfg.layer_kinds()
+    n_re = (len(kinds) - keep_last if recompute == "full" else
+            sum(k in ("mamba3", "m2rnn") for k in kinds[:len(kinds) - keep_last]) if recompute == "selective" else 0)
+    hw_factor = 1.0 + (n_re / max(len(kinds), 1)) / 3.0
     if not args.no_e2e:
         h2d = 2 * args.micro_batch * args.seq * 8             # input_ids + labels, int64, per rank
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
@@ -246,11 +310,14 @@ def main() -> int:
                        "global_batch": args.micro_batch * world, "micro_batch": args.micro_batch, "seq_len": args.seq,
                        "parallelism": f"ep{ep}dp{world}" if world > 1 else "single GPU (16 local experts)",
                        "distributed_optimizer": True, "recompute": recompute, "recompute_keep_last": keep_last,
+                       "grad_dtype": grad_dtype, "collectives": "peer-memory kernels" if pcfg.fused_collectives else "nccl",
                        "l2": "weights + activations per step are far larger than the 126 MB L2",
                        "headline_config": not args.depth and args.seq == 4096 and args.micro_batch == 4 and args.precision == "bf16"},
             "clocks": sampler.summary() if rank == 0 else None,
-            "e2e": e2e, "gpu_launches": launches, "fallback_ops": fallbacks,
+            "e2e": e2e, "gpu_launches": launches, "fallback_ops": fallbacks, "fused_paths": fused_paths,
+            "like_for_like": like, "nccl_path": nccl,
             "model_tflops_per_gpu": mcfg.flops_per_token(args.seq) * value / world / 1e12,
+            "hw_tflops_per_gpu": mcfg.flops_per_token(args.seq) * value / world / 1e12 * hw_factor,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
         }
         print(json.dumps(out))
@@ -258,6 +325,8 @@ def main() -> int:
         # every rank runs the profiled step (it contains collectives); rank 0 keeps the tables
         from cppmega_b200.utils.profiling import profile_steps
         pdir = args.profile_dir if rank == 0 else os.path.join(args.profile_dir, f"rank{rank}")
+        if holder["trainer"] is None:
+            raise SystemExit("--profile-dir needs --no-extras (the side measurements replace the trainer)")
         table = profile_steps(step_device, 1, pdir)
         if rank == 0:
             print(table[:200], file=sys.stderr)

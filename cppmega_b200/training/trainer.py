@@ -135,6 +135,18 @@ class Trainer:
             self.fused["moe"] = bufs is not None
             self._moe_bufs = bufs
 
+    def close(self) -> None:
+        """Release the peer-mapped heaps (every rank of the group must call this in the same phase)."""
+        opt_close = getattr(self.optimizer, "close", None)
+        if opt_close is not None:
+            opt_close()
+        for name in ("_moe_bufs", "_tp_bufs"):
+            bufs = getattr(self, name, None)
+            heap = getattr(bufs, "heap", None)
+            if heap is not None and hasattr(heap, "close"):
+                heap.close()
+            setattr(self, name, None)
+
     # ---- one optimizer step ------------------------------------------------
     def _to_device(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
         return {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}

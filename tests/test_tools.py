@@ -99,6 +99,9 @@ def test_gpu_tool_modules_import_and_list_their_cases():
     for name in ("gemm", "grouped", "rmsnorm", "ce", "scan", "mxfp8_gemm", "longctx"):
         assert name in kernel_bench.CASES, name
     assert callable(moe_bench.main)
+    from cppmega_b200.tools import kernel_bench_reference
+    assert set(kernel_bench_reference.CASES) == {"m2rnn", "sparse_mla", "indexer", "linear_ce", "gemm"}
+    assert kernel_bench_reference.main([]) == 2
     pk = kernel_bench.peaks()
     assert pk["bf16_tflops"] > 0 and pk["kind"] in ("measured", "fallback")
 
