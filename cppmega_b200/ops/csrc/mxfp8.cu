@@ -49,7 +49,7 @@ __device__ __forceinline__ size_t swizzled_index(long long row, int kb, int kb_t
 // one thread = 8 consecutive values; 4 threads = one block of 32
 __global__ void __launch_bounds__(256) quantize_rowwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ payload,
                                                                uint8_t* __restrict__ scales, uint8_t* __restrict__ sw, long long rows,
-                                                               int cols) {
+                                                               int cols, const float* __restrict__ tamax) {
   const int kb_row = cols / 32, kb_tiles = (kb_row + 3) / 4;
   const long long nvec = rows * (cols / 8);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(256) quantize_rowwise_kernel(const __nv_bfloat
     const unsigned live = __activemask();          // whole groups of four threads enter or leave the loop together
     am = fmaxf(am, __shfl_xor_sync(live, am, 1));
     am = fmaxf(am, __shfl_xor_sync(live, am, 2));
-    const uint8_t sb = e8m0_from_amax(am);
+    const uint8_t sb = e8m0_from_amax(tamax ? *tamax : am);
     const float mult = exp2f(127.f - (float)sb);
     uint2 o;
     o.x = (uint32_t)to_e4m3x2(f[0] * mult, f[1] * mult) | ((uint32_t)to_e4m3x2(f[2] * mult, f[3] * mult) << 16);
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(256) quantize_rowwise_kernel(const __nv_bfloat
 // CTA = tile of 32 rows x 128 columns; thread c owns one column: 32 values -> one block
 __global__ void __launch_bounds__(128) quantize_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ payload_t,
                                                                uint8_t* __restrict__ scales_t, uint8_t* __restrict__ sw, long long rows,
-                                                               int cols) {
+                                                               int cols, const float* __restrict__ tamax) {
   const long long r0 = (long long)blockIdx.y * 32;
   const int c = blockIdx.x * 128 + threadIdx.x;
   if (c >= cols) return;
@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(128) quantize_colwise_kernel(const __nv_bfloat
     f[r] = (r0 + r < rows) ? __bfloat162float(x[(size_t)(r0 + r) * cols + c]) : 0.f;
     am = fmaxf(am, fabsf(f[r]));
   }
-  const uint8_t sb = e8m0_from_amax(am);
+  const uint8_t sb = e8m0_from_amax(tamax ? *tamax : am);
   const float mult = exp2f(127.f - (float)sb);
   uint32_t w[8];
 #pragma unroll
@@ -116,7 +116,8 @@ __global__ void __launch_bounds__(128) quantize_colwise_kernel(const __nv_bfloat
 __global__ void __launch_bounds__(256) quantize_both_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ pay_r,
                                                             uint8_t* __restrict__ sc_r, uint8_t* __restrict__ sw_r,
                                                             uint8_t* __restrict__ pay_t, uint8_t* __restrict__ sc_t,
-                                                            uint8_t* __restrict__ sw_t, long long rows, int cols) {
+                                                            uint8_t* __restrict__ sw_t, long long rows, int cols,
+                                                            const float* __restrict__ tamax) {
   __shared__ float tile[32][257];
   const long long r0 = (long long)blockIdx.y * 32;
   const int c0 = blockIdx.x * 256;
@@ -148,7 +149,7 @@ __global__ void __launch_bounds__(256) quantize_both_kernel(const __nv_bfloat16*
     am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
     am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
     if (valid) {
-      const uint8_t sb = e8m0_from_amax(am);
+      const uint8_t sb = e8m0_from_amax(tamax ? *tamax : am);
       const float mult = exp2f(127.f - (float)sb);
       uint2 o;
       o.x = (uint32_t)to_e4m3x2(f[0] * mult, f[1] * mult) | ((uint32_t)to_e4m3x2(f[2] * mult, f[3] * mult) << 16);
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(256) quantize_both_kernel(const __nv_bfloat16*
     f[r] = tile[r][p];
     am = fmaxf(am, fabsf(f[r]));
   }
-  const uint8_t sb = e8m0_from_amax(am);
+  const uint8_t sb = e8m0_from_amax(tamax ? *tamax : am);
   const float mult = exp2f(127.f - (float)sb);
   uint32_t w[8];
 #pragma unroll
@@ -183,6 +184,28 @@ __global__ void __launch_bounds__(256) quantize_both_kernel(const __nv_bfloat16*
   dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
   sc_t[(size_t)col * kb_col + blockIdx.y] = sb;
   if (sw_t) sw_t[swizzled_index(col, (int)blockIdx.y, kbt_col)] = sb;
+}
+
+// absolute maximum of a bf16 tensor: non-negative floats order like their bit patterns, so an integer atomicMax works
+__global__ void __launch_bounds__(256) amax_kernel(const __nv_bfloat16* __restrict__ x, long long nvec, float* __restrict__ out) {
+  float am = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(x)[i];
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 t = __bfloat1622float2(b[j]);
+      am = fmaxf(am, fmaxf(fabsf(t.x), fabsf(t.y)));
+    }
+  }
+  am = warp_max(am);
+  __shared__ float red[8];
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = am;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) am = fmaxf(am, red[w]);
+    if (am == am) atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(am));
+  }
 }
 
 __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ payload, const uint8_t* __restrict__ scales,
@@ -228,34 +251,45 @@ static int grid1d(long long work) {
 
 // x [rows, cols] bf16, cols % 32 == 0 -> payload [rows, cols] u8, scales [rows, cols/32] u8; `swizzled` (optional) also
 // receives the scales in the 128x4 tile order (its padding entries must already hold the neutral scale)
+// `tensor_amax` (optional, every quantise entry point): a device float holding the absolute maximum of the WHOLE tensor.
+// When given, every block uses the one scale derived from it (per-tensor "current scaling" with a power-of-two scale)
+// instead of its own: the tensorwise FP8 recipe on the same payload / scale-byte data path.
 extern "C" int cm_mxfp8_quantize_rowwise(const void* x, void* payload, void* scales, void* swizzled, long long rows, int cols,
-                                         cudaStream_t s) {
+                                         const float* tensor_amax, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (cols % 32) return -10;
   quantize_rowwise_kernel<<<grid1d(rows * (cols / 8)), 256, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)payload, (uint8_t*)scales,
-                                                                  (uint8_t*)swizzled, rows, cols);
+                                                                  (uint8_t*)swizzled, rows, cols, tensor_amax);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 // x [rows, cols] bf16, rows % 32 == 0 -> payload_t [cols, rows] u8, scales_t [cols, rows/32] u8 (+ optional swizzled copy)
 extern "C" int cm_mxfp8_quantize_colwise(const void* x, void* payload_t, void* scales_t, void* swizzled, long long rows, int cols,
-                                         cudaStream_t s) {
+                                         const float* tensor_amax, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (rows % 32) return -10;
   dim3 grid((cols + 127) / 128, (unsigned)(rows / 32));
-  quantize_colwise_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)payload_t, (uint8_t*)scales_t, (uint8_t*)swizzled, rows, cols);
+  quantize_colwise_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)payload_t, (uint8_t*)scales_t, (uint8_t*)swizzled, rows, cols, tensor_amax);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 // x [rows, cols] bf16 (rows % 32 == 0, cols % 32 == 0) -> row-wise payload / scales and the transposed column-wise pair in
 // one pass; the swizzled scale outputs are optional
 extern "C" int cm_mxfp8_quantize_both(const void* x, void* pay_r, void* sc_r, void* sw_r, void* pay_t, void* sc_t, void* sw_t,
-                                      long long rows, int cols, cudaStream_t s) {
+                                      long long rows, int cols, const float* tensor_amax, cudaStream_t s) {
   if (rows <= 0) return 0;
   if ((rows % 32) || (cols % 32)) return -10;
   dim3 grid((cols + 255) / 256, (unsigned)(rows / 32));
   quantize_both_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)pay_r, (uint8_t*)sc_r, (uint8_t*)sw_r, (uint8_t*)pay_t,
-                                           (uint8_t*)sc_t, (uint8_t*)sw_t, rows, cols);
+                                           (uint8_t*)sc_t, (uint8_t*)sw_t, rows, cols, tensor_amax);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// out (device float, zeroed by the caller) = max(out, max |x|) over n bf16 values (n % 8 == 0)
+extern "C" int cm_amax_bf16(const void* x, long long n, float* out, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (n % 8) return -10;
+  amax_kernel<<<grid1d(n / 8), 256, 0, s>>>((const __nv_bfloat16*)x, n / 8, out);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -59,9 +59,10 @@ def _declare(L: ctypes.CDLL) -> None:
         if fn is not None:
             fn.argtypes = args
             fn.restype = i32
-    from . import extra, kernels4
+    from . import attention, extra, kernels4
     extra.declare(L)
     kernels4.declare(L)
+    attention.declare(L)
 
 
 def stream_ptr() -> int:
@@ -358,9 +359,10 @@ def _register() -> None:
     F_.register_cuda("rmsnorm", rmsnorm)
     F_.register_cuda("swiglu", swiglu)
     F_.register_cuda("adamw_shard", adamw_shard)
-    from . import extra, kernels4
+    from . import attention, extra, kernels4
     extra.register()
     kernels4.register()
+    attention.register()
 
 
 if torch.cuda.is_available():

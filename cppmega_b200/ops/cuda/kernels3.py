@@ -30,6 +30,13 @@ def supported(Q, K, V, Zeta, Phi, D, Z, div) -> bool:
             and None not in (Zeta, Phi, D, Z) and Z.dtype == torch.bfloat16)
 
 
+class _ShapeOnly:
+    """Stand-in that answers ``shape`` / ``dtype`` like tensor ``x`` would after padding its last dimension to ``n``."""
+
+    def __init__(self, x: torch.Tensor, n: int):
+        self.shape, self.dtype = (*x.shape[:-1], n), x.dtype
+
+
 def _as_bsgrn(x: torch.Tensor) -> torch.Tensor:
     """[B,S,R,G,N] (possibly a permuted view) -> contiguous [B,S,G,R,N]."""
     y = x.permute(0, 1, 3, 2, 4)
@@ -96,7 +103,27 @@ class MimoScanFn(torch.autograd.Function):
         return (*lean_backward(saved, dy, ctx.div, ctx.chunk), None)
 
 
+def _pad_state_dim(x: torch.Tensor, n: int, to: int = 128) -> torch.Tensor:
+    """[..., n] -> [..., to]: each half of the state dimension keeps its place at the start of the wider half
+    (``[first half | 0 | second half | 0]``), so the rotary pairs ``(i, n/2 + i)`` become ``(i, to/2 + i)``."""
+    h, z = n // 2, x.new_zeros(*x.shape[:-1], to // 2 - n // 2)
+    return torch.cat([x[..., :h], z, x[..., h:], z], dim=-1)
+
+
+def _padded_to_128(Q, K, Qb, Kb, angles):
+    """A scan with state dimension 32 or 64 is the scan with state dimension 128 on zero-padded Q / K / biases: the
+    padded state rows stay zero, the padded rotary pairs get angle 0.  The kernels are instantiated for 128."""
+    N = Q.shape[-1]
+    ang = torch.cat([angles, angles.new_zeros(*angles.shape[:-1], 32 - angles.shape[-1])], dim=-1)
+    return _pad_state_dim(Q, N), _pad_state_dim(K, N), _pad_state_dim(Qb, N), _pad_state_dim(Kb, N), ang
+
+
 def mimo_scan(Q, K, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, angles, D, Z, div, chunk):
+    N = Q.shape[-1]
+    if (N in (32, 64) and div == 4 and angles.shape[-1] == N // 4 and V.is_cuda
+            and supported(_ShapeOnly(Q, 128), K, V, Zeta, Phi, D, Z, div)):
+        Qp, Kp, Qbp, Kbp, angp = _padded_to_128(Q, K, Qb, Kb, angles)
+        return mimo_scan(Qp, Kp, V, ADT, DT, Trap, Qbp, Kbp, Psi, Zeta, Phi, angp, D, Z, div, chunk)
     if not supported(Q, K, V, Zeta, Phi, D, Z, div):
         from ..mimo_scan_lean import mimo_scan_lean
         F_._FALLBACKS["mimo_scan"] += 1

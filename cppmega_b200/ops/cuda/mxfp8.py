@@ -45,11 +45,13 @@ def _lib():
     L = lib()
     if not getattr(L, "_mx_declared", False):
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-        L.cm_mxfp8_quantize_rowwise.argtypes = [vp, vp, vp, vp, i64, i32, vp]
-        L.cm_mxfp8_quantize_colwise.argtypes = [vp, vp, vp, vp, i64, i32, vp]
+        L.cm_mxfp8_quantize_rowwise.argtypes = [vp, vp, vp, vp, i64, i32, vp, vp]
+        L.cm_mxfp8_quantize_colwise.argtypes = [vp, vp, vp, vp, i64, i32, vp, vp]
+        L.cm_amax_bf16.argtypes = [vp, i64, vp, vp]
+        L.cm_amax_bf16.restype = i32
         L.cm_mxfp8_dequantize.argtypes = [vp, vp, vp, i64, vp]
         L.cm_mxfp8_swizzle_scales.argtypes = [vp, vp, i64, i32, vp]
-        L.cm_mxfp8_quantize_both.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i32, vp]
+        L.cm_mxfp8_quantize_both.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i32, vp, vp]
         L.cm_mxfp8_grouped_rows.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]
         L.cm_mxfp8_grouped_k.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp]
         L.cm_mxfp8_gemm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, vp, vp]
@@ -72,9 +74,31 @@ def _swizzled_buffer(rows: int, kb: int, device) -> torch.Tensor:
     return torch.empty(n, dtype=torch.uint8, device=device)
 
 
-def quantize_rowwise(x: torch.Tensor, for_gemm: bool = False) -> Mxfp8Tensor:
+def tensor_amax(x: torch.Tensor) -> torch.Tensor:
+    """Device scalar max |x| of a bf16 tensor (one pass, no host sync): the scale source of the tensorwise recipe."""
+    from . import stream_ptr
+    x = x.contiguous()
+    out = torch.zeros(1, dtype=torch.float32, device=x.device)
+    if x.numel() % 8:
+        out.copy_(x.abs().max().float())
+        return out
+    _check(_lib().cm_amax_bf16(x.data_ptr(), x.numel(), out.data_ptr(), stream_ptr()), "cm_amax_bf16")
+    F_.count_launch("fp8_amax")
+    return out
+
+
+def _amax_ptr(x: torch.Tensor, tensorwise):
+    """``tensorwise``: False / None (block scales), True (measure the tensor's amax now), or a device scalar."""
+    if tensorwise is None or tensorwise is False:
+        return None, None
+    am = tensor_amax(x) if tensorwise is True else tensorwise
+    return am, am.data_ptr()
+
+
+def quantize_rowwise(x: torch.Tensor, for_gemm: bool = False, tensorwise=None) -> Mxfp8Tensor:
     """Blocks of 32 along the last dimension of a 2-D bf16 tensor.  ``for_gemm`` also writes the scales in the tile
-    order the block-scaled GEMM reads, from the same kernel."""
+    order the block-scaled GEMM reads, from the same kernel.  ``tensorwise``: one power-of-two scale for the whole
+    tensor (written into every scale byte) instead of one per block."""
     from . import stream_ptr
     assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.shape[1] % 32 == 0
     x = x.contiguous()
@@ -82,13 +106,14 @@ def quantize_rowwise(x: torch.Tensor, for_gemm: bool = False) -> Mxfp8Tensor:
     pay = torch.empty(rows, cols, dtype=torch.uint8, device=x.device)
     sc = torch.empty(rows, cols // 32, dtype=torch.uint8, device=x.device)
     sw = _swizzled_buffer(rows, cols // 32, x.device) if for_gemm else None
+    _am, amp = _amax_ptr(x, tensorwise)
     _check(_lib().cm_mxfp8_quantize_rowwise(x.data_ptr(), pay.data_ptr(), sc.data_ptr(), sw.data_ptr() if for_gemm else None,
-                                            rows, cols, stream_ptr()), "cm_mxfp8_quantize_rowwise")
+                                            rows, cols, amp, stream_ptr()), "cm_mxfp8_quantize_rowwise")
     F_.count_launch("mxfp8_quantize")
     return Mxfp8Tensor(pay, sc, (rows, cols), sw)
 
 
-def quantize_colwise(x: torch.Tensor, for_gemm: bool = False) -> Mxfp8Tensor:
+def quantize_colwise(x: torch.Tensor, for_gemm: bool = False, tensorwise=None) -> Mxfp8Tensor:
     """Blocks of 32 along the rows; the result is stored transposed: payload [cols, rows], scales [cols, rows/32]."""
     from . import stream_ptr
     assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.shape[0] % 32 == 0
@@ -97,13 +122,14 @@ def quantize_colwise(x: torch.Tensor, for_gemm: bool = False) -> Mxfp8Tensor:
     pay = torch.empty(cols, rows, dtype=torch.uint8, device=x.device)
     sc = torch.empty(cols, rows // 32, dtype=torch.uint8, device=x.device)
     sw = _swizzled_buffer(cols, rows // 32, x.device) if for_gemm else None
+    _am, amp = _amax_ptr(x, tensorwise)
     _check(_lib().cm_mxfp8_quantize_colwise(x.data_ptr(), pay.data_ptr(), sc.data_ptr(), sw.data_ptr() if for_gemm else None,
-                                            rows, cols, stream_ptr()), "cm_mxfp8_quantize_colwise")
+                                            rows, cols, amp, stream_ptr()), "cm_mxfp8_quantize_colwise")
     F_.count_launch("mxfp8_quantize")
     return Mxfp8Tensor(pay, sc, (cols, rows), sw)
 
 
-def quantize_both(x: torch.Tensor, for_gemm: bool = True):
+def quantize_both(x: torch.Tensor, for_gemm: bool = True, tensorwise=None):
     """Row-wise and transposed column-wise MXFP8 copies of a 2-D bf16 tensor from one read of it."""
     from . import stream_ptr
     assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.shape[0] % 32 == 0 and x.shape[1] % 32 == 0
@@ -117,8 +143,9 @@ def quantize_both(x: torch.Tensor, for_gemm: bool = True):
     sw_r = _swizzled_buffer(rows, cols // 32, dev) if for_gemm else None
     sw_t = _swizzled_buffer(cols, rows // 32, dev) if for_gemm else None
     ptr = lambda t: t.data_ptr() if t is not None else None
+    _am, amp = _amax_ptr(x, tensorwise)
     _check(_lib().cm_mxfp8_quantize_both(x.data_ptr(), pay_r.data_ptr(), sc_r.data_ptr(), ptr(sw_r), pay_t.data_ptr(),
-                                         sc_t.data_ptr(), ptr(sw_t), rows, cols, stream_ptr()), "cm_mxfp8_quantize_both")
+                                         sc_t.data_ptr(), ptr(sw_t), rows, cols, amp, stream_ptr()), "cm_mxfp8_quantize_both")
     F_.count_launch("mxfp8_quantize")
     return Mxfp8Tensor(pay_r, sc_r, (rows, cols), sw_r), Mxfp8Tensor(pay_t, sc_t, (cols, rows), sw_t)
 
@@ -166,14 +193,15 @@ def eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.shape[-1] % 32 == 0 and w.shape[0] % 32 == 0 and rows % 32 == 0 and rows > 0)
 
 
-def quantize_weight(w: torch.Tensor, colwise: bool) -> Mxfp8Tensor:
-    """MXFP8 copy of a parameter, kept on the parameter until the optimizer next writes it (``_version`` changes), so
+def quantize_weight(w: torch.Tensor, colwise: bool, tensorwise: bool = False) -> Mxfp8Tensor:
+    """FP8 copy of a parameter, kept on the parameter until the optimizer next writes it (``_version`` changes), so
     the replayed forward of a recomputed layer and every micro-batch of a step reuse one quantisation."""
-    key = "_mx_col" if colwise else "_mx_row"
+    key = ("_tw_col" if colwise else "_tw_row") if tensorwise else ("_mx_col" if colwise else "_mx_row")
     hit = getattr(w, key, None)
     if hit is not None and hit[0] == w._version:
         return hit[1]
-    q = quantize_colwise(w.detach(), True) if colwise else quantize_rowwise(w.detach(), True)
+    tw = True if tensorwise else None
+    q = quantize_colwise(w.detach(), True, tw) if colwise else quantize_rowwise(w.detach(), True, tw)
     try:
         setattr(w, key, (w._version, q))
     except AttributeError:
@@ -232,18 +260,22 @@ def grouped_wgrad_mxfp8(dy_t: Mxfp8Tensor, x_t: Mxfp8Tensor, seg_offsets: torch.
 
 
 class Mxfp8LinearFn(torch.autograd.Function):
-    """y = q_K(x) q_K(W)^T;  dx = q_N(dy) q_N(W);  dW = q_T(dy)^T q_T(x)  (q_D: MXFP8 rounding along D)."""
+    """y = q_K(x) q_K(W)^T;  dx = q_N(dy) q_N(W);  dW = q_T(dy)^T q_T(x)  (q_D: FP8 rounding along D).  ``tensorwise``:
+    one power-of-two scale per tensor (measured from the tensor itself: current scaling) instead of one per 32 values;
+    the row-wise and transposed copies of one tensor share the measured amax."""
 
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, tensorwise=False):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        xq, x_t = quantize_both(x2)                     # along K, and [K, T] along tokens: the wgrad operand (1 byte/value)
-        wq = quantize_weight(w, colwise=False)          # along K
+        tw = tensor_amax(x2) if tensorwise else None
+        xq, x_t = quantize_both(x2, True, tw)           # along K, and [K, T] along tokens: the wgrad operand (1 byte/value)
+        wq = quantize_weight(w, colwise=False, tensorwise=tensorwise)          # along K
         y = gemm_mxfp8(xq, wq)
         ctx.save_for_backward(x_t.payload, x_t.scales, x_t._swizzled, w)
         ctx.xshape = x.shape
+        ctx.tensorwise = tensorwise
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -252,19 +284,20 @@ class Mxfp8LinearFn(torch.autograd.Function):
         xt_pay, xt_sc, xt_sw, w = ctx.saved_tensors
         K, T = xt_pay.shape
         dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+        tw = tensor_amax(dy2) if ctx.tensorwise else None
         dx = dw = None
         dyq = dy_t = None
         if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
-            dyq, dy_t = quantize_both(dy2)                               # one read of dy for both products
+            dyq, dy_t = quantize_both(dy2, True, tw)                     # one read of dy for both products
         if ctx.needs_input_grad[0]:
-            dyq = dyq if dyq is not None else quantize_rowwise(dy2, True)   # along N
-            w_t = quantize_weight(w, colwise=True)                       # [K, N] along N
+            dyq = dyq if dyq is not None else quantize_rowwise(dy2, True, tw)   # along N
+            w_t = quantize_weight(w, colwise=True, tensorwise=ctx.tensorwise)   # [K, N] along N
             dx = gemm_mxfp8(dyq, w_t).view(ctx.xshape)                   # [T,N] x [K,N]^T
         if ctx.needs_input_grad[1]:
-            dy_t = dy_t if dy_t is not None else quantize_colwise(dy2, True)   # [N, T] along tokens
+            dy_t = dy_t if dy_t is not None else quantize_colwise(dy2, True, tw)   # [N, T] along tokens
             x_t = Mxfp8Tensor(xt_pay, xt_sc, (K, T), xt_sw)              # [K, T]
             dw = wgrad_into_main_grad(w, lambda out, acc: _wgrad(dy_t, x_t, out, acc))
-        return dx, dw
+        return dx, dw, None
 
 
 def _wgrad(dy_t: Mxfp8Tensor, x_t: Mxfp8Tensor, out, accumulate: bool):
@@ -274,7 +307,7 @@ def _wgrad(dy_t: Mxfp8Tensor, x_t: Mxfp8Tensor, out, accumulate: bool):
     return gemm_mxfp8(dy_t, x_t, out=out, accumulate=accumulate)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor):
+def linear(x: torch.Tensor, w: torch.Tensor, tensorwise: bool = False):
     if not eligible(x, w):
         return None
-    return Mxfp8LinearFn.apply(x, w)
+    return Mxfp8LinearFn.apply(x, w, tensorwise)

@@ -88,13 +88,21 @@ def _cuda(name: str, *tensors) -> Optional[Callable]:
 # ---- dense ---------------------------------------------------------------
 
 _PRECISION_RECIPE = "bf16"
+RECIPES = ("bf16", "mxfp8", "tensorwise")
 
 
 def set_precision_recipe(name: str) -> None:
-    """``bf16`` or ``mxfp8``: with ``mxfp8`` every eligible linear layer (2-D bf16 weight, all three dims multiples
-    of 32) rounds its operands to MXFP8 along the reduced dimension and saves its activation as an MXFP8 tensor."""
+    """Precision of the linear layers (2-D bf16 weight, all three dims multiples of 32) and the expert GEMMs:
+
+    * ``bf16``: bf16 operands;
+    * ``mxfp8``: operands rounded to E4M3 with one E8M0 scale per 32 values along the reduced dimension; the activation
+      saved for the weight gradient is kept in that form;
+    * ``tensorwise``: E4M3 with ONE power-of-two scale per tensor, measured from the tensor at every use (current
+      scaling) - the reference's production FP8 recipe (docs/production_status.md:13-18) on the same kernels.
+
+    This is the process-wide default; :func:`precision_scope` and :func:`install_precision_rules` narrow it to modules."""
     global _PRECISION_RECIPE
-    if name not in ("bf16", "mxfp8"):
+    if name not in RECIPES:
         raise ValueError(f"unknown precision recipe {name!r}")
     _PRECISION_RECIPE = name
 
@@ -103,15 +111,65 @@ def precision_recipe() -> str:
     return _PRECISION_RECIPE
 
 
+class precision_scope:
+    """``with precision_scope("mxfp8"): ...`` - the recipe of every linear called inside (forward; each op remembers its
+    recipe for its backward)."""
+
+    def __init__(self, name: str):
+        if name not in RECIPES:
+            raise ValueError(f"unknown precision recipe {name!r}")
+        self.name = name
+
+    def __enter__(self):
+        self.prev = _PRECISION_RECIPE
+        set_precision_recipe(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        set_precision_recipe(self.prev)
+        return False
+
+
+def install_precision_rules(model, rules, default: str = "bf16"):
+    """Per-module precision selection.  ``rules``: sequence of ``(glob pattern, recipe)`` matched against the qualified
+    module names of ``model`` (first match wins; e.g. ``("*.mixer.in_proj", "mxfp8")`` or ``("decoder.layers.*.mlp",
+    "tensorwise")``); modules that match run their forward under that recipe, everything else under ``default``.
+    Counterpart of the reference's layer-selective FP8 (cppmega/megatron/selective_fp8_moe_patch.py:60-149: FP8 on MoE
+    layers only) and of its per-module precision file (configs/te_precision/mamba_mxfp8_eval_bf16.yaml:1-29: MXFP8 on
+    the Mamba in / out projections only).  Returns ``(handles, matched module names)``; ``h.remove()`` undoes a hook."""
+    import fnmatch
+    set_precision_recipe(default)
+    handles, matched = [], []
+    for name, mod in model.named_modules():
+        recipe = next((r for pat, r in rules if fnmatch.fnmatchcase(name, pat)), None)
+        if recipe is None:
+            continue
+        if recipe not in RECIPES:
+            raise ValueError(f"unknown precision recipe {recipe!r} for pattern matching {name!r}")
+        stack = []
+
+        def pre(_m, _args, recipe=recipe, stack=stack):
+            stack.append(_PRECISION_RECIPE)
+            set_precision_recipe(recipe)
+
+        def post(_m, _args, _out, stack=stack):
+            set_precision_recipe(stack.pop())
+
+        handles.append(mod.register_forward_pre_hook(pre))
+        handles.append(mod.register_forward_hook(post, always_call=True))
+        matched.append(name)
+    return handles, matched
+
+
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``x @ w^T``; w is [out, in]."""
-    if _PRECISION_RECIPE == "mxfp8" and x.is_cuda:
+    if _PRECISION_RECIPE != "bf16" and x.is_cuda:
         _ensure_ext()
         from .cuda import mxfp8
-        y = mxfp8.linear(x, w)
+        y = mxfp8.linear(x, w, tensorwise=_PRECISION_RECIPE == "tensorwise")
         if y is not None:
             return y
-        _FALLBACKS["mxfp8_linear(shape)"] += 1
+        _FALLBACKS["fp8_linear(shape)"] += 1
     fn = _cuda("linear", x)
     if fn is not None:
         y = fn(x, w)
@@ -269,6 +327,11 @@ def causal_attention(q, k, v, scale: float):
     fn = _cuda("causal_attention", q)
     if fn is not None:
         return fn(q, k, v, scale)
+    return causal_attention_library(q, k, v, scale)
+
+
+def causal_attention_library(q, k, v, scale: float):
+    """The library path (``scaled_dot_product_attention``): CPU, and shapes the kernel does not take."""
     dq, dv = q.shape[-1], v.shape[-1]
     if q.is_cuda and dv < dq:          # library flash kernels want one head size: zero-pad V
         v = F.pad(v, (0, dq - dv))

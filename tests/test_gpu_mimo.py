@@ -90,3 +90,33 @@ def test_mimo_scan_backward_many_chunks(B, S, H, G):
     for n, x, r in zip(names, a1, a2):
         assert x.grad is not None and torch.isfinite(x.grad.float()).all(), n
         assert _rel(x.grad, r.grad) < 6e-2, (n, _rel(x.grad, r.grad))
+
+
+@pytest.mark.parametrize("N,B,S,H,G", [(64, 2, 256, 8, 1), (32, 2, 64, 4, 2)])
+def test_mimo_scan_smaller_state_dims(N, B, S, H, G):
+    """State dimension 64 (the shape of the reference's published kernel timings: B2 S256 H8 G1 N64 P64 R4) and 32
+    (the CPU plumbing configuration) run on the kernels through zero padding; forward and all gradients against the
+    fp32 definition at the ORIGINAL state dimension."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.ops import mimo_scan_ref as R
+    from cppmega_b200.ops.cuda import kernels3
+    Qn, Kn, V, Z, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D = _inputs(B, S, H, G, N=N, seed=3)
+    Q5, K5 = Qn.permute(0, 1, 3, 2, 4), Kn.permute(0, 1, 3, 2, 4)
+    args = [Q5, K5, V, ADT, DT, Trap, Qb, Kb, Psi, Zeta, Phi, ang, D, Z]
+    a1 = [t.detach().clone().requires_grad_() for t in args]
+    a2 = [t.detach().float().clone().requires_grad_() for t in args]
+    F_.reset_counters()
+    y1 = kernels3.mimo_scan(*a1, 4, 16)
+    assert F_.launch_counts().get("mimo_scan_fwd", 0) == 3 and not F_.fallback_counts()
+    y2 = R.mimo_scan_chunked(*a2, 4, 16)
+    g = torch.randn_like(y2)
+    y1.backward(g.to(y1.dtype))
+    y2.backward(g)
+    torch.cuda.synchronize()
+    cu.check_errors()
+    assert _rel(y1, y2) < 2e-2
+    names = "Q K V ADT DT Trap Qb Kb Psi Zeta Phi angles D Z".split()
+    for n, x, r in zip(names, a1, a2):
+        assert x.grad.shape == r.grad.shape, n
+        assert _rel(x.grad, r.grad) < 6e-2, (n, _rel(x.grad, r.grad))

@@ -60,3 +60,38 @@ def test_mimo_scan_lean_matches_sequential():
     assert _rel(y2, y1) < 2e-2
     for i, (x, r) in enumerate(zip(a2, a1)):
         assert _rel(x.grad, r.grad) < 5e-2, i
+
+
+def _attn_ref(q, k, v, scale):
+    """fp32 causal attention, [B,S,H,D] layout."""
+    B, S, H, _ = q.shape
+    s = torch.einsum("bihd,bjhd->bhij", q.float(), k.float()) * scale
+    s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=q.device).tril(), float("-inf"))
+    return torch.einsum("bhij,bjhd->bihd", torch.softmax(s, dim=-1), v.float())
+
+
+@pytest.mark.parametrize("B,S,H", [(1, 128, 2), (2, 512, 4), (1, 1024, 3)])
+def test_dense_causal_attention_kernels(B, S, H):
+    """Forward and the three gradients of the tcgen05 attention kernels against the fp32 definition: one key tile, several
+    key tiles (online softmax, the state gradients kept in TMEM over the query loop), batch and head strides."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops import functional as F_
+    torch.manual_seed(S)
+    q = (torch.randn(B, S, H, 128, device="cuda") * 0.7).bfloat16().requires_grad_()
+    k = (torch.randn(B, S, H, 128, device="cuda") * 0.7).bfloat16().requires_grad_()
+    v = torch.randn(B, S, H, 64, device="cuda").bfloat16().requires_grad_()
+    scale = 128 ** -0.5
+    F_.reset_counters()
+    o = F_.causal_attention(q, k, v, scale)
+    assert F_.launch_counts().get("causal_attention", 0) == 1 and not F_.fallback_counts()
+    g = torch.randn_like(o)
+    o.backward(g)
+    torch.cuda.synchronize()
+    cu.check_errors()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf = _attn_ref(qr, kr, vr, scale)
+    orf.backward(g.float())
+    assert _rel(o, orf) < 1.5e-2
+    for name, a, b in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        assert torch.isfinite(a.float()).all(), name
+        assert _rel(a, b) < 2.5e-2, (name, _rel(a, b))
