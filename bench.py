@@ -124,8 +124,9 @@ def main() -> int:
                     help="main measurement on the NCCL collectives instead of the peer-memory kernels")
     ap.add_argument("--no-extras", action="store_true", help="skip the like_for_like and nccl_path side measurements")
     ap.add_argument("--extra-steps", type=int, default=3, help="timed steps of each side measurement")
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8"],
-                    help="mxfp8: block-scaled FP8 linears (an extra measurement; the headline number is bf16)")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8", "tensorwise"],
+                    help="mxfp8 / tensorwise: FP8 linears and expert GEMMs (an extra measurement; the headline number is bf16)")
+    ap.add_argument("--fp8-modules", nargs="*", default=[], help="restrict --precision to these module patterns (moe, mamba_proj, globs)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--profile-dir", default=None, help="after timing, capture one step with the torch profiler here")
     args = ap.parse_args()
@@ -177,7 +178,7 @@ def main() -> int:
 
     def make_trainer(pctx, rc, kl):
         tcfg = TrainConfig(micro_batch_size=args.micro_batch, seq_length=args.seq, dtype="bf16", recompute=rc,
-                           recompute_keep_last=kl, precision_recipe=args.precision,
+                           recompute_keep_last=kl, precision_recipe=args.precision, precision_modules=tuple(args.fp8_modules),
                            optimizer=OptimizerConfig(lr=1e-5, weight_decay=0.1, grad_dtype=grad_dtype), log_interval=0)
         return Trainer(mcfg, tcfg, pctx, device=device)
 
@@ -303,7 +304,7 @@ def main() -> int:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": value / PUBLISHED_TOK_S_BOX, "dtype": "bf16" if args.precision == "bf16" else "mxfp8 linears, bf16 elsewhere", "data": "synthetic uniform tokens, random-init weights",
+            "vs_baseline": value / PUBLISHED_TOK_S_BOX, "dtype": "bf16" if args.precision == "bf16" else f"{args.precision} fp8 linears ({' '.join(args.fp8_modules) or 'all'}), bf16 elsewhere", "data": "synthetic uniform tokens, random-init weights",
             "impl": "ours",
             "config": {"model": f"{mcfg.name} {n_params / 1e9:.2f}B params on rank 0 ({mcfg.param_count()['total'] / 1e9:.2f}B total), "
                                 f"{mcfg.depth} layers {mcfg.pattern}, hidden {mcfg.hidden_size}, vocab {mcfg.vocab_size}, MTP {mcfg.mtp.num_layers}",

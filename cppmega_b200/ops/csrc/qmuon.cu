@@ -136,3 +136,102 @@ extern "C" int cm_qmuon_emit_mxfp8(const void* q, const float* absmax, const flo
   qmuon_emit_mxfp8_kernel<<<grid, 256, 0, s>>>((const int8_t*)q, absmax, inv_norm, (uint8_t*)payload, (uint8_t*)scales, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ---------------------------------------------------------------------------------------------
+// AdamW with 8-bit state ("adam8bit"): the scalar / embedding optimizer beside Muon in the reference's small-memory
+// lanes (cppmega/recipes/run_profiles.py:181 `muon_scalar_optimizer`).  Per 256-element block, with am_m = max |m| and
+// am_v = max sqrt(v) kept in fp32, the codes are companded so that small entries of a block keep relative precision:
+//   m8 = round(127 sign(m) sqrt(|m| / am_m))        v8 = round(255 sqrt(sqrt(v) / am_v))
+//   m = b1 deq(m8) + (1-b1) g ;  v = b2 deq(v8)^2 + (1-b2) g^2 ;  p -= lr (m^/(sqrt(v^)+eps) + wd p) ;  requantise.
+// One warp per block, 8 elements per lane.  `active` (optional, one byte per element): 0 = leave the element alone
+// (ranges another optimizer owns).  `gate` as in cm_adamw_gated.
+// ---------------------------------------------------------------------------------------------
+namespace cm {
+
+template <typename GradT, typename OutT>
+__global__ void __launch_bounds__(256) adam8bit_kernel(float* __restrict__ master, int8_t* __restrict__ m8, uint8_t* __restrict__ v8,
+                                                       float* __restrict__ am_m, float* __restrict__ am_v, const GradT* __restrict__ g,
+                                                       OutT* __restrict__ out, const uint8_t* __restrict__ wd_mask,
+                                                       const uint8_t* __restrict__ active, const float* __restrict__ clip,
+                                                       long long n, long long nblocks, float lr, float b1, float b2, float eps,
+                                                       float wd, float inv_bc1, float inv_bc2, const int* __restrict__ gate) {
+  if (gate && *reinterpret_cast<const volatile int*>(gate) != 0) return;
+  const float cs = clip ? *clip : 1.f;
+  const int lane = threadIdx.x & 31;
+  const long long wpb = blockDim.x >> 5;
+  for (long long blk = blockIdx.x * wpb + (threadIdx.x >> 5); blk < nblocks; blk += (long long)gridDim.x * wpb) {
+    const long long base = blk * QB + lane * 8;
+    const float sm = am_m[blk] * (1.f / (127.f * 127.f)), sv = am_v[blk] * (1.f / (255.f * 255.f));
+    float m[8], r[8];
+    bool on[8];
+    float mx_m = 0.f, mx_r = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const long long i = base + j;
+      m[j] = r[j] = 0.f;
+      on[j] = false;
+      if (i < n) {
+        const float qm = float(m8[i]), qv = float(v8[i]);
+        const float m_old = qm * fabsf(qm) * sm, r_old = qv * qv * sv;
+        on[j] = !active || active[i];
+        if (on[j]) {
+          const float gi = float(g[i]) * cs;
+          m[j] = b1 * m_old + (1.f - b1) * gi;
+          const float v = b2 * r_old * r_old + (1.f - b2) * gi * gi;
+          r[j] = sqrtf(v);
+          float p = master[i];
+          float upd = (m[j] * inv_bc1) / (sqrtf(v * inv_bc2) + eps);
+          if (wd_mask[i]) upd += wd * p;
+          p -= lr * upd;
+          master[i] = p;
+          out[i] = OutT(p);
+        } else {
+          m[j] = m_old;
+          r[j] = r_old;
+        }
+        mx_m = fmaxf(mx_m, fabsf(m[j]));
+        mx_r = fmaxf(mx_r, r[j]);
+      }
+    }
+    mx_m = warp_max(mx_m);
+    mx_r = warp_max(mx_r);
+    const float im = mx_m > 0.f ? 1.f / mx_m : 0.f, ir = mx_r > 0.f ? 1.f / mx_r : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const long long i = base + j;
+      if (i < n) {
+        const float qa = fminf(floorf(127.f * sqrtf(fabsf(m[j]) * im) + 0.5f), 127.f);
+        m8[i] = (int8_t)(m[j] < 0.f ? -qa : qa);
+        v8[i] = (uint8_t)fminf(floorf(255.f * sqrtf(r[j] * ir) + 0.5f), 255.f);
+      }
+    }
+    if (lane == 0) {
+      am_m[blk] = mx_m;
+      am_v[blk] = mx_r;
+    }
+  }
+}
+
+}  // namespace cm
+
+// master fp32 [n]; m8 int8 [n], v8 uint8 [n]; am_m, am_v fp32 [ceil(n/256)]; g fp32 (grad_kind 0) or bf16 (1); out bf16
+// (out_kind 1) or fp32 (0); wd_mask uint8 [n]; active uint8 [n] or null; clip device scalar or null; gate device word or null
+extern "C" int cm_adam8bit(float* master, int8_t* m8, uint8_t* v8, float* am_m, float* am_v, const void* g, void* out,
+                           const uint8_t* wd_mask, const uint8_t* active, const float* clip, long long n, float lr, float b1,
+                           float b2, float eps, float wd, float bc1, float bc2, int grad_kind, int out_kind, const int* gate,
+                           cudaStream_t s) {
+  if (n <= 0) return 0;
+  const long long nblocks = (n + cm::QB - 1) / cm::QB;
+  long long blocks = (nblocks + 7) / 8;
+  const int grid = (int)(blocks < (long long)cm::sm_count() * 8 ? blocks : (long long)cm::sm_count() * 8);
+  const float i1 = 1.f / bc1, i2 = 1.f / bc2;
+#define CM_A8(GT, OT)                                                                                                      \
+  cm::adam8bit_kernel<GT, OT><<<grid, 256, 0, s>>>(master, m8, v8, am_m, am_v, (const GT*)g, (OT*)out, wd_mask, active, clip, n, \
+                                                   nblocks, lr, b1, b2, eps, wd, i1, i2, gate)
+  if (grad_kind == 0 && out_kind == 1) CM_A8(float, __nv_bfloat16);
+  else if (grad_kind == 1 && out_kind == 1) CM_A8(__nv_bfloat16, __nv_bfloat16);
+  else if (grad_kind == 0 && out_kind == 0) CM_A8(float, float);
+  else CM_A8(__nv_bfloat16, float);
+#undef CM_A8
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -209,17 +209,18 @@ def quantize_weight(w: torch.Tensor, colwise: bool, tensorwise: bool = False) ->
     return q
 
 
-def quantize_expert_weights(w: torch.Tensor, transposed: bool) -> Mxfp8Tensor:
-    """MXFP8 copy of a stacked expert weight [E, N, K], cached until the optimizer writes it.  ``transposed`` False:
+def quantize_expert_weights(w: torch.Tensor, transposed: bool, tensorwise: bool = False) -> Mxfp8Tensor:
+    """FP8 copy of a stacked expert weight [E, N, K], cached until the optimizer writes it.  ``transposed`` False:
     [E * N, K] quantised along K (forward operand).  True: the stack read as [E * N, K] and quantised along its rows,
     stored transposed [K, E * N] - the dgrad operand, whose reduction axis is N and whose expert e occupies the
-    columns [e N, (e + 1) N)."""
-    key = "_mx_ecol" if transposed else "_mx_erow"
+    columns [e N, (e + 1) N).  ``tensorwise``: one scale for the whole stack."""
+    key = ("_tw_ecol" if transposed else "_tw_erow") if tensorwise else ("_mx_ecol" if transposed else "_mx_erow")
     hit = getattr(w, key, None)
     if hit is not None and hit[0] == w._version:
         return hit[1]
     w2 = w.detach().reshape(-1, w.shape[-1])
-    q = quantize_colwise(w2, True) if transposed else quantize_rowwise(w2, True)
+    tw = True if tensorwise else None
+    q = quantize_colwise(w2, True, tw) if transposed else quantize_rowwise(w2, True, tw)
     try:
         setattr(w, key, (w._version, q))
     except AttributeError:

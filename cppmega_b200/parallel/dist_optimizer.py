@@ -32,7 +32,7 @@ import torch.nn as nn
 
 @dataclass
 class OptimizerConfig:
-    optimizer: str = "adamw"           # adamw | muon
+    optimizer: str = "adamw"           # adamw | adam8bit | muon
     lr: float = 1e-4
     min_lr: float = 0.0
     weight_decay: float = 0.1
@@ -45,7 +45,7 @@ class OptimizerConfig:
     muon_momentum: float = 0.95
     muon_ns_steps: int = 5
     muon_quantized_momentum: bool = False
-    muon_scalar_optimizer: str = "adamw"
+    muon_scalar_optimizer: str = "adamw"   # adamw | adam8bit: optimizer of the parameters Muon does not take
     loss_scale: float = 1.0
 
 
@@ -226,6 +226,11 @@ class DistributedOptimizer:
         self.zero_grad()
         self.fused_step: Optional[Callable] = None       # set by parallel.fused_optimizer.attach()
 
+    def _scalar_8bit(self) -> bool:
+        """8-bit AdamW state: for every parameter (``optimizer == "adam8bit"``) or for what Muon leaves over."""
+        c = self.cfg
+        return c.optimizer == "adam8bit" or (c.optimizer == "muon" and c.muon_scalar_optimizer == "adam8bit")
+
     def _buffer_allocator(self, is_expert: bool, params, grad_dtype) -> Optional[Callable]:
         """Hook for subclasses that place the flat buffers in special memory."""
         return None
@@ -262,9 +267,17 @@ class DistributedOptimizer:
                                 cs, ce = max(ms, lo), min(me, hi)
                                 muon_cross.append({"local": (cs - lo, ce - lo), "bucket": (ms - b.start, me - b.start),
                                                    "inner": (cs - ms, ce - ms), "shape": shape})
+                use8 = self._scalar_8bit()
+                need_m = not use8 or ((muon_segments or muon_cross) and
+                                      (muon_cross or not self.cfg.muon_quantized_momentum))
+                a8 = None
+                if use8:
+                    from ..optim.adam8bit import Adam8bitState
+                    a8 = Adam8bitState.zeros(hi - lo, master.device)
                 self.state.append({
                     "buf": buf, "bucket": b, "lo": lo, "hi": hi, "master": master,
-                    "m": torch.zeros_like(master), "v": torch.zeros_like(master),
+                    "m": torch.zeros_like(master) if need_m else None, "v": None if use8 else torch.zeros_like(master),
+                    "a8": a8,
                     "wd_mask": wd_mask, "muon": muon_segments, "muon_cross": muon_cross,
                     "muon_gather": self.cfg.optimizer == "muon" and _bucket_has_cut_matrix(buf, b),
                 })
@@ -396,6 +409,16 @@ class DistributedOptimizer:
                 if st["muon_gather"]:          # same decision on every rank of the group: the gather is a collective
                     muon_ops.muon_update_cut_matrices(st, g, clip, lr, cfg)
                     skip = list(st["muon"]) + [(c["local"][0], c["local"][1], c["shape"]) for c in st["muon_cross"]]
+            if st["a8"] is not None:
+                from ..optim.adam8bit import adam8bit_update
+                active = None
+                if skip:
+                    active = torch.ones(st["hi"] - st["lo"], dtype=torch.uint8, device=g.device)
+                    for s0, e0, _ in skip:
+                        active[s0:e0] = 0
+                adam8bit_update(st["master"], st["a8"], g, out, st["wd_mask"], clip, lr, cfg.beta1, cfg.beta2, cfg.eps,
+                                cfg.weight_decay, bc1, bc2, active=active)
+                continue
             adamw_ops.adamw_shard_update(st["master"], st["m"], st["v"], g, out, st["wd_mask"], clip,
                                          lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2,
                                          skip_segments=skip)
@@ -410,15 +433,29 @@ class DistributedOptimizer:
         the moments; used when a checkpoint was written under a different parallel layout."""
         for s in self.state:
             s["master"].copy_(s["buf"].param_buffer[s["lo"]:s["hi"]].float())
-            s["m"].zero_()
-            s["v"].zero_()
+            for k in ("m", "v"):
+                if s[k] is not None:
+                    s[k].zero_()
+            if s["a8"] is not None:
+                for t in (s["a8"].m8, s["a8"].v8, s["a8"].am_m, s["a8"].am_v):
+                    t.zero_()
 
     def state_dict(self) -> dict:
         return {
             "step": self.step_count, "lr": self.lr,
-            "shards": [{"lo": s["lo"], "hi": s["hi"], "master": s["master"].cpu(), "m": s["m"].cpu(),
-                        "v": s["v"].cpu()} for s in self.state],
+            "shards": [self._shard_state(s) for s in self.state],
         }
+
+    @staticmethod
+    def _shard_state(s) -> dict:
+        d = {"lo": s["lo"], "hi": s["hi"], "master": s["master"].cpu()}
+        for k in ("m", "v"):
+            if s[k] is not None:
+                d[k] = s[k].cpu()
+        if s["a8"] is not None:
+            a = s["a8"]
+            d["a8"] = {"m8": a.m8.cpu(), "v8": a.v8.cpu(), "am_m": a.am_m.cpu(), "am_v": a.am_v.cpu()}
+        return d
 
     def load_state_dict(self, sd: dict) -> None:
         self.step_count, self.lr = sd["step"], sd.get("lr", self.lr)
@@ -428,7 +465,11 @@ class DistributedOptimizer:
             if (s["lo"], s["hi"]) != (t["lo"], t["hi"]):
                 raise ValueError("optimizer shard ranges differ from the checkpoint")
             for k in ("master", "m", "v"):
-                s[k].copy_(t[k].to(s[k].device))
+                if s[k] is not None and k in t:
+                    s[k].copy_(t[k].to(s[k].device))
+            if s["a8"] is not None and "a8" in t:
+                for k, v in t["a8"].items():
+                    getattr(s["a8"], k).copy_(v.to(s["master"].device))
             s["buf"].param_buffer[s["lo"]:s["hi"]].copy_(s["master"].to(s["buf"].dtype))
         for buf in self.buffers:
             buf.gather_params()

@@ -325,38 +325,47 @@ def _grouped_wgrad(dy, x, seg_offsets, E, w=None):
     return run(None, False) if w is None else wgrad_into_main_grad(w, run)
 
 
-def _mx_experts_ok(w1, w2) -> bool:
-    """Block-scaled expert GEMMs want every expert's rows / columns to start on a 128 boundary of the stacked weights."""
-    return (F_.precision_recipe() == "mxfp8" and w1.dtype == torch.bfloat16 and w1.shape[1] % 128 == 0 and w1.shape[2] % 128 == 0
-            and w2.shape[1] % 128 == 0 and w2.shape[2] % 128 == 0)
+def _fp8_mode(w1, w2) -> Optional[str]:
+    """``None`` (bf16 experts), ``"mxfp8"`` or ``"tensorwise"``: the recipe in force where the layer's forward runs.  The
+    block-scaled expert GEMMs want every expert's rows / columns to start on a 128 boundary of the stacked weights."""
+    rec = F_.precision_recipe()
+    if rec == "bf16":
+        return None
+    ok = (w1.dtype == torch.bfloat16 and w1.shape[1] % 128 == 0 and w1.shape[2] % 128 == 0
+          and w2.shape[1] % 128 == 0 and w2.shape[2] % 128 == 0)
+    return rec if ok else None
 
 
-def _experts_fwd_mx(xin, w1, w2, tile_expert, yout):
+def _experts_fwd_mx(xin, w1, w2, tile_expert, yout, tensorwise: bool):
     """h = xin W1^T, yout = swiglu(h) W2^T on the block-scaled grouped GEMM; returns h."""
     from ..ops.cuda import mxfp8 as mx, swiglu
     E = w1.shape[0]
-    h = mx.grouped_rows_mxfp8(mx.quantize_rowwise(xin, True), mx.quantize_expert_weights(w1, False), tile_expert, E, w1.shape[1], False)
+    tw = True if tensorwise else None
+    h = mx.grouped_rows_mxfp8(mx.quantize_rowwise(xin, True, tw), mx.quantize_expert_weights(w1, False, tensorwise), tile_expert, E,
+                              w1.shape[1], False)
     a = swiglu(h)
-    mx.grouped_rows_mxfp8(mx.quantize_rowwise(a, True), mx.quantize_expert_weights(w2, False), tile_expert, E, w2.shape[1], False, out=yout)
+    mx.grouped_rows_mxfp8(mx.quantize_rowwise(a, True, tw), mx.quantize_expert_weights(w2, False, tensorwise), tile_expert, E,
+                          w2.shape[1], False, out=yout)
     return h
 
 
-def _experts_bwd_mx(grad_in, h, xin, w1, w2, plan, grad_out):
-    """Expert backward in MXFP8: every operand is quantised along the axis its product reduces over; a tensor that
+def _experts_bwd_mx(grad_in, h, xin, w1, w2, plan, grad_out, tensorwise: bool):
+    """Expert backward in FP8: every operand is quantised along the axis its product reduces over; a tensor that
     feeds both a dgrad (along features) and a wgrad (along tokens) is read once for both copies."""
     from ..ops.cuda import lib, mxfp8 as mx, stream_ptr, swiglu, wgrad_into_main_grad, _check
     E, cap = w1.shape[0], grad_in.shape[0]
+    tw = (lambda t: mx.tensor_amax(t)) if tensorwise else (lambda t: None)
     a = swiglu(h)
-    g_row, g_col = mx.quantize_both(grad_in)                                            # [cap, H] and [H, cap]
-    da = mx.grouped_rows_mxfp8(g_row, mx.quantize_expert_weights(w2, True), plan.tile_expert, E, w2.shape[2], True)     # [cap, F]
-    a_col = mx.quantize_colwise(a, True)                                                # [F, cap]
+    g_row, g_col = mx.quantize_both(grad_in, True, tw(grad_in))                         # [cap, H] and [H, cap]
+    da = mx.grouped_rows_mxfp8(g_row, mx.quantize_expert_weights(w2, True, tensorwise), plan.tile_expert, E, w2.shape[2], True)     # [cap, F]
+    a_col = mx.quantize_colwise(a, True, tw(a))                                         # [F, cap]
     dw2 = wgrad_into_main_grad(w2, lambda out, acc: mx.grouped_wgrad_mxfp8(g_col, a_col, plan.seg_offsets, E, out, acc))
     dh = torch.empty_like(h)
     _check(lib().cm_swiglu_bwd(h.data_ptr(), da.data_ptr(), dh.data_ptr(), cap, w2.shape[2], stream_ptr()), "cm_swiglu_bwd")
     F_.count_launch("swiglu_bwd")
-    dh_row, dh_col = mx.quantize_both(dh)                                               # [cap, 2F] and [2F, cap]
-    mx.grouped_rows_mxfp8(dh_row, mx.quantize_expert_weights(w1, True), plan.tile_expert, E, w1.shape[2], True, out=grad_out)
-    x_col = mx.quantize_colwise(xin, True)                                              # [H, cap]
+    dh_row, dh_col = mx.quantize_both(dh, True, tw(dh))                                 # [cap, 2F] and [2F, cap]
+    mx.grouped_rows_mxfp8(dh_row, mx.quantize_expert_weights(w1, True, tensorwise), plan.tile_expert, E, w1.shape[2], True, out=grad_out)
+    x_col = mx.quantize_colwise(xin, True, tw(xin))                                     # [H, cap]
     dw1 = wgrad_into_main_grad(w1, lambda out, acc: mx.grouped_wgrad_mxfp8(dh_col, x_col, plan.seg_offsets, E, out, acc))
     return dw1, dw2
 
@@ -378,8 +387,9 @@ class _FusedMoEFn(torch.autograd.Function):
         heap.barrier(f0 + 0, ep0)
         _zero_pad(xin, plan, cap)
         with torch.no_grad():
-            if _mx_experts_ok(w1, w2):
-                h = _experts_fwd_mx(xin, w1, w2, plan.tile_expert, yout)
+            fp8 = _fp8_mode(w1, w2)
+            if fp8 is not None:
+                h = _experts_fwd_mx(xin, w1, w2, plan.tile_expert, yout, fp8 == "tensorwise")
             else:
                 h = _grouped(xin, w1, plan.tile_expert, cap, False)
                 a = swiglu(h)
@@ -391,6 +401,7 @@ class _FusedMoEFn(torch.autograd.Function):
         ctx.save_for_backward(h, w1, w2, p32, xin, yout)
         ctx.plan, ctx.bufs, ctx.slot, ctx.cap = plan, bufs, layer_slot, cap
         ctx.x_dtype, ctx.p_dtype = x.dtype, probs.dtype
+        ctx.fp8 = fp8                              # the backward runs under the recipe of its forward, whatever is set then
         return y
 
     @staticmethod
@@ -412,9 +423,9 @@ class _FusedMoEFn(torch.autograd.Function):
         Fh = w2.shape[2]
         # recompute a = swiglu(h); expert backward on the padded layout
         from ..ops.cuda import swiglu as _sw
-        if _mx_experts_ok(w1, w2):
+        if ctx.fp8 is not None:
             with torch.no_grad():
-                dw1, dw2 = _experts_bwd_mx(grad_in, h, xin, w1, w2, plan, grad_out)
+                dw1, dw2 = _experts_bwd_mx(grad_in, h, xin, w1, w2, plan, grad_out, ctx.fp8 == "tensorwise")
             heap.barrier(f0 + 3, epb)
             dx = _pull_combine(heap, grad_out, plan, None, H, ctx.x_dtype)
             return dx, dprobs.to(ctx.p_dtype), dw1, dw2, None, None, None

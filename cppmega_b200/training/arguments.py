@@ -124,12 +124,18 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--train-iters", type=int, default=100)
     g.add_argument("--bf16", action="store_true")
     g.add_argument("--fp32", action="store_true")
-    g.add_argument("--fp8-recipe", default=None, choices=["mxfp8", "tensorwise"])
+    g.add_argument("--fp8-recipe", default=None, choices=["mxfp8", "tensorwise"],
+                   help="mxfp8: E4M3 with E8M0 scales per 32 values; tensorwise: E4M3 with one current-scaling scale per tensor")
+    g.add_argument("--fp8-modules", nargs="*", default=[],
+                   help="restrict the FP8 recipe to modules whose qualified name matches one of these glob patterns "
+                        "(shorthands: moe, mamba_proj); everything else stays bf16")
     g.add_argument("--recompute-granularity", default=None, choices=["selective", "full"])
     g.add_argument("--cuda-graph-scope", nargs="*", default=[],
                    help="layer kinds captured as CUDA graphs: mamba attn mlp (moe_router / moe_preprocess are accepted and ignored)")
     g.add_argument("--seed", type=int, default=1234)
-    g.add_argument("--optimizer", default="adamw", choices=["adam", "adamw", "muon"])
+    g.add_argument("--optimizer", default="adamw", choices=["adam", "adamw", "adam8bit", "muon"])
+    g.add_argument("--muon-scalar-optimizer", default="adamw", choices=["adamw", "adam8bit"],
+                   help="optimizer of the parameters Muon does not take (scalars, norms, embeddings, output layer)")
     g.add_argument("--lr", type=float, default=1e-5)
     g.add_argument("--min-lr", type=float, default=0.0)
     g.add_argument("--lr-decay-style", default="constant", choices=["constant", "cosine", "linear", "wsd"])
@@ -277,14 +283,16 @@ def configs_from_namespace(ns: argparse.Namespace) -> Tuple[ModelConfig, Paralle
     ocfg = OptimizerConfig(optimizer="adamw" if ns.optimizer in ("adam", "adamw") else ns.optimizer, lr=ns.lr,
                            min_lr=ns.min_lr, weight_decay=ns.weight_decay, beta1=ns.adam_beta1, beta2=ns.adam_beta2,
                            eps=ns.adam_eps, clip_grad=ns.clip_grad, grad_dtype="bf16" if ns.grad_reduce_in_bf16 else "fp32",
-                           muon_momentum=ns.muon_momentum, muon_quantized_momentum=ns.muon_quantized_momentum)
+                           muon_momentum=ns.muon_momentum, muon_quantized_momentum=ns.muon_quantized_momentum,
+                           muon_scalar_optimizer=ns.muon_scalar_optimizer)
     sched = LRSchedule(lr=ns.lr, min_lr=ns.min_lr, warmup_steps=ns.lr_warmup_iters, decay_steps=ns.lr_decay_iters,
                        style=ns.lr_decay_style)
     tcfg = TrainConfig(micro_batch_size=ns.micro_batch_size, global_batch_size=ns.global_batch_size,
                        seq_length=mcfg.seq_length, dtype="fp32" if ns.fp32 else "bf16",
                        recompute=ns.recompute_granularity or "none", seed=ns.seed, log_interval=ns.log_interval,
                        check_finite=not ns.no_check_for_nan_in_loss_and_grad,
-                       precision_recipe=ns.fp8_recipe or "bf16", optimizer=ocfg, lr_schedule=sched,
+                       precision_recipe=ns.fp8_recipe or "bf16", precision_modules=tuple(ns.fp8_modules),
+                       optimizer=ocfg, lr_schedule=sched,
                        pipeline_schedule=ns.pipeline_schedule, cuda_graph_scope=tuple(ns.cuda_graph_scope))
     extras = {k: getattr(ns, k) for k in ("train_iters", "data_path", "mock_data", "save", "load", "save_interval",
                                           "log_throughput", "monitor_port", "profile", "profile_step_start",
@@ -405,6 +413,8 @@ def render_args(mcfg: ModelConfig, pcfg: ParallelConfig, tcfg: TrainConfig, *, t
     a.append("--fp32" if tcfg.dtype == "fp32" else "--bf16")
     if tcfg.precision_recipe != "bf16":
         kv("--fp8-recipe", tcfg.precision_recipe)
+        if tcfg.precision_modules:
+            a.extend(["--fp8-modules", *tcfg.precision_modules])
     if tcfg.recompute != "none":
         kv("--recompute-granularity", tcfg.recompute)
     if tcfg.cuda_graph_scope:
@@ -426,6 +436,8 @@ def render_args(mcfg: ModelConfig, pcfg: ParallelConfig, tcfg: TrainConfig, *, t
     kv("--clip-grad", o.clip_grad)
     if o.grad_dtype == "bf16":
         a.append("--grad-reduce-in-bf16")
+    if o.optimizer == "muon" and o.muon_scalar_optimizer != "adamw":
+        kv("--muon-scalar-optimizer", o.muon_scalar_optimizer)
     if o.optimizer == "muon":
         kv("--muon-momentum", o.muon_momentum)
         if o.muon_quantized_momentum:

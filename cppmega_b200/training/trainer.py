@@ -38,7 +38,9 @@ class TrainConfig:
     seed: int = 1234
     log_interval: int = 1
     check_finite: bool = True
-    precision_recipe: str = "bf16"               # bf16 | mxfp8 (block-scaled linears)
+    precision_recipe: str = "bf16"               # bf16 | mxfp8 (E8M0 1x32 block scales) | tensorwise (one scale per tensor)
+    precision_modules: tuple = ()                # glob patterns of module names that run under precision_recipe; the rest
+                                                 # stays bf16.  Empty: every eligible linear.  Shorthands: "moe", "mamba_proj"
     cuda_graph_scope: tuple = ()                 # subset of ("mamba", "attn", "mlp"): layers captured as CUDA graphs
     optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
     lr_schedule: Optional[LRSchedule] = None
@@ -51,6 +53,34 @@ class TrainConfig:
 
 class NonFiniteLossError(RuntimeError):
     pass
+
+
+PRECISION_MODULE_SETS = {
+    # FP8 on the MoE layers only (cppmega/megatron/selective_fp8_moe_patch.py:60-149)
+    "moe": ("*.mlp.experts", "*.mlp.shared_experts", "*.mlp.shared_experts.*", "*.mlp"),
+    # FP8 on the Mamba in / out projections only (configs/te_precision/mamba_mxfp8_eval_bf16.yaml:1-29)
+    "mamba_proj": ("*.mixer.in_proj", "*.mixer.out_proj"),
+}
+
+
+def _install_precision(model, cfg: "TrainConfig"):
+    """Global recipe, or - with ``precision_modules`` - the recipe on the named modules and bf16 elsewhere."""
+    from ..ops import functional as F_
+    if cfg.precision_recipe not in F_.RECIPES:
+        raise ValueError(f"unknown precision recipe {cfg.precision_recipe!r}; known: {F_.RECIPES}")
+    if not cfg.precision_modules or cfg.precision_recipe == "bf16":
+        F_.set_precision_recipe(cfg.precision_recipe)
+        return []
+    pats = []
+    for p in cfg.precision_modules:
+        pats.extend(PRECISION_MODULE_SETS.get(p, (p,)))
+    if "moe" in cfg.precision_modules:                      # "*.mlp" must only hit MoE layers, not dense MLPs
+        moe_names = {n for n, m in model.named_modules() if type(m).__name__ == "MoELayer"}
+        pats = [p for p in pats if p != "*.mlp"] + sorted(moe_names)
+    _handles, matched = F_.install_precision_rules(model, [(p, cfg.precision_recipe) for p in pats], default="bf16")
+    if not matched:
+        raise ValueError(f"precision_modules {cfg.precision_modules} match no module of the model")
+    return matched
 
 
 class Trainer:
@@ -76,7 +106,7 @@ class Trainer:
         # with pipeline stages the embedding copies are summed before the data-parallel reduction,
         # so the reduction cannot start from inside backward
         from ..ops import functional as F_
-        F_.set_precision_recipe("mxfp8" if train_cfg.precision_recipe == "mxfp8" else "bf16")
+        self.precision_modules = _install_precision(self.model, train_cfg)
         self.fused = {"optimizer": False, "moe": False}
         opt_cls = DistributedOptimizer
         if device.type == "cuda" and self.pc.world_size > 1 and train_cfg.optimizer.optimizer == "adamw":

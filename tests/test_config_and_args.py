@@ -119,3 +119,69 @@ def test_rank_groups():
     with pytest.raises(ValueError):
         ParallelConfig(cp=2)
     assert nam56r_tiny().plan().needs_mamba3
+
+
+def test_precision_rules_scope_the_recipe_to_matching_modules():
+    import torch
+    import torch.nn as nn
+    from cppmega_b200.ops import functional as F_
+
+    seen = {}
+
+    class Probe(nn.Module):
+        def __init__(self, tag):
+            super().__init__()
+            self.tag = tag
+
+        def forward(self, x):
+            seen[self.tag] = F_.precision_recipe()
+            return x
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mixer = nn.Module()
+            self.mixer.in_proj = Probe("in_proj")
+            self.mixer.inner = Probe("inner")
+            self.mlp = Probe("mlp")
+
+        def forward(self, x):
+            return self.mlp(self.mixer.inner(self.mixer.in_proj(x)))
+
+    net = nn.Sequential(Layer())
+    try:
+        handles, matched = F_.install_precision_rules(net, [("*.mixer.in_proj", "mxfp8"), ("*.mlp", "tensorwise")], default="bf16")
+        assert matched == ["0.mixer.in_proj", "0.mlp"]
+        net(torch.zeros(1))
+        assert seen == {"in_proj": "mxfp8", "inner": "bf16", "mlp": "tensorwise"}
+        assert F_.precision_recipe() == "bf16"                      # restored after the forward
+        with F_.precision_scope("mxfp8"):
+            assert F_.precision_recipe() == "mxfp8"
+        assert F_.precision_recipe() == "bf16"
+        for h in handles:
+            h.remove()
+        with pytest.raises(ValueError):
+            F_.set_precision_recipe("fp4")
+    finally:
+        F_.set_precision_recipe("bf16")
+
+
+def test_fp8_arguments_round_trip_and_module_sets():
+    from cppmega_b200.training.arguments import parse_args, render_args
+    mcfg, pcfg, tcfg, _ = parse_args(["--model-preset", "nam56r_tiny", "--mock-data", "--fp8-recipe", "tensorwise", "--fp8-modules", "moe"])
+    assert tcfg.precision_recipe == "tensorwise" and tcfg.precision_modules == ("moe",)
+    argv = render_args(mcfg, pcfg, tcfg, mock_data=True)
+    assert parse_args(argv)[2].precision_modules == ("moe",)
+    from cppmega_b200.models import build_model
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.parallel.state import single_process_context
+    from cppmega_b200.training.trainer import _install_precision
+    model = build_model(mcfg, single_process_context())
+    try:
+        matched = _install_precision(model, tcfg)
+        assert matched and all(".mlp" in m for m in matched)
+        kinds = {n for n, m in model.named_modules() if type(m).__name__ == "MoELayer"}
+        assert kinds <= set(matched)
+        assert F_.precision_recipe() == "bf16"                      # default outside the selected modules
+    finally:
+        F_.set_precision_recipe("bf16")

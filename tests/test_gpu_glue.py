@@ -422,3 +422,44 @@ def test_moe_transport_skips_and_reports_rows_beyond_capacity():
     expect = (x.float() * keep.sum(1, keepdim=True)).bfloat16()     # every kept copy returns the token itself
     assert _rel(y, expect) < 1e-2
     assert (d.view(T, k)[~keep] == 0).all()
+
+
+def _tensorwise_q(t):
+    """fp32 restatement of the tensorwise FP8 recipe: one power-of-two scale from the tensor's amax, E4M3 rounding."""
+    from cppmega_b200.ops import reference as ref
+    sb = ref.e8m0_from_amax(t.float().abs().max().reshape(1)).float()
+    mult = torch.exp2(127.0 - sb)
+    return (t.float() * mult).to(torch.float8_e4m3fn).float() / mult
+
+
+def test_tensorwise_fp8_quantisers_and_linear():
+    """The tensorwise recipe: every scale byte of a tensor is the same, the payload is the E4M3 rounding under that one
+    scale, both orientations agree, and the linear's three products match the fp32 products of the rounded operands."""
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.ops.cuda import mxfp8
+    torch.manual_seed(4)
+    x = (torch.randn(96, 256, device="cuda") * 2.5).bfloat16()
+    am = mxfp8.tensor_amax(x)
+    assert float(am) == float(x.float().abs().max())
+    r = mxfp8.quantize_rowwise(x, tensorwise=True)
+    assert r.scales.unique().numel() == 1
+    assert torch.equal(mxfp8.dequantize(r).float(), _tensorwise_q(x).bfloat16().float())
+    br, bc = mxfp8.quantize_both(x, True, am)
+    assert torch.equal(br.payload, r.payload) and bc.scales.unique().numel() == 1
+    assert torch.equal(bc.payload, r.payload.t().contiguous())            # same scale: the transposed copy is a pure transpose
+    c = mxfp8.quantize_colwise(x, tensorwise=am)
+    assert torch.equal(c.payload, bc.payload) and torch.equal(c.scales, bc.scales)
+
+    xx = (torch.randn(4, 64, 256, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(128, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    with F_.precision_scope("tensorwise"):
+        y = F_.linear(xx, w)
+    g = torch.randn_like(y)
+    y.backward(g)                                                         # outside the scope: the op remembers its recipe
+    assert F_.precision_recipe() == "bf16"
+    x2, g2 = xx.detach().reshape(-1, 256), g.reshape(-1, 128)
+    q = _tensorwise_q
+    assert _rel(y.reshape(-1, 128), q(x2) @ q(w.detach()).t()) < 1e-2
+    assert _rel(xx.grad.reshape(-1, 256), q(g2) @ q(w.detach())) < 1e-2
+    assert _rel(w.grad, q(g2).t() @ q(x2)) < 1e-2
+    assert _rel(y.reshape(-1, 128), x2.float() @ w.detach().float().t()) < 6e-2
