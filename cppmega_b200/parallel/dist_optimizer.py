@@ -296,12 +296,18 @@ class DistributedOptimizer:
                         return
                     b = buf.bucket_of[param]
                     b.pending -= 1
-                    if b.pending == 0 and self.overlap and not b.reduced:
-                        buf.reduce_bucket(b, async_op=True, scale=self._grad_scale / buf.grad_div)
+                    if b.pending == 0 and not b.reduced:
+                        self._on_bucket_ready(buf, b)
                 self._hooks.append(p.register_post_accumulate_grad_hook(hook))
                 # GEMM epilogues may add weight gradients directly into the flat buffer (CUDA, 2-D/3-D bf16 weights)
                 p.fuse_wgrad_accumulation = bool(p.is_cuda and p.dim() >= 2 and p.dtype == torch.bfloat16)
         self._last_microbatch = True
+
+    def _on_bucket_ready(self, buf: ParamGroupBuffer, b: Bucket) -> None:
+        """Called from inside backward (last micro-batch) when every gradient of bucket ``b`` has been produced: with
+        ``overlap_grad_reduce`` the bucket's reduction starts now, under the rest of the backward pass."""
+        if self.overlap:
+            buf.reduce_bucket(b, async_op=True, scale=self._grad_scale / buf.grad_div)
 
     def set_microbatch(self, is_last: bool, grad_scale: float = 1.0):
         """Call before each backward: gradient reduction only fires on the last micro-batch."""

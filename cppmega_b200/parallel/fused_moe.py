@@ -453,7 +453,8 @@ class FusedMoEDispatcher:
         return _FusedMoEFn.apply(flat, probs, experts.weight1, experts.weight2, ids, self.bufs, self.slot)
 
 
-def attach(model, pc, device, tokens_per_rank: int, per_layer: bool = True, capacity_factor: Optional[float] = None) -> Optional[FusedMoEBuffers]:
+def attach(model, pc, device, tokens_per_rank: int, per_layer: bool = True, capacity_factor: Optional[float] = None,
+           overlap_shared_expert: bool = True) -> Optional[FusedMoEBuffers]:
     """Install the fused dispatcher on every MoE layer of ``model`` (EP > 1, bf16, peer access)."""
     layers = model.moe_layers()
     if not layers:
@@ -471,4 +472,6 @@ def attach(model, pc, device, tokens_per_rank: int, per_layer: bool = True, capa
                            num_local_experts=model.cfg.moe.num_experts // pc.ep)
     for slot, m in enumerate(layers):
         m.fused_dispatcher = FusedMoEDispatcher(bufs, slot)
+        # the routed path is mostly NVLink transfers and flag waits: the shared expert's GEMMs run beside it on a second stream
+        m.overlap_shared_expert = overlap_shared_expert
     return bufs

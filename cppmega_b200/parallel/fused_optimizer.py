@@ -7,10 +7,13 @@ Per step and per shard, two kernels replace reduce-scatter + cast/scale + update
 2. ``adamw_push``: AdamW on the fp32 master slice, then stores the new bf16 values into every rank's
    parameter buffer with peer stores.
 
-Cross-GPU ordering uses two flag words per heap: ``GRAD`` (my backward is complete - peers may
-pull) and ``PARAM`` (my pushes are complete - peers may run the next forward and may overwrite
-their gradient buffers).  All waits are bounded device-side waits.  The gradient norm needs one
-scalar all-reduce between the two kernels (NCCL, 4 bytes).
+The reduction overlaps the backward pass bucket by bucket: when the last gradient of a bucket has been produced
+(inside backward) this rank raises that bucket's ``GRAD`` flag on every peer and queues, on a second stream, a bounded
+wait for the same flag of all peers followed by ``reduce_shard`` of its slice of the bucket - the counterpart of
+``--overlap-grad-reduce`` (cppmega/recipes/nam56r_nemo_recipe.py:236-240), with peer loads instead of NCCL.  ``step()``
+joins the second stream, all-reduces the squared norm (NCCL, 4 bytes) and runs ``adamw_push``.  The ``PARAM`` flag (my
+pushes are complete - peers may run the next forward and may overwrite their gradient buffers) closes the step.  All
+waits are bounded device-side waits.
 
 Buffers whose reduction group has one rank (e.g. experts when EP spans the whole data-parallel
 group) use the local fused AdamW kernel.
@@ -26,14 +29,18 @@ import torch.distributed as dist
 from .dist_optimizer import DistributedOptimizer, OptimizerConfig, ParamGroupBuffer
 from .symm_mem import SymmetricHeap
 
-FLAG_GRAD = 0
+FLAG_GRAD = 0                 # kept for layout compatibility: whole-buffer "gradients ready" (unused with per-bucket flags)
 FLAG_PARAM = 1
+FLAG_BUCKET_BASE = 8          # flag index of bucket 0 of a heap's buffers (each heap has its own flag words)
 
 
 class FusedDistributedOptimizer(DistributedOptimizer):
     def __init__(self, model, cfg: OptimizerConfig, pc, **kw):
         self._heaps: Dict[bool, Optional[SymmetricHeap]] = {}
         self._pc_for_alloc = pc
+        self._side = None                        # second stream for the per-bucket pulls
+        self._sq = None                          # [dense, expert] squared-norm accumulators of the running step
+        self._bucket_flag, self._bucket_state = {}, {}
         kw["overlap"] = False                      # gradients stay local until the fused pull
         kw["distributed"] = True
         super().__init__(model, cfg, pc, **kw)
@@ -49,6 +56,16 @@ class FusedDistributedOptimizer(DistributedOptimizer):
             if buf.n > 1:
                 st["red"] = torch.empty(st["hi"] - st["lo"], dtype=torch.float32, device=st["master"].device)
         self._param_wait_pending = False
+        # flag index and state entry of every (buffer, bucket) that lives in a heap
+        per_heap = {}
+        for st in self.state:
+            buf, b = st["buf"], st["bucket"]
+            if getattr(buf, "heap", None) is None:
+                continue
+            k = per_heap.get(id(buf.heap), 0)
+            per_heap[id(buf.heap)] = k + 1
+            self._bucket_flag[(id(buf), b.index)] = FLAG_BUCKET_BASE + k
+            self._bucket_state[(id(buf), b.index)] = st
         if cfg.optimizer == "muon" or any(st.get("muon") or st.get("muon_cross") for st in self.state):
             raise NotImplementedError("the fused optimizer path implements AdamW; use the NCCL path for Muon")
 
@@ -88,15 +105,12 @@ class FusedDistributedOptimizer(DistributedOptimizer):
                     if not b.reduced:
                         buf.reduce_bucket(b, async_op=False, scale=self._grad_scale / buf.grad_div)
                 buf.finish()
-
-    def zero_grad(self):
-        # peers may still be pulling last step's gradients or pushing parameters: wait for their
-        # PARAM flag before touching either buffer
-        if getattr(self, "_param_wait_pending", False):
-            for h in self._heaps_in_use():
-                h.wait(FLAG_PARAM, self.step_count)
-            self._param_wait_pending = False
-        super().zero_grad()
+            else:
+                for b in buf.buckets:        # buckets whose hook never fired (parameters without a gradient this step)
+                    if not b.reduced:
+                        self._on_bucket_ready(buf, b)
+        if self._side is not None:
+            torch.cuda.current_stream().wait_stream(self._side)
 
     @torch.no_grad()
     def step(self, lr: Optional[float] = None):
@@ -107,30 +121,17 @@ class FusedDistributedOptimizer(DistributedOptimizer):
         self.finish_grad_sync()
         step = self.step_count + 1
         heaps = self._heaps_in_use()
-        for h in heaps:
-            h.signal(FLAG_GRAD, step)
-        for h in heaps:
-            h.wait(FLAG_GRAD, step)
         dev = self.state[0]["master"].device
-        dense_sq = torch.zeros((), dtype=torch.float32, device=dev)
-        expert_sq = torch.zeros((), dtype=torch.float32, device=dev)
+        dense_sq, expert_sq = self._sq[0].clone(), self._sq[1].clone()       # filled by the per-bucket pulls
         s = cu.stream_ptr()
         for st in self.state:
             buf: ParamGroupBuffer = st["buf"]
-            sq = expert_sq if buf.is_expert else dense_sq
-            if "red" in st:
-                gk = 0 if buf.grad_buffer.dtype == torch.float32 else 1
-                arr = buf.heap.peer_ptr_array(buf.grad_buffer)
-                rc = self.L.cm_reduce_shard(arr, buf.n, buf.rank, st["lo"], st["hi"] - st["lo"],
-                                            float(self._grad_scale / buf.grad_div), st["red"].data_ptr(), sq.data_ptr(), gk,
-                                            cu.err_word(dev).data_ptr(), s)
-                if rc:
-                    raise RuntimeError(f"cm_reduce_shard failed ({rc})")
-                from ..ops import functional as F_
-                F_.count_launch("reduce_shard")
-            else:
+            if "red" not in st:
                 g = buf.grad_buffer[st["lo"]:st["hi"]]
-                sq += self._sumsq_tp_aware(st, g)
+                if buf.is_expert:
+                    expert_sq += self._sumsq_tp_aware(st, g)
+                else:
+                    dense_sq += self._sumsq_tp_aware(st, g)
         gnorm = self._finish_norm(dense_sq, expert_sq)
         clip = torch.ones_like(gnorm)
         if cfg.clip_grad > 0:

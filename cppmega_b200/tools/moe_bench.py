@@ -42,7 +42,7 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--capacity-factor", type=float, default=None)
-    ap.add_argument("--overlap-shared", action="store_true", help="run the shared expert on a second stream beside the routed path")
+    ap.add_argument("--no-overlap-shared", action="store_true", help="keep the shared expert on the main stream (default: second stream beside the routed path)")
     ns = ap.parse_args(argv)
     from cppmega_b200.config.model import nam56r_full
     from cppmega_b200.models.moe import MoELayer
@@ -78,7 +78,7 @@ def main(argv=None) -> int:
             return probs.to(flat.dtype), ids, scores
 
     layer.router = FixedRouter()
-    layer.overlap_shared_expert = ns.overlap_shared
+    overlap_shared = not ns.no_overlap_shared
     ids = layer.router(x.reshape(T, H))[1]
     load = torch.bincount(ids.reshape(-1), minlength=E).float()
     per_rank = load.view(world, -1).sum(1)
@@ -113,11 +113,11 @@ def main(argv=None) -> int:
         cu.check_errors()
         return float(t)
 
-    res = {"tokens_per_rank": T, "ep": world, "skew": ns.skew, "precision": ns.precision, "overlap_shared": ns.overlap_shared,
+    res = {"tokens_per_rank": T, "ep": world, "skew": ns.skew, "precision": ns.precision, "overlap_shared": overlap_shared,
            "max_rank_load_over_mean": float(dist_worst), "capacity_factor": cap}
     layer.fused_dispatcher = None
     res["nccl_ms"] = timed() if world > 1 else None
-    bufs = fused_moe.attach(_OneLayer(mcfg, layer), pc, dev, tokens_per_rank=T, capacity_factor=cap)
+    bufs = fused_moe.attach(_OneLayer(mcfg, layer), pc, dev, tokens_per_rank=T, capacity_factor=cap, overlap_shared_expert=overlap_shared)
     res["fused_ms"] = timed() if bufs is not None else None
     Fe, Fs = mcfg.moe.expert_ffn, mcfg.moe.shared_expert_ffn
     flops = 3 * 2.0 * T * (topk * 3 * H * Fe + 3 * H * Fs)                 # fwd + dgrad + wgrad, SwiGLU = 3 matrices
