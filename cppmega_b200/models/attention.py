@@ -60,11 +60,11 @@ class DSAIndexer(nn.Module):
                                                     seed=seed_for(name + ".linear_weights_proj", seed))
         self.scale = self.h ** -0.5 * self.d ** -0.5
 
-    def project(self, x: torch.Tensor, q_latent: torch.Tensor):
+    def project(self, x: torch.Tensor, q_latent: torch.Tensor, pos_offset: int = 0):
         B, S, _ = x.shape
         q = self.linear_wq_b(q_latent).reshape(B, S, self.h, self.d)
         k = self.k_norm(self.linear_wk(x))
-        cos, sin = ref.rope_tables(S, self.rope_dim, self.rope_base, device=x.device)
+        cos, sin = ref.rope_tables(S, self.rope_dim, self.rope_base, device=x.device, offset=pos_offset)
         if self.rope_dim < self.d:
             q_r, q_n = split_last_dim(q, (self.rope_dim, self.d - self.rope_dim))
             k_r, k_n = split_last_dim(k, (self.rope_dim, self.d - self.rope_dim))
@@ -75,11 +75,18 @@ class DSAIndexer(nn.Module):
         w = self.linear_weights_proj(x).float() * self.scale
         return q, k, w
 
-    def forward(self, x: torch.Tensor, q_latent: torch.Tensor):
+    def forward(self, x: torch.Tensor, q_latent: torch.Tensor, cg=None):
         """Returns (indices int32 [B,S,topk], (q_idx, k_idx, w)); inputs are detached: the
-        indexer learns only through the optional KL loss."""
-        q, k, w = self.project(x.detach(), q_latent.detach())
-        idx = F_.indexer_topk(q.detach(), k.detach(), w.detach(), self.topk)
+        indexer learns only through the optional KL loss.  With a context group ``cg`` the index keys of all chunks are
+        gathered and the indices address the whole sequence."""
+        off = cg.q_offset(x.shape[1]) if cg is not None else 0
+        q, k, w = self.project(x.detach(), q_latent.detach(), off)
+        if cg is not None and cg.size > 1:
+            from ..parallel.context_parallel import gather_context
+            k = gather_context(k, cg)
+            idx = F_.indexer_topk(q.detach(), k.detach(), w.detach(), self.topk, q_offset=off)
+        else:
+            idx = F_.indexer_topk(q.detach(), k.detach(), w.detach(), self.topk)
         return idx, (q, k, w)
 
 
@@ -118,6 +125,7 @@ class MLAttention(nn.Module):
             self.core_attention.indexer = DSAIndexer(hidden, mla, dsa, pc, n + ".core_attention.indexer",
                                                      std=init_std, dtype=dtype, seed=seed, eps=eps)
         self.last_indexer_loss: Optional[torch.Tensor] = None
+        self.context_group = None        # parallel.context_parallel.ContextGroup: DSA layers only, set by the caller
 
     @property
     def is_index_publisher(self) -> bool:
@@ -145,7 +153,10 @@ class MLAttention(nn.Module):
         kv_c = self.linear_kv_down_proj(x)
         kv_lat, k_pe = split_last_dim(kv_c, (dc, dr))
         kv_lat = self.kv_layernorm(kv_lat)
-        cos, sin = ref.rope_tables(S, dr, mla.rope_base, device=x.device)
+        cg = self.context_group if self.sparse else None
+        if cg is not None and cg.size > 1 and self.dsa.indexer_loss_coeff > 0:
+            raise NotImplementedError("the indexer KL loss is not defined over a split sequence")
+        cos, sin = ref.rope_tables(S, dr, mla.rope_base, device=x.device, offset=cg.q_offset(S) if cg is not None else 0)
         q_nope, q_pe = split_last_dim(q, (dq, dr))
         q_pe = F_.apply_rope(q_pe, cos, sin)
         k_pe = copy_to_tp(F_.apply_rope(k_pe, cos, sin), pc)                    # [B,S,dr] shared by heads
@@ -163,6 +174,9 @@ class MLAttention(nn.Module):
             q_abs = F_.head_linear(q_nope, w_uk.transpose(1, 2))                 # [B,S,Hl,dc] = q_nope . W_uk
             q_full = cat_last_dim([q_abs, q_pe])                                # [B,S,Hl,dc+dr]
             kv_full = cat_last_dim([lat_tp, k_pe])                               # [B,S,dc+dr]
+            if cg is not None and cg.size > 1:                                  # keys of every chunk; indices are global
+                from ..parallel.context_parallel import gather_context
+                kv_full = gather_context(kv_full, cg)
             o_lat = F_.sparse_mla(q_full, kv_full, idx, self.softmax_scale, dc)  # [B,S,Hl,dc]
             o = F_.head_linear(o_lat, w_uv)                                      # [B,S,Hl,dv] = o_lat . W_uv^T
         return self.linear_proj(o.reshape(B, S, Hl * dv))
@@ -174,7 +188,7 @@ class MLAttention(nn.Module):
         if reuse:
             cache.stats["reused"] += 1
             return cache.indices
-        idx, (qi, ki, wi) = indexer(x, q_lat)
+        idx, (qi, ki, wi) = indexer(x, q_lat, self.context_group)
         if cache is not None:
             cache.stats["computed"] += 1
             if self.dsa.index_cache:
@@ -186,6 +200,6 @@ class MLAttention(nn.Module):
             k_nope = torch.einsum("bsc,hdc->bshd", kv_lat.detach(), w_up[:, :dq].detach().to(kv_lat.dtype))
             kk = torch.cat([k_nope, k_pe.detach().unsqueeze(2).expand(-1, -1, Hl, -1)], dim=-1)
             qq = torch.cat([q_nope, q_pe], dim=-1).detach()
-            self.last_indexer_loss = ref.indexer_kl_loss(qq, kk, self.softmax_scale, qi, ki, wi,
-                                                         self.dsa.indexer_loss_coeff)
+            kl = ref.indexer_kl_loss if qq.shape[1] <= 1024 else ref.indexer_kl_loss_chunked      # bounded transient at long S
+            self.last_indexer_loss = kl(qq, kk, self.softmax_scale, qi, ki, wi, self.dsa.indexer_loss_coeff)
         return idx

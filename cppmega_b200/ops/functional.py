@@ -300,16 +300,21 @@ def m2rnn_scan(q, k, v, W, f):
 
 # ---- DSA ---------------------------------------------------------------------
 
-def indexer_topk(q_idx, k_idx, w, topk: int):
-    fn = _cuda("indexer_topk", q_idx)
+def indexer_topk(q_idx, k_idx, w, topk: int, q_offset: Optional[int] = None):
+    """``q_offset``: sequence position of query 0 when the keys cover more than the queries (context parallelism: the
+    keys are gathered over the group, the queries are this rank's chunk); ``None``: queries are the last positions."""
+    plain = q_offset is None or (q_offset == 0 and k_idx.shape[1] == q_idx.shape[1])
+    fn = _cuda("indexer_topk", q_idx) if plain else None
     if fn is not None:
         with torch.no_grad():
             out = fn(q_idx, k_idx, w, topk)
         if out is not None:
             return out
         _FALLBACKS["indexer_topk(shape)"] += 1
+    elif not plain:
+        _miss("indexer_topk(query offset)", q_idx)
     with torch.no_grad():
-        return ref.indexer_topk(q_idx, k_idx, w, topk)
+        return ref.indexer_topk(q_idx, k_idx, w, topk, q_offset)
 
 
 def sparse_mla(q, kv, indices, scale: float, d_v: int):

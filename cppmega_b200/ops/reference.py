@@ -152,12 +152,14 @@ def indexer_scores(q_idx: torch.Tensor, k_idx: torch.Tensor, w: torch.Tensor) ->
     return out
 
 
-def indexer_topk(q_idx, k_idx, w, topk: int) -> torch.Tensor:
+def indexer_topk(q_idx, k_idx, w, topk: int, q_offset: Optional[int] = None) -> torch.Tensor:
     """Causal top-k key positions per query; int32 [B,S,topk], -1 where fewer than
-    ``topk`` keys are visible."""
+    ``topk`` keys are visible.  Query ``i`` sits at sequence position ``q_offset + i`` and sees the keys at positions
+    ``<=`` its own (default: the queries are the last ``S`` positions of the key sequence)."""
     sc = indexer_scores(q_idx, k_idx, w)
     B, S, Sk = sc.shape
-    causal = torch.ones(S, Sk, dtype=torch.bool, device=sc.device).tril(Sk - S)
+    off = Sk - S if q_offset is None else int(q_offset)
+    causal = torch.ones(S, Sk, dtype=torch.bool, device=sc.device).tril(off)
     sc = sc.masked_fill(~causal, float("-inf"))
     kk = min(topk, Sk)
     vals, idx = torch.topk(sc, kk, dim=-1)
@@ -199,6 +201,34 @@ def indexer_kl_loss(attn_q, attn_k, scale, q_idx, k_idx, w, coeff: float = 1.0):
     logq = torch.log_softmax(sc, dim=-1)
     kl = torch.where(p > 0, p * (torch.log(p.clamp_min(1e-30)) - logq), torch.zeros_like(p)).sum(-1)
     return coeff * kl.mean()
+
+
+def indexer_kl_loss_chunked(attn_q, attn_k, scale, q_idx, k_idx, w, coeff: float = 1.0, rows: int = 512):
+    """Same value and gradients as :func:`indexer_kl_loss`, evaluated ``rows`` query positions at a time with each
+    block recomputed in backward: the transient is ``[B, H, rows, S]`` instead of ``[B, H, S, S]`` (7 GiB per layer
+    at the NAM56R shape), which is what the reference's two-stage split kernels and its fused warm-up kernel buy
+    (cppmega/megatron/dsa_splitk_indexer_loss.py:56-321, cppmega/megatron/lemyx_dsa_warmup.py:77-178)."""
+    from torch.utils.checkpoint import checkpoint
+    B, S = attn_q.shape[:2]
+    Sk = attn_k.shape[1]
+
+    def block(aq, ak, qi, ki, wi, r0):
+        n = aq.shape[1]
+        pos = torch.arange(r0, r0 + n, device=aq.device)
+        causal = torch.arange(Sk, device=aq.device)[None, :] <= (pos + (Sk - S))[:, None]              # [n, Sk]
+        a = torch.einsum("bihd,bjhd->bhij", aq.float(), ak.float()) * scale
+        p = torch.softmax(a.masked_fill(~causal, float("-inf")), dim=-1).mean(dim=1)                  # [B, n, Sk]
+        sc = indexer_scores(qi, ki, wi).masked_fill(~causal, float("-inf"))
+        logq = torch.log_softmax(sc, dim=-1)
+        return torch.where(p > 0, p * (torch.log(p.clamp_min(1e-30)) - logq), torch.zeros_like(p)).sum()
+
+    total = attn_q.new_zeros((), dtype=torch.float32)
+    for r0 in range(0, S, rows):
+        r1 = min(S, r0 + rows)
+        args = (attn_q[:, r0:r1], attn_k, q_idx[:, r0:r1], k_idx, w[:, r0:r1], r0)
+        needs = any(torch.is_tensor(t) and t.requires_grad for t in args)
+        total = total + (checkpoint(block, *args, use_reentrant=False) if needs else block(*args))
+    return coeff * total / (B * S)
 
 
 # ---------------------------------------------------------------------------

@@ -112,6 +112,53 @@ class FusedDistributedOptimizer(DistributedOptimizer):
         if self._side is not None:
             torch.cuda.current_stream().wait_stream(self._side)
 
+    def zero_grad(self):
+        # peers may still be pulling last step's gradients or pushing parameters: wait for their
+        # PARAM flag before touching either buffer
+        if getattr(self, "_param_wait_pending", False):
+            for h in self._heaps_in_use():
+                h.wait(FLAG_PARAM, self.step_count)
+            self._param_wait_pending = False
+        super().zero_grad()
+        if getattr(self, "state", None):
+            dev = self.state[0]["master"].device
+            self._sq = torch.zeros(2, dtype=torch.float32, device=dev)       # [dense, expert] squared gradient norms of this step
+
+    def _side_stream(self):
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.state[0]["master"].device)
+        return self._side
+
+    def _on_bucket_ready(self, buf, b) -> None:
+        """Inside backward: publish this bucket's gradients to the peers and start pulling its shard on the second stream."""
+        key = (id(buf), b.index)
+        st = self._bucket_state.get(key)
+        if st is None:                       # a buffer without peers: scaled in finish_grad_sync
+            return
+        from ..ops import cuda as cu
+        from ..ops import functional as F_
+        step = self.step_count + 1
+        flag = self._bucket_flag[key]
+        heap = buf.heap
+        heap.signal(flag, step)                                   # after the kernels that wrote these gradients (this stream)
+        ev = torch.cuda.Event()
+        ev.record()
+        side = self._side_stream()
+        side.wait_event(ev)                                       # this rank's own gradients are read by the pull as well
+        dev = st["master"].device
+        with torch.cuda.stream(side):
+            heap.wait(flag, step)
+            sq = self._sq[1:2] if buf.is_expert else self._sq[0:1]
+            gk = 0 if buf.grad_buffer.dtype == torch.float32 else 1
+            arr = heap.peer_ptr_array(buf.grad_buffer)
+            rc = self.L.cm_reduce_shard(arr, buf.n, buf.rank, st["lo"], st["hi"] - st["lo"],
+                                        float(self._grad_scale / buf.grad_div), st["red"].data_ptr(), sq.data_ptr(), gk,
+                                        cu.err_word(dev).data_ptr(), cu.stream_ptr())
+            if rc:
+                raise RuntimeError(f"cm_reduce_shard failed ({rc})")
+            F_.count_launch("reduce_shard")
+        b.reduced = True
+
     @torch.no_grad()
     def step(self, lr: Optional[float] = None):
         from ..ops import cuda as cu

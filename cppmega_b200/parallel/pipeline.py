@@ -43,11 +43,16 @@ def schedule_1f1b(pp: int, stage: int, num_microbatches: int) -> List[tuple]:
     return acts
 
 
-def _p2p(ops):
+def _p2p(ops, wait: bool = True):
+    """Post a batch of sends / receives as one group; ``wait=False`` returns the requests un-waited (sends: the stream
+    that produced the tensor carries on; the caller keeps the tensor and the requests until :meth:`PipelineComm.drain`)."""
     if not ops:
-        return
-    for r in dist.batch_isend_irecv(ops):
-        r.wait()
+        return []
+    reqs = dist.batch_isend_irecv(ops)
+    if wait:
+        for r in reqs:
+            r.wait()
+    return reqs
 
 
 class PipelineComm:
@@ -55,6 +60,7 @@ class PipelineComm:
         self.pc, self.shape, self.dtype, self.device = pc, tuple(shape), dtype, device
         self.prev = pc.pp_ranks[pc.pp_rank - 1] if pc.pp_rank > 0 else None
         self.next = pc.pp_ranks[pc.pp_rank + 1] if pc.pp_rank < pc.pp - 1 else None
+        self._pending = []                     # (requests, tensor) of sends that nobody has waited for yet
 
     def _buf(self):
         return torch.empty(self.shape, dtype=self.dtype, device=self.device)
@@ -67,8 +73,10 @@ class PipelineComm:
         return t.requires_grad_()
 
     def send_forward(self, t: torch.Tensor) -> None:
+        """Pure sends do not hold the compute stream: the request is waited for at the end of the schedule."""
         if self.next is not None:
-            _p2p([dist.P2POp(dist.isend, t.detach().contiguous(), self.next)])
+            t = t.detach().contiguous()
+            self._pending.append((_p2p([dist.P2POp(dist.isend, t, self.next)], wait=False), t))
 
     def recv_backward(self) -> Optional[torch.Tensor]:
         if self.next is None:
@@ -79,7 +87,14 @@ class PipelineComm:
 
     def send_backward(self, g: Optional[torch.Tensor]) -> None:
         if self.prev is not None and g is not None:
-            _p2p([dist.P2POp(dist.isend, g.contiguous(), self.prev)])
+            g = g.contiguous()
+            self._pending.append((_p2p([dist.P2POp(dist.isend, g, self.prev)], wait=False), g))
+
+    def drain(self) -> None:
+        for reqs, _t in self._pending:
+            for r in reqs:
+                r.wait()
+        self._pending = []
 
     def send_forward_recv_backward(self, t: torch.Tensor) -> Optional[torch.Tensor]:
         if self.next is None:
@@ -177,6 +192,7 @@ def run_pipeline_schedule(trainer, microbatches: List[Dict[str, torch.Tensor]]) 
                 comm.send_backward(gin)
             k += 1
 
+    comm.drain()
     sync_embedding_copies(model, pc)
     dev = trainer.device
     zero = torch.zeros((), device=dev)
@@ -321,7 +337,7 @@ def run_chunked_schedule(trainer, microbatches: List[Dict[str, torch.Tensor]]) -
                 continue
             buf = torch.empty(shape, dtype=dtype, device=dev)
             recv_buf[msg[0]] = buf
-            recv_req[msg[0]] = dist.irecv(buf, src=pc.pp_ranks[src])
+            recv_req[msg[0]] = dist.irecv(buf, src=pc.pp_ranks[src], group=pc.pp_directed.get((src, me)))
     handoff: Dict[tuple, torch.Tensor] = {}
     send_reqs = []
 
@@ -340,7 +356,7 @@ def run_chunked_schedule(trainer, microbatches: List[Dict[str, torch.Tensor]]) -
             handoff[key] = tensor
         else:
             t = tensor.contiguous()
-            send_reqs.append((dist.isend(t, dst=pc.pp_ranks[dst]), t))
+            send_reqs.append((dist.isend(t, dst=pc.pp_ranks[dst], group=pc.pp_directed.get((me, dst))), t))
 
     inputs: Dict[tuple, Optional[torch.Tensor]] = {}
     outputs: Dict[tuple, torch.Tensor] = {}

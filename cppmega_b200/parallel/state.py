@@ -78,6 +78,9 @@ class ParallelContext:
     edp_group: Optional[dist.ProcessGroup] = None
     world_group: Optional[dist.ProcessGroup] = None
     embd_group: Optional[dist.ProcessGroup] = None     # first+last pipeline stage (embedding copies)
+    # one group per ORDERED pair of pipeline stages (src, dst): messages src -> dst travel on a communicator that carries
+    # nothing else, so pre-posted receives of one direction can never queue in front of sends of the other direction
+    pp_directed: dict = field(default_factory=dict)
     tp_ranks: List[int] = field(default_factory=lambda: [0])
     pp_ranks: List[int] = field(default_factory=lambda: [0])
     dp_ranks: List[int] = field(default_factory=lambda: [0])
@@ -165,7 +168,7 @@ def group_rank_lists(world: int, cfg: ParallelConfig):
 
 
 def initialize(cfg: ParallelConfig = ParallelConfig(), backend: Optional[str] = None,
-               timeout_s: float = 600.0) -> ParallelContext:
+               timeout_s: float = 600.0, directed_pp_groups: bool = True) -> ParallelContext:
     """Create (or reuse) the default process group from ``RANK``/``WORLD_SIZE``/``MASTER_*``
     and build every sub-group.  With ``WORLD_SIZE`` unset or 1 returns a single-process context."""
     global _CTX
@@ -207,6 +210,16 @@ def initialize(cfg: ParallelConfig = ParallelConfig(), backend: Optional[str] = 
             g = dist.new_group(ranks=pair, backend=backend)
             if rank in pair:
                 embd_group = g
+    pp_directed = {}
+    if cfg.pp > 1 and (cfg.vpp > 1 or directed_pp_groups):
+        for ranks in lists["pp"]:
+            for a in range(cfg.pp):
+                for b in range(cfg.pp):
+                    if a == b:
+                        continue
+                    g = dist.new_group(ranks=sorted([ranks[a], ranks[b]]), backend=backend)
+                    if rank in ranks:
+                        pp_directed[(a, b)] = g
     tp_rank, ep_rank, edp_rank, dp_rank, pp_rank = rank_coordinates(rank, world, cfg)
     _CTX = ParallelContext(
         config=cfg, world_size=world, rank=rank, local_rank=local_rank,
@@ -214,7 +227,7 @@ def initialize(cfg: ParallelConfig = ParallelConfig(), backend: Optional[str] = 
         tp_group=groups["tp"], pp_group=groups["pp"], dp_group=groups["dp"],
         ep_group=groups["ep"], edp_group=groups["edp"], world_group=dist.group.WORLD, embd_group=embd_group,
         tp_ranks=mine["tp"], pp_ranks=mine["pp"], dp_ranks=mine["dp"],
-        ep_ranks=mine["ep"], edp_ranks=mine["edp"],
+        ep_ranks=mine["ep"], edp_ranks=mine["edp"], pp_directed=pp_directed,
     )
     return _CTX
 

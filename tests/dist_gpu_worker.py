@@ -21,31 +21,48 @@ from cppmega_b200.training.trainer import TrainConfig, Trainer, synthetic_batche
 def main():
     mode, steps = sys.argv[1], int(sys.argv[2])
     recompute = sys.argv[3] if len(sys.argv) > 3 else "none"
-    world = int(os.environ["WORLD_SIZE"])
-    local_rank = int(os.environ["LOCAL_RANK"])
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     tp_mode = mode.startswith("tp_")
+    pp_mode = mode in ("pp", "pp_vpp2", "dualpipev", "single4")
     seq = 256 if tp_mode else 128                      # fused TP wants (seq / tp) % 128 == 0
+    schedule = {"pp_vpp2": "interleaved", "dualpipev": "dualpipev"}.get(mode, "1f1b")
+    n_mb = 4 if pp_mode else world
     if tp_mode:
         pc = pstate.initialize(ParallelConfig(tp=world, sequence_parallel=True, fused_collectives=(mode == "tp_fused")))
+    elif pp_mode:
+        cfgs = {"pp": ParallelConfig(pp=world), "pp_vpp2": ParallelConfig(pp=world, vpp=2), "dualpipev": ParallelConfig(pp=world),
+                "single4": ParallelConfig()}
+        pc = pstate.initialize(cfgs[mode])
     else:
         ep = min(world, nam56r_tiny().moe.num_experts)
         pc = pstate.initialize(ParallelConfig(ep=ep, fused_collectives=(mode == "fused")))
     mcfg = nam56r_tiny(seq_length=seq)
-    tcfg = TrainConfig(micro_batch_size=2, seq_length=seq, dtype="bf16", recompute=recompute,
-                       optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0), log_interval=0)
+    tcfg = TrainConfig(micro_batch_size=2, global_batch_size=2 * n_mb if pp_mode else None, seq_length=seq, dtype="bf16",
+                       recompute=recompute, optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0), log_interval=0,
+                       pipeline_schedule=schedule)
     trainer = Trainer(mcfg, tcfg, pc, device=torch.device("cuda", local_rank))
-    stream = synthetic_batches(mcfg.vocab_size, 2, seq, num_microbatches=world, seed=0, pin=False, rank=0)
+    stream = synthetic_batches(mcfg.vocab_size, 2, seq, num_microbatches=n_mb, seed=0, pin=False, rank=0)
     F_.reset_counters()
     losses = []
     for _ in range(steps):
         mbs = next(stream)
-        res = trainer.train_step([mbs[pc.dp_rank]])
-        rec = trainer.reduce_loss_for_logging(res)
+        if pp_mode:
+            res = trainer.train_step(mbs)
+            has_loss = pc.is_first_pp if mode == "dualpipev" else pc.is_last_pp
+            rec = (trainer.reduce_loss_for_logging(res) if has_loss
+                   else {"loss": 0.0, "lm_loss": 0.0, "grad_norm": float(res["grad_norm"])})
+        else:
+            res = trainer.train_step([mbs[pc.dp_rank]])
+            rec = trainer.reduce_loss_for_logging(res)
         losses.append([rec["loss"], rec["lm_loss"], rec["grad_norm"]])
     torch.cuda.synchronize()
     cu.check_errors()
-    if pc.rank == 0:
+    report = 0
+    if mode in ("pp", "pp_vpp2"):
+        report = world - 1
+    if pc.rank == report:
         print("RESULT " + json.dumps({"mode": mode, "losses": losses, "fused": trainer.fused,
                                       "launches": F_.launch_counts()}), flush=True)
     pstate.destroy()

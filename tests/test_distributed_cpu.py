@@ -73,3 +73,14 @@ def test_muon_update_does_not_depend_on_the_shard_layout():
         assert abs(b[0] - g[0]) < 2e-3 * max(1.0, abs(b[0])), (step, one, two)
         assert abs(b[2] - g[2]) < 2e-2 * max(1.0, abs(b[2])), (step, one, two)
     assert one["losses"][-1][0] < one["losses"][0][0]
+
+
+def test_context_parallel_sparse_attention_matches_full_sequence():
+    """A DSA layer on a sequence split over 2 ranks (index keys and latent KV gathered, queries at their global
+    positions) reproduces the single-process output, input gradient and parameter gradients."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker_cp.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    rec = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    assert rec["y"] < 1e-5 and rec["dx"] < 1e-4 and rec["param_grads"] < 1e-4, rec

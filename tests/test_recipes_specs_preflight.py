@@ -225,3 +225,19 @@ def test_moe_plan_overflow_is_clipped_to_the_buffer():
     assert dropped > 0                                          # these are skipped + reported by push / pull
     kept = torch.cat([p.dest_row[(p.dest_rank == 0) & (p.dest_row < cap)] for p in plans])
     assert kept.unique().numel() == kept.numel() and int(kept.max()) < cap
+
+
+def test_chunked_indexer_kl_loss_equals_dense_form():
+    from cppmega_b200.ops import reference as ref
+    torch.manual_seed(3)
+    B, S, H, D, Hi, Di = 2, 70, 3, 8, 4, 6
+    aq, ak = torch.randn(B, S, H, D), torch.randn(B, S, H, D)
+    mk = lambda *s: torch.randn(*s, requires_grad=True)
+    qi, ki, w = mk(B, S, Hi, Di), mk(B, S, Di), mk(B, S, Hi)
+    dense = ref.indexer_kl_loss(aq, ak, 0.3, qi, ki, w, 0.7)
+    g1 = torch.autograd.grad(dense, (qi, ki, w))
+    chunked = ref.indexer_kl_loss_chunked(aq, ak, 0.3, qi, ki, w, 0.7, rows=16)
+    g2 = torch.autograd.grad(chunked, (qi, ki, w))
+    assert abs(float(dense) - float(chunked)) < 1e-5 * max(1.0, abs(float(dense)))
+    for a, b in zip(g1, g2):
+        assert (a - b).abs().max() < 1e-5

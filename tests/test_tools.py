@@ -141,3 +141,39 @@ def test_nan_hunter_names_the_first_bad_module():
     with NonFiniteHunter(net) as h2:
         net(torch.ones(3, 4)).sum().backward()
         assert h2.first is None and "finite" in h2.report()
+
+
+def test_dashboard_discovers_runs_and_renders_them():
+    """Two fake runs publish records on their metrics endpoints; the dashboard finds them, computes the analytics and
+    serves the overview, the detail page and the JSON API."""
+    import json as _json
+    import urllib.request
+    from cppmega_b200.tools.dashboard import Dashboard, analytics
+    from cppmega_b200.utils.monitor import MetricsServer
+    servers = [MetricsServer(0).start() for _ in range(2)]
+    try:
+        for k, s in enumerate(servers):
+            for it in range(1, 9):
+                s.publish({"iteration": it, "loss": 10.0 - 0.5 * it - k, "grad_norm": 1.0, "elapsed_ms": 100.0 + it,
+                           "tokens_per_s": 1000.0 * (k + 1), "tflops_per_gpu": 400.0})
+        ports = [s.port for s in servers]
+        dash = Dashboard("127.0.0.1", ports + [1], 0).serve(block=False)       # port 1: nothing listens there
+        import threading
+        t = threading.Thread(target=dash._httpd.serve_forever, daemon=True)
+        t.start()
+        try:
+            base = f"http://127.0.0.1:{dash.listen[1]}"
+            runs = _json.loads(urllib.request.urlopen(base + "/api/runs", timeout=5).read())
+            assert sorted(r["port"] for r in runs) == sorted(ports)
+            a = runs[0]["analytics"]
+            assert a["records"] == 8 and a["loss_slope_per_iteration"] < 0 and a["median_tokens_per_s"] in (1000.0, 2000.0)
+            page = urllib.request.urlopen(base + "/", timeout=5).read().decode()
+            assert all(str(p) in page for p in ports) and "<svg" in page
+            detail = urllib.request.urlopen(f"{base}/run/{ports[0]}", timeout=5).read().decode()
+            assert "loss_slope_per_iteration" in detail and "tokens/s" in detail
+        finally:
+            dash.stop()
+    finally:
+        for s in servers:
+            s.stop()
+    assert analytics([])["records"] == 0
