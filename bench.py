@@ -127,6 +127,10 @@ def main() -> int:
     ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8", "tensorwise"],
                     help="mxfp8 / tensorwise: FP8 linears and expert GEMMs (an extra measurement; the headline number is bf16)")
     ap.add_argument("--fp8-modules", nargs="*", default=[], help="restrict --precision to these module patterns (moe, mamba_proj, globs)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence parallelism); data parallel = gpus / tp")
+    ap.add_argument("--ep", type=int, default=0, help="expert-parallel size (default: the data-parallel size)")
+    ap.add_argument("--fp8-activations", default="off", choices=["off", "mxfp8", "tensor"],
+                    help="FP8-compress the activations kept for backward (first and last layer stay bf16)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--profile-dir", default=None, help="after timing, capture one step with the torch profiler here")
     args = ap.parse_args()
@@ -158,8 +162,14 @@ def main() -> int:
     if args.seq != 4096:
         overrides["seq_length"] = args.seq
     mcfg = get_preset(args.model, **overrides)
-    ep = world if mcfg.moe.num_experts % world == 0 else 1
-    pcfg = ParallelConfig(tp=1, pp=1, ep=ep, distributed_optimizer=True, fused_collectives=not args.no_fused_collectives)
+    tp = max(args.tp, 1)
+    if world % tp:
+        print(f"bench.py: --tp {tp} does not divide {world} GPUs", file=sys.stderr)
+        return 2
+    dp = world // tp
+    ep = args.ep if args.ep > 0 else (dp if mcfg.moe.num_experts % dp == 0 else 1)
+    pcfg = ParallelConfig(tp=tp, pp=1, ep=ep, sequence_parallel=tp > 1, distributed_optimizer=True,
+                          fused_collectives=not args.no_fused_collectives)
     pc = pstate.initialize(pcfg)
     recompute = args.recompute
     if recompute == "auto":
@@ -179,6 +189,7 @@ def main() -> int:
     def make_trainer(pctx, rc, kl):
         tcfg = TrainConfig(micro_batch_size=args.micro_batch, seq_length=args.seq, dtype="bf16", recompute=rc,
                            recompute_keep_last=kl, precision_recipe=args.precision, precision_modules=tuple(args.fp8_modules),
+                           fp8_activations=args.fp8_activations,
                            optimizer=OptimizerConfig(lr=1e-5, weight_decay=0.1, grad_dtype=grad_dtype), log_interval=0)
         return Trainer(mcfg, tcfg, pctx, device=device)
 
@@ -186,7 +197,7 @@ def main() -> int:
     n_params = sum(p.numel() for p in trainer.model.parameters())
     holder = {"trainer": trainer}
 
-    host_batches = synthetic_batches(mcfg.vocab_size, args.micro_batch, args.seq, seed=1234, rank=rank)
+    host_batches = synthetic_batches(mcfg.vocab_size, args.micro_batch, args.seq, seed=1234, rank=pc.dp_rank)   # one stream per data-parallel rank
     dev_pool = []
     for _ in range(2):
         mb = next(host_batches)
@@ -239,7 +250,7 @@ def main() -> int:
         sampler.stop()
     cu.check_errors()
 
-    tokens_per_step = args.micro_batch * args.seq * world
+    tokens_per_step = args.micro_batch * args.seq * dp
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     fused_paths = dict(trainer.fused)
 
@@ -298,7 +309,7 @@ def main() -> int:
     if not args.no_e2e:
         h2d = 2 * args.micro_batch * args.seq * 8             # input_ids + labels, int64, per rank
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
-               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
+               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,      # every rank copies its (TP-replicated) batch
                "ms_per_step": ms_e2e / args.steps, "last_loss": last_loss[-1] if last_loss else None}
     if rank == 0:
         out = {
@@ -308,12 +319,13 @@ def main() -> int:
             "impl": "ours",
             "config": {"model": f"{mcfg.name} {n_params / 1e9:.2f}B params on rank 0 ({mcfg.param_count()['total'] / 1e9:.2f}B total), "
                                 f"{mcfg.depth} layers {mcfg.pattern}, hidden {mcfg.hidden_size}, vocab {mcfg.vocab_size}, MTP {mcfg.mtp.num_layers}",
-                       "global_batch": args.micro_batch * world, "micro_batch": args.micro_batch, "seq_len": args.seq,
-                       "parallelism": f"ep{ep}dp{world}" if world > 1 else "single GPU (16 local experts)",
+                       "global_batch": args.micro_batch * dp, "micro_batch": args.micro_batch, "seq_len": args.seq,
+                       "parallelism": (f"tp{tp}ep{ep}dp{dp} (sequence parallel)" if tp > 1 else f"ep{ep}dp{world}") if world > 1 else "single GPU (16 local experts)",
                        "distributed_optimizer": True, "recompute": recompute, "recompute_keep_last": keep_last,
-                       "grad_dtype": grad_dtype, "collectives": "peer-memory kernels" if pcfg.fused_collectives else "nccl",
+                       "grad_dtype": grad_dtype, "fp8_activations": args.fp8_activations, "collectives": "peer-memory kernels" if pcfg.fused_collectives else "nccl",
                        "l2": "weights + activations per step are far larger than the 126 MB L2",
-                       "headline_config": not args.depth and args.seq == 4096 and args.micro_batch == 4 and args.precision == "bf16"},
+                       "headline_config": not args.depth and args.seq == 4096 and args.micro_batch == 4 and args.precision == "bf16" and tp == 1
+                                          and args.fp8_activations == "off"},
             "clocks": sampler.summary() if rank == 0 else None,
             "e2e": e2e, "gpu_launches": launches, "fallback_ops": fallbacks, "fused_paths": fused_paths,
             "like_for_like": like, "nccl_path": nccl,

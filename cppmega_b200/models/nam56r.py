@@ -180,22 +180,31 @@ class NAM56RModel(nn.Module):
         cache = index_cache if index_cache is not None else IndexCacheState()
         self.index_cache = cache
         n_layers = len(self.decoder.layers)
+        from ..utils import fp8_activations as fa
+        act = getattr(self, "fp8_activations", None) or {}
         for pos, (key, layer) in enumerate(self.decoder.layers.items()):
-            ck = self.training and (self.recompute == "full" or
-                                    (self.recompute == "selective" and layer.kind in ("mamba3", "m2rnn")))
-            if pos >= n_layers - self.recompute_keep_last or getattr(layer, "_graphed", None) is not None:
-                ck = False      # kept layers and CUDA-graph-captured layers hold their activations
-            if ck and layer.kind == "dsa" and self.cfg.dsa.indexer_loss_coeff > 0:
-                ck = False      # the indexer loss needs the layer's own graph
-            if ck and layer.kind == "dsa":
-                # pick the indices once, outside the checkpoint, so the recomputation in
-                # backward replays the layer with the same selection
-                idx = layer.select_indices(x, cache)
-                x = checkpoint(layer, x, None, idx)
-            elif ck:
-                x = checkpoint(layer, x, None, None)
-            else:
-                x = layer(x, cache)
+            fa.set_current_layer_idx(pos)
+            with fa.fp8_activation_context(n_layers=n_layers, enabled=bool(act) and self.training, **act):
+                x = self._run_layer(pos, n_layers, layer, x, cache)
+        fa.set_current_layer_idx(-1)
+        return x
+
+    def _run_layer(self, pos: int, n_layers: int, layer, x: torch.Tensor, cache) -> torch.Tensor:
+        ck = self.training and (self.recompute == "full" or
+                                (self.recompute == "selective" and layer.kind in ("mamba3", "m2rnn")))
+        if pos >= n_layers - self.recompute_keep_last or getattr(layer, "_graphed", None) is not None:
+            ck = False      # kept layers and CUDA-graph-captured layers hold their activations
+        if ck and layer.kind == "dsa" and self.cfg.dsa.indexer_loss_coeff > 0:
+            ck = False      # the indexer loss needs the layer's own graph
+        if ck and layer.kind == "dsa":
+            # pick the indices once, outside the checkpoint, so the recomputation in
+            # backward replays the layer with the same selection
+            idx = layer.select_indices(x, cache)
+            x = checkpoint(layer, x, None, idx)
+        elif ck:
+            x = checkpoint(layer, x, None, None)
+        else:
+            x = layer(x, cache)
         return x
 
     def aux_losses(self) -> Optional[torch.Tensor]:

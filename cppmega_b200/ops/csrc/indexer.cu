@@ -165,19 +165,9 @@ __global__ void __launch_bounds__(NT) indexer_topk_kernel(const float* __restric
   for (int shift = 24; shift >= 0; shift -= 8) {
     if (tid < 256) hist[tid] = 0;
     __syncthreads();
-    // Index scores are sums of non-negative terms of similar size: in the high-byte passes nearly every key of a row falls
-    // into one or two bins.  The lanes of a warp that hit the same bin are counted once (match + popcount), so the
-    // shared-memory atomics stay a handful per warp instead of serialising thousands of increments of one address.
 #pragma unroll
-    for (int e = 0; e < PER; ++e) {
-      const bool in = key[e] != 0u && (key[e] & mask) == prefix;
-      const unsigned vote = __ballot_sync(0xffffffffu, in);
-      if (in) {
-        const unsigned bin = (key[e] >> shift) & 255u;
-        const unsigned peers = __match_any_sync(vote, bin);
-        if (lane == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
-      }
-    }
+    for (int e = 0; e < PER; ++e)
+      if (key[e] != 0u && (key[e] & mask) == prefix) atomicAdd(&hist[(key[e] >> shift) & 255], 1);
     __syncthreads();
     // inclusive scan over bins in descending order: thread t < 256 looks at bin 255 - t
     const int h = tid < 256 ? hist[255 - tid] : 0;

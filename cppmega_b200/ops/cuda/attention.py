@@ -19,6 +19,7 @@ def declare(L: ctypes.CDLL) -> None:
         if fn is not None:
             fn.argtypes = args
             fn.restype = i32
+    _declare_head_linear(L)
 
 
 def supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
@@ -76,3 +77,88 @@ def causal_attention(q, k, v, scale: float):
 
 def register() -> None:
     F_.register_cuda("causal_attention", causal_attention)
+    F_.register_cuda("head_linear", head_linear)
+
+
+# ---------------------------------------------------------------------------
+# per-head linear maps of the absorbed sparse-attention path (ops/csrc/head_linear.cu)
+# ---------------------------------------------------------------------------
+
+def _declare_head_linear(L: ctypes.CDLL) -> None:
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    for name, args in (("cm_head_linear", [vp, vp, vp, i32, i32, i64, i64, i64, i64, i32, vp, vp]),
+                       ("cm_head_linear_wgrad", [vp, vp, vp, i32, i32, i64, i64, i64, i64, vp, vp])):
+        fn = getattr(L, name, None)
+        if fn is not None:
+            fn.argtypes = args
+            fn.restype = i32
+
+
+def _token_view(x: torch.Tensor):
+    """(tensor, tokens, token stride, head stride) of a [..., H, 64] bf16 operand the kernel can read in place: the
+    leading dimensions must collapse to one stride; otherwise the operand is copied to a packed tensor."""
+    from . import fast_contiguous
+    H = x.shape[-2]
+    T = x.numel() // (H * 64)
+    lead_sizes, lead_strides = x.shape[:-2], x.stride()[:-2]
+    ok = x.stride(-1) == 1 and x.stride(-2) % 8 == 0 and x.data_ptr() % 16 == 0
+    tok = None
+    if ok:
+        tok = lead_strides[-1] if lead_sizes else H * 64
+        expect = tok
+        for n, s in zip(reversed(lead_sizes), reversed(lead_strides)):
+            if n != 1 and s != expect:
+                ok = False
+                break
+            expect *= n
+        ok = ok and tok % 8 == 0 and tok >= 64
+    if not ok:
+        x = fast_contiguous(x)
+        return x, T, H * 64, 64
+    return x, T, tok, x.stride(-2)
+
+
+def head_linear_raw(x: torch.Tensor, w: torch.Tensor, transposed: bool) -> torch.Tensor:
+    """``y[..., h, :] = x[..., h, :] @ w[h].T`` (``transposed`` False, ``w`` [H, 64 out, 64 in]) or ``x @ w[h]``."""
+    from . import lib, err_word, stream_ptr, _check
+    xs, T, x_tok, x_head = _token_view(x)
+    H = x.shape[-2]
+    y = torch.empty(*x.shape[:-1], 64, dtype=torch.bfloat16, device=x.device)
+    _check(lib().cm_head_linear(xs.data_ptr(), w.data_ptr(), y.data_ptr(), T, H, x_tok, x_head, H * 64, 64, int(transposed),
+                                err_word(x.device).data_ptr(), stream_ptr()), "cm_head_linear")
+    F_.count_launch("head_linear")
+    return y
+
+
+class HeadLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        wc = w.contiguous()
+        ctx.save_for_backward(x, wc)
+        return head_linear_raw(x, wc, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import lib, err_word, stream_ptr, _check
+        x, wc = ctx.saved_tensors
+        dy = dy.to(torch.bfloat16)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = head_linear_raw(dy, wc, True)
+        if ctx.needs_input_grad[1]:
+            H = x.shape[-2]
+            dys, T, dy_tok, dy_head = _token_view(dy)
+            xs, _, x_tok, x_head = _token_view(x)
+            dw32 = torch.zeros(H, 64, 64, dtype=torch.float32, device=x.device)
+            _check(lib().cm_head_linear_wgrad(dys.data_ptr(), xs.data_ptr(), dw32.data_ptr(), T, H, dy_tok, dy_head, x_tok, x_head,
+                                              err_word(x.device).data_ptr(), stream_ptr()), "cm_head_linear_wgrad")
+            F_.count_launch("head_linear_wgrad")
+            dw = dw32.to(wc.dtype)
+        return dx, dw
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor):
+    if (not x.is_cuda or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() < 3 or x.shape[-1] != 64
+            or w.dim() != 3 or tuple(w.shape[1:]) != (64, 64) or w.shape[0] != x.shape[-2] or x.numel() == 0):
+        return None
+    return HeadLinearFn.apply(x, w)

@@ -231,7 +231,13 @@ def rmsnorm_gated(x, weight, z=None, eps: float = 1e-5, group_size=None, norm_be
 
 def head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """Per-head product ``y[..., h, :] = x[..., h, :] @ w[h]^T`` with ``x`` [..., H, in] and ``w`` [H, out, in] (the
-    absorbed MLA up-projections of the sparse-attention path).  A batched library GEMM on every device: counted."""
+    absorbed MLA up-projections of the sparse-attention path).  64-wide heads in bf16 run on the streaming tcgen05 kernel;
+    anything else is a batched library GEMM and is counted."""
+    fn = _cuda("head_linear", x)
+    if fn is not None:
+        y = fn(x, w)
+        if y is not None:
+            return y
     _miss("head_linear(library bmm)", x)
     return torch.einsum("...hi,hoi->...ho", x, w.to(x.dtype))
 

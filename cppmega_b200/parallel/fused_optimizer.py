@@ -169,16 +169,19 @@ class FusedDistributedOptimizer(DistributedOptimizer):
         step = self.step_count + 1
         heaps = self._heaps_in_use()
         dev = self.state[0]["master"].device
-        dense_sq, expert_sq = self._sq[0].clone(), self._sq[1].clone()       # filled by the per-bucket pulls
         s = cu.stream_ptr()
-        for st in self.state:
-            buf: ParamGroupBuffer = st["buf"]
-            if "red" not in st:
-                g = buf.grad_buffer[st["lo"]:st["hi"]]
-                if buf.is_expert:
-                    expert_sq += self._sumsq_tp_aware(st, g)
-                else:
-                    dense_sq += self._sumsq_tp_aware(st, g)
+        if pc.tp > 1:
+            dense_sq, expert_sq = self._tensor_parallel_fixup()
+        else:
+            dense_sq, expert_sq = self._sq[0].clone(), self._sq[1].clone()   # filled by the per-bucket pulls
+            for st in self.state:
+                buf: ParamGroupBuffer = st["buf"]
+                if "red" not in st:
+                    g = buf.grad_buffer[st["lo"]:st["hi"]]
+                    if buf.is_expert:
+                        expert_sq += self._sumsq_tp_aware(st, g)
+                    else:
+                        dense_sq += self._sumsq_tp_aware(st, g)
         gnorm = self._finish_norm(dense_sq, expert_sq)
         clip = torch.ones_like(gnorm)
         if cfg.clip_grad > 0:
@@ -211,14 +214,58 @@ class FusedDistributedOptimizer(DistributedOptimizer):
         self._param_wait_pending = bool(heaps)
         return {"grad_norm": gnorm, "clip_coef": clip}
 
+    handles_sequence_parallel_grads = True       # the trainer must not all-reduce ``main_grad`` (peers pull from it)
+
+    def _tensor_parallel_fixup(self):
+        """TP > 1 with sequence parallelism, after the data-parallel reduction of every shard.  (1) Gradients of
+        parameters that every TP rank holds whole but computes from its own sequence shard (norm weights, routers,
+        experts) are partial sums: their segments of the reduced shards are all-reduced over the TP group, coalesced
+        into one flat buffer.  (2) The squared norm is recomputed from the final values, counting tensors replicated
+        over TP ``1 / tp`` so that the TP all-reduce of the norm counts them once.  Returns (dense, expert) sums."""
+        pc = self.pc
+        tp = pc.tp
+        dev = self.state[0]["master"].device
+        partial, replicated = [], []               # (shard view, is_expert)
+        whole = []
+        for st in self.state:
+            buf, lo, hi = st["buf"], st["lo"], st["hi"]
+            src = st["red"] if "red" in st else buf.grad_buffer[lo:hi]
+            whole.append((src, buf.is_expert))
+            for p in st["bucket"].params:
+                off = buf.offsets[p]
+                a, b = max(off, lo), min(off + p.numel(), hi)
+                if a >= b:
+                    continue
+                seg = src[a - lo:b - lo]
+                if getattr(p, "sequence_parallel_grad", False):
+                    partial.append(seg)
+                if not getattr(p, "tensor_model_parallel", False):
+                    replicated.append((seg, buf.is_expert))
+        if partial:
+            flat = torch.cat([x.reshape(-1).float() for x in partial])
+            dist.all_reduce(flat, group=pc.tp_group)
+            o = 0
+            for x in partial:
+                x.copy_(flat[o:o + x.numel()])
+                o += x.numel()
+        sq = torch.zeros(2, dtype=torch.float32, device=dev)
+        for src, is_expert in whole:
+            xf = src.float()
+            sq[1 if is_expert else 0] += (xf * xf).sum()
+        for seg, is_expert in replicated:
+            xf = seg.float()
+            sq[1 if is_expert else 0] -= (1.0 - 1.0 / tp) * (xf * xf).sum()
+        return sq[0].clone(), sq[1].clone()
+
     def _finish_norm(self, dense_sq, expert_sq):
-        """Same reduction tree as ``DistributedOptimizer.grad_norm`` on already-sharded sums.
-        (Replicated-over-TP tensors are not down-weighted on this path: it requires tp == 1.)"""
+        """Same reduction tree as ``DistributedOptimizer.grad_norm`` on already-sharded sums."""
         pc = self.pc
         if pc.dp > 1:
             dist.all_reduce(dense_sq, group=pc.dp_group)
             dist.all_reduce(expert_sq, group=pc.dp_group)
         total = dense_sq + expert_sq
+        if pc.tp > 1:
+            dist.all_reduce(total, group=pc.tp_group)
         if pc.pp > 1:
             dist.all_reduce(total, group=pc.pp_group)
         return total.sqrt()
@@ -231,5 +278,5 @@ class FusedDistributedOptimizer(DistributedOptimizer):
 
 def fused_optimizer_supported(pc, device: torch.device) -> bool:
     from .symm_mem import peer_access_available
-    return (device.type == "cuda" and pc.world_size > 1 and pc.tp == 1 and pc.dp > 1
+    return (device.type == "cuda" and pc.world_size > 1 and pc.dp > 1
             and pc.config.distributed_optimizer and pc.config.fused_collectives and peer_access_available(pc))

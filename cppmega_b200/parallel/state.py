@@ -218,8 +218,19 @@ def initialize(cfg: ParallelConfig = ParallelConfig(), backend: Optional[str] = 
                     if a == b:
                         continue
                     g = dist.new_group(ranks=sorted([ranks[a], ranks[b]]), backend=backend)
-                    if rank in ranks:
+                    if rank in (ranks[a], ranks[b]):
                         pp_directed[(a, b)] = g
+                        if backend == "nccl":
+                            # NCCL creates a point-to-point communicator at the first send / receive of a pair, and that
+                            # creation blocks the host until the peer arrives.  The schedules pre-post receives in an
+                            # order that differs between ranks, so open every channel here, in one global order.
+                            one = torch.zeros(1, device=torch.device("cuda", torch.cuda.current_device()))
+                            if rank == ranks[a]:
+                                dist.send(one, dst=ranks[b], group=g)
+                            else:
+                                dist.recv(one, src=ranks[a], group=g)
+    if pp_directed and backend == "nccl":
+        torch.cuda.synchronize()
     tp_rank, ep_rank, edp_rank, dp_rank, pp_rank = rank_coordinates(rank, world, cfg)
     _CTX = ParallelContext(
         config=cfg, world_size=world, rank=rank, local_rank=local_rank,

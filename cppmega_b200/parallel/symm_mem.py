@@ -115,6 +115,24 @@ class SymmetricHeap:
         off = self.offset_of(t)
         return [b + off for b in self.peer_base]
 
+    def peer_tensor(self, t: torch.Tensor, peer: int) -> torch.Tensor:
+        """Tensor view of peer ``peer``'s copy of the symmetric tensor ``t`` (same shape and dtype), usable as the
+        destination of this package's own copy / GEMM-epilogue stores.  Never hand it to a library kernel."""
+        if peer == self.me:
+            return t
+        nbytes = t.numel() * t.element_size()
+        raw = torch.as_tensor(_RawCudaArray(self.peer_base[peer] + self.offset_of(t), nbytes), device=self.device)
+        return raw.view(t.dtype).view(t.shape)
+
+    def wait_one(self, index: int, rank: int, value: int, timeout_ns: Optional[int] = None) -> None:
+        """Bounded device-side wait until rank ``rank`` (position in the group) has signalled ``value`` on ``index``."""
+        from ..ops.cuda import err_word, stream_ptr
+        rc = self.L.cm_wait_flags(self.flags.data_ptr(), index * self.world + rank, 1, value,
+                                  self.timeout_ns if timeout_ns is None else timeout_ns,
+                                  err_word(self.device).data_ptr(), stream_ptr())
+        if rc:
+            raise RuntimeError(f"cm_wait_flags failed ({rc})")
+
     def peer_ptr_array(self, t: torch.Tensor):
         ptrs = self.peer_ptrs(t)
         return (ctypes.c_void_p * self.world)(*ptrs)

@@ -129,6 +129,11 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--fp8-modules", nargs="*", default=[],
                    help="restrict the FP8 recipe to modules whose qualified name matches one of these glob patterns "
                         "(shorthands: moe, mamba_proj); everything else stays bf16")
+    g.add_argument("--fp8-activations", default="off", choices=["off", "mxfp8", "tensor"],
+                   help="store the activations saved for backward as E4M3 + scales (block scales / one scale per tensor)")
+    g.add_argument("--fp8-activations-bf16-first", type=int, default=1, help="layers at the start of the stack that keep bf16")
+    g.add_argument("--fp8-activations-bf16-last", type=int, default=1, help="layers at the end of the stack that keep bf16")
+    g.add_argument("--fp8-activations-clamp", action="store_true", help="tensor recipe: limit the measured maximum to 448")
     g.add_argument("--recompute-granularity", default=None, choices=["selective", "full"])
     g.add_argument("--cuda-graph-scope", nargs="*", default=[],
                    help="layer kinds captured as CUDA graphs: mamba attn mlp (moe_router / moe_preprocess are accepted and ignored)")
@@ -292,6 +297,8 @@ def configs_from_namespace(ns: argparse.Namespace) -> Tuple[ModelConfig, Paralle
                        recompute=ns.recompute_granularity or "none", seed=ns.seed, log_interval=ns.log_interval,
                        check_finite=not ns.no_check_for_nan_in_loss_and_grad,
                        precision_recipe=ns.fp8_recipe or "bf16", precision_modules=tuple(ns.fp8_modules),
+                       fp8_activations=ns.fp8_activations, fp8_activations_bf16_first=ns.fp8_activations_bf16_first,
+                       fp8_activations_bf16_last=ns.fp8_activations_bf16_last, fp8_activations_clamp=ns.fp8_activations_clamp,
                        optimizer=ocfg, lr_schedule=sched,
                        pipeline_schedule=ns.pipeline_schedule, cuda_graph_scope=tuple(ns.cuda_graph_scope))
     extras = {k: getattr(ns, k) for k in ("train_iters", "data_path", "mock_data", "save", "load", "save_interval",
@@ -415,6 +422,12 @@ def render_args(mcfg: ModelConfig, pcfg: ParallelConfig, tcfg: TrainConfig, *, t
         kv("--fp8-recipe", tcfg.precision_recipe)
         if tcfg.precision_modules:
             a.extend(["--fp8-modules", *tcfg.precision_modules])
+    if tcfg.fp8_activations != "off":
+        kv("--fp8-activations", tcfg.fp8_activations)
+        kv("--fp8-activations-bf16-first", tcfg.fp8_activations_bf16_first)
+        kv("--fp8-activations-bf16-last", tcfg.fp8_activations_bf16_last)
+        if tcfg.fp8_activations_clamp:
+            a.append("--fp8-activations-clamp")
     if tcfg.recompute != "none":
         kv("--recompute-granularity", tcfg.recompute)
     if tcfg.cuda_graph_scope:

@@ -41,6 +41,10 @@ class TrainConfig:
     precision_recipe: str = "bf16"               # bf16 | mxfp8 (E8M0 1x32 block scales) | tensorwise (one scale per tensor)
     precision_modules: tuple = ()                # glob patterns of module names that run under precision_recipe; the rest
                                                  # stays bf16.  Empty: every eligible linear.  Shorthands: "moe", "mamba_proj"
+    fp8_activations: str = "off"                 # off | mxfp8 | tensor: FP8-compress the activations saved for backward
+    fp8_activations_bf16_first: int = 1          # layers at the start / end of the stack whose saved tensors stay bf16
+    fp8_activations_bf16_last: int = 1
+    fp8_activations_clamp: bool = False          # "tensor" recipe: limit the measured maximum to the E4M3 range
     cuda_graph_scope: tuple = ()                 # subset of ("mamba", "attn", "mlp"): layers captured as CUDA graphs
     optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
     lr_schedule: Optional[LRSchedule] = None
@@ -107,6 +111,11 @@ class Trainer:
         # so the reduction cannot start from inside backward
         from ..ops import functional as F_
         self.precision_modules = _install_precision(self.model, train_cfg)
+        if train_cfg.fp8_activations not in ("off", "", None):
+            act = {"recipe": train_cfg.fp8_activations, "bf16_first": train_cfg.fp8_activations_bf16_first,
+                   "bf16_last": train_cfg.fp8_activations_bf16_last, "clamp": train_cfg.fp8_activations_clamp}
+            for m in (self.model.chunks if self.chunked else [self.model]):
+                m.fp8_activations = act
         self.fused = {"optimizer": False, "moe": False}
         opt_cls = DistributedOptimizer
         if device.type == "cuda" and self.pc.world_size > 1 and train_cfg.optimizer.optimizer == "adamw":
@@ -157,11 +166,15 @@ class Trainer:
             rows = self.cfg.micro_batch_size * (self.cfg.seq_length // pc.tp)
             self._tp_bufs = fused_tp.install(pc, self.device, rows, width)
             self.fused["tp"] = self._tp_bufs is not None
-        if pc.ep > 1 and pc.tp == 1 and self.cfg.torch_dtype() == torch.bfloat16:
+        if pc.ep > 1 and self.cfg.torch_dtype() == torch.bfloat16:
             from ..parallel import fused_moe
+            # under sequence parallelism every TP rank routes its own sequence shard through the experts of its EP group;
+            # the shared expert's TP GEMMs then stay on the main stream (one TP transfer in flight at a time)
+            seq_local = self.cfg.seq_length // pc.tp if pc.sequence_parallel else self.cfg.seq_length
             bufs = fused_moe.attach(self.model, pc, self.device,
-                                    tokens_per_rank=self.cfg.micro_batch_size * self.cfg.seq_length,
-                                    per_layer=self.cfg.recompute != "full" or self.cfg.recompute_keep_last > 0)
+                                    tokens_per_rank=self.cfg.micro_batch_size * seq_local,
+                                    per_layer=self.cfg.recompute != "full" or self.cfg.recompute_keep_last > 0,
+                                    overlap_shared_expert=pc.tp == 1)
             self.fused["moe"] = bufs is not None
             self._moe_bufs = bufs
 
@@ -217,7 +230,7 @@ class Trainer:
         mbs = batch if isinstance(batch, list) else self._split(batch)
         self.optimizer.zero_grad()
         res = self.forward_backward(mbs)
-        if self._sp_params and self.pc.sequence_parallel:
+        if self._sp_params and self.pc.sequence_parallel and not getattr(self.optimizer, "handles_sequence_parallel_grads", False):
             self.optimizer.finish_grad_sync()      # sums commute: TP all-reduce after the DP reduction
             allreduce_sequence_parallel_grads_main(self._sp_params, self.pc)
         lr = self.lr_schedule(self.step)

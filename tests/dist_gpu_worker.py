@@ -25,12 +25,16 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     tp_mode = mode.startswith("tp_")
+    tpdp_mode = mode.startswith("tpdp_")                # TP 2 x DP (world / 2), EP = DP
     pp_mode = mode in ("pp", "pp_vpp2", "dualpipev", "single4")
-    seq = 256 if tp_mode else 128                      # fused TP wants (seq / tp) % 128 == 0
+    seq = 256 if (tp_mode or tpdp_mode) else 128                      # fused TP wants (seq / tp) % 128 == 0
     schedule = {"pp_vpp2": "interleaved", "dualpipev": "dualpipev"}.get(mode, "1f1b")
     n_mb = 4 if pp_mode else world
     if tp_mode:
         pc = pstate.initialize(ParallelConfig(tp=world, sequence_parallel=True, fused_collectives=(mode == "tp_fused")))
+    elif tpdp_mode:
+        pc = pstate.initialize(ParallelConfig(tp=2, ep=world // 2, sequence_parallel=True,
+                                              fused_collectives=(mode == "tpdp_fused")))
     elif pp_mode:
         cfgs = {"pp": ParallelConfig(pp=world), "pp_vpp2": ParallelConfig(pp=world, vpp=2), "dualpipev": ParallelConfig(pp=world),
                 "single4": ParallelConfig()}
