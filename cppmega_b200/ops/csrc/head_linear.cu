@@ -107,23 +107,28 @@ __global__ void __launch_bounds__(THREADS, 2) head_linear_kernel(const __grid_co
     const int s = h & 1;
     // the next head's product runs while this head's rows are converted and stored
     if (tid == 0 && h + 1 < a.H && !*abort_flag) issue_mma(h + 1);
-    ok = mbar_wait(&sh->done[s], (h >> 1) & 1, abort_flag, a.err, ERR_WAIT_TMEM_FULL);
+    ok = __syncthreads_and(mbar_wait(&sh->done[s], (h >> 1) & 1, abort_flag, a.err, ERR_WAIT_TMEM_FULL));   // uniform: the reads below are warp-wide
     tc_fence_after();
-    if (ok && t0 + tid < a.T) {
-      __nv_bfloat16* yrow = a.y + (size_t)(t0 + tid) * a.y_tok + (size_t)h * a.y_head;
+    if (ok) {
+      // The TMEM read is a warp-wide (.sync.aligned) instruction: every lane takes part, also the lanes whose token is
+      // past the end of a partial last tile; only their stores are skipped.
+      const bool row_valid = t0 + tid < a.T;
+      __nv_bfloat16* yrow = a.y + (size_t)(row_valid ? t0 + tid : 0) * a.y_tok + (size_t)h * a.y_head;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(tmem + lane_addr + s * HD + c * 32, r);
         tmem_ld_wait();
+        if (row_valid) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 o;
-          o.x = pack_bf16(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
-          o.y = pack_bf16(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
-          o.z = pack_bf16(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
-          o.w = pack_bf16(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
-          reinterpret_cast<uint4*>(yrow)[c * 4 + q] = o;
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
+            o.y = pack_bf16(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
+            o.z = pack_bf16(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
+            o.w = pack_bf16(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
+            reinterpret_cast<uint4*>(yrow)[c * 4 + q] = o;
+          }
         }
       }
     }
@@ -202,9 +207,12 @@ __global__ void __launch_bounds__(THREADS, 1) head_linear_wgrad_kernel(const __g
       }
     }
   }
-  // everyone waits for the last product (the commit of the last tile covers all earlier ones)
+  // Everyone waits for the last product (the commit of the last tile covers all earlier ones).  A parity wait only tells
+  // the two most recent phases apart, so the other threads may look at the barrier only after thread 0 has consumed all
+  // earlier phases of it, i.e. after its loop.
+  __syncthreads();
   const int last = n_tiles - 1;
-  const bool ok = mbar_wait(&sh->done[last & 1], (last >> 1) & 1, abort_flag, a.err, ERR_WAIT_TMEM_FULL);
+  const bool ok = __syncthreads_and(mbar_wait(&sh->done[last & 1], (last >> 1) & 1, abort_flag, a.err, ERR_WAIT_TMEM_FULL));
   tc_fence_after();
   if (ok) {
     // TMEM lane = output feature (0..63: head 2hp, 64..127: head 2hp+1); columns = input features of the two heads

@@ -304,9 +304,20 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const long long*
 
 using namespace cm;
 
+// Blocks (of 256 threads) per SM that one row-transport launch may occupy.  8 fills every thread slot of the SM: fastest
+// alone, but a GEMM CTA launched on another stream then cannot become resident until the transfer drains.  The pipelined
+// MoE path lowers it so that transfers and expert GEMMs really share the SMs.
+static int g_transport_blocks_per_sm = 8;
+
+extern "C" int cm_moe_set_transport_blocks_per_sm(int n) {
+  const int old = g_transport_blocks_per_sm;
+  if (n >= 1 && n <= 8) g_transport_blocks_per_sm = n;
+  return old;
+}
+
 static int grid_for(long long warps_needed) {
   long long blocks = (warps_needed + 7) / 8;
-  long long cap = (long long)sm_count() * 8;
+  long long cap = (long long)sm_count() * g_transport_blocks_per_sm;
   return (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
 }
 

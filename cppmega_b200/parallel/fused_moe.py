@@ -15,6 +15,12 @@ Backward mirrors it: weighted output gradients are pushed to the owners, the gro
 kernels run there, input gradients are pulled back and summed over k; the routing-weight gradient
 is a row-dot against the owners' saved outputs.
 
+With EP > 1 and enough tokens the call is split into two token chunks with their own plans, buffer halves and
+flags: a second ("transport") stream carries plan + push of chunk 1 while the expert GEMMs of chunk 0 run, and the
+combine of chunk 0 while the GEMMs of chunk 1 run (backward likewise), so about half of the NVLink time sits under
+tensor-core work.  Cross-GPU order is carried by the flags (signalled on the stream that produced the data, awaited
+with a bounded wait on the stream that consumes it), same-GPU order between the two streams by events.
+
 Symmetric buffers: per layer an input and an output row buffer (they must survive until that
 layer's backward), plus two buffers shared by all layers for the backward traffic.  Capacity is
 ``capacity_factor`` times the mean load (the worst case, ``ep`` times, when the buffers are shared by all
@@ -34,7 +40,10 @@ from .symm_mem import SymmetricHeap
 
 TILE = 128
 FLAG_BASE = 16
-FLAGS_PER_LAYER = 5          # dispatch, expert outputs, grad dispatch, grad outputs, count exchange
+FLAGS_PER_CHUNK = 5          # dispatch, expert outputs, grad dispatch, grad outputs, count exchange
+MAX_CHUNKS = 2               # token chunks per call whose transfers and expert GEMMs overlap (two streams)
+FLAGS_PER_LAYER = FLAGS_PER_CHUNK * MAX_CHUNKS
+MIN_CHUNK_COPIES = 8192      # below this many routed copies per chunk the pipeline is not worth its launches
 
 
 def _lib():
@@ -166,10 +175,10 @@ class FusedMoEBuffers:
             capacity_factor = 2.0 if per_layer else float(pc.ep)
         capacity_factor = min(float(capacity_factor), float(pc.ep))
         self.capacity_factor = capacity_factor
-        pad_rows = max(16, num_local_experts) * TILE          # every local expert segment may end in a partial tile
-        self.capacity = int((mean_rows * capacity_factor + pad_rows + TILE - 1) // TILE * TILE)
+        pad_rows = MAX_CHUNKS * max(16, num_local_experts) * TILE      # every local expert segment of every chunk may end in a partial tile
+        self.capacity = int((mean_rows * capacity_factor + pad_rows + MAX_CHUNKS * TILE - 1) // (MAX_CHUNKS * TILE) * (MAX_CHUNKS * TILE))
         n_bufs = (2 * num_layers if per_layer else 2) + 2
-        nbytes = n_bufs * (self.capacity * hidden * 2 + 4096) + num_layers * 4096 * 2
+        nbytes = n_bufs * (self.capacity * hidden * 2 + 4096) + num_layers * 4096 * 2 * MAX_CHUNKS
         self.heap = SymmetricHeap(pc.ep_group, pc.ep_ranks, nbytes, device)
         self.per_layer = per_layer
         self.layer_bufs: List = []
@@ -180,18 +189,31 @@ class FusedMoEBuffers:
         self.grad_in_ = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
         self.grad_out_ = self.heap.alloc((self.capacity, hidden), torch.bfloat16)
         self.num_layers = num_layers
-        self.count_bufs = {}                  # (layer slot, expert count) -> [ep, E] int64 exchange buffer
+        self.count_bufs = {}                  # (layer slot, chunk, expert count) -> [ep, E] int64 exchange buffer
         self.epoch = 0
+        self.chunks = MAX_CHUNKS              # 1: everything on the calling stream, one plan per call
+        self._comm = None
         _ = El
 
-    def gather_counts(self, layer_slot: int, epoch: int, counts: torch.Tensor) -> torch.Tensor:
+    def chunks_for(self, tokens: int, topk: int) -> int:
+        n = max(1, min(int(self.chunks), MAX_CHUNKS))
+        while n > 1 and (tokens % n or (tokens // n) * topk < MIN_CHUNK_COPIES):
+            n -= 1
+        return n
+
+    def comm_stream(self):
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(device=self.heap.device)
+        return self._comm
+
+    def gather_counts(self, layer_slot: int, chunk: int, epoch: int, counts: torch.Tensor) -> torch.Tensor:
         """[E] per-expert copy counts of this rank -> [ep, E] of all ranks, through peer stores and one flag barrier
-        (flag 4 of the layer's group of five) instead of a library all-gather."""
-        key = (layer_slot, counts.numel())
+        (flag 4 of the chunk's group of five) instead of a library all-gather."""
+        key = (layer_slot, chunk, counts.numel())
         buf = self.count_bufs.get(key)
         if buf is None:
             buf = self.count_bufs[key] = self.heap.alloc((self.heap.world, counts.numel()), torch.int64)
-        return self.heap.all_gather_words(counts.to(torch.int64).contiguous(), buf, FLAG_BASE + FLAGS_PER_LAYER * layer_slot + 4, epoch)
+        return self.heap.all_gather_words(counts.to(torch.int64).contiguous(), buf, _flag0(layer_slot, chunk) + 4, epoch)
 
     def capacity_for(self, ncopies: int) -> int:
         return self.capacity
@@ -207,10 +229,32 @@ class FusedMoEBuffers:
         return self.epoch
 
 
+def set_transport_blocks_per_sm(n: int) -> int:
+    """Blocks of 256 threads per SM that a push / pull launch may take (1..8); returns the previous value.  8 is fastest
+    for a transfer that runs alone; the two-stream pipeline wants fewer, so that a transfer leaves room on every SM for
+    the expert GEMM CTA of the other chunk."""
+    L = _lib()
+    L.cm_moe_set_transport_blocks_per_sm.argtypes = [ctypes.c_int]
+    L.cm_moe_set_transport_blocks_per_sm.restype = ctypes.c_int
+    return int(L.cm_moe_set_transport_blocks_per_sm(int(n)))
+
+
+def _flag0(layer_slot: int, chunk: int) -> int:
+    return FLAG_BASE + FLAGS_PER_LAYER * layer_slot + FLAGS_PER_CHUNK * chunk
+
+
 class _LocalHeap:
     """Stand-in for the symmetric heap when all experts live on this GPU: one "peer", no flags."""
 
     world = 1
+
+    @staticmethod
+    def signal(*_args) -> None:
+        return None
+
+    @staticmethod
+    def wait(*_args) -> None:
+        return None
 
     @staticmethod
     def peer_ptr_array(t: torch.Tensor):
@@ -233,6 +277,12 @@ class LocalMoEBuffers:
 
     def capacity_for(self, ncopies: int) -> int:
         return (ncopies + self.num_experts * (TILE - 1) + TILE - 1) // TILE * TILE
+
+    def chunks_for(self, tokens: int, topk: int) -> int:
+        return 1
+
+    def comm_stream(self):
+        return torch.cuda.current_stream()
 
     def _row_buf(self, cap: int):
         return torch.empty(cap, self.hidden, dtype=torch.bfloat16, device=self.device)
@@ -259,9 +309,10 @@ def _push(heap: SymmetricHeap, src, plan: MoEPlan, dst_buf, scale=None):
     F_.count_launch("moe_push_rows")
 
 
-def _pull_combine(heap: SymmetricHeap, src_buf, plan: MoEPlan, weights, H, dtype):
+def _pull_combine(heap: SymmetricHeap, src_buf, plan: MoEPlan, weights, H, dtype, out=None):
     from ..ops.cuda import err_word, stream_ptr
-    out = torch.empty(plan.T, H, dtype=dtype, device=src_buf.device)
+    if out is None:
+        out = torch.empty(plan.T, H, dtype=dtype, device=src_buf.device)
     rc = _lib().cm_moe_pull_combine(heap.peer_ptr_array(src_buf), heap.world, plan.dest_rank.data_ptr(),
                                     plan.dest_row.data_ptr(), None if weights is None else weights.data_ptr(),
                                     out.data_ptr(), plan.T, plan.k, H, src_buf.shape[0],
@@ -272,9 +323,10 @@ def _pull_combine(heap: SymmetricHeap, src_buf, plan: MoEPlan, weights, H, dtype
     return out
 
 
-def _pull_rowdot(heap: SymmetricHeap, src_buf, plan: MoEPlan, dy):
+def _pull_rowdot(heap: SymmetricHeap, src_buf, plan: MoEPlan, dy, out=None):
     from ..ops.cuda import err_word, stream_ptr
-    out = torch.empty(plan.T, plan.k, dtype=torch.float32, device=dy.device)
+    if out is None:
+        out = torch.empty(plan.T, plan.k, dtype=torch.float32, device=dy.device)
     rc = _lib().cm_moe_pull_rowdot(heap.peer_ptr_array(src_buf), heap.world, plan.dest_rank.data_ptr(),
                                    plan.dest_row.data_ptr(), dy.data_ptr(), out.data_ptr(), plan.T, plan.k, dy.shape[1],
                                    src_buf.shape[0], err_word(dy.device).data_ptr(), stream_ptr())
@@ -370,36 +422,87 @@ def _experts_bwd_mx(grad_in, h, xin, w1, w2, plan, grad_out, tensorwise: bool):
     return dw1, dw2
 
 
+class _ChunkState:
+    """What one token chunk of a call keeps between its pipeline stages and for the backward pass."""
+    __slots__ = ("index", "tok", "f0", "plan", "xin", "yout", "h", "event")
+
+
 class _FusedMoEFn(torch.autograd.Function):
+    """Stages per chunk c (T = transport stream, M = the calling stream):
+
+        forward    T: plan, push rows, signal DISPATCH[c]      M: wait DISPATCH[c], fc1 / SwiGLU / fc2, signal OUT[c]
+                   T: wait OUT[c], pull + combine into y[c]
+        backward   T: row-dot of dy with the owners' outputs (d probs), push weighted dy, signal GDISPATCH[c]
+                   M: wait GDISPATCH[c], expert dgrad / wgrad, signal GOUT[c]      T: wait GOUT[c], pull + sum into dx[c]
+
+    All T stages of a call are queued in chunk order, so T works on chunk c+1 while M works on chunk c.  Every T section
+    starts by waiting for an event of M, hence later transport work can never overtake earlier work of the calling
+    stream on a tensor both touch; M waits for T's last stage before the call returns."""
+
+    @staticmethod
+    def _chunks(bufs, layer_slot, ids, cap_total, n):
+        T = ids.shape[0]
+        Tc = T // n
+        cap_c = (cap_total // n) // TILE * TILE
+        xin_all, yout_all = bufs.bufs(layer_slot, cap_total)
+        out = []
+        for c in range(n):
+            ch = _ChunkState()
+            ch.index, ch.tok, ch.f0 = c, slice(c * Tc, (c + 1) * Tc), _flag0(layer_slot, c)
+            ch.xin, ch.yout = xin_all[c * cap_c:(c + 1) * cap_c], yout_all[c * cap_c:(c + 1) * cap_c]
+            ch.plan = ch.h = ch.event = None
+            out.append(ch)
+        return out, cap_c, xin_all, yout_all
+
     @staticmethod
     def forward(ctx, x, probs, w1, w2, ids, bufs: FusedMoEBuffers, layer_slot: int):
         from ..ops.cuda import swiglu
         pc, heap = bufs.pc, bufs.heap
-        cap = bufs.capacity_for(ids.numel())
-        H = x.shape[1]
+        T, H = x.shape
+        cap_total = bufs.capacity_for(ids.numel())
+        n = bufs.chunks_for(T, ids.shape[1])
         ep0 = bufs.next_epoch()
-        gather = (lambda c: bufs.gather_counts(layer_slot, ep0, c)) if hasattr(bufs, "gather_counts") else None
-        plan = MoEPlan(ids, w1.shape[0] * pc.ep, pc.ep, pc.ep_rank, pc.ep_group, cap, gather)
-        xin, yout = bufs.bufs(layer_slot, cap)
-        f0 = FLAG_BASE + FLAGS_PER_LAYER * layer_slot
+        chunks, cap_c, xin_all, yout_all = _FusedMoEFn._chunks(bufs, layer_slot, ids, cap_total, n)
         x = x.contiguous()
-        _push(heap, x, plan, xin)
-        heap.barrier(f0 + 0, ep0)
-        _zero_pad(xin, plan, cap)
-        with torch.no_grad():
-            fp8 = _fp8_mode(w1, w2)
-            if fp8 is not None:
-                h = _experts_fwd_mx(xin, w1, w2, plan.tile_expert, yout, fp8 == "tensorwise")
-            else:
-                h = _grouped(xin, w1, plan.tile_expert, cap, False)
-                a = swiglu(h)
-                _grouped(a, w2, plan.tile_expert, cap, False, out=yout)
-        heap.barrier(f0 + 1, ep0)
         p32 = probs.float().contiguous()
-        y = _pull_combine(heap, yout, plan, p32.reshape(-1), H, x.dtype)
+        y = torch.empty(T, H, dtype=x.dtype, device=x.device)
+        fp8 = _fp8_mode(w1, w2)
+        main = torch.cuda.current_stream()
+        comm = bufs.comm_stream() if n > 1 else main
+        has_gather = hasattr(bufs, "gather_counts")
+        comm.wait_event(main.record_event())
+        with torch.cuda.stream(comm):
+            for ch in chunks:
+                gather = (lambda cnt, c=ch.index: bufs.gather_counts(layer_slot, c, ep0, cnt)) if has_gather else None
+                ch.plan = MoEPlan(ids[ch.tok], w1.shape[0] * pc.ep, pc.ep, pc.ep_rank, pc.ep_group, cap_c, gather)
+                _push(heap, x[ch.tok], ch.plan, ch.xin)
+                heap.signal(ch.f0 + 0, ep0)
+                ch.event = comm.record_event()
+        for ch in chunks:
+            main.wait_event(ch.event)
+            heap.wait(ch.f0 + 0, ep0)                      # every rank's rows of this chunk have landed here
+            _zero_pad(ch.xin, ch.plan, cap_c)
+            with torch.no_grad():
+                if fp8 is not None:
+                    ch.h = _experts_fwd_mx(ch.xin, w1, w2, ch.plan.tile_expert, ch.yout, fp8 == "tensorwise")
+                else:
+                    ch.h = _grouped(ch.xin, w1, ch.plan.tile_expert, cap_c, False)
+                    a = swiglu(ch.h)
+                    _grouped(a, w2, ch.plan.tile_expert, cap_c, False, out=ch.yout)
+            heap.signal(ch.f0 + 1, ep0)
+            ch.event = main.record_event()
+        with torch.cuda.stream(comm):
+            for ch in chunks:
+                comm.wait_event(ch.event)
+                heap.wait(ch.f0 + 1, ep0)                  # every owner's outputs of this chunk are complete
+                _pull_combine(heap, ch.yout, ch.plan, p32[ch.tok].reshape(-1), H, x.dtype, out=y[ch.tok])
+            done = comm.record_event()
+        main.wait_event(done)
         # xin / yout go through save_for_backward as well: activation checkpointing only drops what it sees there
-        ctx.save_for_backward(h, w1, w2, p32, xin, yout)
-        ctx.plan, ctx.bufs, ctx.slot, ctx.cap = plan, bufs, layer_slot, cap
+        ctx.save_for_backward(w1, w2, p32, xin_all, yout_all, *[ch.h for ch in chunks])
+        for ch in chunks:
+            ch.h = ch.event = None
+        ctx.chunks, ctx.bufs, ctx.slot, ctx.cap_c, ctx.cap_total = chunks, bufs, layer_slot, cap_c, cap_total
         ctx.x_dtype, ctx.p_dtype = x.dtype, probs.dtype
         ctx.fp8 = fp8                              # the backward runs under the recipe of its forward, whatever is set then
         return y
@@ -407,39 +510,61 @@ class _FusedMoEFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         from ..ops.cuda import lib, stream_ptr, _check
-        h, w1, w2, p32, xin, yout = ctx.saved_tensors
-        plan, bufs = ctx.plan, ctx.bufs
-        pc, heap, cap = bufs.pc, bufs.heap, ctx.cap
-        grad_in, grad_out = bufs.grad_bufs(cap)
-        H = dy.shape[1]
+        from ..ops.cuda import swiglu as _sw
+        w1, w2, p32, xin_all, yout_all, *hs = ctx.saved_tensors
+        chunks, bufs, cap_c = ctx.chunks, ctx.bufs, ctx.cap_c
+        heap = bufs.heap
+        n = len(chunks)
+        grad_in_all, grad_out_all = bufs.grad_bufs(ctx.cap_total)
+        T, H = dy.shape
         dy = dy.contiguous()
         epb = bufs.next_epoch()
-        f0 = FLAG_BASE + FLAGS_PER_LAYER * ctx.slot
-        dprobs = _pull_rowdot(heap, yout, plan, dy)
-        _push(heap, dy, plan, grad_in, scale=p32.reshape(-1))
-        heap.barrier(f0 + 2, epb)
-        _zero_pad(grad_in, plan, cap)      # padding rows feed the wgrad products: 0 * stale NaN would poison them
-        E = w1.shape[0]
-        Fh = w2.shape[2]
-        # recompute a = swiglu(h); expert backward on the padded layout
-        from ..ops.cuda import swiglu as _sw
-        if ctx.fp8 is not None:
+        E, Fh = w1.shape[0], w2.shape[2]
+        dprobs = torch.empty(T, p32.shape[1], dtype=torch.float32, device=dy.device)
+        dx = torch.empty(T, H, dtype=ctx.x_dtype, device=dy.device)
+        main = torch.cuda.current_stream()
+        comm = bufs.comm_stream() if n > 1 else main
+        gin = [grad_in_all[c * cap_c:(c + 1) * cap_c] for c in range(n)]
+        gout = [grad_out_all[c * cap_c:(c + 1) * cap_c] for c in range(n)]
+        events = [None] * n
+        comm.wait_event(main.record_event())
+        with torch.cuda.stream(comm):
+            for ch in chunks:
+                c = ch.index
+                _pull_rowdot(heap, ch.yout, ch.plan, dy[ch.tok], out=dprobs[ch.tok])
+                _push(heap, dy[ch.tok], ch.plan, gin[c], scale=p32[ch.tok].reshape(-1))
+                heap.signal(ch.f0 + 2, epb)
+                events[c] = comm.record_event()
+        dw1 = dw2 = None
+        for ch in chunks:
+            c, plan, h, xin = ch.index, ch.plan, hs[ch.index], ch.xin
+            main.wait_event(events[c])
+            heap.wait(ch.f0 + 2, epb)
+            _zero_pad(gin[c], plan, cap_c)      # padding rows feed the wgrad products: 0 * stale NaN would poison them
             with torch.no_grad():
-                dw1, dw2 = _experts_bwd_mx(grad_in, h, xin, w1, w2, plan, grad_out, ctx.fp8 == "tensorwise")
-            heap.barrier(f0 + 3, epb)
-            dx = _pull_combine(heap, grad_out, plan, None, H, ctx.x_dtype)
-            return dx, dprobs.to(ctx.p_dtype), dw1, dw2, None, None, None
-        with torch.no_grad():
-            a = _sw(h)
-            da = _grouped(grad_in, w2, plan.tile_expert, cap, True)                  # [cap, F]
-            dw2 = _grouped_wgrad(grad_in, a, plan.seg_offsets, E, w2)                   # [E, H, F]
-            dh = torch.empty_like(h)
-            _check(lib().cm_swiglu_bwd(h.data_ptr(), da.data_ptr(), dh.data_ptr(), cap, Fh, stream_ptr()), "cm_swiglu_bwd")
-            F_.count_launch("swiglu_bwd")
-            _grouped(dh, w1, plan.tile_expert, cap, True, out=grad_out)               # [cap, H]
-            dw1 = _grouped_wgrad(dh, xin, plan.seg_offsets, E, w1)                        # [E, 2F, H]
-        heap.barrier(f0 + 3, epb)
-        dx = _pull_combine(heap, grad_out, plan, None, H, ctx.x_dtype)
+                if ctx.fp8 is not None:
+                    g1, g2 = _experts_bwd_mx(gin[c], h, xin, w1, w2, plan, gout[c], ctx.fp8 == "tensorwise")
+                else:
+                    a = _sw(h)                                                       # recompute a = swiglu(h)
+                    da = _grouped(gin[c], w2, plan.tile_expert, cap_c, True)         # [cap, F]
+                    g2 = _grouped_wgrad(gin[c], a, plan.seg_offsets, E, w2)          # [E, H, F]
+                    dh = torch.empty_like(h)
+                    _check(lib().cm_swiglu_bwd(h.data_ptr(), da.data_ptr(), dh.data_ptr(), cap_c, Fh, stream_ptr()), "cm_swiglu_bwd")
+                    F_.count_launch("swiglu_bwd")
+                    _grouped(dh, w1, plan.tile_expert, cap_c, True, out=gout[c])     # [cap, H]
+                    g1 = _grouped_wgrad(dh, xin, plan.seg_offsets, E, w1)            # [E, 2F, H]
+            fused_acc = getattr(w1, "grad_added_to_main_grad", False)                # the GEMM epilogue accumulated in place
+            dw1 = g1 if (dw1 is None or fused_acc) else dw1 + g1
+            dw2 = g2 if (dw2 is None or getattr(w2, "grad_added_to_main_grad", False)) else dw2 + g2
+            heap.signal(ch.f0 + 3, epb)
+            events[c] = main.record_event()
+        with torch.cuda.stream(comm):
+            for ch in chunks:
+                comm.wait_event(events[ch.index])
+                heap.wait(ch.f0 + 3, epb)
+                _pull_combine(heap, gout[ch.index], ch.plan, None, H, ctx.x_dtype, out=dx[ch.tok])
+            done = comm.record_event()
+        main.wait_event(done)
         return dx, dprobs.to(ctx.p_dtype), dw1, dw2, None, None, None
 
 

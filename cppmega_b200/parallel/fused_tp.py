@@ -1,8 +1,9 @@
 """Tensor-parallel linears with the sequence-parallel collectives fused into the GEMMs, over peer memory.
 
-Two implementations of each, selected by ``FusedTP.mode``:
+Two implementations of each, selected by ``FusedTP.mode`` (``"auto"``, the default, takes the staged all-gather and the
+direct reduce-scatter, the faster form of each in ``tools/tp_bench.py``):
 
-``"staged"`` (default) - every activation shard crosses NVLink exactly once.
+``"staged"`` - every activation shard crosses NVLink exactly once.
 
 * ``ag_gemm``  (column-parallel forward, row-parallel dgrad):  ``y = gather_seq(x) . op(W)``.  On a second stream a copy
   kernel stores this rank's shard into slot ``me`` of every peer's gathered buffer and raises one flag per source;
@@ -71,8 +72,18 @@ class FusedTP:
         # stream, one flag per source) and the GEMMs read local memory, starting with this rank's own shard.
         # "direct": the GEMM's TMA loads read the peers' memory tile by tile (each remote tile crosses the link once
         # per column of output tiles that needs it); kept for comparison.
-        self.mode = "staged"
+        self.mode = "auto"
         self._copy_stream = None
+
+    def _mode(self, kind: str) -> str:
+        """``kind``: "ag" (all-gather -> GEMM and the gathered weight gradients) or "rs" (GEMM -> reduce-scatter).
+        "auto" takes the faster form of each, measured at TP 2 on the NAM56R projections: the staged all-gather
+        (0.71 of the roofline against 0.10 for remote tile reads, which cross NVLink once per output-tile column), and
+        the one-launch GEMM whose epilogue scatters to the owners (its per-shard form pays a wave of tail tiles per
+        launch: 0.38 against 0.54)."""
+        if self.mode == "auto":
+            return "staged" if kind == "ag" else "direct"
+        return self.mode
 
     def supported(self, batch: int, rows_per_seg: int, width_in: int, width_out: int) -> bool:
         return (rows_per_seg % 128 == 0 and batch * rows_per_seg * max(width_in, width_out) <= self.max_elems
@@ -204,7 +215,7 @@ class FusedTP:
     def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool, keep_staged: bool = False) -> torch.Tensor:
         """x_local [B, S/tp, K] bf16 -> [B, S, N];  w is [N, K] (b_mn False) or [K, N] (b_mn True)."""
         from ..ops.cuda import err_word, stream_ptr
-        if self.mode == "staged":
+        if self._mode("ag") == "staged":
             out, self._last_gathered = self._ag_gemm_staged(x_local, w, b_mn, keep_staged)
             return out
         B, Sl, K = x_local.shape
@@ -243,7 +254,7 @@ class FusedTP:
     def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
         """x [B, S, K] bf16 (K = this rank's slice of the reduction) -> [B, S/tp, N] summed over the TP group."""
         from ..ops.cuda import err_word, stream_ptr
-        if self.mode == "staged":
+        if self._mode("rs") == "staged":
             return self._gemm_rs_staged(x if x.is_contiguous() else x.contiguous(), w, b_mn)
         B, S, K = x.shape
         Sl = S // self.tp
@@ -313,7 +324,7 @@ class ColumnLinearSPFn(torch.autograd.Function):
             dx = tp.gemm_rs(dy, w, b_mn=True)                                   # [B,S,N_l] . W[N_l,K] -> scatter
         if ctx.needs_input_grad[1]:
             dy2 = dy.reshape(-1, dy.shape[-1])                                   # [T, N_l]: the local operand A
-            if tp.mode == "staged":
+            if tp._mode("ag") == "staged":
                 gathered = tp.push_shard(x_local)                                # gather(x) again: operand B, from local slots
                 dw = wgrad_into_main_grad(w, lambda out, acc: tp._wgrad_staged(gathered, x_local.shape[0], dy2, False, out, acc,
                                                                                tuple(w.shape)))
@@ -343,7 +354,7 @@ class RowLinearSPFn(torch.autograd.Function):
         dx = dw = None
         need_dw = ctx.needs_input_grad[1]
         staged = None
-        if tp.mode == "staged":
+        if tp._mode("ag") == "staged":
             gathered = None
             if ctx.needs_input_grad[0]:
                 dx = tp.ag_gemm(dy_local, w, b_mn=True, keep_staged=need_dw)    # gather(dy)[B,S,N] . W[N,K_l]

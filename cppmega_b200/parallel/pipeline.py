@@ -302,9 +302,10 @@ def schedule_actions(schedule: str, pp: int, vpp: int, num_microbatches: int):
 def run_chunked_schedule(trainer, microbatches: List[Dict[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
     """Execute one optimizer step of an interleaved or V-shaped schedule.
 
-    Every rank knows every rank's action list, hence the exact order in which each peer will send to it: all
-    receives are posted up front in that order (point-to-point channels are FIFO per pair), sends are posted as
-    results appear, and a chunk hand-over inside one rank (the turn of the V) is a plain tensor hand-off."""
+    Every rank knows every rank's action list, hence the exact order in which each peer will send to it: receives are
+    posted in that order (point-to-point channels are FIFO per pair) when their tensor is first needed, sends are posted
+    as results appear and not waited for until the step ends, and a chunk hand-over inside one rank (the turn of the V)
+    is a plain tensor hand-off."""
     pc: ParallelContext = trainer.pc
     model: ChunkedModel = trainer.model
     M = len(microbatches)
@@ -325,25 +326,39 @@ def run_chunked_schedule(trainer, microbatches: List[Dict[str, torch.Tensor]]) -
             return ("B", c, mb), owner(c - 1)
         return None
 
-    # receives, posted per source in the source's own order
-    recv_buf: Dict[tuple, torch.Tensor] = {}
-    recv_req: Dict[tuple, object] = {}
+    # Expected messages per source, in the source's own send order (a channel is FIFO).  A receive is posted when its
+    # tensor is first needed, together with any earlier message of the same channel that has not been posted yet.
+    # Posting everything up front is valid on a buffered transport, but an NCCL receive is a kernel that occupies its
+    # stream until the matching send arrives: receives queued ahead of this rank's own compute and sends in launch order
+    # can starve them (the interleaved and V-shaped schedules stopped that way on two GPUs).
+    expected: Dict[int, List[tuple]] = {}
+    channel_of: Dict[tuple, int] = {}
     for src in range(pc.pp):
         if src == me:
             continue
+        keys = []
         for action in per_rank[src]:
             msg = message_of(action)
-            if msg is None or msg[1] != me:
-                continue
-            buf = torch.empty(shape, dtype=dtype, device=dev)
-            recv_buf[msg[0]] = buf
-            recv_req[msg[0]] = dist.irecv(buf, src=pc.pp_ranks[src], group=pc.pp_directed.get((src, me)))
+            if msg is not None and msg[1] == me:
+                keys.append(msg[0])
+                channel_of[msg[0]] = src
+        expected[src] = keys
+    posted: Dict[int, int] = {src: 0 for src in expected}
+    recv_buf: Dict[tuple, torch.Tensor] = {}
+    recv_req: Dict[tuple, object] = {}
     handoff: Dict[tuple, torch.Tensor] = {}
     send_reqs = []
 
     def fetch(key):
         if key in handoff:
             return handoff.pop(key)
+        src = channel_of[key]
+        while key not in recv_req:
+            k = expected[src][posted[src]]
+            posted[src] += 1
+            buf = torch.empty(shape, dtype=dtype, device=dev)
+            recv_buf[k] = buf
+            recv_req[k] = dist.irecv(buf, src=pc.pp_ranks[src], group=pc.pp_directed.get((src, me)))
         recv_req.pop(key).wait()
         return recv_buf.pop(key)
 

@@ -220,10 +220,40 @@ def bench_scan_bar() -> List[dict]:
     dy = torch.randn_like(y)
     ms_b = time_ms(lambda: torch.autograd.grad(y, args, dy, retain_graph=True), iters=20, warmup=5)
     cu.check_errors()
-    return [{"kernel": "mimo_scan at the reference's published shape", "B": B, "S": S, "H": H, "G": G, "N": N, "P": P, "R": R,
-             "fwd_us": ms_f * 1e3, "bwd_us": ms_b * 1e3, "reference_tilelang_b200_fwd_us": 54.0,
-             "reference_tilelang_b200_bwd_us": 72.0 + 179.0,
-             "note": "includes the zero-padding of the state dimension 64 -> 128 and, in backward, the head->group reductions"}]
+    row = {"kernel": "mimo_scan at the reference's published shape", "B": B, "S": S, "H": H, "G": G, "N": N, "P": P, "R": R,
+           "fwd_us": ms_f * 1e3, "bwd_us": ms_b * 1e3, "reference_tilelang_b200_fwd_us": 54.0,
+           "reference_tilelang_b200_bwd_us": 72.0 + 179.0,
+           "note": "includes the zero-padding of the state dimension 64 -> 128 and, in backward, the head->group reductions"}
+    # At this size (128 chunks) the ~30 launches of a call cost more on the host than on the device: the same calls
+    # replayed from a CUDA graph, which is how the trainer runs launch-bound layers (TrainConfig.cuda_graph_scope).
+    try:
+        def capture(fn):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    fn()
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
+            return graph
+
+        def fwd_only():
+            with torch.no_grad():
+                kernels3.mimo_scan(*args, 4, 16)
+
+        def fwd_bwd():
+            torch.autograd.grad(kernels3.mimo_scan(*args, 4, 16), args, dy)
+
+        g_f, g_fb = capture(fwd_only), capture(fwd_bwd)
+        us_f = time_ms(g_f.replay, iters=20, warmup=5) * 1e3
+        us_fb = time_ms(g_fb.replay, iters=20, warmup=5) * 1e3
+        cu.check_errors()
+        row.update(graph_fwd_us=us_f, graph_fwd_bwd_us=us_fb, graph_bwd_us=us_fb - us_f)
+    except Exception as e:                                   # keep the eager numbers if the capture is refused
+        row["graph_error"] = f"{type(e).__name__}: {str(e)[:160]}"
+    return [row]
 
 
 CASES["scan_bar"] = bench_scan_bar

@@ -7,7 +7,8 @@ One MoE layer of the NAM56R recipe (hidden 4096, 16 experts top-4 + shared exper
 16384 tokens per rank.  The router weight is replaced by fixed logits: N(0,1) (near-uniform load) or N(0,1) + log of a
 Zipf(1.2) popularity (``--skew zipf``).  Timed on the device with CUDA events, max over ranks:
 
-* ``fused``  peer-memory dispatch / combine kernels around the grouped tcgen05 GEMMs (``parallel/fused_moe.py``);
+* ``fused``  peer-memory dispatch / combine kernels around the grouped tcgen05 GEMMs (``parallel/fused_moe.py``), two token
+             chunks pipelined over two streams (``fused_one_chunk_ms``: the same without the pipeline);
 * ``nccl``   the same layer through ``AllToAllDispatcher`` (NCCL all-to-all + permute) and the same grouped GEMMs.
 
 The roofline is the slower of the expert + shared GEMM FLOPs at the measured bf16 peak and the bytes that must cross
@@ -42,6 +43,7 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--capacity-factor", type=float, default=None)
+    ap.add_argument("--sweep-transport", action="store_true", help="also time the pipelined path with 8 / 4 / 2 / 1 transport blocks per SM")
     ap.add_argument("--no-overlap-shared", action="store_true", help="keep the shared expert on the main stream (default: second stream beside the routed path)")
     ns = ap.parse_args(argv)
     from cppmega_b200.config.model import nam56r_full
@@ -119,6 +121,19 @@ def main(argv=None) -> int:
     res["nccl_ms"] = timed() if world > 1 else None
     bufs = fused_moe.attach(_OneLayer(mcfg, layer), pc, dev, tokens_per_rank=T, capacity_factor=cap, overlap_shared_expert=overlap_shared)
     res["fused_ms"] = timed() if bufs is not None else None
+    if bufs is not None and world > 1:
+        res["chunks"] = bufs.chunks_for(T, topk)
+        res["transport_blocks_per_sm"] = fused_moe.set_transport_blocks_per_sm(8)
+        fused_moe.set_transport_blocks_per_sm(res["transport_blocks_per_sm"])
+        if ns.sweep_transport:
+            res["fused_ms_by_transport_blocks_per_sm"] = {}
+            for n in (8, 4, 2, 1):
+                fused_moe.set_transport_blocks_per_sm(n)
+                res["fused_ms_by_transport_blocks_per_sm"][str(n)] = timed()
+            fused_moe.set_transport_blocks_per_sm(res["transport_blocks_per_sm"])
+        bufs.chunks = 1                                   # the same kernels without the two-chunk / two-stream pipeline
+        fused_moe.set_transport_blocks_per_sm(8)
+        res["fused_one_chunk_ms"] = timed()
     Fe, Fs = mcfg.moe.expert_ffn, mcfg.moe.shared_expert_ffn
     flops = 3 * 2.0 * T * (topk * 3 * H * Fe + 3 * H * Fs)                 # fwd + dgrad + wgrad, SwiGLU = 3 matrices
     pk = peaks()

@@ -43,6 +43,8 @@ def main():
         ep = min(world, nam56r_tiny().moe.num_experts)
         pc = pstate.initialize(ParallelConfig(ep=ep, fused_collectives=(mode == "fused")))
     mcfg = nam56r_tiny(seq_length=seq)
+    from cppmega_b200.parallel import fused_moe  # noqa: E402
+    fused_moe.MIN_CHUNK_COPIES = 64              # the tiny model routes 512 copies per call: still take the two-chunk pipeline
     tcfg = TrainConfig(micro_batch_size=2, global_batch_size=2 * n_mb if pp_mode else None, seq_length=seq, dtype="bf16",
                        recompute=recompute, optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0), log_interval=0,
                        pipeline_schedule=schedule)
