@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for Nsight Compute captures of single kernels.
 
-    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,scan_fwd,scan_bwd,m2rnn,m2rnn_bwd,sparse_mla,indexer,ce,rmsnorm,rmsnorm_bwd,adamw,quantize,strided_copy,moe_local,mxfp8_gemm}
+    python -m cppmega_b200.tools.ncu_cases {gemm,gemm_wgrad,attention,head_linear,scan_fwd,scan_bwd,m2rnn,m2rnn_bwd,sparse_mla,indexer,ce,rmsnorm,rmsnorm_bwd,adamw,quantize,strided_copy,moe_local,mxfp8_gemm}
 
 Each case launches its kernel three times on inputs that exceed the 126 MB L2 but hold at most a few GB, so a
 ``--set full`` capture of one launch finishes in a minute or two:
@@ -236,7 +236,37 @@ def case_moe_local():
     pstate.destroy()
 
 
-CASES = {"gemm": case_gemm, "gemm_wgrad": lambda: case_gemm(True, True), "scan_fwd": case_scan_fwd,
+def case_attention():
+    """Dense causal MLA attention (qk 128, v 64) at the model's shape: batch 4, seq 4096, 32 heads; forward + backward."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops import functional as F_
+    B, S, H = 4, 4096, 32
+    q = (torch.randn(B, S, H, 128, device="cuda") * 0.5).bfloat16().requires_grad_()
+    k = (torch.randn(B, S, H, 128, device="cuda") * 0.5).bfloat16().requires_grad_()
+    v = torch.randn(B, S, H, 64, device="cuda").bfloat16().requires_grad_()
+    g = torch.randn(B, S, H, 64, device="cuda").bfloat16()
+    for _ in range(3):
+        F_.causal_attention(q, k, v, 128 ** -0.5).backward(g)
+    torch.cuda.synchronize()
+    cu.check_errors()
+    assert not F_.fallback_counts(), F_.fallback_counts()
+
+
+def case_head_linear():
+    """Per-head 64 x 64 maps of the absorbed sparse-attention path: 16,384 tokens x 32 heads, forward + backward."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops import functional as F_
+    x = torch.randn(4, 4096, 32, 64, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(32, 64, 64, device="cuda") * 0.1).bfloat16().requires_grad_()
+    g = torch.randn_like(x)
+    for _ in range(3):
+        F_.head_linear(x, w).backward(g)
+    torch.cuda.synchronize()
+    cu.check_errors()
+    assert not F_.fallback_counts(), F_.fallback_counts()
+
+
+CASES = {"gemm": case_gemm, "attention": case_attention, "head_linear": case_head_linear, "gemm_wgrad": lambda: case_gemm(True, True), "scan_fwd": case_scan_fwd,
          "scan_bwd": case_scan_bwd, "m2rnn": case_m2rnn, "ce": case_ce, "rmsnorm": case_rmsnorm, "mxfp8_gemm": case_mxfp8_gemm,
          "m2rnn_bwd": case_m2rnn_bwd, "sparse_mla": case_sparse_mla, "indexer": case_indexer,
          "rmsnorm_bwd": case_rmsnorm_bwd, "adamw": case_adamw, "quantize": case_quantize, "strided_copy": case_strided_copy, "moe_local": case_moe_local}
