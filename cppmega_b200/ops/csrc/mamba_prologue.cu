@@ -284,3 +284,80 @@ extern "C" int cm_angle_cumsum_bwd(float* g, const float* raw, const float* dt, 
     angle_reduce_kernel<<<(unsigned)((long long)B * S), 256, 0, s>>>(g, raw, dt, dsb, dsh, dss, draw, ddt, B, S, H, A);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ------------------------------------------------------------------------------------------
+// Widening of the state dimension for the 128-wide scan kernels, several tensors in one launch.
+//   split job:   in [rows, n] -> out [rows, w]:  out[:, 0:n/2] = in[:, 0:n/2], out[:, w/2 : w/2 + n/2] = in[:, n/2:n], rest 0
+//                (each half of the state keeps its place at the start of the wider half, so the rotary pairs (i, n/2 + i)
+//                 become (i, w/2 + i));
+//   plain job:   out[:, 0:n] = in, rest 0 (the rotary angles).
+// inverse = 1 runs the adjoint: in [rows, w] -> out [rows, n] (the gradient of the narrow tensor).
+// ------------------------------------------------------------------------------------------
+namespace cm {
+constexpr int PAD_MAX_JOBS = 8;
+struct PadJobs {
+  const void* in[PAD_MAX_JOBS];
+  void* out[PAD_MAX_JOBS];
+  long long rows[PAD_MAX_JOBS];
+  int n[PAD_MAX_JOBS], w[PAD_MAX_JOBS], elem[PAD_MAX_JOBS], split[PAD_MAX_JOBS];
+  int count;
+};
+
+template <typename T>
+__device__ __forceinline__ void pad_rows(const T* __restrict__ in, T* __restrict__ out, long long rows, int n, int w, bool split,
+                                         bool inverse) {
+  const int wide = inverse ? n : w;                      // columns of the tensor this launch writes
+  const long long total = rows * wide;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / wide;
+    const int c = (int)(i - r * wide);
+    if (!inverse) {                                      // c indexes the wide row
+      int src = -1;
+      if (split) {
+        if (c < n / 2) src = c;
+        else if (c >= w / 2 && c < w / 2 + n / 2) src = c - w / 2 + n / 2;
+      } else if (c < n) {
+        src = c;
+      }
+      out[i] = src >= 0 ? in[r * n + src] : T(0);
+    } else {                                             // c indexes the narrow row
+      const int src = split ? (c < n / 2 ? c : c - n / 2 + w / 2) : c;
+      out[i] = in[r * w + src];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) pad_state_kernel(const PadJobs jobs, int inverse) {
+  const int j = blockIdx.y;
+  if (j >= jobs.count) return;
+  if (jobs.elem[j] == 2)
+    pad_rows(reinterpret_cast<const uint16_t*>(jobs.in[j]), reinterpret_cast<uint16_t*>(jobs.out[j]), jobs.rows[j], jobs.n[j],
+             jobs.w[j], jobs.split[j] != 0, inverse != 0);
+  else
+    pad_rows(reinterpret_cast<const uint32_t*>(jobs.in[j]), reinterpret_cast<uint32_t*>(jobs.out[j]), jobs.rows[j], jobs.n[j],
+             jobs.w[j], jobs.split[j] != 0, inverse != 0);
+}
+}  // namespace cm
+
+// ins / outs: `count` device pointers; rows / n / w / elem (2 or 4 bytes) / split: per job.  All tensors row-contiguous.
+extern "C" int cm_pad_state_dims(const void* const* ins, void* const* outs, const long long* rows, const int* n, const int* w,
+                                 const int* elem, const int* split, int count, int inverse, cudaStream_t s) {
+  if (count <= 0) return 0;
+  if (count > cm::PAD_MAX_JOBS) return -10;
+  cm::PadJobs jobs;
+  jobs.count = count;
+  long long most = 0;
+  for (int j = 0; j < count; ++j) {
+    if ((elem[j] != 2 && elem[j] != 4) || n[j] <= 0 || w[j] < n[j] || (split[j] && ((n[j] | w[j]) & 1))) return -10;
+    jobs.in[j] = ins[j]; jobs.out[j] = outs[j]; jobs.rows[j] = rows[j];
+    jobs.n[j] = n[j]; jobs.w[j] = w[j]; jobs.elem[j] = elem[j]; jobs.split[j] = split[j];
+    const long long tot = rows[j] * (inverse ? n[j] : w[j]);
+    if (tot > most) most = tot;
+  }
+  long long blocks = (most + 255) / 256;
+  const long long cap = (long long)cm::sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  cm::pad_state_kernel<<<dim3((unsigned)blocks, (unsigned)count), 256, 0, s>>>(jobs, inverse);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

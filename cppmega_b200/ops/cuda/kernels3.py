@@ -110,10 +110,65 @@ def _pad_state_dim(x: torch.Tensor, n: int, to: int = 128) -> torch.Tensor:
     return torch.cat([x[..., :h], z, x[..., h:], z], dim=-1)
 
 
+def _pad_launch(ins, outs, specs, inverse: bool) -> None:
+    """One launch of ``cm_pad_state_dims`` over several tensors; ``specs``: (n, w, split) per tensor."""
+    from . import lib, stream_ptr, _check
+    L = lib()
+    k = len(ins)
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    if not getattr(L, "_pad_declared", False):
+        L.cm_pad_state_dims.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp]
+        L.cm_pad_state_dims.restype = i32
+        L._pad_declared = True
+    narrow = outs if inverse else ins
+    rows = (i64 * k)(*[t.numel() // spec[0] for t, spec in zip(narrow, specs)])
+    _check(L.cm_pad_state_dims((vp * k)(*[t.data_ptr() for t in ins]), (vp * k)(*[t.data_ptr() for t in outs]), rows,
+                               (i32 * k)(*[sp[0] for sp in specs]), (i32 * k)(*[sp[1] for sp in specs]),
+                               (i32 * k)(*[t.element_size() for t in ins]), (i32 * k)(*[int(sp[2]) for sp in specs]),
+                               k, int(inverse), stream_ptr()), "cm_pad_state_dims")
+    F_.count_launch("pad_state_dims")
+
+
+class PadStateFn(torch.autograd.Function):
+    """(Q, K, Qb, Kb, angles) with state dimension n -> the same tensors widened to 128 (angles to 32) by one kernel; the
+    backward is one launch of its adjoint."""
+
+    @staticmethod
+    def forward(ctx, Q, K, Qb, Kb, angles):
+        n, a = Q.shape[-1], angles.shape[-1]
+        ins = [t.contiguous() for t in (Q, K, Qb, Kb, angles)]
+        specs = [(n, 128, True)] * 4 + [(a, 32, False)]
+        outs = [torch.empty(*t.shape[:-1], sp[1], dtype=t.dtype, device=t.device) for t, sp in zip(ins, specs)]
+        _pad_launch(ins, outs, specs, False)
+        ctx.specs, ctx.shapes = specs, [t.shape for t in ins]
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        specs, shapes = [], []
+        ins, slots = [], []
+        for i, (g, sp, shp) in enumerate(zip(grads, ctx.specs, ctx.shapes)):
+            if g is not None and ctx.needs_input_grad[i]:
+                ins.append(g.contiguous())
+                specs.append(sp)
+                shapes.append(shp)
+                slots.append(i)
+        outs = [torch.empty(shp, dtype=g.dtype, device=g.device) for g, shp in zip(ins, shapes)]
+        if ins:
+            _pad_launch(ins, outs, specs, True)
+        res = [None] * 5
+        for i, o in zip(slots, outs):
+            res[i] = o
+        return tuple(res)
+
+
 def _padded_to_128(Q, K, Qb, Kb, angles):
     """A scan with state dimension 32 or 64 is the scan with state dimension 128 on zero-padded Q / K / biases: the
     padded state rows stay zero, the padded rotary pairs get angle 0.  The kernels are instantiated for 128."""
     N = Q.shape[-1]
+    if (Q.is_cuda and Q.dtype == K.dtype and Q.element_size() in (2, 4) and Qb.dtype == Kb.dtype == torch.float32
+            and angles.dtype == torch.float32 and N % 2 == 0):
+        return PadStateFn.apply(Q, K, Qb, Kb, angles)
     ang = torch.cat([angles, angles.new_zeros(*angles.shape[:-1], 32 - angles.shape[-1])], dim=-1)
     return _pad_state_dim(Q, N), _pad_state_dim(K, N), _pad_state_dim(Qb, N), _pad_state_dim(Kb, N), ang
 

@@ -243,9 +243,12 @@ def bench_scan_bar() -> List[dict]:
             with torch.no_grad():
                 kernels3.mimo_scan(*args, 4, 16)
 
-        def fwd_bwd():
-            torch.autograd.grad(kernels3.mimo_scan(*args, 4, 16), args, dy)
+        def fwd_bwd():                      # gradients land in .grad tensors that the capture itself allocates
+            for t in args:
+                t.grad = None
+            kernels3.mimo_scan(*args, 4, 16).backward(dy)
 
+        del y                                   # no autograd graph from before the capture may stay alive
         g_f, g_fb = capture(fwd_only), capture(fwd_bwd)
         us_f = time_ms(g_f.replay, iters=20, warmup=5) * 1e3
         us_fb = time_ms(g_fb.replay, iters=20, warmup=5) * 1e3

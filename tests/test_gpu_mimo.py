@@ -120,3 +120,26 @@ def test_mimo_scan_smaller_state_dims(N, B, S, H, G):
     for n, x, r in zip(names, a1, a2):
         assert x.grad.shape == r.grad.shape, n
         assert _rel(x.grad, r.grad) < 6e-2, (n, _rel(x.grad, r.grad))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [64, 32])
+def test_state_dim_padding_kernel_matches_the_concatenations(n):
+    """One launch widens Q / K / biases (split halves) and the angles (zero-extended); its adjoint narrows the gradients."""
+    from cppmega_b200.ops.cuda import kernels3
+    torch.manual_seed(n)
+    dev = "cuda"
+    Q = torch.randn(2, 64, 4, 2, n, device=dev).bfloat16().requires_grad_()
+    K = torch.randn(2, 64, 4, 2, n, device=dev).bfloat16().permute(0, 1, 2, 3, 4).requires_grad_()
+    Qb, Kb = torch.randn(8, 4, n, device=dev).requires_grad_(), torch.randn(8, 4, n, device=dev).requires_grad_()
+    ang = torch.randn(2, 64, 8, n // 4, device=dev).requires_grad_()
+    outs = kernels3.PadStateFn.apply(Q, K, Qb, Kb, ang)
+    refs = [kernels3._pad_state_dim(t, n) for t in (Q, K, Qb, Kb)] + [
+        torch.cat([ang, ang.new_zeros(*ang.shape[:-1], 32 - ang.shape[-1])], dim=-1)]
+    gs = [torch.randn_like(o) for o in outs]
+    got = torch.autograd.grad(outs, (Q, K, Qb, Kb, ang), gs)
+    want = torch.autograd.grad(refs, (Q, K, Qb, Kb, ang), gs)
+    for o, r in zip(outs, refs):
+        assert o.shape == r.shape and torch.equal(o, r)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
