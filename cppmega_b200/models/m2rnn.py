@@ -73,8 +73,7 @@ class M2RNNMixer(nn.Module):
         conv_in, f_in, g = proj[..., :self.in_dim].split((self.conv_dim, H, self.g_dim), dim=-1)
         f = torch.exp(-torch.exp(self.A_log) * F.softplus(f_in.float() + self.dt_bias))       # [B,S,H] fp32
         if self.conv1d is not None:
-            c = self.conv1d(conv_in.transpose(1, 2))[..., :S]
-            conv_in = F.silu(c).transpose(1, 2)
+            conv_in = F_.causal_conv1d_silu(conv_in, self.conv1d.weight, self.conv1d.bias)    # read in place from proj
         q = conv_in[..., :self.q_dim].reshape(B, S, cfg.num_q_heads, cfg.k_head_dim)
         k = conv_in[..., self.q_dim:self.q_dim + self.k_dim].reshape(B, S, cfg.num_k_heads, cfg.k_head_dim)
         v = conv_in[..., self.q_dim + self.k_dim:].reshape(B, S, H, cfg.v_head_dim)

@@ -99,8 +99,7 @@ class SSDMixer(nn.Module):
         trap = rest.pop(0) if v.trapezoid else None
         ang = rest.pop(0) if self.n_angles else None
         if self.conv1d is not None:
-            xbc = torch.cat([xs, Bm, Cm], dim=-1).transpose(1, 2)
-            xbc = F.silu(self.conv1d(xbc)[..., :S]).transpose(1, 2)
+            xbc = F_.causal_conv1d_silu(torch.cat([xs, Bm, Cm], dim=-1), self.conv1d.weight, self.conv1d.bias)
             xs, Bm, Cm = torch.split(xbc, [self.d_inner, G * N, G * N], dim=-1)
         else:
             xs = F.silu(xs)

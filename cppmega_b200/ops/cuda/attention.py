@@ -78,6 +78,7 @@ def causal_attention(q, k, v, scale: float):
 def register() -> None:
     F_.register_cuda("causal_attention", causal_attention)
     F_.register_cuda("head_linear", head_linear)
+    F_.register_cuda("causal_conv1d_silu", causal_conv1d_silu)
 
 
 # ---------------------------------------------------------------------------
@@ -162,3 +163,75 @@ def head_linear(x: torch.Tensor, w: torch.Tensor):
             or w.dim() != 3 or tuple(w.shape[1:]) != (64, 64) or w.shape[0] != x.shape[-2] or x.numel() == 0):
         return None
     return HeadLinearFn.apply(x, w)
+
+
+# ---------------------------------------------------------------------------
+# depthwise causal conv1d + SiLU, channels-last (ops/csrc/conv1d.cu)
+# ---------------------------------------------------------------------------
+
+def _declare_conv(L: ctypes.CDLL) -> None:
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    if getattr(L, "_conv_declared", False):
+        return
+    L.cm_causal_conv1d_silu_fwd.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i64, vp]
+    L.cm_causal_conv1d_silu_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, i64, vp]
+    L.cm_causal_conv1d_silu_fwd.restype = L.cm_causal_conv1d_silu_bwd.restype = i32
+    L._conv_declared = True
+
+
+def _conv_view(x: torch.Tensor):
+    """(tensor, token stride) for a [B, S, C] bf16 operand the kernel can read in place: channels contiguous, batch stride
+    = S * token stride, 16-byte aligned rows; anything else is copied to a packed tensor."""
+    B, S, C = x.shape
+    sb, ss, sc = x.stride()
+    if sc == 1 and ss >= C and ss % 8 == 0 and (B == 1 or sb == S * ss) and x.data_ptr() % 16 == 0:
+        return x, ss
+    x = x.contiguous()
+    return x, C
+
+
+class CausalConv1dSiluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        from . import lib, stream_ptr, _check
+        L = lib()
+        _declare_conv(L)
+        B, S, C = x.shape
+        xv, ldx = _conv_view(x)
+        wc = w.contiguous()
+        bc = None if bias is None else bias.contiguous()
+        y = torch.empty(B, S, C, dtype=torch.bfloat16, device=x.device)
+        _check(L.cm_causal_conv1d_silu_fwd(xv.data_ptr(), wc.data_ptr(), None if bc is None else bc.data_ptr(), y.data_ptr(),
+                                           B, S, C, wc.shape[1], ldx, stream_ptr()), "cm_causal_conv1d_silu_fwd")
+        F_.count_launch("causal_conv1d_silu")
+        ctx.save_for_backward(x, wc, bc if bc is not None else wc.new_empty(0))
+        ctx.has_bias = bc is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import lib, stream_ptr, _check
+        L = lib()
+        x, w, bias = ctx.saved_tensors
+        B, S, C = x.shape
+        k = w.shape[1]
+        xv, ldx = _conv_view(x)
+        dy = dy.contiguous()
+        g = torch.empty(B, S, C, dtype=torch.bfloat16, device=x.device)
+        dx = torch.empty(B, S, C, dtype=torch.bfloat16, device=x.device)
+        dw = torch.zeros(C, k, dtype=torch.float32, device=x.device)
+        db = torch.zeros(C, dtype=torch.float32, device=x.device)
+        _check(L.cm_causal_conv1d_silu_bwd(xv.data_ptr(), w.data_ptr(), bias.data_ptr() if ctx.has_bias else None, dy.data_ptr(),
+                                           g.data_ptr(), dx.data_ptr(), dw.data_ptr(), db.data_ptr(), B, S, C, k, ldx, C,
+                                           stream_ptr()), "cm_causal_conv1d_silu_bwd")
+        F_.count_launch("causal_conv1d_silu_bwd", 2)
+        return dx, dw.to(w.dtype), (db.to(bias.dtype) if ctx.has_bias else None)
+
+
+def causal_conv1d_silu(x, w, bias):
+    """x [B, S, C] bf16 (may be a column slice of a wider projection), w [C, k] bf16, bias [C] bf16 or None."""
+    if (x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or (bias is not None and bias.dtype != torch.bfloat16)
+            or x.dim() != 3 or x.shape[2] % 8 or not 1 <= w.shape[1] <= 8 or x.numel() == 0):
+        F_._miss("causal_conv1d_silu(shape/dtype)", x)
+        return None
+    return CausalConv1dSiluFn.apply(x, w, bias)

@@ -351,6 +351,19 @@ def causal_attention_library(q, k, v, scale: float):
     return o.transpose(1, 2)[..., :dv]
 
 
+def causal_conv1d_silu(x, weight, bias=None):
+    """``silu(depthwise causal conv1d over the sequence)`` on a channels-last tensor: x [B, S, C], weight [C, k] (or the
+    [C, 1, k] parameter of ``nn.Conv1d(groups=C)``), bias [C].  Output [B, S, C]."""
+    if weight.dim() == 3:
+        weight = weight.squeeze(1)
+    fn = _cuda("causal_conv1d_silu", x)
+    if fn is not None:
+        y = fn(x, weight, bias)
+        if y is not None:
+            return y
+    return ref.causal_conv1d_silu(x, weight, bias)
+
+
 # ---- loss --------------------------------------------------------------------
 
 def linear_cross_entropy(hidden, weight, labels, ignore_index: int = -100, reduction: str = "none"):

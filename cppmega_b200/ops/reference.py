@@ -231,6 +231,15 @@ def indexer_kl_loss_chunked(attn_q, attn_k, scale, q_idx, k_idx, w, coeff: float
     return coeff * total / (B * S)
 
 
+def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y[b, s, c] = silu(bias[c] + sum_j weight[c, j] * x[b, s - (k-1) + j, c])`` with zeros before the sequence start:
+    the depthwise ``nn.Conv1d(C, C, k, groups=C, padding=k-1)`` truncated to S outputs, on a channels-last tensor."""
+    S, k = x.shape[1], weight.shape[1]
+    y = F.conv1d(x.transpose(1, 2), weight.unsqueeze(1).to(x.dtype), None if bias is None else bias.to(x.dtype),
+                 padding=k - 1, groups=x.shape[2])[..., :S]
+    return F.silu(y).transpose(1, 2)
+
+
 # ---------------------------------------------------------------------------
 # fused linear + cross entropy
 # ---------------------------------------------------------------------------

@@ -125,3 +125,32 @@ def test_head_linear_kernels(T, H, sliced):
     wt = (torch.randn(H, 64, 64, device="cuda") * 0.2).bfloat16()
     y2 = F_.head_linear(x.detach(), wt.transpose(1, 2))
     assert _rel(y2, torch.einsum("bshi,hio->bsho", x.detach().float(), wt.float())) < 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,S,C,k,sliced", [(2, 200, 136, 4, True), (1, 64, 64, 2, False), (3, 130, 72, 3, True)])
+def test_causal_conv1d_silu_kernels(B, S, C, k, sliced):
+    """Depthwise causal conv + SiLU, channels-last, read in place from a wider projection: output, input gradient, weight
+    and bias gradients against the fp32 definition (segments of 64 tokens: S = 200 / 130 cross segment boundaries)."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.ops import reference as ref
+    torch.manual_seed(S + C)
+    base = torch.randn(B, S, C + 40 if sliced else C, device="cuda").bfloat16()
+    x = (base[..., :C] if sliced else base).detach().requires_grad_()
+    w = (torch.randn(C, 1, k, device="cuda") * 0.5).bfloat16().requires_grad_()
+    b = (torch.randn(C, device="cuda") * 0.1).bfloat16().requires_grad_()
+    F_.reset_counters()
+    y = F_.causal_conv1d_silu(x, w, b)
+    assert F_.launch_counts().get("causal_conv1d_silu", 0) == 1 and not F_.fallback_counts()
+    g = torch.randn_like(y)
+    y.backward(g)
+    torch.cuda.synchronize()
+    cu.check_errors()
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = ref.causal_conv1d_silu(xr, wr.squeeze(1), br)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 1.5e-2
+    assert _rel(w.grad, wr.grad) < 1.5e-2
+    assert _rel(b.grad, br.grad) < 1.5e-2
