@@ -136,6 +136,89 @@ def register(name: str, fn: Callable[[], List[dict]]) -> None:
     CASES[name] = fn
 
 
+def bench_glue() -> List[dict]:
+    """The small fused operators against the library ops they replace, same inputs, same harness:
+    depthwise causal conv1d + SiLU of the M2RNN mixer (7344 channels, kernel 4), the per-head 64 x 64 maps of the
+    absorbed sparse-attention path (32 heads), the state-dimension widening of the scan; forward + backward."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.ops import reference as ref
+    pk = peaks()
+    out = []
+    dev = "cuda"
+    B, S = 4, 4096
+
+    def fwd_bwd(fn, inputs, g):
+        def run():
+            for t in inputs:
+                t.grad = None
+            fn().backward(g)
+        return run
+
+    # conv1d + SiLU, read in place from a wider projection
+    C, k = 7344, 4
+    proj = torch.randn(B, S, C + 56 + 816, device=dev).bfloat16()
+    x = proj[..., :C].detach().requires_grad_()
+    w = (torch.randn(C, 1, k, device=dev) * 0.5).bfloat16().requires_grad_()
+    b = torch.zeros(C, device=dev).bfloat16().requires_grad_()
+    g = torch.randn(B, S, C, device=dev).bfloat16()
+    ours = time_ms(fwd_bwd(lambda: F_.causal_conv1d_silu(x, w, b), (x, w, b), g))
+    lib = time_ms(fwd_bwd(lambda: ref.causal_conv1d_silu(x, w.squeeze(1), b), (x, w, b), g))
+    byts = B * S * C * 2 * 7.0              # x, y, dy, g (write + k-fold cached read), dx: about seven passes
+    out.append({"kernel": "causal_conv1d_silu fwd+bwd", "B": B, "S": S, "C": C, "k": k, "ms": ours, "library_ms": lib,
+                "speedup": lib / ours, "frac_of_" + pk["kind"] + "_hbm": byts / ours / 1e6 / pk["hbm_gbs"]})
+    # per-head maps
+    H = 32
+    xh = torch.randn(B, S, H, 64, device=dev).bfloat16().requires_grad_()
+    wh = (torch.randn(H, 64, 64, device=dev) * 0.1).bfloat16().requires_grad_()
+    gh = torch.randn(B, S, H, 64, device=dev).bfloat16()
+    ours = time_ms(fwd_bwd(lambda: F_.head_linear(xh, wh), (xh, wh), gh))
+    lib = time_ms(fwd_bwd(lambda: torch.einsum("bshi,hoi->bsho", xh, wh), (xh, wh), gh))
+    byts = B * S * H * 64 * 2 * 6.0         # x, y | dy, dx | dy, x again for the weight gradient
+    out.append({"kernel": "head_linear fwd+bwd", "tokens": B * S, "heads": H, "ms": ours, "library_ms": lib,
+                "speedup": lib / ours, "frac_of_" + pk["kind"] + "_hbm": byts / ours / 1e6 / pk["hbm_gbs"]})
+    cu.check_errors()
+    assert not F_.fallback_counts(), F_.fallback_counts()
+    return out
+
+
+CASES["glue"] = bench_glue
+
+
+def bench_fp8_activations() -> List[dict]:
+    """Training step of the four-layer production-width slice (one Mamba3, one DSA, one MoE, one M2RNN layer; hidden 1024)
+    with and without FP8 storage of the saved activations: step time and peak allocator memory."""
+    from cppmega_b200.config.model import nam56r_slice
+    from cppmega_b200.parallel.dist_optimizer import OptimizerConfig
+    from cppmega_b200.training.trainer import TrainConfig, Trainer, synthetic_batches
+    from cppmega_b200.utils import fp8_activations as fa
+    out = []
+    mb, seq = 4, 4096
+    for mode in ("off", "mxfp8", "tensor"):
+        cfg = nam56r_slice(seq_length=seq)
+        tc = TrainConfig(micro_batch_size=mb, seq_length=seq, dtype="bf16", fp8_activations=mode, fp8_activations_bf16_first=0,
+                         fp8_activations_bf16_last=0, log_interval=0, optimizer=OptimizerConfig(lr=1e-4, weight_decay=0.0))
+        tr = Trainer(cfg, tc, device=torch.device("cuda", 0))
+        stream = synthetic_batches(cfg.vocab_size, mb, seq, seed=0)
+        batches = [next(stream) for _ in range(2)]
+        for i in range(3):
+            loss = tr.train_step(batches[i % 2])["loss"]
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        fa.reset_stats()
+        ms = time_ms(lambda: tr.train_step(batches[0]), iters=5, warmup=1)
+        out.append({"case": "nam56r_slice train step", "fp8_activations": mode, "ms_per_step": ms,
+                    "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30, "loss": float(loss),
+                    "packed_tensors_per_step": fa.STATS["packed"] / 6, "saved_gb_per_step":
+                    (fa.STATS["bytes_in"] - fa.STATS["bytes_out"]) / 6 / 2**30})
+        del tr
+        torch.cuda.empty_cache()
+    return out
+
+
+CASES["fp8_activations"] = bench_fp8_activations
+
+
 def main(argv: List[str]) -> int:
     out_path = None
     names = []

@@ -76,7 +76,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         counts = mcfg.param_count()
         print(f"[cppmega_b200] {mcfg.name}: {counts['total'] / 1e9:.2f}B params ({counts['active'] / 1e9:.2f}B active), "
               f"pattern {mcfg.plan().full_pattern[:64]}..., world {pc.world_size} ({pcfg.describe(pc.world_size)}), "
-              f"fused paths {trainer.fused}", flush=True)
+              f"paths {trainer.describe_paths()}", flush=True)
     start_iter = 0
     consumed_steps = 0
     if extras["load"]:

@@ -150,6 +150,44 @@ class Trainer:
         self.tokens_seen = 0
         self.watchdog = None
 
+    def describe_paths(self) -> Dict[str, str]:
+        """Which of the optional fast paths this run takes, and for those it does not, why: ``{"optimizer": "on", "moe":
+        "off: pipeline stages > 1", ...}``.  Printed once at start-up by ``pretrain``."""
+        pc, cfg, dev = self.pc, self.cfg, self.device
+        bf16 = cfg.torch_dtype() == torch.bfloat16
+
+        def first(*checks):
+            for bad, why in checks:
+                if bad:
+                    return "off: " + why
+            return "on"
+
+        peers = True
+        if dev.type == "cuda" and pc.world_size > 1:
+            from ..parallel.symm_mem import peer_access_available
+            peers = peer_access_available(pc)
+        common = ((dev.type != "cuda", "no GPU"), (not pc.config.fused_collectives, "fused collectives disabled"),
+                  (not peers, "no peer access between the GPUs of the group"))
+        out = {
+            "optimizer": "on" if self.fused.get("optimizer") else first(
+                *common, (pc.world_size == 1, "single process"), (cfg.optimizer.optimizer != "adamw", "optimizer is not adamw"),
+                (pc.pp > 1, "pipeline stages > 1"), (not pc.config.distributed_optimizer, "distributed optimizer off"),
+                (pc.dp == 1, "data-parallel size 1"), (True, "not selected")),
+            "moe": "on" if self.fused.get("moe") else first(
+                *common, (not bf16, "dtype is not bf16"), (not self.model.moe_layers() if hasattr(self.model, "moe_layers") else True, "no MoE layers"),
+                (pc.ep == 1 and pc.tp > 1, "EP 1 with TP > 1"), (True, "not selected")),
+            "tp": "on" if self.fused.get("tp") else first(
+                (pc.tp == 1, "tensor-parallel size 1"), *common, (not pc.sequence_parallel, "sequence parallelism off"),
+                (not bf16, "dtype is not bf16"), (True, "not selected")),
+            "cuda_graphs": f"on ({self.graphed_layers} layers)" if self.graphed_layers else first(
+                (not cfg.cuda_graph_scope, "no --cuda-graph-scope"), (dev.type != "cuda", "no GPU"), (self.chunked, "chunked pipeline"),
+                (pc.tp > 1, "TP > 1"), (True, "no layer of the requested kinds")),
+            "precision": cfg.precision_recipe + (f" on {len(self.precision_modules)} modules" if self.precision_modules else ""),
+            "fp8_activations": cfg.fp8_activations,
+            "recompute": cfg.recompute + (f" (last {cfg.recompute_keep_last} layers kept)" if cfg.recompute_keep_last else ""),
+        }
+        return out
+
     def _attach_fused_paths(self):
         """Swap the NCCL collectives for the peer-memory kernels where the topology allows it."""
         from ..parallel.symm_mem import peer_access_available

@@ -185,3 +185,15 @@ def test_fp8_arguments_round_trip_and_module_sets():
         assert F_.precision_recipe() == "bf16"                      # default outside the selected modules
     finally:
         F_.set_precision_recipe("bf16")
+
+
+def test_trainer_reports_which_fast_paths_are_off_and_why():
+    import torch
+    from cppmega_b200.config.model import nam56r_tiny
+    from cppmega_b200.training.trainer import TrainConfig, Trainer
+    tr = Trainer(nam56r_tiny(seq_length=32), TrainConfig(micro_batch_size=1, seq_length=32, dtype="fp32", log_interval=0),
+                 device=torch.device("cpu"))
+    paths = tr.describe_paths()
+    assert paths["optimizer"].startswith("off: ") and paths["moe"].startswith("off: ") and paths["tp"].startswith("off: ")
+    assert "no GPU" in paths["optimizer"] and "tensor-parallel size 1" in paths["tp"]
+    assert paths["cuda_graphs"].startswith("off: ") and paths["recompute"] == "none"
