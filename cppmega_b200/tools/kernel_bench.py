@@ -205,13 +205,18 @@ def bench_fp8_activations() -> List[dict]:
             loss = tr.train_step(batches[i % 2])["loss"]
         torch.cuda.synchronize()
         torch.cuda.reset_peak_memory_stats()
+        resident = torch.cuda.memory_allocated()           # parameters, optimizer state, buffers: everything but activations
         fa.reset_stats()
         ms = time_ms(lambda: tr.train_step(batches[0]), iters=5, warmup=1)
         out.append({"case": "nam56r_slice train step", "fp8_activations": mode, "ms_per_step": ms,
-                    "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30, "loss": float(loss),
+                    "activation_peak_gb": (torch.cuda.max_memory_allocated() - resident) / 2**30,
+                    "resident_gb": resident / 2**30, "loss": float(loss),
                     "packed_tensors_per_step": fa.STATS["packed"] / 6, "saved_gb_per_step":
                     (fa.STATS["bytes_in"] - fa.STATS["bytes_out"]) / 6 / 2**30})
-        del tr
+        tr.close()
+        del tr, stream, batches
+        import gc
+        gc.collect()
         torch.cuda.empty_cache()
     return out
 

@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import functools
 import threading
+import weakref
 from contextlib import nullcontext
 from dataclasses import dataclass
 from typing import Any, Optional, Tuple
@@ -32,7 +33,7 @@ MIN_ELEMENTS = 16384            # below this the two extra kernels cost more tha
 E4M3_MAX = 448.0
 
 _state = threading.local()
-STATS = {"packed": 0, "passed": 0, "bytes_in": 0, "bytes_out": 0}
+STATS = {"packed": 0, "shared": 0, "passed": 0, "bytes_in": 0, "bytes_out": 0}
 
 
 def reset_stats() -> None:
@@ -84,12 +85,20 @@ def is_bf16_layer(layer_idx: int, n_layers: int, bf16_first: int, bf16_last: int
 
 
 # ---- packer -----------------------------------------------------------------------------------------------------------
-@dataclass
+@dataclass(eq=False)
 class PackedActivation:
     payload: torch.Tensor           # uint8 / float8_e4m3fn bytes, flat [rows, cols]
     scales: torch.Tensor            # uint8 E8M0, [rows, cols / 32]
     shape: Tuple[int, ...]
     dtype: torch.dtype
+
+
+def _is_weight(t: torch.Tensor) -> bool:
+    """A trainable leaf or a view of one (``w.t()`` saved by a matrix product): parameters are not activations."""
+    if t.is_leaf and t.requires_grad:
+        return True
+    base = t._base
+    return base is not None and base.is_leaf and base.requires_grad
 
 
 def _as_rows(t: torch.Tensor) -> Optional[torch.Tensor]:
@@ -109,12 +118,19 @@ class Fp8ActivationPacker:
         if recipe not in ("mxfp8", "tensor"):
             raise ValueError(f"fp8 activation recipe must be 'mxfp8' or 'tensor', not {recipe!r}")
         self.recipe, self.clamp, self.min_elements = recipe, clamp, min_elements
+        # one packed copy per distinct tensor: a normed activation that feeds three linears is saved three times
+        self._seen: "weakref.WeakValueDictionary" = weakref.WeakValueDictionary()
 
     def pack(self, t: Any) -> Any:
         if (not isinstance(t, torch.Tensor) or _disabled() or t.dtype != torch.bfloat16 or t.numel() < self.min_elements
-                or isinstance(t, torch.nn.Parameter) or getattr(t, "_keep_bf16", False)):
+                or isinstance(t, torch.nn.Parameter) or _is_weight(t)):
             STATS["passed"] += 1
             return t
+        key = (t.data_ptr(), t._version, tuple(t.shape), tuple(t.stride()))
+        hit = self._seen.get(key)
+        if hit is not None:
+            STATS["shared"] += 1
+            return hit
         x = _as_rows(t)
         if x is None:
             STATS["passed"] += 1
@@ -143,7 +159,9 @@ class Fp8ActivationPacker:
         STATS["packed"] += 1
         STATS["bytes_in"] += t.numel() * 2
         STATS["bytes_out"] += payload.numel() + scales.numel()
-        return PackedActivation(payload, scales, tuple(t.shape), t.dtype)
+        packed = PackedActivation(payload, scales, tuple(t.shape), t.dtype)
+        self._seen[key] = packed
+        return packed
 
     @staticmethod
     def unpack(p: Any) -> Any:
