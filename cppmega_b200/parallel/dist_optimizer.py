@@ -282,6 +282,22 @@ class DistributedOptimizer:
                     "muon_gather": self.cfg.optimizer == "muon" and _bucket_has_cut_matrix(buf, b),
                 })
 
+    def close(self) -> None:
+        """Detach from the parameters: the gradient hooks live in the tensors' autograd metadata, where the cycle
+        parameter -> hook -> optimizer -> flat buffer -> parameter is invisible to the garbage collector, so a dropped
+        optimizer (and the model with it) would otherwise stay allocated."""
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+        for buf in getattr(self, "buffers", []):
+            for p in buf.params:
+                for name in ("main_grad", "grad_added_to_main_grad"):
+                    if hasattr(p, name):
+                        try:
+                            delattr(p, name)
+                        except AttributeError:
+                            pass
+
     def _install_hooks(self):
         for buf in self.buffers:
             for p in buf.params:

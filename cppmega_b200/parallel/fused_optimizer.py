@@ -271,6 +271,7 @@ class FusedDistributedOptimizer(DistributedOptimizer):
         return total.sqrt()
 
     def close(self):
+        super().close()
         for h in self._heaps_in_use():
             h.close()
         self._heaps = {}

@@ -55,3 +55,24 @@ def test_optimizer_state_is_not_dropped_silently(tmp_path):
         info = sharded.load_checkpoint(str(tmp_path), model, pc, opt, allow_optimizer_reset=True)
     assert "moments zeroed" in info["optimizer_reset"]
     _ = d
+
+
+def test_a_closed_trainer_is_released():
+    """The gradient hooks sit in the tensors' autograd metadata (a cycle the garbage collector cannot see): ``close()``
+    removes them, after which dropping the trainer frees model, flat buffers and optimizer state."""
+    import gc
+    import weakref
+    import torch
+    from cppmega_b200.config.model import nam56r_tiny
+    from cppmega_b200.parallel.dist_optimizer import OptimizerConfig
+    from cppmega_b200.training.trainer import TrainConfig, Trainer, synthetic_batches
+    cfg = nam56r_tiny(seq_length=32)
+    tr = Trainer(cfg, TrainConfig(micro_batch_size=1, seq_length=32, dtype="fp32", log_interval=0,
+                                  optimizer=OptimizerConfig(lr=1e-3)), device=torch.device("cpu"))
+    stream = synthetic_batches(cfg.vocab_size, 1, 32, seed=0, pin=False)
+    float(tr.train_step(next(stream))["loss"])
+    wm, wo = weakref.ref(tr.model), weakref.ref(tr.optimizer)
+    tr.close()
+    del tr, stream
+    gc.collect()
+    assert wm() is None and wo() is None
