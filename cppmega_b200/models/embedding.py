@@ -190,10 +190,10 @@ class VocabParallelEmbedding(nn.Module):
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         if self.pc.tp == 1:
-            return F.embedding(ids, self.weight)
+            return F_.embedding(ids, self.weight)
         local = ids - self.lo
         mask = (local < 0) | (local >= self.per)
-        out = F.embedding(local.masked_fill(mask, 0), self.weight)
+        out = F_.embedding(local.masked_fill(mask, 0), self.weight)
         out = out.masked_fill(mask.unsqueeze(-1), 0.0)
         return _AllReduceSum.apply(out, self.pc.tp_group)
 

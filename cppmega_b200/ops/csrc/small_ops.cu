@@ -226,3 +226,84 @@ extern "C" int cm_rope(const void* x, const float* cosv, const float* sinv, void
   rope_kernel<<<grid_1d(rows * (D / 2)), 256, 0, s>>>((const __nv_bfloat16*)x, cosv, sinv, (__nv_bfloat16*)out, rows, S, R, D, ldx, ldo, sign);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ------------------------------------------------------------------------------------------
+// Word embedding: gather forward, and a backward that adds every token's output-gradient row straight into the row of
+// the weight's gradient buffer (fp32 or bf16) with vector atomics - no dense [vocab, hidden] gradient tensor, no
+// separate accumulation pass.  One warp per token; ids outside [0, vocab) are skipped (forward writes zeros).
+// ------------------------------------------------------------------------------------------
+namespace cm {
+
+__global__ void __launch_bounds__(256) embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
+                                                            __nv_bfloat16* __restrict__ out, long long T, long long vocab, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long w0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nw = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int nvec = H / 8;
+  for (long long t = w0; t < T; t += nw) {
+    const long long id = ids[t];
+    uint4* o = reinterpret_cast<uint4*>(out + t * H);
+    if (id < 0 || id >= vocab) {
+      for (int v = lane; v < nvec; v += 32) o[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const uint4* s = reinterpret_cast<const uint4*>(w + id * H);
+    for (int v = lane; v < nvec; v += 32) o[v] = s[v];
+  }
+}
+
+template <typename G>
+__global__ void __launch_bounds__(256) embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
+                                                            G* __restrict__ dw, long long T, long long vocab, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long w0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nw = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int nvec = H / 8;
+  for (long long t = w0; t < T; t += nw) {
+    const long long id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    const uint4* s = reinterpret_cast<const uint4*>(dout + t * H);
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 x = s[v];
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&x);
+      if constexpr (sizeof(G) == 4) {
+        float* d = reinterpret_cast<float*>(dw) + id * H + v * 8;
+        const float2 f0 = __bfloat1622float2(b[0]), f1 = __bfloat1622float2(b[1]), f2 = __bfloat1622float2(b[2]),
+                     f3 = __bfloat1622float2(b[3]);
+        atomicAdd(reinterpret_cast<float4*>(d), make_float4(f0.x, f0.y, f1.x, f1.y));
+        atomicAdd(reinterpret_cast<float4*>(d) + 1, make_float4(f2.x, f2.y, f3.x, f3.y));
+      } else {
+        __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(dw) + id * H + v * 8);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) atomicAdd(d + j, b[j]);
+      }
+    }
+  }
+}
+
+static int embedding_grid(long long T) {
+  long long blocks = (T + 7) / 8;
+  const long long cap = (long long)sm_count() * 8;
+  return (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+}  // namespace cm
+
+// ids [T] int64, w [vocab, H] bf16, out [T, H] bf16; H % 8 == 0
+extern "C" int cm_embedding_fwd(const long long* ids, const void* w, void* out, long long T, long long vocab, int H, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (H % 8) return -10;
+  cm::embedding_fwd_kernel<<<cm::embedding_grid(T), 256, 0, s>>>(ids, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, T, vocab, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// dw [vocab, H] (+)= scatter of dout [T, H] bf16 by ids; grad_kind 0: fp32 buffer, 1: bf16 buffer
+extern "C" int cm_embedding_bwd(const long long* ids, const void* dout, void* dw, long long T, long long vocab, int H, int grad_kind,
+                                cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (H % 8) return -10;
+  if (grad_kind == 0)
+    cm::embedding_bwd_kernel<float><<<cm::embedding_grid(T), 256, 0, s>>>(ids, (const __nv_bfloat16*)dout, (float*)dw, T, vocab, H);
+  else
+    cm::embedding_bwd_kernel<__nv_bfloat16><<<cm::embedding_grid(T), 256, 0, s>>>(ids, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dw, T, vocab, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -21,6 +21,8 @@ def declare(L: ctypes.CDLL) -> None:
     sig["cm_sparse_mla_bwd"] = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, vp]
     sig["cm_router_topk_fwd"] = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp]
     sig["cm_router_topk_bwd"] = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp]
+    sig["cm_embedding_fwd"] = [vp, vp, vp, i64, i64, i32, vp]
+    sig["cm_embedding_bwd"] = [vp, vp, vp, i64, i64, i32, i32, vp]
     sig["cm_ngram_embed_fwd"] = [vp] * 8 + [i32] * 6 + [vp]
     sig["cm_ngram_embed_bwd"] = [vp] * 8 + [i32] * 6 + [vp]
     sig["cm_rope"] = [vp, vp, vp, vp, i64, i32, i32, i32, i64, i64, ctypes.c_float, vp]
@@ -300,7 +302,54 @@ def apply_rope(x, cos, sin):
     return RopeFn.apply(x, cos.float().contiguous(), sin.float().contiguous())
 
 
+class EmbeddingFn(torch.autograd.Function):
+    """Row gather; the backward adds the output-gradient rows straight into the weight's flat gradient buffer when the
+    optimizer allows it (``w.fuse_wgrad_accumulation``), else into a fresh fp32 tensor."""
+
+    @staticmethod
+    def forward(ctx, ids, w):
+        from . import lib, stream_ptr, _check
+        flat = ids.reshape(-1).long().contiguous()
+        V, H = w.shape
+        out = torch.empty(flat.numel(), H, dtype=torch.bfloat16, device=w.device)
+        _check(lib().cm_embedding_fwd(flat.data_ptr(), w.data_ptr(), out.data_ptr(), flat.numel(), V, H, stream_ptr()),
+               "cm_embedding_fwd")
+        F_.count_launch("embedding")
+        ctx.save_for_backward(flat)
+        ctx.w = w
+        return out.view(*ids.shape, H)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from . import lib, stream_ptr, _check, wgrad_into_main_grad
+        (flat,) = ctx.saved_tensors
+        w = ctx.w
+        V, H = w.shape
+        d2 = dout.reshape(-1, H)
+        if d2.dtype != torch.bfloat16 or not d2.is_contiguous():
+            d2 = d2.to(torch.bfloat16).contiguous()
+
+        def run(out, acc):
+            fresh = out is None
+            if fresh:
+                out = torch.zeros(V, H, dtype=torch.float32, device=w.device)
+            _check(lib().cm_embedding_bwd(flat.data_ptr(), d2.data_ptr(), out.data_ptr(), flat.numel(), V, H,
+                                          0 if out.dtype == torch.float32 else 1, stream_ptr()), "cm_embedding_bwd")
+            F_.count_launch("embedding_bwd")
+            return out.to(w.dtype) if fresh else out
+
+        return None, wgrad_into_main_grad(w, run)
+
+
+def embedding(ids, w):
+    if w.dtype != torch.bfloat16 or w.dim() != 2 or w.shape[1] % 8 or not w.is_contiguous() or ids.numel() == 0:
+        F_._miss("embedding(shape/dtype)", w)
+        return None
+    return EmbeddingFn.apply(ids, w)
+
+
 def register() -> None:
+    F_.register_cuda("embedding", embedding)
     F_.register_cuda("router_topk", router_topk)
     F_.register_cuda("ngram_hash_embed", ngram_hash_embed)
     F_.register_cuda("apply_rope", apply_rope)

@@ -351,6 +351,17 @@ def causal_attention_library(q, k, v, scale: float):
     return o.transpose(1, 2)[..., :dv]
 
 
+def embedding(ids, weight):
+    """Row gather ``weight[ids]``; on the GPU the backward adds the gradient rows into the weight's gradient buffer with
+    vector atomics instead of building a dense [vocab, hidden] gradient."""
+    fn = _cuda("embedding", weight)
+    if fn is not None:
+        y = fn(ids, weight)
+        if y is not None:
+            return y
+    return F.embedding(ids, weight)
+
+
 def causal_conv1d_silu(x, weight, bias=None):
     """``silu(depthwise causal conv1d over the sequence)`` on a channels-last tensor: x [B, S, C], weight [C, k] (or the
     [C, 1, k] parameter of ``nn.Conv1d(groups=C)``), bias [C].  Output [B, S, C]."""

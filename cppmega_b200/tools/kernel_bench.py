@@ -137,9 +137,9 @@ def register(name: str, fn: Callable[[], List[dict]]) -> None:
 
 
 def bench_glue() -> List[dict]:
-    """The small fused operators against the library ops they replace, same inputs, same harness:
-    depthwise causal conv1d + SiLU of the M2RNN mixer (7344 channels, kernel 4), the per-head 64 x 64 maps of the
-    absorbed sparse-attention path (32 heads), the state-dimension widening of the scan; forward + backward."""
+    """The small fused operators against the library ops they replace, same inputs, same harness: depthwise causal
+    conv1d + SiLU of the M2RNN mixer, the per-head 64 x 64 maps of the absorbed sparse-attention path (32 heads), the
+    word-embedding gather / scatter-add into an fp32 gradient buffer (vocabulary 131,072); forward + backward."""
     from cppmega_b200.ops import cuda as cu
     from cppmega_b200.ops import functional as F_
     from cppmega_b200.ops import reference as ref
@@ -155,9 +155,12 @@ def bench_glue() -> List[dict]:
             fn().backward(g)
         return run
 
-    # conv1d + SiLU, read in place from a wider projection
-    C, k = 7344, 4
-    proj = torch.randn(B, S, C + 56 + 816, device=dev).bfloat16()
+    # conv1d + SiLU, read in place from a wider projection (the M2RNN mixer of the NAM56R recipe: q + k + v channels)
+    from cppmega_b200.config.model import nam56r_full
+    mc = nam56r_full()
+    r = mc.m2rnn
+    C, k = (r.num_q_heads + r.num_k_heads) * r.k_head_dim + r.heads(mc.hidden_size) * r.v_head_dim, r.conv_kernel
+    proj = torch.randn(B, S, (2 * C + 63) // 8 * 8, device=dev).bfloat16()
     x = proj[..., :C].detach().requires_grad_()
     w = (torch.randn(C, 1, k, device=dev) * 0.5).bfloat16().requires_grad_()
     b = torch.zeros(C, device=dev).bfloat16().requires_grad_()
@@ -177,6 +180,27 @@ def bench_glue() -> List[dict]:
     byts = B * S * H * 64 * 2 * 6.0         # x, y | dy, dx | dy, x again for the weight gradient
     out.append({"kernel": "head_linear fwd+bwd", "tokens": B * S, "heads": H, "ms": ours, "library_ms": lib,
                 "speedup": lib / ours, "frac_of_" + pk["kind"] + "_hbm": byts / ours / 1e6 / pk["hbm_gbs"]})
+    # word embedding: gather + gradient rows added into the fp32 flat gradient buffer
+    V, Hd = 131072, 4096
+    we = torch.nn.Parameter((torch.randn(V, Hd, device=dev) * 0.02).bfloat16())
+    ids = torch.randint(0, V, (B, S), device=dev)
+    ge = torch.randn(B, S, Hd, device=dev).bfloat16()
+    main = torch.zeros(V, Hd, device=dev, dtype=torch.float32)
+
+    def lib_embed():
+        we.grad = None
+        torch.nn.functional.embedding(ids, we).backward(ge)
+        main.add_(we.grad)
+
+    def our_embed():
+        we.grad = None
+        F_.embedding(ids, we).backward(ge)
+
+    lib = time_ms(lib_embed)
+    we.main_grad, we.fuse_wgrad_accumulation = main, True
+    ours = time_ms(our_embed)
+    out.append({"kernel": "embedding fwd + bwd into the fp32 gradient buffer", "tokens": B * S, "vocab": V, "hidden": Hd, "ms": ours,
+                "library_ms": lib, "speedup": lib / ours})
     cu.check_errors()
     assert not F_.fallback_counts(), F_.fallback_counts()
     return out

@@ -463,3 +463,40 @@ def test_tensorwise_fp8_quantisers_and_linear():
     assert _rel(xx.grad.reshape(-1, 256), q(g2) @ q(w.detach())) < 1e-2
     assert _rel(w.grad, q(g2).t() @ q(x2)) < 1e-2
     assert _rel(y.reshape(-1, 128), x2.float() @ w.detach().float().t()) < 6e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("grad_dtype", [None, torch.float32, torch.bfloat16])
+def test_embedding_kernels_gather_and_scatter_add(grad_dtype):
+    """Row gather, and the backward that adds gradient rows with vector atomics: into a fresh tensor (``None``) or straight
+    into the parameter's flat gradient buffer (fp32 / bf16), where a second use of the same table accumulates."""
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops import functional as F_
+    torch.manual_seed(0)
+    V, H = 1000, 256
+    w = torch.nn.Parameter(torch.randn(V, H, device="cuda").bfloat16())
+    ids = torch.randint(0, V, (3, 517), device="cuda")
+    ids[0, :40] = 7                                            # repeated token: colliding atomics
+    g = torch.randn(3, 517, H, device="cuda").bfloat16()
+    if grad_dtype is not None:
+        w.main_grad = torch.zeros(V, H, device="cuda", dtype=grad_dtype)
+        w.fuse_wgrad_accumulation = True
+    F_.reset_counters()
+    y = F_.embedding(ids, w)
+    assert torch.equal(y, torch.nn.functional.embedding(ids, w))
+    (y * 1.0).backward(g)
+    y2 = F_.embedding(ids[:1], w)                              # second use of the table in the same step
+    y2.backward(g[:1])
+    torch.cuda.synchronize()
+    cu.check_errors()
+    assert F_.launch_counts().get("embedding", 0) == 2 and F_.launch_counts().get("embedding_bwd", 0) == 2
+    wr = w.detach().float().requires_grad_()
+    (torch.nn.functional.embedding(ids, wr) * g.float()).sum().backward()
+    (torch.nn.functional.embedding(ids[:1], wr) * g[:1].float()).sum().backward()
+    if grad_dtype is None:
+        got = w.grad.float()
+    else:
+        assert getattr(w, "grad_added_to_main_grad", False)
+        got = w.main_grad.float()
+    tol = 2e-2 if grad_dtype != torch.float32 else 1e-3
+    assert (got - wr.grad).norm() / wr.grad.norm() < tol
