@@ -138,6 +138,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--cuda-graph-scope", nargs="*", default=[],
                    help="layer kinds captured as CUDA graphs: mamba attn mlp (moe_router / moe_preprocess are accepted and ignored)")
     g.add_argument("--seed", type=int, default=1234)
+    g.add_argument("--inject-failure-at-iteration", type=int, default=0,
+                   help="testing aid: the last rank raises after this iteration unless the run was resumed from a checkpoint")
     g.add_argument("--optimizer", default="adamw", choices=["adam", "adamw", "adam8bit", "muon"])
     g.add_argument("--muon-scalar-optimizer", default="adamw", choices=["adamw", "adam8bit"],
                    help="optimizer of the parameters Muon does not take (scalars, norms, embeddings, output layer)")
@@ -303,7 +305,7 @@ def configs_from_namespace(ns: argparse.Namespace) -> Tuple[ModelConfig, Paralle
                        pipeline_schedule=ns.pipeline_schedule, cuda_graph_scope=tuple(ns.cuda_graph_scope))
     extras = {k: getattr(ns, k) for k in ("train_iters", "data_path", "mock_data", "save", "load", "save_interval",
                                           "log_throughput", "monitor_port", "profile", "profile_step_start",
-                                          "profile_step_end", "step_timeout_s", "no_load_optim")}
+                                          "profile_step_end", "step_timeout_s", "no_load_optim", "inject_failure_at_iteration")}
     return mcfg, pcfg, tcfg, extras
 
 

@@ -126,6 +126,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                 sharded.save_checkpoint(extras["save"], it + 1, trainer.model, pc, trainer.optimizer,
                                         extra={"tokens_seen": trainer.tokens_seen, "consumed_steps": it + 1},
                                         rank_extra={"rng": _rng_state()})
+            if (extras.get("inject_failure_at_iteration") and it + 1 == extras["inject_failure_at_iteration"]
+                    and start_iter == 0 and pc.rank == pc.world_size - 1):
+                raise RuntimeError(f"injected failure on rank {pc.rank} after iteration {it + 1}")     # host-side fault injection
     finally:
         if trainer.watchdog is not None:
             trainer.watchdog.stop()

@@ -154,3 +154,40 @@ def test_causal_conv1d_silu_kernels(B, S, C, k, sliced):
     assert _rel(x.grad, xr.grad) < 1.5e-2
     assert _rel(w.grad, wr.grad) < 1.5e-2
     assert _rel(b.grad, br.grad) < 1.5e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("variant", ["ssd", "noconv_ssd"])
+def test_ssd_variant_mixers_on_gpu_match_the_cpu_fp32_module(variant):
+    """The alternative SSM mixers (Mamba2-style SSD with the fused causal conv + SiLU kernel, and the no-conv variant with
+    QK-norm / biases / data-dependent A / trapezoid / rotary state) in bf16 on the GPU against the same module in fp32 on
+    the CPU: output and input gradient."""
+    import copy
+    from cppmega_b200.config.model import nam56r_tiny
+    from cppmega_b200.models.mamba_variants import build_variant_mixer
+    from cppmega_b200.ops import cuda as cu
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.parallel.state import single_process_context
+    cfg = nam56r_tiny(seq_length=128, mamba_variant=variant)
+    pc = single_process_context()
+    ref_mod = build_variant_mixer(cfg, pc, 1, dtype=torch.float32, seed=3, out_std=0.02)
+    gpu_mod = copy.deepcopy(ref_mod).to("cuda").to(torch.bfloat16)
+    for n, p in gpu_mod.named_parameters():                       # per-head fp32 parameters stay fp32, as in the model
+        if p.dim() <= 1 and "norm" not in n and "conv" not in n:
+            p.data = p.data.float()
+    torch.manual_seed(5)
+    x = torch.randn(2, 128, cfg.hidden_size) * 0.5
+    g = torch.randn(2, 128, cfg.hidden_size) * 0.1
+    xr = x.clone().requires_grad_()
+    yr = ref_mod(xr)
+    yr.backward(g)
+    xg = x.cuda().bfloat16().requires_grad_()
+    F_.reset_counters()
+    yg = gpu_mod(xg)
+    yg.backward(g.cuda().bfloat16())
+    torch.cuda.synchronize()
+    cu.check_errors()
+    if variant == "ssd":
+        assert F_.launch_counts().get("causal_conv1d_silu", 0) == 1
+    assert _rel(yg, yr) < 4e-2
+    assert _rel(xg.grad, xr.grad) < 6e-2

@@ -177,3 +177,35 @@ def test_dashboard_discovers_runs_and_renders_them():
         for s in servers:
             s.stop()
     assert analytics([])["records"] == 0
+
+
+def test_supervised_launch_resumes_from_the_last_checkpoint_after_a_rank_failure(tmp_path, capfd):
+    """Host-side fault injection on two gloo ranks: the last rank raises after iteration 3 of a fresh run; the supervisor
+    starts the job again with ``--load`` and it finishes from the checkpoint of iteration 2."""
+    import socket
+    from cppmega_b200.checkpoint import sharded
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    save = str(tmp_path / "ckpt")
+    rc = launch.main(["smoke_tiny", "--max-restarts", "2", "--master-port", str(port),
+                      "--set", "training.train_iters=6", "--set", f"training.save={save}", "--set", "training.save_interval=2",
+                      "--extra", "--inject-failure-at-iteration", "3"])
+    out = capfd.readouterr().out
+    assert rc == 0, out[-2000:]
+    assert "restarting from iteration 2" in out
+    assert sharded.latest_iteration(save) == 6
+
+
+def test_supervisor_gives_up_after_the_allowed_restarts():
+    calls = []
+
+    def run(cmd):
+        calls.append(cmd)
+        return 7
+
+    rc = launch.supervise(["--save", "/nonexistent/ckpt"], 1, 29500, 2, run=run)
+    assert rc == 7 and len(calls) == 3
+    assert all("--load" not in c for c in calls)                 # nothing was ever saved: every attempt starts fresh
+    ports = [c[c.index("--master-port") + 1] if "--master-port" in c else None for c in calls]
+    assert ports == [None, None, None]                           # one process: plain python, no rendezvous
