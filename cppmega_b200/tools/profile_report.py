@@ -24,7 +24,7 @@ GROUPS: List[Tuple[str, str]] = [
     ("MXFP8 GEMM + quantise", r"mxfp8_gemm_kernel|quantize_(rowwise|colwise|both)_kernel|dequantize_kernel|swizzle_scales"),
     ("Mamba3 MIMO scan", r"mimo_|angle_|head_reduce_kernel|state_scan"),
     ("M2RNN", r"m2rnn_"),
-    ("cross-entropy (non-GEMM part)", r"ce_fwd_bwd|cross_entropy|ce_"),
+    ("cross-entropy (non-GEMM part)", r"ce_fwd_bwd|cross_entropy|(?<![a-z])ce_"),
     ("MoE transport / permute", r"moe_|router_topk|zero_pad"),
     ("optimizer", r"adamw|reduce_shard|sumsq|muon|qmuon"),
     ("norms / SwiGLU / RoPE / small ops", r"rmsnorm|swiglu|rope_|ngram"),
