@@ -432,54 +432,70 @@ __global__ void __launch_bounds__(TPB) rmsnorm_bwd_wide(const __nv_bfloat16* __r
 // ---------------------------------------------------------------------------------------------
 // SwiGLU: in = [a | b] (width 2F), out = silu(a) * b
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
-                                                         long long rows, int F) {
+// Rows are walked by (blockIdx.x, threadIdx.y), columns by threadIdx.x: no per-element 64-bit division.  `rows_limit`
+// (optional, device): only the first min(rows, *rows_limit) rows are processed - the padded expert-sorted MoE buffers
+// are sized for the worst case and the number of rows in use is only known on the device.
+constexpr int SWIGLU_TX = 64, SWIGLU_TY = 4;
+
+__global__ void __launch_bounds__(SWIGLU_TX * SWIGLU_TY) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in,
+                                                                           __nv_bfloat16* __restrict__ out, long long rows, int F,
+                                                                           const int* __restrict__ rows_limit) {
   const int fv = F / 8;
-  const long long total = rows * fv;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / fv;
-    const int c = int(i - r * fv);
-    const uint4 a = reinterpret_cast<const uint4*>(in + r * 2 * F)[c];
-    const uint4 b = reinterpret_cast<const uint4*>(in + r * 2 * F + F)[c];
-    const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a);
-    const __nv_bfloat162* bb = reinterpret_cast<const __nv_bfloat162*>(&b);
-    uint4 o;
-    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+  if (rows_limit) rows = min(rows, (long long)*rows_limit);
+  for (long long r = blockIdx.x * (long long)SWIGLU_TY + threadIdx.y; r < rows; r += (long long)gridDim.x * SWIGLU_TY) {
+    const uint4* pa = reinterpret_cast<const uint4*>(in + r * 2 * F);
+    const uint4* pb = reinterpret_cast<const uint4*>(in + r * 2 * F + F);
+    uint4* po = reinterpret_cast<uint4*>(out + r * F);
+    for (int c = threadIdx.x; c < fv; c += SWIGLU_TX) {
+      const uint4 a = pa[c];
+      const uint4 b = pb[c];
+      const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* bb = reinterpret_cast<const __nv_bfloat162*>(&b);
+      uint4 o;
+      uint32_t* op = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 af = __bfloat1622float2(ab[j]), bf = __bfloat1622float2(bb[j]);
-      op[j] = pack_bf16(af.x / (1.f + __expf(-af.x)) * bf.x, af.y / (1.f + __expf(-af.y)) * bf.y);
+      for (int j = 0; j < 4; ++j) {
+        float2 af = __bfloat1622float2(ab[j]), bf = __bfloat1622float2(bb[j]);
+        op[j] = pack_bf16(af.x / (1.f + __expf(-af.x)) * bf.x, af.y / (1.f + __expf(-af.y)) * bf.y);
+      }
+      po[c] = o;
     }
-    reinterpret_cast<uint4*>(out + r * F)[c] = o;
   }
 }
 
-__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
-                                                         __nv_bfloat16* __restrict__ din, long long rows, int F) {
+__global__ void __launch_bounds__(SWIGLU_TX * SWIGLU_TY) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in,
+                                                                           const __nv_bfloat16* __restrict__ dout,
+                                                                           __nv_bfloat16* __restrict__ din, long long rows, int F,
+                                                                           const int* __restrict__ rows_limit) {
   const int fv = F / 8;
-  const long long total = rows * fv;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / fv;
-    const int c = int(i - r * fv);
-    const uint4 a = reinterpret_cast<const uint4*>(in + r * 2 * F)[c];
-    const uint4 b = reinterpret_cast<const uint4*>(in + r * 2 * F + F)[c];
-    const uint4 g = reinterpret_cast<const uint4*>(dout + r * F)[c];
-    const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a);
-    const __nv_bfloat162* bb = reinterpret_cast<const __nv_bfloat162*>(&b);
-    const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&g);
-    uint4 da, db;
-    uint32_t* dap = reinterpret_cast<uint32_t*>(&da);
-    uint32_t* dbp = reinterpret_cast<uint32_t*>(&db);
+  if (rows_limit) rows = min(rows, (long long)*rows_limit);
+  for (long long r = blockIdx.x * (long long)SWIGLU_TY + threadIdx.y; r < rows; r += (long long)gridDim.x * SWIGLU_TY) {
+    const uint4* pa = reinterpret_cast<const uint4*>(in + r * 2 * F);
+    const uint4* pb = reinterpret_cast<const uint4*>(in + r * 2 * F + F);
+    const uint4* pg = reinterpret_cast<const uint4*>(dout + r * F);
+    uint4* qa = reinterpret_cast<uint4*>(din + r * 2 * F);
+    uint4* qb = reinterpret_cast<uint4*>(din + r * 2 * F + F);
+    for (int c = threadIdx.x; c < fv; c += SWIGLU_TX) {
+      const uint4 a = pa[c];
+      const uint4 b = pb[c];
+      const uint4 g = pg[c];
+      const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* bb = reinterpret_cast<const __nv_bfloat162*>(&b);
+      const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&g);
+      uint4 da, db;
+      uint32_t* dap = reinterpret_cast<uint32_t*>(&da);
+      uint32_t* dbp = reinterpret_cast<uint32_t*>(&db);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 af = __bfloat1622float2(ab[j]), bf = __bfloat1622float2(bb[j]), gf = __bfloat1622float2(gb[j]);
-      const float s0 = 1.f / (1.f + __expf(-af.x)), s1 = 1.f / (1.f + __expf(-af.y));
-      const float d0 = s0 * (1.f + af.x * (1.f - s0)), d1 = s1 * (1.f + af.y * (1.f - s1));
-      dap[j] = pack_bf16(gf.x * bf.x * d0, gf.y * bf.y * d1);
-      dbp[j] = pack_bf16(gf.x * af.x * s0, gf.y * af.y * s1);
+      for (int j = 0; j < 4; ++j) {
+        float2 af = __bfloat1622float2(ab[j]), bf = __bfloat1622float2(bb[j]), gf = __bfloat1622float2(gb[j]);
+        const float s0 = 1.f / (1.f + __expf(-af.x)), s1 = 1.f / (1.f + __expf(-af.y));
+        const float d0 = s0 * (1.f + af.x * (1.f - s0)), d1 = s1 * (1.f + af.y * (1.f - s1));
+        dap[j] = pack_bf16(gf.x * bf.x * d0, gf.y * bf.y * d1);
+        dbp[j] = pack_bf16(gf.x * af.x * s0, gf.y * af.y * s1);
+      }
+      qa[c] = da;
+      qb[c] = db;
     }
-    reinterpret_cast<uint4*>(din + r * 2 * F)[c] = da;
-    reinterpret_cast<uint4*>(din + r * 2 * F + F)[c] = db;
   }
 }
 
@@ -721,22 +737,36 @@ extern "C" int cm_rmsnorm_bwd(const void* x, const void* w, const void* dy, cons
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-extern "C" int cm_swiglu_fwd(const void* in, void* out, long long rows, int F, cudaStream_t s) {
+static int swiglu_grid(long long rows) {
+  const long long blocks = (rows + SWIGLU_TY - 1) / SWIGLU_TY;
+  const long long cap = (long long)sm_count() * 16;
+  return (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+// `rows_limit` (optional device int): process only the first min(rows, *rows_limit) rows
+extern "C" int cm_swiglu_fwd_rows(const void* in, void* out, long long rows, int F, const int* rows_limit, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (F % 8) return -10;
-  long long total = rows * (F / 8);
-  int grid = (int)((total + 255) / 256 < (long long)sm_count() * 16 ? (total + 255) / 256 : (long long)sm_count() * 16);
-  swiglu_fwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, F);
+  swiglu_fwd_kernel<<<swiglu_grid(rows), dim3(SWIGLU_TX, SWIGLU_TY), 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, F,
+                                                                              rows_limit);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-extern "C" int cm_swiglu_bwd(const void* in, const void* dout, void* din, long long rows, int F, cudaStream_t s) {
+extern "C" int cm_swiglu_bwd_rows(const void* in, const void* dout, void* din, long long rows, int F, const int* rows_limit,
+                                  cudaStream_t s) {
   if (rows <= 0) return 0;
   if (F % 8) return -10;
-  long long total = rows * (F / 8);
-  int grid = (int)((total + 255) / 256 < (long long)sm_count() * 16 ? (total + 255) / 256 : (long long)sm_count() * 16);
-  swiglu_bwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)dout, (__nv_bfloat16*)din, rows, F);
+  swiglu_bwd_kernel<<<swiglu_grid(rows), dim3(SWIGLU_TX, SWIGLU_TY), 0, s>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)dout,
+                                                                              (__nv_bfloat16*)din, rows, F, rows_limit);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int cm_swiglu_fwd(const void* in, void* out, long long rows, int F, cudaStream_t s) {
+  return cm_swiglu_fwd_rows(in, out, rows, F, nullptr, s);
+}
+
+extern "C" int cm_swiglu_bwd(const void* in, const void* dout, void* din, long long rows, int F, cudaStream_t s) {
+  return cm_swiglu_bwd_rows(in, dout, din, rows, F, nullptr, s);
 }
 
 // grad_kind: 0 fp32, 1 bf16; out_kind: 0 fp32, 1 bf16.  `gate` (may be null): a device word; when it is non-zero at run

@@ -49,6 +49,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "cm_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, i32, i32, vp],
         "cm_swiglu_fwd": [vp, vp, i64, i32, vp],
         "cm_swiglu_bwd": [vp, vp, vp, i64, i32, vp],
+        "cm_swiglu_fwd_rows": [vp, vp, i64, i32, vp, vp],
+        "cm_swiglu_bwd_rows": [vp, vp, vp, i64, i32, vp, vp],
         "cm_adamw": [vp, vp, vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, f32, i32, i32, vp],
         "cm_adamw_gated": [vp, vp, vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, f32, f32, i32, i32, vp, vp],
         "cm_sumsq": [vp, i64, vp, i32, vp],
@@ -317,6 +319,25 @@ class SwiGLUFn(torch.autograd.Function):
                "cm_swiglu_bwd")
         F_.count_launch("swiglu_bwd")
         return din.view(ctx.shape)
+
+
+def swiglu_rows(h: torch.Tensor, rows_limit: torch.Tensor) -> torch.Tensor:
+    """``silu(h[:, :F]) * h[:, F:]`` on the first ``rows_limit[0]`` rows of a 2-D bf16 tensor (a device int32: the rows in use
+    of a worst-case-sized buffer); the rows after them are left unwritten.  No autograd."""
+    out = torch.empty(h.shape[0], h.shape[1] // 2, dtype=h.dtype, device=h.device)
+    _check(lib().cm_swiglu_fwd_rows(h.data_ptr(), out.data_ptr(), h.shape[0], h.shape[1] // 2, rows_limit.data_ptr(), stream_ptr()),
+           "cm_swiglu_fwd_rows")
+    F_.count_launch("swiglu")
+    return out
+
+
+def swiglu_bwd_rows(h: torch.Tensor, da: torch.Tensor, rows_limit: torch.Tensor) -> torch.Tensor:
+    """Gradient of :func:`swiglu_rows` with respect to ``h`` (same row limit)."""
+    dh = torch.empty_like(h)
+    _check(lib().cm_swiglu_bwd_rows(h.data_ptr(), da.data_ptr(), dh.data_ptr(), h.shape[0], h.shape[1] // 2, rows_limit.data_ptr(),
+                                    stream_ptr()), "cm_swiglu_bwd_rows")
+    F_.count_launch("swiglu_bwd")
+    return dh
 
 
 def swiglu(gu):

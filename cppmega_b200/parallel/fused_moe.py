@@ -456,7 +456,7 @@ class _FusedMoEFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, probs, w1, w2, ids, bufs: FusedMoEBuffers, layer_slot: int):
-        from ..ops.cuda import swiglu
+        from ..ops.cuda import swiglu_rows
         pc, heap = bufs.pc, bufs.heap
         T, H = x.shape
         cap_total = bufs.capacity_for(ids.numel())
@@ -487,7 +487,7 @@ class _FusedMoEFn(torch.autograd.Function):
                     ch.h = _experts_fwd_mx(ch.xin, w1, w2, ch.plan.tile_expert, ch.yout, fp8 == "tensorwise")
                 else:
                     ch.h = _grouped(ch.xin, w1, ch.plan.tile_expert, cap_c, False)
-                    a = swiglu(ch.h)
+                    a = swiglu_rows(ch.h, ch.plan.seg_offsets[-1:])      # only the rows in use of the worst-case buffer
                     _grouped(a, w2, ch.plan.tile_expert, cap_c, False, out=ch.yout)
             heap.signal(ch.f0 + 1, ep0)
             ch.event = main.record_event()
@@ -509,8 +509,7 @@ class _FusedMoEFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        from ..ops.cuda import lib, stream_ptr, _check
-        from ..ops.cuda import swiglu as _sw
+        from ..ops.cuda import swiglu_bwd_rows, swiglu_rows
         w1, w2, p32, xin_all, yout_all, *hs = ctx.saved_tensors
         chunks, bufs, cap_c = ctx.chunks, ctx.bufs, ctx.cap_c
         heap = bufs.heap
@@ -545,12 +544,11 @@ class _FusedMoEFn(torch.autograd.Function):
                 if ctx.fp8 is not None:
                     g1, g2 = _experts_bwd_mx(gin[c], h, xin, w1, w2, plan, gout[c], ctx.fp8 == "tensorwise")
                 else:
-                    a = _sw(h)                                                       # recompute a = swiglu(h)
+                    used = plan.seg_offsets[-1:]                                     # rows in use (device int32)
+                    a = swiglu_rows(h, used)                                         # recompute a = swiglu(h)
                     da = _grouped(gin[c], w2, plan.tile_expert, cap_c, True)         # [cap, F]
                     g2 = _grouped_wgrad(gin[c], a, plan.seg_offsets, E, w2)          # [E, H, F]
-                    dh = torch.empty_like(h)
-                    _check(lib().cm_swiglu_bwd(h.data_ptr(), da.data_ptr(), dh.data_ptr(), cap_c, Fh, stream_ptr()), "cm_swiglu_bwd")
-                    F_.count_launch("swiglu_bwd")
+                    dh = swiglu_bwd_rows(h, da, used)
                     _grouped(dh, w1, plan.tile_expert, cap_c, True, out=gout[c])     # [cap, H]
                     g1 = _grouped_wgrad(dh, xin, plan.seg_offsets, E, w1)            # [E, 2F, H]
             fused_acc = getattr(w1, "grad_added_to_main_grad", False)                # the GEMM epilogue accumulated in place
