@@ -131,6 +131,7 @@ class DSAConfig:
     index_head_dim: int = 64
     index_topk: int = 256
     indexer_loss_coeff: float = 0.0
+    warmup_dense: bool = False          # indexer warm-up: sparse layers attend densely while the KL loss trains the indexer
     index_cache: bool = True
     full_layer_ranks: Tuple[int, ...] = (0, 3, 6)
     indexer_dtype: str = "bf16"

@@ -166,6 +166,14 @@ class MLAttention(nn.Module):
             k_nope, v = split_last_dim(kv, (dq, dv))
             k = cat_last_dim([k_nope, k_pe.unsqueeze(2).expand(B, S, Hl, dr)])
             o = F_.causal_attention(cat_last_dim([q_nope, q_pe]), k, v.contiguous(), self.softmax_scale)
+        elif self.dsa.warmup_dense and self.training and self.dsa.indexer_loss_coeff > 0 and indices is None:
+            # indexer warm-up: dense attention output and the KL loss that trains the indexer, from the same score blocks
+            kv = self.linear_kv_up_proj(kv_lat).reshape(B, S, Hl, dq + dv)
+            k_nope, v = split_last_dim(kv, (dq, dv))
+            k = cat_last_dim([k_nope, k_pe.unsqueeze(2).expand(B, S, Hl, dr)])
+            _idx, (qi, ki, wi) = self.core_attention.indexer(x, q_lat, self.context_group)
+            o, self.last_indexer_loss = ref.dsa_warmup_attention_and_kl(
+                cat_last_dim([q_nope, q_pe]), k, v, self.softmax_scale, qi, ki, wi, self.dsa.indexer_loss_coeff)
         else:
             idx = indices if indices is not None else self._indices(x, q_lat, index_cache, (q_nope, q_pe, kv_lat, k_pe))
             w_up = self.linear_kv_up_proj.weight.reshape(Hl, dq + dv, dc)

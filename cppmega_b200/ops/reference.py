@@ -240,6 +240,44 @@ def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[tor
     return F.silu(y).transpose(1, 2)
 
 
+def dsa_warmup_attention_and_kl(q, k, v, scale, q_idx, k_idx, w, coeff: float = 1.0, rows: int = 512):
+    """Indexer warm-up in one pass: dense causal attention output AND the indexer KL loss from the same score blocks.
+
+    During warm-up the sparse layers attend to every key (the indexer is not trusted yet) while the indexer is trained
+    to imitate the head-averaged attention distribution.  Per block of ``rows`` queries the scores ``q k^T`` are formed
+    once; their softmax gives the output ``P v`` and, detached and averaged over heads, the target of
+    ``KL(target || softmax(index scores))``.  Blocks are recomputed in backward, so the transient is
+    ``[B, H, rows, S]``.  q / k [B,S,H,Dqk], v [B,S,H,Dv]; returns (out [B,S,H,Dv], loss).  Same value as
+    :func:`indexer_kl_loss` on detached q / k plus ordinary dense attention; the reference reaches this through an external
+    fused FlashAttention + lightning-indexer + KL kernel (cppmega/megatron/lemyx_dsa_warmup.py:77-178)."""
+    from torch.utils.checkpoint import checkpoint
+    B, S, H, _ = q.shape
+
+    def block(qb, kk, vv, qi, ki, wi, r0):
+        n = qb.shape[1]
+        pos = torch.arange(r0, r0 + n, device=qb.device)
+        causal = torch.arange(S, device=qb.device)[None, :] <= pos[:, None]                           # [n, S]
+        a = torch.einsum("bihd,bjhd->bhij", qb.float(), kk.float()) * scale
+        p = torch.softmax(a.masked_fill(~causal, float("-inf")), dim=-1)                              # [B, H, n, S]
+        out = torch.einsum("bhij,bjhd->bihd", p, vv.float()).to(vv.dtype)
+        target = p.detach().mean(dim=1)                                                               # [B, n, S]
+        sc = indexer_scores(qi, ki, wi).masked_fill(~causal, float("-inf"))
+        logq = torch.log_softmax(sc, dim=-1)
+        kl = torch.where(target > 0, target * (torch.log(target.clamp_min(1e-30)) - logq), torch.zeros_like(target)).sum()
+        return out, kl
+
+    outs = []
+    total = q.new_zeros((), dtype=torch.float32)
+    for r0 in range(0, S, rows):
+        r1 = min(S, r0 + rows)
+        args = (q[:, r0:r1], k, v, q_idx[:, r0:r1], k_idx, w[:, r0:r1], r0)
+        needs = any(torch.is_tensor(t) and t.requires_grad for t in args)
+        o, kl = checkpoint(block, *args, use_reentrant=False) if needs else block(*args)
+        outs.append(o)
+        total = total + kl
+    return torch.cat(outs, dim=1), coeff * total / (B * S)
+
+
 # ---------------------------------------------------------------------------
 # fused linear + cross entropy
 # ---------------------------------------------------------------------------

@@ -68,6 +68,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--dsa-indexer-head-dim", type=int, default=None)
     g.add_argument("--dsa-indexer-topk", type=int, default=None)
     g.add_argument("--dsa-indexer-loss-coeff", type=float, default=None)
+    g.add_argument("--dsa-warmup-dense", action="store_true", default=None,
+                   help="indexer warm-up: sparse layers attend densely while the KL loss trains the indexer")
     g.add_argument("--index-cache", dest="index_cache", action="store_true", default=None)
     g.add_argument("--no-index-cache", dest="index_cache", action="store_false")
     g.add_argument("--index-cache-full-layers", default=None)
@@ -234,6 +236,7 @@ def configs_from_namespace(ns: argparse.Namespace) -> Tuple[ModelConfig, Paralle
     _set(dsa, "index_head_dim", ns.dsa_indexer_head_dim)
     _set(dsa, "index_topk", ns.dsa_indexer_topk)
     _set(dsa, "indexer_loss_coeff", ns.dsa_indexer_loss_coeff)
+    _set(dsa, "warmup_dense", ns.dsa_warmup_dense)
     _set(dsa, "index_cache", ns.index_cache)
     if ns.index_cache_full_layers is not None:
         dsa["full_layer_ranks"] = parse_int_list(ns.index_cache_full_layers)
@@ -360,6 +363,8 @@ def render_args(mcfg: ModelConfig, pcfg: ParallelConfig, tcfg: TrainConfig, *, t
         kv("--dsa-indexer-head-dim", mcfg.dsa.index_head_dim)
         kv("--dsa-indexer-topk", mcfg.dsa.index_topk)
         kv("--dsa-indexer-loss-coeff", mcfg.dsa.indexer_loss_coeff)
+        if mcfg.dsa.warmup_dense:
+            a.append("--dsa-warmup-dense")
         a.append("--index-cache" if mcfg.dsa.index_cache else "--no-index-cache")
         kv("--index-cache-full-layers", ",".join(map(str, mcfg.dsa.full_layer_ranks)))
     moe = mcfg.moe

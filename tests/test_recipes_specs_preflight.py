@@ -241,3 +241,42 @@ def test_chunked_indexer_kl_loss_equals_dense_form():
     assert abs(float(dense) - float(chunked)) < 1e-5 * max(1.0, abs(float(dense)))
     for a, b in zip(g1, g2):
         assert (a - b).abs().max() < 1e-5
+
+
+def test_dsa_warmup_pass_gives_dense_attention_and_the_indexer_kl_loss():
+    """One chunked pass returns the dense causal attention output and the same KL loss as the separate definition; the loss
+    sends gradients to the indexer operands only, the output to q / k / v."""
+    import torch
+    from cppmega_b200.ops import reference as ref
+    torch.manual_seed(0)
+    B, S, H, D, Dv, Hi, Di = 2, 48, 3, 16, 8, 2, 8
+    q, k = torch.randn(B, S, H, D, requires_grad=True), torch.randn(B, S, H, D, requires_grad=True)
+    v = torch.randn(B, S, H, Dv, requires_grad=True)
+    qi, ki = torch.randn(B, S, Hi, Di, requires_grad=True), torch.randn(B, S, Di, requires_grad=True)
+    w = torch.randn(B, S, Hi, requires_grad=True)
+    out, loss = ref.dsa_warmup_attention_and_kl(q, k, v, D ** -0.5, qi, ki, w, coeff=0.5, rows=20)
+    want_loss = ref.indexer_kl_loss(q.detach(), k.detach(), D ** -0.5, qi, ki, w, 0.5)
+    want_out = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                                is_causal=True, scale=D ** -0.5).transpose(1, 2)
+    assert torch.allclose(loss, want_loss, atol=1e-5) and torch.allclose(out, want_out, atol=1e-5)
+    gq, gqi = torch.autograd.grad(loss, (q, qi), allow_unused=True)
+    assert gq is None and gqi is not None and gqi.abs().sum() > 0
+    (gv,) = torch.autograd.grad(out.sum(), (v,), retain_graph=True)
+    assert gv.abs().sum() > 0
+
+
+def test_model_runs_the_dsa_warmup_mode():
+    import dataclasses
+    import torch
+    from cppmega_b200.config.model import nam56r_tiny
+    from cppmega_b200.parallel.dist_optimizer import OptimizerConfig
+    from cppmega_b200.training.trainer import TrainConfig, Trainer, synthetic_batches
+    cfg = nam56r_tiny(seq_length=64)
+    cfg = dataclasses.replace(cfg, dsa=dataclasses.replace(cfg.dsa, warmup_dense=True, indexer_loss_coeff=0.1))
+    tr = Trainer(cfg, TrainConfig(micro_batch_size=2, seq_length=64, dtype="fp32", log_interval=0,
+                                  optimizer=OptimizerConfig(lr=1e-3)), device=torch.device("cpu"))
+    stream = synthetic_batches(cfg.vocab_size, 2, 64, seed=0, pin=False)
+    losses = [float(tr.train_step(next(stream))["loss"]) for _ in range(2)]
+    assert all(l == l and l < 20 for l in losses)
+    dsa_layers = [l for l in tr.model.decoder.layers.values() if l.kind == "dsa"]
+    assert dsa_layers and all(l.self_attention.last_indexer_loss is not None for l in dsa_layers)
