@@ -41,6 +41,29 @@ def enable_cuda(*names: str) -> None:
         _DISABLED.discard(n)
 
 
+# kernels whose reductions use floating-point atomics (the order of the additions, hence the last bits, varies from run to run)
+ATOMIC_REDUCTION_OPS = ("embedding", "ngram_hash_embed", "causal_conv1d_silu", "head_linear", "sparse_mla", "mimo_scan_bwd",
+                        "causal_attention")
+_deterministic = False
+
+
+def set_deterministic(on: bool = True) -> None:
+    """Bitwise-reproducible reruns for debugging: the operators in ``ATOMIC_REDUCTION_OPS`` go through their PyTorch
+    definitions and the tensor library is put in deterministic mode (it then refuses or replaces its own atomic kernels).
+    Slower; meant for comparing two runs of a few steps, e.g. when hunting a race in a new kernel."""
+    global _deterministic
+    _deterministic = bool(on)
+    if on:
+        disable_cuda(*ATOMIC_REDUCTION_OPS)
+    else:
+        enable_cuda(*ATOMIC_REDUCTION_OPS)
+    torch.use_deterministic_algorithms(bool(on), warn_only=True)
+
+
+def is_deterministic() -> bool:
+    return _deterministic
+
+
 def fallback_counts() -> Dict[str, int]:
     return dict(_FALLBACKS)
 

@@ -140,6 +140,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--cuda-graph-scope", nargs="*", default=[],
                    help="layer kinds captured as CUDA graphs: mamba attn mlp (moe_router / moe_preprocess are accepted and ignored)")
     g.add_argument("--seed", type=int, default=1234)
+    g.add_argument("--deterministic-mode", action="store_true",
+                   help="debugging: bitwise-reproducible reruns (kernels with atomic reductions run their PyTorch definitions)")
     g.add_argument("--inject-failure-at-iteration", type=int, default=0,
                    help="testing aid: the last rank raises after this iteration unless the run was resumed from a checkpoint")
     g.add_argument("--optimizer", default="adamw", choices=["adam", "adamw", "adam8bit", "muon"])
@@ -304,6 +306,7 @@ def configs_from_namespace(ns: argparse.Namespace) -> Tuple[ModelConfig, Paralle
                        precision_recipe=ns.fp8_recipe or "bf16", precision_modules=tuple(ns.fp8_modules),
                        fp8_activations=ns.fp8_activations, fp8_activations_bf16_first=ns.fp8_activations_bf16_first,
                        fp8_activations_bf16_last=ns.fp8_activations_bf16_last, fp8_activations_clamp=ns.fp8_activations_clamp,
+                       deterministic=ns.deterministic_mode,
                        optimizer=ocfg, lr_schedule=sched,
                        pipeline_schedule=ns.pipeline_schedule, cuda_graph_scope=tuple(ns.cuda_graph_scope))
     extras = {k: getattr(ns, k) for k in ("train_iters", "data_path", "mock_data", "save", "load", "save_interval",
@@ -435,6 +438,8 @@ def render_args(mcfg: ModelConfig, pcfg: ParallelConfig, tcfg: TrainConfig, *, t
         kv("--fp8-activations-bf16-last", tcfg.fp8_activations_bf16_last)
         if tcfg.fp8_activations_clamp:
             a.append("--fp8-activations-clamp")
+    if tcfg.deterministic:
+        a.append("--deterministic-mode")
     if tcfg.recompute != "none":
         kv("--recompute-granularity", tcfg.recompute)
     if tcfg.cuda_graph_scope:

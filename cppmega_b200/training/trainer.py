@@ -45,6 +45,7 @@ class TrainConfig:
     fp8_activations_bf16_first: int = 1          # layers at the start / end of the stack whose saved tensors stay bf16
     fp8_activations_bf16_last: int = 1
     fp8_activations_clamp: bool = False          # "tensor" recipe: limit the measured maximum to the E4M3 range
+    deterministic: bool = False                  # debugging: atomic-reduction kernels -> PyTorch definitions, library deterministic mode
     cuda_graph_scope: tuple = ()                 # subset of ("mamba", "attn", "mlp"): layers captured as CUDA graphs
     optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
     lr_schedule: Optional[LRSchedule] = None
@@ -110,6 +111,8 @@ class Trainer:
         # with pipeline stages the embedding copies are summed before the data-parallel reduction,
         # so the reduction cannot start from inside backward
         from ..ops import functional as F_
+        if train_cfg.deterministic:
+            F_.set_deterministic(True)
         self.precision_modules = _install_precision(self.model, train_cfg)
         if train_cfg.fp8_activations not in ("off", "", None):
             act = {"recipe": train_cfg.fp8_activations, "bf16_first": train_cfg.fp8_activations_bf16_first,

@@ -197,3 +197,19 @@ def test_trainer_reports_which_fast_paths_are_off_and_why():
     assert paths["optimizer"].startswith("off: ") and paths["moe"].startswith("off: ") and paths["tp"].startswith("off: ")
     assert "no GPU" in paths["optimizer"] and "tensor-parallel size 1" in paths["tp"]
     assert paths["cuda_graphs"].startswith("off: ") and paths["recompute"] == "none"
+
+
+def test_deterministic_mode_routes_atomic_kernels_to_their_definitions():
+    import torch
+    from cppmega_b200.ops import functional as F_
+    from cppmega_b200.training.arguments import parse_args
+    _m, _p, tcfg, _e = parse_args(["--model-preset", "nam56r_tiny", "--deterministic-mode", "--mock-data"])
+    assert tcfg.deterministic
+    try:
+        F_.set_deterministic(True)
+        assert F_.is_deterministic() and set(F_.ATOMIC_REDUCTION_OPS) <= F_._DISABLED
+        assert torch.are_deterministic_algorithms_enabled()
+    finally:
+        F_.set_deterministic(False)
+    assert not F_.is_deterministic() and not (set(F_.ATOMIC_REDUCTION_OPS) & F_._DISABLED)
+    assert not torch.are_deterministic_algorithms_enabled()
