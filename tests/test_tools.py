@@ -209,3 +209,11 @@ def test_supervisor_gives_up_after_the_allowed_restarts():
     assert all("--load" not in c for c in calls)                 # nothing was ever saved: every attempt starts fresh
     ports = [c[c.index("--master-port") + 1] if "--master-port" in c else None for c in calls]
     assert ports == [None, None, None]                           # one process: plain python, no rendezvous
+
+
+def test_tp_bench_needs_ranks_and_knows_the_recipe_shapes(capsys):
+    from cppmega_b200.tools import tp_bench
+    assert tp_bench.main([]) == 0
+    assert '"unavailable"' in capsys.readouterr().out
+    shapes = {name: (kind, k, n) for name, kind, k, n in tp_bench._shapes()}
+    assert shapes["mamba_in_proj"] == ("ag_gemm", 4096, 24960) and shapes["mamba_out_proj"] == ("gemm_rs", 8192, 4096)
