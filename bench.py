@@ -293,11 +293,19 @@ def main() -> int:
                 gc.collect()
                 torch.cuda.empty_cache()
                 barrier()
-                pc_nccl = dataclasses.replace(pc, config=dataclasses.replace(pc.config, fused_collectives=False))
-                holder["trainer"] = make_trainer(pc_nccl, recompute, keep_last)
-                nccl = short_run("nccl_path")
-                nccl["fused_paths"] = dict(holder["trainer"].fused)
-                nccl["fused_over_nccl"] = nccl["ms_per_step"] / (ms_dev / args.steps)
+                # The second trainer needs the memory of the first: go on only if EVERY rank got (nearly) all of it back,
+                # so that no rank can run out of memory alone and leave the others waiting in a collective.
+                free_b, total_b = torch.cuda.mem_get_info()
+                enough = torch.tensor([1 if free_b >= 0.9 * total_b else 0], device=device, dtype=torch.int32)
+                dist.all_reduce(enough, op=dist.ReduceOp.MIN)
+                if int(enough.item()) == 0:
+                    nccl = {"skipped": f"only {free_b / 2**30:.0f} of {total_b / 2**30:.0f} GiB free after closing the fused trainer"}
+                else:
+                    pc_nccl = dataclasses.replace(pc, config=dataclasses.replace(pc.config, fused_collectives=False))
+                    holder["trainer"] = make_trainer(pc_nccl, recompute, keep_last)
+                    nccl = short_run("nccl_path")
+                    nccl["fused_paths"] = dict(holder["trainer"].fused)
+                    nccl["fused_over_nccl"] = nccl["ms_per_step"] / (ms_dev / args.steps)
             except Exception as e:
                 nccl = {"failed": f"{type(e).__name__}: {str(e)[:200]}"}
     # FLOPs the GPU actually executes: a recomputed layer runs its forward twice (the scan and sparse-attention kernels
