@@ -280,3 +280,27 @@ def test_model_runs_the_dsa_warmup_mode():
     assert all(l == l and l < 20 for l in losses)
     dsa_layers = [l for l in tr.model.decoder.layers.values() if l.kind == "dsa"]
     assert dsa_layers and all(l.self_attention.last_indexer_loss is not None for l in dsa_layers)
+
+
+def test_moe_chunk_selection_and_flag_layout():
+    """Host-side bookkeeping of the two-chunk MoE pipeline: when a call is split, and that every (layer, chunk, purpose)
+    gets its own flag word block inside the heap's flag area for a 64-layer model on 8 ranks."""
+    import types
+    from cppmega_b200.parallel import fused_moe as fm
+    from cppmega_b200.parallel.symm_mem import FLAG_WORDS
+    stub = types.SimpleNamespace(chunks=fm.MAX_CHUNKS)
+    pick = lambda tokens, topk: fm.FusedMoEBuffers.chunks_for(stub, tokens, topk)
+    assert pick(16384, 4) == 2                              # the benchmark shape: two chunks of 8192 tokens
+    assert pick(16383, 4) == 1                              # odd token count: not split
+    assert pick(2048, 4) == 1                               # 4096 copies per chunk: below the threshold
+    stub.chunks = 1
+    assert pick(16384, 4) == 1
+    seen = set()
+    for layer in range(64):
+        for chunk in range(fm.MAX_CHUNKS):
+            f0 = fm._flag0(layer, chunk)
+            for purpose in range(fm.FLAGS_PER_CHUNK):
+                idx = f0 + purpose
+                assert idx not in seen and idx >= fm.FLAG_BASE
+                seen.add(idx)
+    assert (max(seen) + 1) * 8 <= FLAG_WORDS                # 8 ranks: one word per rank and flag
